@@ -1,0 +1,377 @@
+// Host side of the C ABI declared in include/bsgemm.h: argument checks, TMA tensor
+// maps, grid / cluster selection and kernel launch.  Takes the role of the reference's
+// GemmUniversalAdapter (include/cutlass/gemm/device/gemm_universal_adapter.h:232-611).
+//
+// No allocation happens here; cuTensorMapEncodeTiled is resolved through the runtime
+// (cudaGetDriverEntryPoint), so the library loads on machines without a driver.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/bsgemm.h"
+#include "gemm_kernel.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int32_t fail(int32_t code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || p == nullptr) return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(p);
+  return fn;
+}
+
+// K-major byte matrix (rows x row_bytes), box = 128 bytes x box_rows, 128-byte swizzle.
+int32_t make_operand_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return fail(BSG_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  cuuint64_t dims[2] = {row_bytes, rows};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {128, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(BSG_ERR_CUDA, "cuTensorMapEncodeTiled(operand) failed with %d", int(r));
+  return BSG_OK;
+}
+
+// Interleaved scale factors as (row_atoms, k_atoms, 512 bytes); box = box_row_atoms x box_k_atoms x 512 bytes.
+int32_t make_sf_map(CUtensorMap* map, const void* base, uint64_t k_atoms, uint64_t row_atoms, uint32_t box_k_atoms,
+                    uint32_t box_row_atoms) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return fail(BSG_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  cuuint64_t dims[3] = {128, k_atoms, row_atoms};
+  cuuint64_t strides[2] = {512, 512 * k_atoms};
+  cuuint32_t box[3] = {128, box_k_atoms, box_row_atoms};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(BSG_ERR_CUDA, "cuTensorMapEncodeTiled(scale factors) failed with %d", int(r));
+  return BSG_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Everything the launcher needs, independent of dense / grouped origin.
+struct Problem {
+  int32_t kind, out_kind;
+  int32_t num_groups;
+  int64_t rows_per_group;   // dense / batched
+  int64_t total_rows;
+  int64_t N, K;
+  const void *A, *B, *SFA, *SFB, *C;
+  void *D, *SFD;
+  const int32_t* offsets;
+  bool b_per_group;
+  int64_t ldc, ldd;
+  float alpha, beta;
+  const float *alpha_ptr, *beta_ptr, *norm_ptr;
+  int32_t tile_n, cta_group, sm_count, raster_band;
+  // gating (tensor parallel)
+  const uint32_t* ready_flags;
+  int32_t rows_per_flag;
+  uint32_t flag_target;
+  int32_t tile_m_rotate;
+};
+
+struct Plan {
+  int32_t cta_group, tile_n, stages, smem_bytes;
+  int64_t num_tiles;   // -1 if unknown on the host
+};
+
+int32_t validate(const Problem& q, Plan* plan) {
+  if (q.kind != BSG_KIND_NVFP4 && q.kind != BSG_KIND_MXFP8) return fail(BSG_ERR_NOT_SUPPORTED, "unknown operand kind %d", q.kind);
+  if (q.out_kind != BSG_OUT_BF16 && q.out_kind != BSG_OUT_NVFP4) return fail(BSG_ERR_NOT_SUPPORTED, "unknown output kind %d", q.out_kind);
+  if (q.num_groups < 1 || q.num_groups > BSG_MAX_GROUPS) return fail(BSG_ERR_INVALID_PROBLEM, "group / batch count %d outside [1, %d]", q.num_groups, BSG_MAX_GROUPS);
+  if (q.N < 1 || q.K < 1 || q.total_rows < 0) return fail(BSG_ERR_INVALID_PROBLEM, "extents must be positive (rows=%lld N=%lld K=%lld)", (long long)q.total_rows, (long long)q.N, (long long)q.K);
+  if (q.total_rows > 0x7FFFFFFF / 2 || q.N > 0x7FFFFFFF / 2 || q.K > 0x7FFFFFFF / 2) return fail(BSG_ERR_INVALID_PROBLEM, "extent exceeds 2^30");
+  const int64_t k_align = q.kind == BSG_KIND_NVFP4 ? 32 : 16;   // 16 bytes of K per row
+  if (q.K % k_align != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "K=%lld must be a multiple of %lld", (long long)q.K, (long long)k_align);
+  if (!q.A || !q.B || !q.SFA || !q.SFB || !q.D) return fail(BSG_ERR_INVALID_PROBLEM, "A, B, SFA, SFB and D must be non-null");
+  if (!aligned16(q.A) || !aligned16(q.B) || !aligned16(q.D) || (q.C && !aligned16(q.C)))
+    return fail(BSG_ERR_MISALIGNED_OPERAND, "A, B, C and D must be 16-byte aligned");
+  if (!aligned16(q.SFA) || !aligned16(q.SFB)) return fail(BSG_ERR_MISALIGNED_OPERAND, "scale-factor tensors must be 16-byte aligned");
+  if (q.out_kind == BSG_OUT_BF16) {
+    if (q.N % 8 != 0 || q.ldd % 8 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "bf16 output needs N and ldd to be multiples of 8");
+  } else {
+    if (!q.SFD || !q.norm_ptr) return fail(BSG_ERR_INVALID_PROBLEM, "NVFP4 output needs SFD and norm_constant");
+    if (q.N % 16 != 0 || q.ldd % 32 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "NVFP4 output needs N %% 16 == 0 and ldd %% 32 == 0");
+    if (q.offsets) return fail(BSG_ERR_NOT_SUPPORTED, "NVFP4 output is not available for grouped GEMM");
+  }
+  if (q.C && (q.ldc % 8 != 0)) return fail(BSG_ERR_MISALIGNED_OPERAND, "ldc must be a multiple of 8");
+  if (q.ldd < q.N || (q.C && q.ldc < q.N)) return fail(BSG_ERR_INVALID_PROBLEM, "row pitch smaller than N");
+  if (q.beta != 0.0f && !q.C && !q.beta_ptr) return fail(BSG_ERR_INVALID_PROBLEM, "beta != 0 needs C");
+  int32_t cg = q.cta_group == 0 ? 2 : q.cta_group;
+  int32_t tn = q.tile_n == 0 ? (q.N > 128 ? 256 : 128) : q.tile_n;
+  if (cg != 1 && cg != 2) return fail(BSG_ERR_NOT_SUPPORTED, "cta_group must be 1 or 2");
+  if (tn != 128 && tn != 256) return fail(BSG_ERR_NOT_SUPPORTED, "tile_n must be 128 or 256");
+  plan->cta_group = cg;
+  plan->tile_n = tn;
+  if (q.offsets) {
+    plan->num_tiles = -1;
+  } else {
+    const int64_t tile_m = 128 * cg;
+    plan->num_tiles = int64_t(q.num_groups) * ((q.rows_per_group + tile_m - 1) / tile_m) * ((q.N + tn - 1) / tn);
+  }
+  return BSG_OK;
+}
+
+template <int KIND, int CG, int BN>
+int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_t stream, int sm_count, bool dry) {
+  using Cf = bsg::Cfg<KIND, CG, BN>;
+  if (dry) return BSG_OK;
+  const int64_t k_bytes = KIND == bsg::kKindNvfp4 ? q.K / 2 : q.K;
+  const int64_t k_atoms = ((q.K + Cf::kSfVec - 1) / Cf::kSfVec + 3) / 4;
+  const int64_t n_atoms = (q.N + 127) / 128;
+  const int64_t b_groups = q.b_per_group ? q.num_groups : 1;
+  int64_t sfa_row_atoms;
+  if (q.offsets) sfa_row_atoms = q.total_rows / 128 + q.num_groups;   // upper bound; fetches are clamped per group
+  else sfa_row_atoms = int64_t(q.num_groups) * ((q.rows_per_group + 127) / 128);
+
+  CUtensorMap tmA, tmB, tmSFA, tmSFB;
+  int32_t rc;
+  if ((rc = make_operand_map(&tmA, q.A, k_bytes, q.total_rows, Cf::kCtaM)) != BSG_OK) return rc;
+  if ((rc = make_operand_map(&tmB, q.B, k_bytes, b_groups * q.N, Cf::kBRowsCta)) != BSG_OK) return rc;
+  if ((rc = make_sf_map(&tmSFA, q.SFA, k_atoms, sfa_row_atoms, Cf::kKAtoms, 1)) != BSG_OK) return rc;
+  if ((rc = make_sf_map(&tmSFB, q.SFB, k_atoms, b_groups * n_atoms, Cf::kKAtoms, BN / 128)) != BSG_OK) return rc;
+
+  bsg::GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.num_groups = q.num_groups;
+  p.rows_per_group = int32_t(q.rows_per_group);
+  p.total_rows = int32_t(q.total_rows);
+  p.N = int32_t(q.N);
+  p.K = int32_t(q.K);
+  p.offsets = q.offsets;
+  p.b_rows_per_group = q.b_per_group ? int32_t(q.N) : 0;
+  p.sfb_atoms_per_group = q.b_per_group ? int32_t(n_atoms) : 0;
+  p.tiles_n = int32_t((q.N + BN - 1) / BN);
+  p.raster_band = q.raster_band > 0 ? q.raster_band : 8;
+  p.out_kind = q.out_kind;
+  p.C = static_cast<const __nv_bfloat16*>(q.C);
+  p.D = q.D;
+  p.SFD = static_cast<uint8_t*>(q.SFD);
+  p.ldc = q.ldc;
+  p.ldd = q.ldd;
+  p.alpha = q.alpha;
+  p.beta = q.beta;
+  p.alpha_ptr = q.alpha_ptr;
+  p.beta_ptr = q.beta_ptr;
+  p.norm_ptr = q.norm_ptr;
+  p.status = status;
+  p.ready_flags = q.ready_flags;
+  p.rows_per_flag = q.rows_per_flag;
+  p.flag_target = q.flag_target;
+  p.tile_m_rotate = q.tile_m_rotate;
+
+  auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::kSmemBytes);
+  if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+
+  int64_t clusters = sm_count / CG;
+  if (plan.num_tiles >= 0 && plan.num_tiles < clusters) clusters = plan.num_tiles;
+  if (clusters < 1) clusters = 1;
+
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(unsigned(clusters * CG), 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = Cf::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmSFA, tmSFB, p);
+  if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(e));
+  return BSG_OK;
+}
+
+template <int KIND>
+int32_t dispatch_shape(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_t s, int sm, bool dry) {
+  if (plan.cta_group == 2) {
+    return plan.tile_n == 256 ? launch<KIND, 2, 256>(q, plan, status, s, sm, dry) : launch<KIND, 2, 128>(q, plan, status, s, sm, dry);
+  }
+  return plan.tile_n == 256 ? launch<KIND, 1, 256>(q, plan, status, s, sm, dry) : launch<KIND, 1, 128>(q, plan, status, s, sm, dry);
+}
+
+template <int KIND, int CG, int BN>
+void fill_caps_for(bsg_caps* caps) {
+  using Cf = bsg::Cfg<KIND, CG, BN>;
+  caps->tile_m = Cf::kTileM;
+  caps->tile_n = BN;
+  caps->tile_k = Cf::kTileK;
+  caps->cta_group = CG;
+  caps->stages = Cf::kStages;
+  caps->smem_bytes = Cf::kSmemBytes;
+}
+
+void fill_caps(const Problem& q, const Plan& plan, bsg_caps* caps) {
+  if (!caps) return;
+  const bool fp4 = q.kind == BSG_KIND_NVFP4;
+  if (plan.cta_group == 2 && plan.tile_n == 256) fp4 ? fill_caps_for<0, 2, 256>(caps) : fill_caps_for<1, 2, 256>(caps);
+  else if (plan.cta_group == 2) fp4 ? fill_caps_for<0, 2, 128>(caps) : fill_caps_for<1, 2, 128>(caps);
+  else if (plan.tile_n == 256) fp4 ? fill_caps_for<0, 1, 256>(caps) : fill_caps_for<1, 1, 256>(caps);
+  else fp4 ? fill_caps_for<0, 1, 128>(caps) : fill_caps_for<1, 1, 128>(caps);
+  caps->num_tiles = plan.num_tiles;
+}
+
+int32_t run_problem(const Problem& q, void* workspace, size_t ws_bytes, void* stream_v) {
+  Plan plan;
+  int32_t rc = validate(q, &plan);
+  if (rc != BSG_OK) return rc;
+  if (!workspace) return fail(BSG_ERR_WORKSPACE_NULL, "workspace is null");
+  if (ws_bytes < 16) return fail(BSG_ERR_WORKSPACE_NULL, "workspace smaller than 16 bytes");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 3u) != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "workspace must be 4-byte aligned");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+
+  int dev = 0, major = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (major != 10) return fail(BSG_ERR_ARCH_MISMATCH, "device compute capability %d.x is not sm_100", major);
+  if (q.sm_count > 0 && q.sm_count < sms) sms = q.sm_count;
+  if (q.total_rows == 0) return BSG_OK;   // nothing to compute
+
+  e = cudaMemsetAsync(workspace, 0, 16, stream);
+  if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+  uint32_t* status = static_cast<uint32_t*>(workspace);
+  if (q.kind == BSG_KIND_NVFP4) return dispatch_shape<0>(q, plan, status, stream, sms, false);
+  return dispatch_shape<1>(q, plan, status, stream, sms, false);
+}
+
+Problem from_dense(const bsg_gemm_args* a) {
+  Problem q;
+  memset(&q, 0, sizeof(q));
+  q.kind = a->kind;
+  q.out_kind = a->out_kind;
+  q.num_groups = a->batch < 1 ? 1 : a->batch;
+  q.rows_per_group = a->M;
+  q.total_rows = a->M * q.num_groups;
+  q.N = a->N;
+  q.K = a->K;
+  q.A = a->A; q.B = a->B; q.SFA = a->SFA; q.SFB = a->SFB; q.C = a->C; q.D = a->D; q.SFD = a->SFD;
+  q.offsets = nullptr;
+  q.b_per_group = true;
+  q.ldc = a->ldc ? a->ldc : a->N;
+  q.ldd = a->ldd ? a->ldd : a->N;
+  q.alpha = a->alpha; q.beta = a->beta;
+  q.alpha_ptr = a->alpha_ptr; q.beta_ptr = a->beta_ptr; q.norm_ptr = a->norm_constant;
+  q.tile_n = a->tile_n; q.cta_group = a->cta_group; q.sm_count = a->sm_count; q.raster_band = a->raster_band;
+  return q;
+}
+
+Problem from_grouped(const bsg_grouped_args* a) {
+  Problem q;
+  memset(&q, 0, sizeof(q));
+  q.kind = a->kind;
+  q.out_kind = a->out_kind;
+  q.num_groups = a->num_groups;
+  q.rows_per_group = 0;
+  q.total_rows = a->total_M;
+  q.N = a->N;
+  q.K = a->K;
+  q.A = a->A; q.B = a->B; q.SFA = a->SFA; q.SFB = a->SFB; q.C = a->C; q.D = a->D; q.SFD = nullptr;
+  q.offsets = a->offsets;
+  q.b_per_group = true;
+  q.ldc = a->ldc ? a->ldc : a->N;
+  q.ldd = a->ldd ? a->ldd : a->N;
+  q.alpha = a->alpha; q.beta = a->beta;
+  q.tile_n = a->tile_n; q.cta_group = a->cta_group; q.sm_count = a->sm_count; q.raster_band = a->raster_band;
+  return q;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t bsg_version(void) { return 100; }
+
+const char* bsg_last_error_string(void) { return g_err; }
+
+int32_t bsg_gemm_query(const bsg_gemm_args* args, bsg_caps* caps) {
+  if (!args) return fail(BSG_ERR_INVALID_PROBLEM, "args is null");
+  if (args->M < 0 || args->batch < 0) return fail(BSG_ERR_INVALID_PROBLEM, "negative extent");
+  Problem q = from_dense(args);
+  Plan plan;
+  int32_t rc = validate(q, &plan);
+  if (rc != BSG_OK) return rc;
+  fill_caps(q, plan, caps);
+  return BSG_OK;
+}
+
+int32_t bsg_grouped_query(const bsg_grouped_args* args, bsg_caps* caps) {
+  if (!args) return fail(BSG_ERR_INVALID_PROBLEM, "args is null");
+  if (!args->offsets) return fail(BSG_ERR_INVALID_PROBLEM, "offsets is null");
+  Problem q = from_grouped(args);
+  Plan plan;
+  int32_t rc = validate(q, &plan);
+  if (rc != BSG_OK) return rc;
+  fill_caps(q, plan, caps);
+  return BSG_OK;
+}
+
+int32_t bsg_gemm_workspace_size(const bsg_gemm_args* args, size_t* bytes) {
+  if (!args || !bytes) return fail(BSG_ERR_INVALID_PROBLEM, "null argument");
+  *bytes = 16;
+  return BSG_OK;
+}
+
+int32_t bsg_grouped_workspace_size(const bsg_grouped_args* args, size_t* bytes) {
+  if (!args || !bytes) return fail(BSG_ERR_INVALID_PROBLEM, "null argument");
+  *bytes = 16;
+  return BSG_OK;
+}
+
+int32_t bsg_gemm_run(const bsg_gemm_args* args, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  if (!args) return fail(BSG_ERR_INVALID_PROBLEM, "args is null");
+  if (args->M < 0 || args->batch < 0) return fail(BSG_ERR_INVALID_PROBLEM, "negative extent");
+  Problem q = from_dense(args);
+  return run_problem(q, workspace, workspace_bytes, cuda_stream);
+}
+
+int32_t bsg_grouped_run(const bsg_grouped_args* args, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  if (!args) return fail(BSG_ERR_INVALID_PROBLEM, "args is null");
+  if (!args->offsets) return fail(BSG_ERR_INVALID_PROBLEM, "offsets is null");
+  Problem q = from_grouped(args);
+  return run_problem(q, workspace, workspace_bytes, cuda_stream);
+}
+
+int32_t bsg_read_device_status(const void* workspace, void* cuda_stream) {
+  if (!workspace) return fail(BSG_ERR_WORKSPACE_NULL, "workspace is null");
+  uint32_t st = 0;
+  cudaError_t e = cudaMemcpyAsync(&st, workspace, sizeof(st), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(cuda_stream));
+  if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "reading status: %s", cudaGetErrorString(e));
+  if (st == 0) return BSG_OK;
+  if (st & bsg::kStBadOffsets) return fail(BSG_ERR_INVALID_PROBLEM, "group offsets are not monotone or exceed total_M (device status 0x%x)", st);
+  return fail(BSG_ERR_TIMEOUT, "a bounded device-side wait ran out (device status 0x%x)", st);
+}
+
+}  // extern "C"

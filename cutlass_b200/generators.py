@@ -1,0 +1,71 @@
+"""Seeded synthetic operands for the benchmark configurations and the tests.
+
+Value distributions:
+
+* NVFP4 data: e2m1 codes drawn uniformly from the 15 distinct values
+  {0, +-0.5, +-1, +-1.5, +-2, +-3, +-4, +-6} (-0 is never produced);
+  ue4m3 scale factors uniform over the exponents 2^-2 .. 2^2 with zero mantissa,
+  i.e. codes {0x28, 0x30, 0x38, 0x40, 0x48} = {0.25, 0.5, 1, 2, 4}.
+* MXFP8 data: N(0, 1) rounded to e4m3 (nearest even, saturating);
+  ue8m0 scale factors with exponents uniform in [-3, 3] (codes 124 .. 130).
+
+All generators return numpy arrays in the memory layout the library consumes:
+packed K-major data and the interleaved scale-factor buffer.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from . import formats as F
+
+_E2M1_15 = np.array([0, 1, 2, 3, 4, 5, 6, 7, 9, 10, 11, 12, 13, 14, 15], dtype=np.uint8)
+_UE4M3_POW2 = np.array([0x28, 0x30, 0x38, 0x40, 0x48], dtype=np.uint8)
+
+
+def nvfp4_operand(rows: int, K: int, rng: np.random.Generator):
+    """-> (packed (rows, K/2) uint8, sf codes (rows, K/16) uint8, interleaved sf buffer)."""
+    codes = _E2M1_15[rng.integers(0, 15, size=(rows, K), dtype=np.uint8)]
+    packed = F.pack_e2m1(codes)
+    sf = _UE4M3_POW2[rng.integers(0, 5, size=(rows, F.ceil_div(K, 16)), dtype=np.uint8)]
+    return packed, sf, F.swizzle_sf(sf)
+
+
+def mxfp8_operand(rows: int, K: int, rng: np.random.Generator):
+    """-> (e4m3 codes (rows, K) uint8, sf codes (rows, K/32) uint8, interleaved sf buffer)."""
+    x = rng.standard_normal(size=(rows, K), dtype=np.float32)
+    codes = F.encode_e4m3(x)
+    sf = rng.integers(124, 131, size=(rows, F.ceil_div(K, 32)), dtype=np.uint8)
+    return codes, sf, F.swizzle_sf(sf)
+
+
+def exact_nvfp4_operand(rows: int, K: int, rng: np.random.Generator):
+    """Data in {-1, 0, 1} with power-of-two scales {1, 2, 4}: fp32 accumulation is exact
+    in any order (the trick of operators/test/test_utils/gemm.py:366-403 in the reference)."""
+    codes = np.array([0, 2, 10], dtype=np.uint8)[rng.integers(0, 3, size=(rows, K), dtype=np.uint8)]
+    packed = F.pack_e2m1(codes)
+    sf = np.array([0x38, 0x40, 0x48], dtype=np.uint8)[rng.integers(0, 3, size=(rows, F.ceil_div(K, 16)), dtype=np.uint8)]
+    return packed, sf, F.swizzle_sf(sf)
+
+
+def exact_mxfp8_operand(rows: int, K: int, rng: np.random.Generator):
+    """e4m3 data in {-1, 0, 1} (codes 0xB8, 0x00, 0x38) with ue8m0 scales {1, 2, 4}."""
+    codes = np.array([0x00, 0x38, 0xB8], dtype=np.uint8)[rng.integers(0, 3, size=(rows, K), dtype=np.uint8)]
+    sf = np.array([127, 128, 129], dtype=np.uint8)[rng.integers(0, 3, size=(rows, F.ceil_div(K, 32)), dtype=np.uint8)]
+    return codes, sf, F.swizzle_sf(sf)
+
+
+def bf16_normal(shape, rng: np.random.Generator) -> np.ndarray:
+    """N(0,1) rounded to bf16, returned as uint16 bit patterns."""
+    return F.bf16_round(rng.standard_normal(size=shape, dtype=np.float32))
+
+
+def moe_group_sizes(num_experts: int, tokens: int, top_k: int, rng: np.random.Generator, alpha: float = 1.0) -> np.ndarray:
+    """Per-expert row counts: expert probabilities ~ Dirichlet(alpha), tokens*top_k
+    assignments drawn multinomially.  Sums to tokens*top_k."""
+    p = rng.dirichlet(np.full(num_experts, alpha))
+    return rng.multinomial(tokens * top_k, p).astype(np.int32)
+
+
+def grouped_sfa(sf_per_group) -> np.ndarray:
+    """Concatenate per-group interleaved scale-factor buffers (each padded to 128 rows)."""
+    return np.concatenate([F.swizzle_sf(sf) if sf.shape[0] > 0 else np.zeros(0, np.uint8) for sf in sf_per_group])

@@ -1,0 +1,160 @@
+/*
+ * bsgemm.h -- C ABI of the Blackwell (sm_100a) block-scaled GEMM library.
+ *
+ * Plain C, plain pointers and sizes.  Every entry point returns a bsg_status
+ * (0 = success) and never throws, aborts or allocates unless stated.  All
+ * device pointers are ordinary CUDA device pointers owned by the caller; work
+ * is enqueued on the given stream and the call returns without synchronising.
+ *
+ * Each entry point names the interface of the reference library (NVIDIA
+ * CUTLASS, paths relative to its source tree) whose role it takes over.
+ */
+#ifndef BSGEMM_H_
+#define BSGEMM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes, modelled on cutlass::Status (include/cutlass/cutlass.h). */
+typedef enum bsg_status {
+  BSG_OK = 0,
+  BSG_ERR_MISALIGNED_OPERAND = 1,
+  BSG_ERR_INVALID_PROBLEM = 2,
+  BSG_ERR_NOT_SUPPORTED = 3,
+  BSG_ERR_WORKSPACE_NULL = 4,
+  BSG_ERR_INTERNAL = 5,
+  BSG_ERR_ARCH_MISMATCH = 6,
+  BSG_ERR_TIMEOUT = 7,      /* a bounded device-side wait ran out */
+  BSG_ERR_CUDA = 8
+} bsg_status;
+
+/* Operand formats (A and B share one format; scale format follows it). */
+enum {
+  BSG_KIND_NVFP4 = 0,       /* e2m1 data, ue4m3 scale per 16 K-elements */
+  BSG_KIND_MXFP8 = 1        /* e4m3 data, ue8m0 scale per 32 K-elements */
+};
+
+/* Output formats. */
+enum {
+  BSG_OUT_BF16 = 0,         /* D = bf16(alpha*acc + beta*C) */
+  BSG_OUT_NVFP4 = 1         /* D = e2m1 packed + SFD ue4m3 per 16 N-elements, interleaved layout */
+};
+
+/*
+ * Arguments of one dense (optionally batched) block-scaled GEMM
+ *     D[l] = alpha * (A[l] . SFA[l]) (B[l] . SFB[l])^T + beta * C[l].
+ * Field-for-field stand-in for cutlass::library::BlockScaledGemmArguments
+ * (tools/library/include/cutlass/library/library.h:354-397).
+ *
+ * A is (batch, M, K) and B is (batch, N, K), both K-major and densely packed
+ * (two e2m1 per byte, even K index in the low nibble).  SFA / SFB use the
+ * 128-row x 4-K-block interleaved layout of
+ * include/cutlass/detail/sm100_blockscaled_layout.hpp:49-114, one layout per
+ * batch entry, padding included.  C and D are (batch, M, N) row-major.
+ */
+typedef struct bsg_gemm_args {
+  int32_t kind;             /* BSG_KIND_* */
+  int32_t out_kind;         /* BSG_OUT_* */
+  int32_t batch;            /* L >= 1 */
+  int32_t reserved0;
+  int64_t M, N, K;          /* logical extents (K in elements) */
+  const void* A;
+  const void* B;
+  const void* SFA;
+  const void* SFB;
+  const void* C;            /* bf16, may be NULL when beta == 0 */
+  void* D;                  /* bf16, or packed e2m1 when out_kind == BSG_OUT_NVFP4 */
+  void* SFD;                /* ue4m3, interleaved over (M, N/16); BSG_OUT_NVFP4 only */
+  int64_t ldc;              /* C row pitch in elements (0 = N) */
+  int64_t ldd;              /* D row pitch in elements (0 = N) */
+  float alpha;
+  float beta;
+  const float* alpha_ptr;   /* optional device scalars, override alpha / beta */
+  const float* beta_ptr;
+  const float* norm_constant; /* device fp32 scalar, BSG_OUT_NVFP4 only */
+  int32_t tile_n;           /* 0 = library default, else 128 or 256 */
+  int32_t cta_group;        /* 0 = default, else 1 or 2 (CTAs per MMA) */
+  int32_t sm_count;         /* 0 = all SMs of the current device */
+  int32_t raster_band;      /* 0 = default band height in tiles */
+} bsg_gemm_args;
+
+/*
+ * Arguments of a grouped (MoE) GEMM with ragged M: the rows of all groups are
+ * contiguous in A and D, group g owns rows [offsets[g-1], offsets[g]) and its
+ * own B[g] (N x K) and SFB[g].  SFA holds one interleaved layout per group,
+ * back to back, each padded to 128 rows.  Mirrors
+ * cutlass::library::GroupedGemmBlockScaledArguments
+ * (tools/library/include/cutlass/library/library.h:558-605) in its
+ * contiguous-token form (MoEProblemShape,
+ * include/cutlass/gemm/group_array_problem_shape.hpp:85-131) and the Python
+ * GroupedGemmArguments.offsets contract
+ * (operators/cutlass/operators/arguments/grouped_gemm.py:59-86).
+ */
+typedef struct bsg_grouped_args {
+  int32_t kind;
+  int32_t out_kind;         /* BSG_OUT_BF16 only */
+  int32_t num_groups;       /* 1..BSG_MAX_GROUPS */
+  int32_t reserved0;
+  int64_t total_M;          /* rows of A and D (sum of group sizes) */
+  int64_t N, K;
+  const void* A;            /* (total_M, K) */
+  const void* B;            /* (num_groups, N, K) */
+  const void* SFA;
+  const void* SFB;
+  const void* C;            /* (total_M, N) bf16 or NULL */
+  void* D;                  /* (total_M, N) bf16 */
+  const int32_t* offsets;   /* device int32[num_groups], cumulative END rows */
+  int64_t ldc, ldd;
+  float alpha, beta;
+  int32_t tile_n, cta_group, sm_count, raster_band;
+} bsg_grouped_args;
+
+#define BSG_MAX_GROUPS 256
+
+typedef struct bsg_caps {
+  int32_t tile_m, tile_n, tile_k;   /* MMA tile chosen for these arguments */
+  int32_t cta_group;
+  int32_t stages;                   /* shared-memory pipeline depth */
+  int32_t smem_bytes;
+  int64_t num_tiles;                /* -1 when only known on the device (grouped) */
+} bsg_caps;
+
+/* Library version as major*10000 + minor*100 + patch. */
+int32_t bsg_version(void);
+
+/* Text of the last error raised on the calling thread (never NULL). */
+const char* bsg_last_error_string(void);
+
+/* Can these arguments run?  Fills caps when non-NULL.  Replaces
+ * GemmUniversalAdapter::can_implement (include/cutlass/gemm/device/gemm_universal_adapter.h:232)
+ * and Operator.supports (operators/cutlass/operators/base.py:126). */
+int32_t bsg_gemm_query(const bsg_gemm_args* args, bsg_caps* caps);
+int32_t bsg_grouped_query(const bsg_grouped_args* args, bsg_caps* caps);
+
+/* Bytes of device workspace a run needs (a status word; small).  Replaces
+ * GemmUniversalAdapter::get_workspace_size (gemm_universal_adapter.h:243). */
+int32_t bsg_gemm_workspace_size(const bsg_gemm_args* args, size_t* bytes);
+int32_t bsg_grouped_workspace_size(const bsg_grouped_args* args, size_t* bytes);
+
+/* Enqueue the GEMM.  The workspace must stay alive until the stream reaches the
+ * end of the kernel; its first word receives a device-side status
+ * (see bsg_read_device_status).  Replaces GemmUniversalAdapter::initialize + run
+ * (gemm_universal_adapter.h:313,375) and Operator.run
+ * (operators/cutlass/operators/base.py:165). */
+int32_t bsg_gemm_run(const bsg_gemm_args* args, void* workspace, size_t workspace_bytes,
+                     void* cuda_stream);
+int32_t bsg_grouped_run(const bsg_grouped_args* args, void* workspace, size_t workspace_bytes,
+                        void* cuda_stream);
+
+/* Synchronise the stream and translate the workspace status word
+ * (0 -> BSG_OK, otherwise BSG_ERR_TIMEOUT). */
+int32_t bsg_read_device_status(const void* workspace, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BSGEMM_H_ */

@@ -1,0 +1,124 @@
+// TEST INFRASTRUCTURE -- thin C driver around the reference's own host GEMM.
+//
+// This file contains no reference code: it includes the reference headers where
+// they lie (the build passes -I<reference>/include -I<reference>/tools/util/include)
+// and instantiates cutlass::reference::host::Gemm3x
+// (tools/util/include/cutlass/util/reference/host/gett.hpp:837) with the block-scaled
+// parameter structs (gett.hpp:132,279), the reference's numeric types
+// (include/cutlass/float8.h, float_subbyte.h) and its scale-factor layouts
+// (include/cutlass/detail/sm100_blockscaled_layout.hpp:62,192).
+// Built by oracle/Makefile into oracle/_ref/libbsg_ref.so.  Only tests, the smoke
+// check and the CPU-baseline leg of the benchmark may load it.
+#include <cstdint>
+#include <cstring>
+
+#include "cutlass/cutlass.h"
+#include "cutlass/numeric_types.h"
+#include "cutlass/detail/sm100_blockscaled_layout.hpp"
+#include "cutlass/util/reference/host/gett.hpp"
+#include "cute/tensor.hpp"
+
+using namespace cute;
+
+namespace {
+
+template <int Vec>
+using SfCfg = cutlass::detail::Sm1xxBlockScaledConfig<Vec>;
+template <int Vec>
+using SfOutCfg = cutlass::detail::Sm1xxBlockScaledOutputConfig<Vec>;
+
+template <class ElemAB, class ElemSF, int Vec, class ElemD, bool GenSfd>
+void run_gemm(int M, int N, int K, const void* A, const void* B, const void* SFA, const void* SFB,
+              const cutlass::bfloat16_t* C, float alpha, float beta, void* D, void* SFD, float st) {
+  auto layout_A = make_layout(make_shape(M, K, 1), make_stride(int64_t(K), _1{}, int64_t(M) * K));
+  auto layout_B = make_layout(make_shape(N, K, 1), make_stride(int64_t(K), _1{}, int64_t(N) * K));
+  auto layout_C = make_layout(make_shape(M, N, 1), make_stride(int64_t(N), _1{}, int64_t(M) * N));
+  auto layout_SFA = SfCfg<Vec>::tile_atom_to_shape_SFA(make_shape(M, N, K, 1));
+  auto layout_SFB = SfCfg<Vec>::tile_atom_to_shape_SFB(make_shape(M, N, K, 1));
+
+  Tensor tA = make_tensor(recast_ptr<ElemAB>(const_cast<void*>(A)), layout_A);
+  Tensor tB = make_tensor(recast_ptr<ElemAB>(const_cast<void*>(B)), layout_B);
+  Tensor tSFA = make_tensor(reinterpret_cast<ElemSF*>(const_cast<void*>(SFA)), layout_SFA);
+  Tensor tSFB = make_tensor(reinterpret_cast<ElemSF*>(const_cast<void*>(SFB)), layout_SFB);
+  cutlass::reference::host::GettBlockScalingMainloopParams<float, decltype(tA), decltype(tSFA), decltype(tB), decltype(tSFB)>
+      mainloop{tA, tSFA, tB, tSFB};
+
+  Tensor tC = make_tensor(const_cast<cutlass::bfloat16_t*>(C), layout_C);
+  Tensor tD = make_tensor(recast_ptr<ElemD>(D), layout_C);
+  if constexpr (GenSfd) {
+    auto layout_SFD = SfOutCfg<16>::tile_atom_to_shape_SFD(make_shape(M, N, K, 1));
+    Tensor tSFD = make_tensor(reinterpret_cast<cutlass::float_ue4m3_t*>(SFD), layout_SFD);
+    cutlass::reference::host::GettBlockScalingEpilogueParams<float, float, float, decltype(tC), decltype(tD), decltype(tSFD),
+                                                             cute::Int<16>, cutlass::reference::host::SfStrategy::SfDGen>
+        epi{alpha, beta, tC, tD, tSFD, st};
+    cutlass::reference::host::Gemm3x(mainloop, epi);
+  } else {
+    cutlass::reference::host::GettBlockScalingEpilogueParams<float, float, float, decltype(tC), decltype(tD)> epi{alpha, beta, tC, tD};
+    cutlass::reference::host::Gemm3x(mainloop, epi);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+// fmt: 0 e2m1 (4-bit code), 1 e4m3, 2 ue4m3, 3 ue8m0
+float bsg_ref_decode(int fmt, uint32_t code) {
+  switch (fmt) {
+    case 0: return float(cutlass::float_e2m1_t::bitcast(uint8_t(code & 0xF)));
+    case 1: return float(cutlass::float_e4m3_t::bitcast(uint8_t(code)));
+    case 2: return float(cutlass::float_ue4m3_t::bitcast(uint8_t(code)));
+    default: return float(cutlass::float_ue8m0_t::bitcast(uint8_t(code)));
+  }
+}
+
+uint32_t bsg_ref_encode(int fmt, float x) {
+  switch (fmt) {
+    case 0: return cutlass::float_e2m1_t(x).raw() & 0xF;
+    case 1: return cutlass::float_e4m3_t(x).raw();
+    case 2: return cutlass::float_ue4m3_t(x).raw();
+    default: return cutlass::float_ue8m0_t(x).raw();
+  }
+}
+
+// Element offset of the scale factor of (row, k) in the SFA layout of an (rows x K) operand.
+int64_t bsg_ref_sf_offset(int vec, int rows, int K, int row, int k) {
+  if (vec == 16) {
+    auto l = SfCfg<16>::tile_atom_to_shape_SFA(make_shape(rows, 1, K, 1));
+    return int64_t(l(row, k, 0));
+  }
+  auto l = SfCfg<32>::tile_atom_to_shape_SFA(make_shape(rows, 1, K, 1));
+  return int64_t(l(row, k, 0));
+}
+
+int64_t bsg_ref_sf_size(int vec, int rows, int K) {
+  if (vec == 16) return int64_t(size(filter_zeros(SfCfg<16>::tile_atom_to_shape_SFA(make_shape(rows, 1, K, 1)))));
+  return int64_t(size(filter_zeros(SfCfg<32>::tile_atom_to_shape_SFA(make_shape(rows, 1, K, 1)))));
+}
+
+// kind 0 NVFP4 / 1 MXFP8.  out_mode 0: D fp32, 1: D bf16, 2: D e2m1 + SFD ue4m3 (NVFP4 re-quantisation with norm constant st).
+// C is bf16 (may be null when beta == 0).  Returns 0 on success.
+int bsg_ref_gemm(int kind, int out_mode, int M, int N, int K, const void* A, const void* B, const void* SFA, const void* SFB,
+                 const void* C, float alpha, float beta, void* D, void* SFD, float st) {
+  auto Cb = static_cast<const cutlass::bfloat16_t*>(C);
+  if (kind == 0) {
+    using E = cutlass::float_e2m1_t;
+    using S = cutlass::float_ue4m3_t;
+    if (out_mode == 0) run_gemm<E, S, 16, float, false>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, nullptr, 0.f);
+    else if (out_mode == 1) run_gemm<E, S, 16, cutlass::bfloat16_t, false>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, nullptr, 0.f);
+    else if (out_mode == 2) run_gemm<E, S, 16, cutlass::float_e2m1_t, true>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, SFD, st);
+    else return 1;
+  } else if (kind == 1) {
+    using E = cutlass::float_e4m3_t;
+    using S = cutlass::float_ue8m0_t;
+    if (out_mode == 0) run_gemm<E, S, 32, float, false>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, nullptr, 0.f);
+    else if (out_mode == 1) run_gemm<E, S, 32, cutlass::bfloat16_t, false>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, nullptr, 0.f);
+    else if (out_mode == 2) run_gemm<E, S, 32, cutlass::float_e2m1_t, true>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, SFD, st);
+    else return 1;
+  } else {
+    return 1;
+  }
+  return 0;
+}
+
+}  // extern "C"
