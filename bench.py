@@ -1,0 +1,323 @@
+"""Benchmark of the block-scaled GEMM path.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+N = 1: NVFP4 GEMM, M = N = K = 8192 (bf16 output, alpha = 1, beta = 0), the shape the
+headline metric is quoted on.  A "step" is one GEMM over one set of operands resident in
+HBM; several operand sets are rotated so that every step starts with a cold L2.
+N > 1: tensor-parallel MXFP8 GEMM (M = 16384, N = 28672, K = 8192), A row-sharded and
+all-gathered over NVLink inside the GEMM, B column-sharded; strong scaling, one rank per GPU.
+
+One JSON line is printed by rank 0.  ``value`` is kernel throughput with operands in HBM;
+``e2e`` is the same metric through the operator API with host buffers (pinned host -> device
+copies of the operands and a device -> host read of D inside the timed region);
+``roofline`` compares against the tensor-core peak; ``cpu_baseline`` is the reference's host
+GEMM timed on this machine's CPU cores on a row slab of the same problem.
+
+``--impl reference`` times that CPU implementation alone on the same configuration.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+NOMINAL_FP4_TFLOPS = 9000.0
+NOMINAL_FP8_TFLOPS = 4500.0
+# Algorithmic DRAM bytes of one NVFP4 8192^3 launch: A + B (33.5 MB each), SFA + SFB (4.2 MB each), D bf16 (134 MB).
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f)
+    return {}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:  # noqa: BLE001
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonHwPowerBrakeSlowdown: "hw_power_brake_slowdown",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        med = statistics.median(self.samples) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------- operands
+def gpu_nvfp4_operand(rows: int, K: int, gen, device):
+    """Seeded NVFP4 operand generated on the device: 15 distinct e2m1 values (no -0), ue4m3 scales in {0.25..4}."""
+    import torch
+    from cutlass_b200 import formats as F
+    lut = torch.tensor([0, 1, 2, 3, 4, 5, 6, 7, 9, 10, 11, 12, 13, 14, 15], dtype=torch.uint8, device=device)
+    codes = lut[torch.randint(0, 15, (rows, K), device=device, generator=gen)]
+    packed = (codes[:, 0::2] | (codes[:, 1::2] << 4)).contiguous()
+    sfl = torch.tensor([0x28, 0x30, 0x38, 0x40, 0x48], dtype=torch.uint8, device=device)
+    sf = sfl[torch.randint(0, 5, (F.numel_scale(rows, K, 16),), device=device, generator=gen)]
+    return packed, sf
+
+
+def gpu_mxfp8_operand(rows: int, K: int, gen, device):
+    """Seeded MXFP8 operand: N(0,1) rounded to e4m3, ue8m0 scale exponents uniform in [-3, 3]."""
+    import torch
+    from cutlass_b200 import formats as F
+    data = torch.randn((rows, K), device=device, generator=gen).to(torch.float8_e4m3fn).view(torch.uint8)
+    sf = torch.randint(124, 131, (F.numel_scale(rows, K, 32),), dtype=torch.uint8, device=device, generator=gen)
+    return data, sf
+
+
+# --------------------------------------------------------------------------- CPU baseline
+def cpu_baseline(kind: int, A_slab: np.ndarray, SFA_slab: np.ndarray, B: np.ndarray, SFB: np.ndarray, N: int, K: int, repeats: int = 1):
+    """Times the reference's host GEMM (oracle/_ref when present, else the C port) on a row slab."""
+    import oracle
+    rows = A_slab.shape[0]
+    ref = oracle.load_ref()
+    kind_name = "reference" if ref is not None else "port"
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        if ref is not None:
+            oracle.ref_gemm(kind, 1, A_slab, SFA_slab, B, SFB, rows, N, K)
+        else:
+            oracle.to_bf16(oracle.gemm_fp32(kind, A_slab, SFA_slab, B, SFB, rows, N, K))
+        times.append(time.perf_counter() - t0)
+    best = min(times)
+    cores = oracle.load_oracle().bsg_oracle_threads()
+    return {"value": 2.0 * rows * N * K / best / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": kind_name,
+            "sample": f"rows 0..{rows - 1} of M (full N={N}, K={K}); {best:.2f} s; scaled linearly in M", "seconds": best}
+
+
+# --------------------------------------------------------------------------- single GPU
+def run_single(args) -> dict:
+    import torch
+    import cutlass_b200 as ops
+    from cutlass_b200 import lib as L
+
+    kind = L.KIND_NVFP4
+    M = N = K = 8192
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(0)
+    mode, SW = ops.ScaleMode.Blockwise1x16, ops.ScaleSwizzleMode.Swizzle32x4x4
+
+    bytes_per_set = M * K // 2 + N * K // 2 + 2 * (M * K // 16) + M * N * 2
+    n_sets = max(2, -(-2 * L2_BYTES // bytes_per_set))
+    sets = []
+    for _ in range(n_sets):
+        A, SFA = gpu_nvfp4_operand(M, K, gen, dev)
+        B, SFB = gpu_nvfp4_operand(N, K, gen, dev)
+        D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        sets.append(ops.GemmArguments(ops.ScaledOperand(A, SFA, mode, SW), ops.ScaledOperand(B.t(), SFB, mode, SW), D, torch.float32))
+    op = ops.get_operators(sets[0])[0]
+    artifact = op.compile(sets[0])
+    stream = torch.cuda.current_stream()
+    abi_args = [op.build_args(a) for a in sets]
+    ws = torch.zeros(16, dtype=torch.uint8, device=dev)
+    lib = artifact.library
+
+    def launch(i):
+        rc = lib.bsg_gemm_run(C.byref(abi_args[i % n_sets]), ws.data_ptr(), 16, stream.cuda_stream)
+        if rc != 0:
+            raise RuntimeError(L.last_error())
+
+    for i in range(args.warmup):
+        launch(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clk:
+        e0.record(stream)
+        for i in range(args.steps):
+            launch(i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+    L.check(lib.bsg_read_device_status(ws.data_ptr(), stream.cuda_stream))
+    ms = e0.elapsed_time(e1) / args.steps
+    flops = 2.0 * M * N * K
+    tflops = flops / ms / 1e9
+
+    # ---- end to end through the operator API with host buffers
+    hA = [t.cpu().pin_memory() for t in (sets[0].A.quantized.tensor, sets[0].A.scale.tensor)]
+    hB = [t.cpu().pin_memory() for t in (sets[0].B.quantized.tensor.t().contiguous(), sets[0].B.scale.tensor)]
+    hD = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    dA, dSFA = torch.empty_like(sets[0].A.quantized.tensor), torch.empty_like(sets[0].A.scale.tensor)
+    dB, dSFB = torch.empty((N, K // 2), dtype=torch.uint8, device=dev), torch.empty_like(sets[0].B.scale.tensor)
+    dD = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    e2e_args = ops.GemmArguments(ops.ScaledOperand(dA, dSFA, mode, SW), ops.ScaledOperand(dB.t(), dSFB, mode, SW), dD, torch.float32)
+    h2d = sum(t.numel() * t.element_size() for t in hA + hB)
+    d2h = hD.numel() * hD.element_size()
+
+    def e2e_step():
+        dA.copy_(hA[0], non_blocking=True)
+        dSFA.copy_(hA[1], non_blocking=True)
+        dB.copy_(hB[0], non_blocking=True)
+        dSFB.copy_(hB[1], non_blocking=True)
+        op.run(e2e_args, compiled_artifact=artifact, stream=stream, workspace=ws)
+        hD.copy_(dD, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 20))
+    for _ in range(2):
+        e2e_step()
+    torch.cuda.synchronize()
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    # ---- CPU baseline on a row slab of the same problem
+    slab = args.cpu_rows
+    A_np = sets[0].A.quantized.tensor[:slab].cpu().numpy()
+    SFA_np = sets[0].A.scale.tensor[: (slab // 128) * 128 * (K // 16)].cpu().numpy()
+    B_np = sets[0].B.quantized.tensor.t().contiguous().cpu().numpy()
+    SFB_np = sets[0].B.scale.tensor.cpu().numpy()
+    cpu = cpu_baseline(kind, A_np, SFA_np, B_np, SFB_np, N, K)
+    # parity of the slab against the GPU result of set 0
+    import oracle
+    launch(0)
+    torch.cuda.synchronize()
+    got = sets[0].out.tensor[:slab].view(torch.int16).cpu().numpy().view(np.uint16)
+    want = oracle.ref_gemm(kind, 1, A_np, SFA_np, B_np, SFB_np, slab, N, K) if oracle.load_ref() is not None else \
+        oracle.to_bf16(oracle.gemm_fp32(kind, A_np, SFA_np, B_np, SFB_np, slab, N, K))
+    from cutlass_b200 import formats as F
+    gf, wf = F.bf16_to_f32(got), F.bf16_to_f32(want)
+    rel = float(np.max(np.abs(gf - wf)) / max(float(np.max(np.abs(wf))), 1e-30))
+
+    peaks = measured_peaks()
+    bf16_burst = peaks.get("bf16_tflops")
+    peak = 4.0 * bf16_burst if bf16_burst else 4.0 * 1590.0
+    caps = L.Caps()
+    lib.bsg_gemm_query(C.byref(abi_args[0]), C.byref(caps))
+    return {
+        "metric": "nvfp4_gemm_8192_tflops", "value": round(tflops, 1), "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 5), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3/16), fp32 accumulate, bf16 out",
+        "data": "synthetic",
+        "config": {"workload": "NVFP4 block-scaled GEMM M=N=K=8192, alpha=1, beta=0, bf16 D", "M": M, "N": N, "K": K,
+                   "l2_policy": f"{n_sets} operand/output sets rotated, {bytes_per_set * n_sets >> 20} MiB > L2 126 MiB",
+                   "tile": [caps.tile_m, caps.tile_n, caps.tile_k], "cta_group": caps.cta_group, "stages": caps.stages,
+                   "pct_of_nominal_fp4_peak": round(100.0 * tflops / NOMINAL_FP4_TFLOPS, 1)},
+        "e2e": {"value": round(flops / e2e_ms / 1e9, 1), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": round(e2e_ms, 4), "steps": e2e_steps},
+        "gpu_launches": args.steps,
+        "clocks": clk.summary(),
+        "roofline": {"bound": "tensor", "achieved": round(tflops, 1), "peak": round(peak, 1), "unit": "TFLOP/s",
+                     "frac": round(tflops / peak, 4),
+                     "peak_source": ("4 x bf16_tflops of MEASURED_PEAKS.json (burst; no fp4 figure is measured)" if bf16_burst
+                                     else "4 x fallback bf16 1590"),
+                     "frac_of_nominal_9000": round(tflops / NOMINAL_FP4_TFLOPS, 4),
+                     "traffic": None},
+        "cpu_baseline": {k: (round(v, 5) if isinstance(v, float) else v) for k, v in cpu.items()},
+        "parity": {"slab_rows": slab, "max_rel_err_vs_cpu_reference": rel},
+    }
+
+
+# --------------------------------------------------------------------------- reference arm
+def run_reference(args) -> dict:
+    """The reference's host GEMM on this machine's CPU cores, same configuration, bounded sample per step."""
+    from cutlass_b200 import generators as G
+    kind, M, N, K = 0, 8192, 8192, 8192
+    slab = args.cpu_rows
+    rng = np.random.default_rng(0)
+    A, _, SFA = G.nvfp4_operand(slab, K, rng)
+    B, _, SFB = G.nvfp4_operand(N, K, rng)
+    steps = max(1, min(args.steps, 3))
+    for _ in range(min(args.warmup, 1)):
+        cpu_baseline(kind, A[:128], SFA[: 128 * (K // 16)], B, SFB, N, K)
+    res = [cpu_baseline(kind, A, SFA, B, SFB, N, K) for _ in range(steps)]
+    best = max(res, key=lambda r: r["value"])
+    ms_full = 2.0 * M * N * K / (best["value"] * 1e12) * 1e3
+    return {
+        "impl": "reference", "metric": "nvfp4_gemm_8192_tflops", "value": round(best["value"], 5), "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": round(ms_full, 1),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4, fp32 accumulate, bf16 out",
+        "data": "synthetic",
+        "config": {"workload": "NVFP4 block-scaled GEMM M=N=K=8192, alpha=1, beta=0, bf16 D", "M": M, "N": N, "K": K},
+        "cpu_baseline": {"value": round(best["value"], 5), "unit": "TFLOP/s", "cores": best["cores"], "kind": best["kind"],
+                         "sample": best["sample"]},
+        "e2e": {"value": round(best["value"], 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--cpu-rows", type=int, default=256, help="rows of M in the CPU baseline sample")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps(run_reference(args)))
+        return
+    if args.gpus == 1:
+        print(json.dumps(run_single(args)))
+        return
+    from cutlass_b200 import tp_bench
+    out = tp_bench.run(args)
+    if rank == 0:
+        print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

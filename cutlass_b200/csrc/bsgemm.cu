@@ -10,6 +10,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 
 #include "../../include/bsgemm.h"
 #include "gemm_kernel.cuh"
@@ -69,6 +70,21 @@ int32_t make_sf_map(CUtensorMap* map, const void* base, uint64_t k_atoms, uint64
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(BSG_ERR_CUDA, "cuTensorMapEncodeTiled(scale factors) failed with %d", int(r));
+  return BSG_OK;
+}
+
+// Output matrix for the epilogue's TMA stores: box = 64 elements x 32 rows, 128-byte swizzle.
+int32_t make_out_map(CUtensorMap* map, const void* base, bool bf16, uint64_t cols, uint64_t rows, uint64_t pitch_bytes) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return fail(BSG_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {64, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims,
+                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, bf16 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(BSG_ERR_CUDA, "cuTensorMapEncodeTiled(output) failed with %d", int(r));
   return BSG_OK;
 }
 
@@ -150,8 +166,11 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   if (q.offsets) sfa_row_atoms = q.total_rows / 128 + q.num_groups;   // upper bound; fetches are clamped per group
   else sfa_row_atoms = int64_t(q.num_groups) * ((q.rows_per_group + 127) / 128);
 
-  CUtensorMap tmA, tmB, tmSFA, tmSFB;
+  CUtensorMap tmA, tmB, tmSFA, tmSFB, tmD;
   int32_t rc;
+  if (q.out_kind == BSG_OUT_BF16) rc = make_out_map(&tmD, q.D, true, uint64_t(q.N), uint64_t(q.total_rows), uint64_t(q.ldd) * 2);
+  else rc = make_out_map(&tmD, q.D, false, uint64_t(q.N / 2), uint64_t(q.total_rows), uint64_t(q.ldd) / 2);   // not used by the kernel
+  if (rc != BSG_OK) return rc;
   if ((rc = make_operand_map(&tmA, q.A, k_bytes, q.total_rows, Cf::kCtaM)) != BSG_OK) return rc;
   if ((rc = make_operand_map(&tmB, q.B, k_bytes, b_groups * q.N, Cf::kBRowsCta)) != BSG_OK) return rc;
   if ((rc = make_sf_map(&tmSFA, q.SFA, k_atoms, sfa_row_atoms, Cf::kKAtoms, 1)) != BSG_OK) return rc;
@@ -185,6 +204,9 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   p.rows_per_flag = q.rows_per_flag;
   p.flag_target = q.flag_target;
   p.tile_m_rotate = q.tile_m_rotate;
+#ifdef BSG_PROFILE
+  { const char* dbg = getenv("BSG_DEBUG_FLAGS"); p.debug_flags = dbg ? atoi(dbg) : 0; }
+#endif
 
   auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::kSmemBytes);
@@ -207,7 +229,7 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmSFA, tmSFB, p);
+  e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmSFA, tmSFB, tmD, p);
   if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(e));
   return BSG_OK;
 }
@@ -259,8 +281,6 @@ int32_t run_problem(const Problem& q, void* workspace, size_t ws_bytes, void* st
   if (q.sm_count > 0 && q.sm_count < sms) sms = q.sm_count;
   if (q.total_rows == 0) return BSG_OK;   // nothing to compute
 
-  e = cudaMemsetAsync(workspace, 0, 16, stream);
-  if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
   uint32_t* status = static_cast<uint32_t*>(workspace);
   if (q.kind == BSG_KIND_NVFP4) return dispatch_shape<0>(q, plan, status, stream, sms, false);
   return dispatch_shape<1>(q, plan, status, stream, sms, false);
@@ -363,13 +383,24 @@ int32_t bsg_grouped_run(const bsg_grouped_args* args, void* workspace, size_t wo
   return run_problem(q, workspace, workspace_bytes, cuda_stream);
 }
 
-int32_t bsg_read_device_status(const void* workspace, void* cuda_stream) {
+int32_t bsg_workspace_init(void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  if (!workspace) return fail(BSG_ERR_WORKSPACE_NULL, "workspace is null");
+  if (workspace_bytes < 16) return fail(BSG_ERR_WORKSPACE_NULL, "workspace smaller than 16 bytes");
+  cudaError_t e = cudaMemsetAsync(workspace, 0, 16, static_cast<cudaStream_t>(cuda_stream));
+  if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+  return BSG_OK;
+}
+
+int32_t bsg_read_device_status(void* workspace, void* cuda_stream) {
   if (!workspace) return fail(BSG_ERR_WORKSPACE_NULL, "workspace is null");
   uint32_t st = 0;
-  cudaError_t e = cudaMemcpyAsync(&st, workspace, sizeof(st), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(cuda_stream));
-  if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(cuda_stream));
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  cudaError_t e = cudaMemcpyAsync(&st, workspace, sizeof(st), cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
   if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "reading status: %s", cudaGetErrorString(e));
   if (st == 0) return BSG_OK;
+  e = cudaMemsetAsync(workspace, 0, 16, stream);   // the status is sticky until it has been read
+  if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "clearing status: %s", cudaGetErrorString(e));
   if (st & bsg::kStBadOffsets) return fail(BSG_ERR_INVALID_PROBLEM, "group offsets are not monotone or exceed total_M (device status 0x%x)", st);
   return fail(BSG_ERR_TIMEOUT, "a bounded device-side wait ran out (device status 0x%x)", st);
 }

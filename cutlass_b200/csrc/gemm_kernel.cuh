@@ -13,12 +13,17 @@
 // CTAs of a cluster form one 256-row MMA (cta_group::2): both load their half
 // of A and B, the even CTA issues the MMA, both run their own epilogue.
 //
+// The producer and MMA warps run their loops with all 32 lanes (warp-uniform
+// control flow and operands; only the issuing instructions are predicated on one
+// elected lane), which keeps descriptors and addresses in uniform registers.
+//
 // This takes the place of the reference kernel
 // include/cutlass/gemm/kernel/sm100_gemm_tma_warpspecialized.hpp together with the
 // mainloop include/cutlass/gemm/collective/sm100_blockscaled_mma_warpspecialized.hpp
 // (load :879, mma :949) and the linear-combination / block-scale-factor epilogue
 // (include/cutlass/epilogue/fusion/sm100_visitor_store_tma_warpspecialized.hpp:226-275).
-// Every wait is bounded: on a timeout the kernel records a status bit, drains and returns.
+// Every wait is bounded: on a timeout the kernel records a status bit, keeps going
+// through the motions with short waits, and returns.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -70,7 +75,14 @@ struct GemmParams {
   int32_t rows_per_flag;
   uint32_t flag_target;
   int32_t tile_m_rotate;      // dense only: start the M sweep at this tile row
+  int32_t debug_flags;        // only read when built with -DBSG_PROFILE (ablation switches, timeline capture)
 };
+
+#ifdef BSG_PROFILE
+#define BSG_FLAG(p, bit) (((p).debug_flags & (bit)) != 0)
+#else
+#define BSG_FLAG(p, bit) false
+#endif
 
 template <int KIND, int CG, int BN>
 struct Cfg {
@@ -91,17 +103,18 @@ struct Cfg {
   static constexpr int kSfbBytes = (BN / 128) * kKAtoms * 512;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   static constexpr int kCtlBytes = 8192;
+  static constexpr int kEpiBytes = 4 * 4096;              // per epilogue warp: 32 rows x 128 bytes of bf16 output
   static constexpr int kSmemLimit = 232448;               // 227 KB
-  static constexpr int kStagesRaw = (kSmemLimit - kCtlBytes - 1024) / kStageBytes;
+  static constexpr int kStagesRaw = (kSmemLimit - kCtlBytes - kEpiBytes - 1024) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kCtlBytes + 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kCtlBytes + 1024;
   // TMEM columns: two accumulators (overlapping by 48 columns when BN == 256), then SFA, then SFB.
   static constexpr int kAccStride = BN == 256 ? 208 : 128;
   static constexpr int kAccBars = BN == 256 ? 1 : 2;
   static constexpr int kSfaCol = 464;
   static constexpr int kSfbCol = 480;
-  static constexpr int kChunks = BN / 32;
-  static constexpr int kReleaseChunk = BN == 256 ? 1 : kChunks - 1;   // chunk after whose load the accumulator is released
+  static constexpr int kPairs = BN / 64;                  // the epilogue drains 64 columns at a time
+  static constexpr int kReleasePair = BN == 256 ? 0 : kPairs - 1;   // pair after whose load the accumulator is released
 };
 
 struct alignas(8) Ctl {
@@ -109,7 +122,6 @@ struct alignas(8) Ctl {
   uint64_t empty[8];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
-  uint64_t drain;
   uint32_t tmem_base;
   volatile uint32_t abort;
   int32_t total_tiles;
@@ -127,6 +139,7 @@ struct TileInfo {
   int32_t row_end;    // end row of the group
   int32_t group_row0; // first row of the group
   int32_t sf_atom;    // SFA / SFD row-atom index of the tile's first row
+  int32_t group_atom0;
 };
 
 __device__ __forceinline__ TileInfo decode_tile(const Ctl* ctl, const GemmParams& p, int32_t t, int32_t tile_m) {
@@ -152,25 +165,32 @@ __device__ __forceinline__ TileInfo decode_tile(const Ctl* ctl, const GemmParams
   ti.group_row0 = ctl->row0[lo];
   ti.row0 = ti.group_row0 + tm * tile_m;
   ti.row_end = ti.group_row0 + rows;
-  ti.sf_atom = ctl->atom0[lo] + tm * (tile_m / 128);
+  ti.group_atom0 = ctl->atom0[lo];
+  ti.sf_atom = ti.group_atom0 + tm * (tile_m / 128);
   return ti;
 }
 
-// Bounded mbarrier wait.  Returns false (and raises the CTA abort flag and a status bit) on timeout.
-__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, Ctl* ctl, uint32_t* status, uint32_t code) {
-  if (ptx::mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = ptx::globaltimer_ns();
-  uint32_t spins = 0;
+// Slow path of a barrier wait; only reached when the fast spin gave up, i.e. when
+// something is wrong or the machine is badly oversubscribed.  Bounded by SM cycles.
+__device__ __noinline__ uint32_t slow_wait(uint32_t bar, uint32_t parity, Ctl* ctl) {
+  const long long t0 = clock64();
   while (true) {
-    if (ptx::mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0u) {
-      const uint64_t limit = ctl->abort ? 20000ull : 2000000000ull;   // 20 us once aborting, else 2 s
-      if (ptx::globaltimer_ns() - t0 > limit) break;
-    }
+    if (ptx::mbar_spin(bar, parity, 64)) return 1;
+    const long long limit = ctl->abort ? 40000ll : 4000000000ll;   // ~20 us once aborting, else ~2 s
+    if (clock64() - t0 > limit) break;
   }
   ctl->abort = 1;
-  atomicOr(status, code);
-  return false;
+  return 0;
+}
+
+// Bounded wait on an mbarrier phase.  `dead` is this thread's sticky failure flag: once a wait
+// has timed out, later waits give up quickly so that the kernel still terminates in bounded time.
+__device__ __forceinline__ void wait_barrier(uint32_t bar, uint32_t parity, Ctl* ctl, uint32_t& dead) {
+  uint32_t ok = ptx::mbar_spin(bar, parity, dead ? 16u : 100000u);
+  if (!ok) {
+    ok = dead ? 0u : slow_wait(bar, parity, ctl);
+    if (!ok) dead = 1;
+  }
 }
 
 __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr) {
@@ -183,7 +203,7 @@ __device__ __forceinline__ uint64_t make_desc_sf(uint32_t smem_addr) {
 }
 
 template <int KIND, int CG, int BN>
-__device__ __forceinline__ uint32_t make_idesc() {
+__device__ __forceinline__ constexpr uint32_t make_idesc() {
   constexpr uint32_t fmt = KIND == kKindNvfp4 ? 1u : 0u;       // E2M1 (mxf4) / E4M3 (mxf8f6f4)
   constexpr uint32_t sf_fmt = KIND == kKindNvfp4 ? 0u : 1u;    // UE4M3 / UE8M0
   constexpr uint32_t m = 128u * CG;
@@ -195,21 +215,25 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+__device__ __forceinline__ int32_t bcast(int32_t v) { return __shfl_sync(0xffffffffu, v, 0); }
+__device__ __forceinline__ uint32_t bcast(uint32_t v) { return __shfl_sync(0xffffffffu, v, 0); }
+
 template <int KIND, int CG, int BN>
 __global__ void __launch_bounds__(192, 1)
 bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
-                const GemmParams p) {
+                const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
   using C = Cfg<KIND, CG, BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = sA + C::kStages * C::kABytes;
-  uint8_t* sSFA = sB + C::kStages * C::kBBytes;
+  uint8_t* sEpi = sB + C::kStages * C::kBBytes;                 // 1024-byte aligned (swizzled TMA-store source)
+  uint8_t* sSFA = sEpi + C::kEpiBytes;
   uint8_t* sSFB = sSFA + C::kStages * C::kSfaBytes;
   Ctl* ctl = reinterpret_cast<Ctl*>(sSFB + C::kStages * C::kSfbBytes);
 
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xffffffffu, int(threadIdx.x >> 5), 0);   // warp-uniform for the compiler
   const int lane = threadIdx.x & 31;
   const uint32_t cta_rank = CG == 2 ? ptx::cluster_ctarank() : 0u;
   const bool is_leader = cta_rank == 0;
@@ -226,7 +250,6 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       ptx::mbar_init(ptx::smem_u32(&ctl->tmem_full[s]), 1);
       ptx::mbar_init(ptx::smem_u32(&ctl->tmem_empty[s]), 4 * CG);
     }
-    ptx::mbar_init(ptx::smem_u32(&ctl->drain), 1);
     ctl->abort = 0;
     ptx::fence_mbar_init();
     ptx::fence_proxy_async();
@@ -236,6 +259,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     ptx::prefetch_tmap(&tmB);
     ptx::prefetch_tmap(&tmSFA);
     ptx::prefetch_tmap(&tmSFB);
+    ptx::prefetch_tmap(&tmD);
   }
   // Group table: end rows first (parallel), then a serial prefix by one thread.
   for (int g = threadIdx.x; g < p.num_groups; g += blockDim.x) {
@@ -269,132 +293,162 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if constexpr (CG == 2) { ptx::cluster_arrive(); ptx::cluster_wait(); } else { __syncthreads(); }
   ptx::tc_fence_after();
 
-  const uint32_t tmem_base = ctl->tmem_base;
-  const int32_t total_tiles = ctl->total_tiles;
+  const uint32_t tmem_base = bcast(ctl->tmem_base);
+  const int32_t total_tiles = bcast(ctl->total_tiles);
   const int32_t k_tiles = (p.K + C::kTileK - 1) / C::kTileK;
+  uint32_t dead = 0;
+#ifdef BSG_PROFILE
+  // Timeline capture: the workspace holds, after its first 1024 bytes, 3 regions of 4096 events
+  // (producer, MMA, epilogue) of (code << 48 | SM clock), written by the first cluster only.
+  unsigned long long* dbg = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(p.status) + 1024);
+  const bool dbg_on = BSG_FLAG(p, 256) && cluster_idx == 0 && is_leader;
+  uint32_t dbg_n = 0;
+#define BSG_DBG(region, code) do { if (dbg_on && lane == 0 && dbg_n < 4096) { dbg[(region) * 4096 + dbg_n++] = ((unsigned long long)(code) << 48) | ((unsigned long long)clock64() & 0xFFFFFFFFFFFFull); } } while (0)
+#else
+#define BSG_DBG(region, code) do { } while (0)
+#endif
 
   if (warp == 5) {
     // ---------------------------------------------------------------- TMA producer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int32_t t = cluster_idx; t < total_tiles && ok; t += num_clusters) {
-        const TileInfo ti = decode_tile(ctl, p, t, C::kTileM);
-        const int32_t a_row = ti.row0 + int32_t(cta_rank) * C::kCtaM;
-        const int32_t b_row = ti.g * p.b_rows_per_group + ti.tn * BN + int32_t(cta_rank) * C::kBRowsCta;
-        // The second CTA of a pair may lie wholly past the group's last row: keep its
-        // scale-factor fetch inside the group's own atoms (its rows are never stored).
-        const int32_t group_atoms = (ti.row_end - ti.group_row0 + 127) >> 7;
-        const int32_t sfa_atom = min(ti.sf_atom + int32_t(cta_rank), ctl->atom0[ti.g] + max(group_atoms, 1) - 1);
-        const int32_t sfb_atom = ti.g * p.sfb_atoms_per_group + ti.tn * (BN / 128);
-        if (p.ready_flags != nullptr) {
-          const uint32_t* flag = p.ready_flags + ti.row0 / p.rows_per_flag;
-          const uint64_t t0 = ptx::globaltimer_ns();
-          while (ptx::ld_acquire_sys_u32(flag) < p.flag_target) {
-            if (ptx::globaltimer_ns() - t0 > 2000000000ull || ctl->abort) {
-              ctl->abort = 1;
-              atomicOr(p.status, kStTimeoutFlag);
-              ok = false;
-              break;
-            }
-            __nanosleep(64);
-          }
-          if (!ok) break;
-          asm volatile("fence.proxy.async;" ::: "memory");
-        }
-        for (int32_t kt = 0; kt < k_tiles; ++kt) {
-          if (!bounded_wait(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.status, kStTimeoutEmpty)) {
-            ok = false;
+    const uint32_t elected = ptx::elect_one_sync();
+    const uint32_t sA0 = ptx::smem_u32(sA), sB0 = ptx::smem_u32(sB);
+    const uint32_t sSFA0 = ptx::smem_u32(sSFA), sSFB0 = ptx::smem_u32(sSFB);
+    const uint32_t full0 = ptx::smem_u32(&ctl->full[0]), empty0 = ptx::smem_u32(&ctl->empty[0]);
+    const uint32_t full0_leader = CG == 2 ? ptx::mapa(full0, 0) : full0;
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int32_t t = cluster_idx; t < total_tiles; t += num_clusters) {
+      const TileInfo ti = decode_tile(ctl, p, t, C::kTileM);
+      const int32_t a_row = bcast(ti.row0 + int32_t(cta_rank) * C::kCtaM);
+      const int32_t b_row = bcast(ti.g * p.b_rows_per_group + ti.tn * BN + int32_t(cta_rank) * C::kBRowsCta);
+      // The second CTA of a pair may lie wholly past the group's last row: keep its
+      // scale-factor fetch inside the group's own atoms (its rows are never stored).
+      const int32_t group_atoms = (ti.row_end - ti.group_row0 + 127) >> 7;
+      const int32_t sfa_atom = bcast(min(ti.sf_atom + int32_t(cta_rank), ti.group_atom0 + max(group_atoms, 1) - 1));
+      const int32_t sfb_atom = bcast(ti.g * p.sfb_atoms_per_group + ti.tn * (BN / 128));
+      if (p.ready_flags != nullptr) {
+        const uint32_t* flag = p.ready_flags + ti.row0 / p.rows_per_flag;
+        const long long t0 = clock64();
+        while (ptx::ld_acquire_sys_u32(flag) < p.flag_target) {
+          if (dead || ctl->abort || clock64() - t0 > 4000000000ll) {
+            if (!dead) atomicOr(p.status, kStTimeoutFlag);
+            dead = 1;
+            ctl->abort = 1;
             break;
           }
-          const uint32_t full_local = ptx::smem_u32(&ctl->full[stage]);
-          if (is_leader) ptx::mbar_arrive_expect_tx(full_local, uint32_t(C::kStageBytes) * CG);
-          const uint32_t bar = CG == 2 ? ptx::mapa(full_local, 0) : full_local;
-          ptx::tma_load_2d<CG>(ptx::smem_u32(sA + stage * C::kABytes), &tmA, bar, kt * C::kRowBytes, a_row);
-          ptx::tma_load_2d<CG>(ptx::smem_u32(sB + stage * C::kBBytes), &tmB, bar, kt * C::kRowBytes, b_row);
-          ptx::tma_load_3d<CG>(ptx::smem_u32(sSFA + stage * C::kSfaBytes), &tmSFA, bar, 0, kt * C::kKAtoms, sfa_atom);
-          ptx::tma_load_3d<CG>(ptx::smem_u32(sSFB + stage * C::kSfbBytes), &tmSFB, bar, 0, kt * C::kKAtoms, sfb_atom);
-          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+          __nanosleep(64);
         }
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __syncwarp();
       }
-      // Tail: every stage must have been released, so that no commit-arrive is still
-      // in flight towards this CTA's shared memory when it exits.
-      for (int s = 0; s < C::kStages && ok; ++s) {
-        ok = bounded_wait(ptx::smem_u32(&ctl->empty[stage]), phase ^ 1u, ctl, p.status, kStTimeoutEmpty);
+      for (int32_t kt = 0; kt < k_tiles; ++kt) {
+        wait_barrier(empty0 + stage * 8, phase ^ 1u, ctl, dead);
+        BSG_DBG(0, 1);
+        if (elected) {
+          const uint32_t full_local = full0 + stage * 8;
+          uint32_t txb = 0;
+          if (!BSG_FLAG(p, 2)) txb += C::kABytes + C::kBBytes;
+          if (!BSG_FLAG(p, 16)) txb += C::kSfaBytes + C::kSfbBytes;
+          if (is_leader) { if (txb) ptx::mbar_arrive_expect_tx(full_local, txb * CG); else ptx::mbar_arrive(full_local); }
+          const uint32_t bar = full0_leader + stage * 8;
+          if (!BSG_FLAG(p, 2)) {
+            ptx::tma_load_2d<CG>(sA0 + stage * C::kABytes, &tmA, bar, kt * C::kRowBytes, a_row);
+            ptx::tma_load_2d<CG>(sB0 + stage * C::kBBytes, &tmB, bar, kt * C::kRowBytes, b_row);
+          }
+          if (!BSG_FLAG(p, 16)) {
+            ptx::tma_load_3d<CG>(sSFA0 + stage * C::kSfaBytes, &tmSFA, bar, 0, kt * C::kKAtoms, sfa_atom);
+            ptx::tma_load_3d<CG>(sSFB0 + stage * C::kSfbBytes, &tmSFB, bar, 0, kt * C::kKAtoms, sfb_atom);
+          }
+        }
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
       }
     }
-    __syncwarp();
+    // Tail: every stage must have been released, so that no commit-arrive is still
+    // in flight towards this CTA's shared memory when it exits.
+    for (int s = 0; s < C::kStages; ++s) {
+      wait_barrier(empty0 + stage * 8, phase ^ 1u, ctl, dead);
+      if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+    }
+    if (dead) atomicOr(p.status, kStTimeoutEmpty);
   } else if (warp == 4) {
     // ---------------------------------------------------------------- UMMA issue
-    if (is_leader && lane == 0) {
-      const uint32_t idesc = make_idesc<KIND, CG, BN>();
+    if (is_leader) {
+      constexpr uint32_t idesc = make_idesc<KIND, CG, BN>();
+      const uint32_t elected = ptx::elect_one_sync();
+      const uint32_t sA0 = ptx::smem_u32(sA), sB0 = ptx::smem_u32(sB);
+      const uint32_t sSFA0 = ptx::smem_u32(sSFA), sSFB0 = ptx::smem_u32(sSFB);
+      const uint32_t full0 = ptx::smem_u32(&ctl->full[0]), empty0 = ptx::smem_u32(&ctl->empty[0]);
+      const uint32_t tfull0 = ptx::smem_u32(&ctl->tmem_full[0]), tempty0 = ptx::smem_u32(&ctl->tmem_empty[0]);
       int stage = 0;
       uint32_t phase = 0;
-      bool ok = true;
       int32_t it = 0;
-      for (int32_t t = cluster_idx; t < total_tiles && ok; t += num_clusters, ++it) {
+      // `ready` holds the result of a non-blocking look at the NEXT stage's barrier, taken before the
+      // current stage's instructions are issued, so that the barrier round trip overlaps the issue.
+      uint32_t ready = 0;
+      for (int32_t t = cluster_idx; t < total_tiles; t += num_clusters, ++it) {
         const int acc_bar = it % C::kAccBars;
         const uint32_t acc_phase = uint32_t(it / C::kAccBars) & 1u;
         const uint32_t d_tmem = tmem_base + uint32_t(it & 1) * C::kAccStride;
-        if (!bounded_wait(ptx::smem_u32(&ctl->tmem_empty[acc_bar]), acc_phase ^ 1u, ctl, p.status, kStTimeoutTmemEmpty)) {
-          ok = false;
-          break;
-        }
+        BSG_DBG(1, 9);
+        wait_barrier(tempty0 + acc_bar * 8, acc_phase ^ 1u, ctl, dead);
+        BSG_DBG(1, 10);
         ptx::tc_fence_after();
         for (int32_t kt = 0; kt < k_tiles; ++kt) {
-          if (!bounded_wait(ptx::smem_u32(&ctl->full[stage]), phase, ctl, p.status, kStTimeoutFull)) {
-            ok = false;
-            break;
-          }
+          if (!ready) wait_barrier(full0 + stage * 8, phase, ctl, dead);
+          BSG_DBG(1, 11);
+          int next_stage = stage + 1;
+          uint32_t next_phase = phase;
+          if (next_stage == C::kStages) { next_stage = 0; next_phase ^= 1u; }
+          ready = BSG_FLAG(p, 64) ? 0u : ptx::mbar_spin_test(full0 + next_stage * 8, next_phase, 1);
           ptx::tc_fence_after();
-          const uint32_t sfa_s = ptx::smem_u32(sSFA + stage * C::kSfaBytes);
-          const uint32_t sfb_s = ptx::smem_u32(sSFB + stage * C::kSfbBytes);
-#pragma unroll
-          for (int ka = 0; ka < C::kKAtoms; ++ka) {
-            ptx::utccp_32x128b_warpx4<CG>(tmem_base + C::kSfaCol + 4 * ka, make_desc_sf(sfa_s + ka * 512));
-          }
-#pragma unroll
-          for (int ra = 0; ra < BN / 128; ++ra) {
-#pragma unroll
-            for (int ka = 0; ka < C::kKAtoms; ++ka) {
-              ptx::utccp_32x128b_warpx4<CG>(tmem_base + C::kSfbCol + (BN / 32) * ka + 4 * ra,
-                                            make_desc_sf(sfb_s + (ra * C::kKAtoms + ka) * 512));
-            }
-          }
-          const uint64_t a_desc = make_desc_sw128(ptx::smem_u32(sA + stage * C::kABytes));
-          const uint64_t b_desc = make_desc_sw128(ptx::smem_u32(sB + stage * C::kBBytes));
+          const uint32_t sfa_s = sSFA0 + stage * C::kSfaBytes;
+          const uint32_t sfb_s = sSFB0 + stage * C::kSfbBytes;
+          const uint64_t a_desc = make_desc_sw128(sA0 + stage * C::kABytes);
+          const uint64_t b_desc = make_desc_sw128(sB0 + stage * C::kBBytes);
           const int32_t k_left = p.K - kt * C::kTileK;
           const int n_mma = k_left >= C::kTileK ? 4 : (k_left + C::kMmaK - 1) / C::kMmaK;
+          const uint32_t acc_flag = kt > 0 ? 1u : 0u;
+          if (elected) {
+            if (!BSG_FLAG(p, 1)) {
 #pragma unroll
-          for (int kb = 0; kb < 4; ++kb) {
-            if (kb < n_mma) {
-              uint32_t sfa_t, sfb_t, id = idesc;
-              if constexpr (KIND == kKindNvfp4) {
-                sfa_t = tmem_base + C::kSfaCol + 4 * kb;
-                sfb_t = tmem_base + C::kSfbCol + (BN / 32) * kb;
-              } else {
-                sfa_t = tmem_base + C::kSfaCol;
-                sfb_t = tmem_base + C::kSfbCol;
-                id |= (uint32_t(kb) << 4) | (uint32_t(kb) << 29);   // scale-factor byte of this K block
+              for (int ka = 0; ka < C::kKAtoms; ++ka) {
+                ptx::utccp_32x128b_warpx4<CG>(tmem_base + C::kSfaCol + 4 * ka, make_desc_sf(sfa_s + ka * 512));
               }
-              ptx::umma_block_scaled<KIND, CG>(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, id, sfa_t, sfb_t,
-                                               (kt > 0 || kb > 0) ? 1u : 0u);
+#pragma unroll
+              for (int ra = 0; ra < BN / 128; ++ra) {
+#pragma unroll
+                for (int ka = 0; ka < C::kKAtoms; ++ka) {
+                  ptx::utccp_32x128b_warpx4<CG>(tmem_base + C::kSfbCol + (BN / 32) * ka + 4 * ra,
+                                                make_desc_sf(sfb_s + (ra * C::kKAtoms + ka) * 512));
+                }
+              }
             }
+#pragma unroll
+            for (int kb = 0; kb < 4; ++kb) {
+              if (kb < n_mma && !BSG_FLAG(p, 8)) {
+                uint32_t sfa_t, sfb_t, id = idesc;
+                if constexpr (KIND == kKindNvfp4) {
+                  sfa_t = tmem_base + C::kSfaCol + 4 * kb;
+                  sfb_t = tmem_base + C::kSfbCol + (BN / 32) * kb;
+                } else {
+                  sfa_t = tmem_base + C::kSfaCol;
+                  sfb_t = tmem_base + C::kSfbCol;
+                  id |= (uint32_t(kb) << 4) | (uint32_t(kb) << 29);   // scale-factor byte of this K block
+                }
+                ptx::umma_block_scaled<KIND, CG>(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, id, sfa_t, sfb_t,
+                                                 kb > 0 ? 1u : acc_flag);
+              }
+            }
+            ptx::umma_commit<CG>(empty0 + stage * 8);
           }
-          ptx::umma_commit<CG>(ptx::smem_u32(&ctl->empty[stage]));
-          if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
+          BSG_DBG(1, 12);
+          stage = next_stage;
+          phase = next_phase;
         }
-        if (ok) ptx::umma_commit<CG>(ptx::smem_u32(&ctl->tmem_full[acc_bar]));
+        if (elected) ptx::umma_commit<CG>(tfull0 + acc_bar * 8);
       }
-      if (!ok) {
-        // Drain: nothing issued by this thread may still be running at teardown.
-        ptx::umma_commit<CG>(ptx::smem_u32(&ctl->drain));
-        bounded_wait(ptx::smem_u32(&ctl->drain), 0, ctl, p.status, 0);
-      }
+      if (dead) atomicOr(p.status, kStTimeoutFull | kStTimeoutTmemEmpty);
     }
-    __syncwarp();
   } else {
     // ---------------------------------------------------------------- epilogue (warps 0-3)
     const float alpha = p.alpha_ptr ? *p.alpha_ptr : p.alpha;
@@ -406,135 +460,176 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       st_scaled = __fmul_rn(st, __fdiv_rn(1.0f, 6.0f));
     }
     const int32_t sfd_k_atoms = ((p.N + 15) / 16 + 3) / 4;
-    const uint32_t tmem_empty0 = ptx::smem_u32(&ctl->tmem_empty[0]);
-    bool ok = true;
+    const uint32_t tfull0 = ptx::smem_u32(&ctl->tmem_full[0]);
+    const uint32_t tempty0 = ptx::smem_u32(&ctl->tmem_empty[0]);
+    uint8_t* stage_buf = sEpi + warp * 4096;                     // this warp's 32 x 128-byte staging tile
+    const uint32_t stage_addr = ptx::smem_u32(stage_buf);
     int32_t it = 0;
-    for (int32_t t = cluster_idx; t < total_tiles && ok; t += num_clusters, ++it) {
+    for (int32_t t = cluster_idx; t < total_tiles; t += num_clusters, ++it) {
       const TileInfo ti = decode_tile(ctl, p, t, C::kTileM);
       const int acc_bar = it % C::kAccBars;
       const uint32_t acc_phase = uint32_t(it / C::kAccBars) & 1u;
       const uint32_t acc_col = uint32_t(it & 1) * C::kAccStride;
-      ok = bounded_wait(ptx::smem_u32(&ctl->tmem_full[acc_bar]), acc_phase, ctl, p.status, kStTimeoutTmemFull);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      if (warp == 0) BSG_DBG(2, 19);
+      wait_barrier(tfull0 + acc_bar * 8, acc_phase, ctl, dead);
+      if (warp == 0) BSG_DBG(2, 20);
+      __syncwarp();
       ptx::tc_fence_after();
 
-      const int32_t grow = ti.row0 + int32_t(cta_rank) * C::kCtaM + warp * 32 + lane;
+      const int32_t cta_row0 = ti.row0 + int32_t(cta_rank) * C::kCtaM;
+      const int32_t grow = cta_row0 + warp * 32 + lane;
       const bool row_ok = grow < ti.row_end;
       const int32_t lrow = grow - ti.group_row0;
       const uint32_t lane_addr = tmem_base + (uint32_t(warp * 32) << 16) + acc_col;
       const bool reverse = (BN == 256) && ((it & 1) == 0);
-      const uint32_t empty_bar = tmem_empty0 + acc_bar * 8;
+      const uint32_t empty_bar = tempty0 + acc_bar * 8;
+      // Whole 128-row slab inside the group: bf16 output goes through shared memory and TMA stores.
+      const bool tma_out = (p.out_kind == kOutBf16) && (cta_row0 + C::kCtaM <= ti.row_end) && !BSG_FLAG(p, 128);
 
 #pragma unroll 1
-      for (int ci = 0; ci < C::kChunks; ++ci) {
-        const int c = reverse ? (C::kChunks - 1 - ci) : ci;
-        uint32_t v[32];
-        ptx::tmem_ld_32x32b_x32(lane_addr + c * 32, v);
+      for (int pi = 0; pi < C::kPairs; ++pi) {
+        const int pr = reverse ? (C::kPairs - 1 - pi) : pi;
+        uint32_t v[2][32];
+        ptx::tmem_ld_32x32b_x32(lane_addr + pr * 64, v[0]);
+        ptx::tmem_ld_32x32b_x32(lane_addr + pr * 64 + 32, v[1]);
         ptx::tmem_ld_wait();
-        if (ci == C::kReleaseChunk) {
+        if (pi == C::kReleasePair) {
           ptx::tc_fence_before();
           __syncwarp();
           if (lane == 0) {
             if constexpr (CG == 2) ptx::mbar_arrive_remote(ptx::mapa(empty_bar, 0));
             else ptx::mbar_arrive(empty_bar);
           }
+          if (warp == 0) BSG_DBG(2, 21);
         }
-        const int32_t col0 = ti.tn * BN + c * 32;
-        const int32_t cols_valid = p.N - col0;
-        if (!row_ok || cols_valid <= 0) continue;
+        if (BSG_FLAG(p, 4)) continue;
+        if (tma_out) {
+          // The previous store must have finished reading the staging tile before it is overwritten.
+          if (lane == 0) ptx::bulk_wait_group_read<0>();
+          __syncwarp();
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int32_t col0 = ti.tn * BN + pr * 64 + h * 32;
+          const int32_t cols_valid = p.N - col0;
+          if (cols_valid <= 0 || (!row_ok && !tma_out)) continue;
 
-        float x[32];
+          float x[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) x[j] = __fmul_rn(alpha, __uint_as_float(v[j]));
-        if (use_c) {
-          const __nv_bfloat16* crow = p.C + int64_t(grow) * p.ldc + col0;
-          if (cols_valid >= 32) {
+          for (int j = 0; j < 32; ++j) x[j] = __fmul_rn(alpha, __uint_as_float(v[h][j]));
+          if (use_c && row_ok) {
+            const __nv_bfloat16* crow = p.C + int64_t(grow) * p.ldc + col0;
+            if (cols_valid >= 32) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 cv = __ldg(reinterpret_cast<const uint4*>(crow) + q);
-              const uint32_t w[4] = {cv.x, cv.y, cv.z, cv.w};
+              for (int q = 0; q < 4; ++q) {
+                const uint4 cv = __ldg(reinterpret_cast<const uint4*>(crow) + q);
+                const uint32_t w[4] = {cv.x, cv.y, cv.z, cv.w};
 #pragma unroll
-              for (int h = 0; h < 4; ++h) {
-                const float c_lo = __uint_as_float(w[h] << 16);
-                const float c_hi = __uint_as_float(w[h] & 0xFFFF0000u);
-                x[q * 8 + h * 2 + 0] = __fadd_rn(__fmul_rn(beta, c_lo), x[q * 8 + h * 2 + 0]);
-                x[q * 8 + h * 2 + 1] = __fadd_rn(__fmul_rn(beta, c_hi), x[q * 8 + h * 2 + 1]);
+                for (int e = 0; e < 4; ++e) {
+                  const float c_lo = __uint_as_float(w[e] << 16);
+                  const float c_hi = __uint_as_float(w[e] & 0xFFFF0000u);
+                  x[q * 8 + e * 2 + 0] = __fadd_rn(__fmul_rn(beta, c_lo), x[q * 8 + e * 2 + 0]);
+                  x[q * 8 + e * 2 + 1] = __fadd_rn(__fmul_rn(beta, c_hi), x[q * 8 + e * 2 + 1]);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (j < cols_valid) x[j] = __fadd_rn(__fmul_rn(beta, __bfloat162float(crow[j])), x[j]);
+              }
+            }
+          }
+
+          if (p.out_kind == kOutBf16) {
+            if (tma_out) {
+              // 128-byte-swizzled staging tile: 16-byte chunk c of row r lives at chunk (c ^ (r & 7)).
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                o.x = pack_bf16x2(x[q * 8 + 0], x[q * 8 + 1]);
+                o.y = pack_bf16x2(x[q * 8 + 2], x[q * 8 + 3]);
+                o.z = pack_bf16x2(x[q * 8 + 4], x[q * 8 + 5]);
+                o.w = pack_bf16x2(x[q * 8 + 6], x[q * 8 + 7]);
+                const int chunk = (h * 4 + q) ^ (lane & 7);
+                *reinterpret_cast<uint4*>(stage_buf + lane * 128 + chunk * 16) = o;
+              }
+            } else {
+              __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D) + int64_t(grow) * p.ldd + col0;
+              if (cols_valid >= 32) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  uint4 o;
+                  o.x = pack_bf16x2(x[q * 8 + 0], x[q * 8 + 1]);
+                  o.y = pack_bf16x2(x[q * 8 + 2], x[q * 8 + 3]);
+                  o.z = pack_bf16x2(x[q * 8 + 4], x[q * 8 + 5]);
+                  o.w = pack_bf16x2(x[q * 8 + 6], x[q * 8 + 7]);
+                  reinterpret_cast<uint4*>(drow)[q] = o;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  if (j < cols_valid) drow[j] = __float2bfloat16_rn(x[j]);
+                }
               }
             }
           } else {
+            // NVFP4 re-quantisation, one scale factor per 16 columns of this row; same
+            // operation order as compute_1d_scaling_factor_and_quantized_output of the
+            // reference host GEMM (tools/util/include/cutlass/util/reference/host/gett.hpp:364-481).
+            uint8_t* drow = reinterpret_cast<uint8_t*>(p.D) + (int64_t(grow) * p.ldd + col0) / 2;
+            uint32_t packed[4];
+            uint32_t sf_codes = 0;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (j < cols_valid) x[j] = __fadd_rn(__fmul_rn(beta, __bfloat162float(crow[j])), x[j]);
+            for (int b = 0; b < 2; ++b) {
+              float amax = 0.f;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(x[b * 16 + j]));
+              const float pv = __fmul_rn(amax, st_scaled);
+              const uint32_t q = ptx::cvt_ue4m3(pv);
+              const float qf = ptx::cvt_e4m3_to_f32(q);
+              float sc = __fmul_rn(st, __fdiv_rn(1.0f, qf));
+              sc = fminf(sc, FLT_MAX);
+              sf_codes |= q << (8 * b);
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                float y[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) y[j] = __fmul_rn(x[b * 16 + e * 8 + j], sc);
+                packed[b * 2 + e] = ptx::cvt_e2m1x8(y);
+              }
+            }
+            const int32_t nb = col0 >> 4;
+            uint8_t* sfp = p.SFD + (int64_t(ti.group_atom0) + lrow / 128) * (512ll * sfd_k_atoms) + (nb >> 2) * 512 +
+                           16 * (lrow & 31) + 4 * ((lrow & 127) >> 5) + (nb & 3);
+            if (cols_valid >= 32) {
+              *reinterpret_cast<uint4*>(drow) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              *reinterpret_cast<uint16_t*>(sfp) = uint16_t(sf_codes);
+            } else if (cols_valid >= 16) {
+              *reinterpret_cast<uint2*>(drow) = make_uint2(packed[0], packed[1]);
+              *sfp = uint8_t(sf_codes);
             }
           }
         }
-
-        if (p.out_kind == kOutBf16) {
-          __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D) + int64_t(grow) * p.ldd + col0;
-          if (cols_valid >= 32) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              uint4 o;
-              o.x = pack_bf16x2(x[q * 8 + 0], x[q * 8 + 1]);
-              o.y = pack_bf16x2(x[q * 8 + 2], x[q * 8 + 3]);
-              o.z = pack_bf16x2(x[q * 8 + 4], x[q * 8 + 5]);
-              o.w = pack_bf16x2(x[q * 8 + 6], x[q * 8 + 7]);
-              reinterpret_cast<uint4*>(drow)[q] = o;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (j < cols_valid) drow[j] = __float2bfloat16_rn(x[j]);
-            }
-          }
-        } else {
-          // NVFP4 re-quantisation, one scale factor per 16 columns of this row; same
-          // operation order as compute_1d_scaling_factor_and_quantized_output of the
-          // reference host GEMM (tools/util/include/cutlass/util/reference/host/gett.hpp:364-481).
-          uint8_t* drow = reinterpret_cast<uint8_t*>(p.D) + (int64_t(grow) * p.ldd + col0) / 2;
-          uint32_t packed[4];
-          uint32_t sf_codes = 0;
-#pragma unroll
-          for (int b = 0; b < 2; ++b) {
-            float amax = 0.f;
-#pragma unroll
-            for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(x[b * 16 + j]));
-            const float pv = __fmul_rn(amax, st_scaled);
-            const uint32_t q = ptx::cvt_ue4m3(pv);
-            const float qf = ptx::cvt_e4m3_to_f32(q);
-            float sc = __fmul_rn(st, __fdiv_rn(1.0f, qf));
-            sc = fminf(sc, FLT_MAX);
-            sf_codes |= q << (8 * b);
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              float y[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) y[j] = __fmul_rn(x[b * 16 + h * 8 + j], sc);
-              packed[b * 2 + h] = ptx::cvt_e2m1x8(y);
-            }
-          }
-          const int32_t nb = col0 >> 4;
-          uint8_t* sfp = p.SFD + (int64_t(ctl->atom0[ti.g]) + lrow / 128) * (512ll * sfd_k_atoms) + (nb >> 2) * 512 +
-                         16 * (lrow & 31) + 4 * ((lrow & 127) >> 5) + (nb & 3);
-          if (cols_valid >= 32) {
-            *reinterpret_cast<uint4*>(drow) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            *reinterpret_cast<uint16_t*>(sfp) = uint16_t(sf_codes);
-          } else if (cols_valid >= 16) {
-            *reinterpret_cast<uint2*>(drow) = make_uint2(packed[0], packed[1]);
-            *sfp = uint8_t(sf_codes);
+        if (tma_out) {
+          ptx::fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            ptx::tma_store_2d(&tmD, stage_addr, ti.tn * BN + pr * 64, cta_row0 + warp * 32);
+            ptx::bulk_commit_group();
           }
         }
       }
     }
+    if (lane == 0) ptx::bulk_wait_group<0>();
+    if (dead) atomicOr(p.status, kStTimeoutTmemFull);
   }
 
   // ------------------------------------------------------------------ teardown
   if (ctl->abort) {
     // Give copies and MMAs that may still be in flight time to land before the CTA's
     // shared and tensor memory are handed back.
-    const uint64_t t0 = ptx::globaltimer_ns();
-    while (ptx::globaltimer_ns() - t0 < 1000000ull) __nanosleep(1000);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 4000000ll) __nanosleep(1000);
   }
   __syncwarp();
   ptx::tc_fence_before();

@@ -89,6 +89,66 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Spin on a barrier phase inside one asm statement, so that the compiler sees straight-line,
+// warp-uniform code.  Gives up after `tries` polls; returns 1 when the phase completed.
+__device__ __forceinline__ uint32_t mbar_spin(uint32_t bar, uint32_t parity, uint32_t tries) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      ".reg .u32 n;\n\t"
+      "mov.u32 n, %3;\n\t"
+      "SPIN_LOOP:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "@p bra SPIN_DONE;\n\t"
+      "sub.u32 n, n, 1;\n\t"
+      "setp.ne.u32 q, n, 0;\n\t"
+      "@q bra SPIN_LOOP;\n\t"
+      "SPIN_DONE:\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(tries)
+      : "memory");
+  return ok;
+}
+
+// Same, polling with the non-blocking test_wait.
+__device__ __forceinline__ uint32_t mbar_spin_test(uint32_t bar, uint32_t parity, uint32_t tries) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      ".reg .u32 n;\n\t"
+      "mov.u32 n, %3;\n\t"
+      "SPIN_LOOP:\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "@p bra SPIN_DONE;\n\t"
+      "sub.u32 n, n, 1;\n\t"
+      "setp.ne.u32 q, n, 0;\n\t"
+      "@q bra SPIN_LOOP;\n\t"
+      "SPIN_DONE:\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(tries)
+      : "memory");
+  return ok;
+}
+
+// True in exactly one lane of a fully active warp.
+__device__ __forceinline__ uint32_t elect_one_sync() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(pred));
+  return pred;
+}
+
 // ---------------------------------------------------------------- TMA loads
 // CG == 1: the barrier is in this CTA.  CG == 2: `bar` may be the leader CTA's
 // barrier (cluster address); both CTAs of the pair signal it.
@@ -124,6 +184,25 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, uint
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
   }
+}
+// TMA store of one shared-memory box to global memory (bulk async-group completion).
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int32_t c0, int32_t c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Wait until the bulk stores of all but the newest `N` groups have finished READING shared memory.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Wait until all but the newest `N` groups have completed entirely.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

@@ -65,7 +65,7 @@ def decode_ue4m3(codes: np.ndarray) -> np.ndarray:
 
 def decode_ue8m0(codes: np.ndarray) -> np.ndarray:
     codes = np.asarray(codes, dtype=np.uint8)
-    out = np.exp2(codes.astype(np.float64) - 127.0).astype(np.float32)
+    out = np.exp2(np.minimum(codes, 254).astype(np.float64) - 127.0).astype(np.float32)
     out = np.where(codes == 0xFF, np.float32(np.nan), out)
     return out.astype(np.float32)
 
@@ -115,10 +115,10 @@ def encode_e4m3(x: np.ndarray) -> np.ndarray:
 
 
 def encode_ue4m3(x: np.ndarray) -> np.ndarray:
-    """float32 -> unsigned e4m3 scale factor (negative inputs clamp to 0)."""
+    """float32 -> unsigned e4m3 scale factor (the sign of the input is dropped)."""
     x = np.asarray(x, dtype=np.float32)
     nan = np.isnan(x)
-    mag = np.where(nan, 0.0, np.maximum(x, 0.0)).astype(np.float64)
+    mag = np.where(nan, 0.0, np.abs(x)).astype(np.float64)
     idx = _round_to_grid(mag, _E4M3_POS)
     return np.where(nan, 0x7F, idx).astype(np.uint8)
 

@@ -73,6 +73,7 @@ SYMBOLS = {
     "bsg_grouped_workspace_size": (C.c_int32, [C.POINTER(GroupedArgs), C.POINTER(C.c_size_t)]),
     "bsg_gemm_run": (C.c_int32, [C.POINTER(GemmArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "bsg_grouped_run": (C.c_int32, [C.POINTER(GroupedArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "bsg_workspace_init": (C.c_int32, [C.c_void_p, C.c_size_t, C.c_void_p]),
     "bsg_read_device_status": (C.c_int32, [C.c_void_p, C.c_void_p]),
 }
 

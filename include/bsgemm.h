@@ -140,19 +140,25 @@ int32_t bsg_grouped_query(const bsg_grouped_args* args, bsg_caps* caps);
 int32_t bsg_gemm_workspace_size(const bsg_gemm_args* args, size_t* bytes);
 int32_t bsg_grouped_workspace_size(const bsg_grouped_args* args, size_t* bytes);
 
-/* Enqueue the GEMM.  The workspace must stay alive until the stream reaches the
- * end of the kernel; its first word receives a device-side status
- * (see bsg_read_device_status).  Replaces GemmUniversalAdapter::initialize + run
- * (gemm_universal_adapter.h:313,375) and Operator.run
- * (operators/cutlass/operators/base.py:165). */
+/* Zero a fresh workspace (asynchronously, on the stream) before its first use.  Takes the
+ * place of GemmUniversalAdapter::initialize's workspace set-up (gemm_universal_adapter.h:313)
+ * and Operator.initialize_workspace (operators/cutlass/operators/base.py:208). */
+int32_t bsg_workspace_init(void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/* Enqueue the GEMM; nothing else is put on the stream.  The workspace must have been
+ * initialised once (bsg_workspace_init) and stay alive until the stream reaches the end of
+ * the kernel; its first word accumulates a device-side status over all runs until it is
+ * read (see bsg_read_device_status).  Replaces GemmUniversalAdapter::run
+ * (gemm_universal_adapter.h:375) and Operator.run (operators/cutlass/operators/base.py:165). */
 int32_t bsg_gemm_run(const bsg_gemm_args* args, void* workspace, size_t workspace_bytes,
                      void* cuda_stream);
 int32_t bsg_grouped_run(const bsg_grouped_args* args, void* workspace, size_t workspace_bytes,
                         void* cuda_stream);
 
-/* Synchronise the stream and translate the workspace status word
- * (0 -> BSG_OK, otherwise BSG_ERR_TIMEOUT). */
-int32_t bsg_read_device_status(const void* workspace, void* cuda_stream);
+/* Synchronise the stream, translate the workspace status word (0 -> BSG_OK, a timed-out
+ * device-side wait -> BSG_ERR_TIMEOUT, bad group offsets -> BSG_ERR_INVALID_PROBLEM) and
+ * clear it. */
+int32_t bsg_read_device_status(void* workspace, void* cuda_stream);
 
 #ifdef __cplusplus
 }

@@ -108,7 +108,7 @@ def _nearest_even(mag: np.ndarray, grid: np.ndarray) -> np.ndarray:
 
 
 def to_ue4m3(x: np.ndarray) -> np.ndarray:
-    return _nearest_even(np.maximum(np.asarray(x, dtype=np.float32), 0), _E4M3_POS).astype(np.uint8)
+    return _nearest_even(np.abs(np.asarray(x, dtype=np.float32)), _E4M3_POS).astype(np.uint8)
 
 
 def to_e2m1(x: np.ndarray) -> np.ndarray:

@@ -1,0 +1,122 @@
+"""Helpers of the -m gpu parity tests: run a problem through the C ABI (ctypes, raw device
+pointers) and compute the oracle's answer for the same seeded inputs."""
+import ctypes as C
+
+import numpy as np
+import torch
+
+import oracle
+from cutlass_b200 import formats as F
+from cutlass_b200 import generators as G
+from cutlass_b200 import lib as L
+
+
+def dev(x: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+def make_operands(kind: int, M: int, N: int, K: int, seed: int, exact: bool):
+    rng = np.random.default_rng(seed)
+    if kind == 0:
+        gen = G.exact_nvfp4_operand if exact else G.nvfp4_operand
+    else:
+        gen = G.exact_mxfp8_operand if exact else G.mxfp8_operand
+    A, _, sfa = gen(M, K, rng)
+    B, _, sfb = gen(N, K, rng)
+    return rng, A, sfa, B, sfb
+
+
+def run_dense(kind, M, N, K, A, sfa, B, sfb, Cb=None, alpha=1.0, beta=0.0, out_kind=0, st=None, tile_n=0, cta_group=0,
+              batch=1, check_status=True):
+    """-> bf16 bits (batch*M, N), or (packed e2m1, SFD buffer) for out_kind 1."""
+    lib = L.load()
+    dA, dB, dSFA, dSFB = dev(A), dev(B), dev(sfa), dev(sfb)
+    dC = dev(Cb) if Cb is not None else None
+    a = L.GemmArgs()
+    a.kind, a.out_kind, a.batch = kind, out_kind, batch
+    a.M, a.N, a.K = M, N, K
+    a.A, a.B, a.SFA, a.SFB = dA.data_ptr(), dB.data_ptr(), dSFA.data_ptr(), dSFB.data_ptr()
+    a.C = dC.data_ptr() if dC is not None else None
+    a.alpha, a.beta = alpha, beta
+    a.tile_n, a.cta_group = tile_n, cta_group
+    rows = batch * M
+    keep = []
+    if out_kind == 0:
+        dD = torch.full((rows, N), 0x7FC0, dtype=torch.int16, device="cuda")      # NaN pattern: unwritten cells show up
+    else:
+        dD = torch.full((rows, N // 2), 0x77, dtype=torch.uint8, device="cuda")
+        dSFD = torch.full((batch * F.numel_scale(M, N, 16),), 0x7F, dtype=torch.uint8, device="cuda")
+        dst = torch.tensor([st], dtype=torch.float32, device="cuda")
+        a.SFD, a.norm_constant = dSFD.data_ptr(), dst.data_ptr()
+        keep += [dSFD, dst]
+    a.D = dD.data_ptr()
+    ws = torch.zeros(16, dtype=torch.uint8, device="cuda")
+    L.check(lib.bsg_gemm_run(C.byref(a), ws.data_ptr(), 16, None))
+    if check_status:
+        L.check(lib.bsg_read_device_status(ws.data_ptr(), None))
+    torch.cuda.synchronize()
+    if out_kind == 0:
+        return dD.cpu().numpy().view(np.uint16)
+    return dD.cpu().numpy(), keep[0].cpu().numpy()
+
+
+def oracle_bf16(kind, M, N, K, A, sfa, B, sfb, Cb=None, alpha=1.0, beta=0.0):
+    return oracle.to_bf16(oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K, Cb, alpha, beta))
+
+
+def assert_close_bf16(got_bits, want_bits, rel_tol=1e-2):
+    """bf16 outputs must match the oracle within rel_tol of the largest magnitude, element-wise
+    within rel_tol relative error where the reference is not tiny, and contain no NaN."""
+    got, want = F.bf16_to_f32(got_bits), F.bf16_to_f32(want_bits)
+    assert not np.isnan(got).any(), f"{int(np.isnan(got).sum())} NaN / unwritten outputs"
+    scale = max(float(np.max(np.abs(want))), 1e-30)
+    err = np.abs(got - want)
+    assert float(err.max()) <= rel_tol * scale, f"max abs err {err.max()} vs scale {scale}"
+    big = np.abs(want) > 0.05 * scale
+    if big.any():
+        assert float((err[big] / np.abs(want[big])).max()) <= rel_tol
+
+
+def run_grouped(kind, sizes, N, K, seed, exact=True, alpha=1.0, beta=0.0, tile_n=0, cta_group=0):
+    """Ragged grouped GEMM through the C ABI and the per-group oracle.  -> (got bits, want bits)."""
+    rng = np.random.default_rng(seed)
+    if kind == 0:
+        gen = G.exact_nvfp4_operand if exact else G.nvfp4_operand
+    else:
+        gen = G.exact_mxfp8_operand if exact else G.mxfp8_operand
+    total = int(np.sum(sizes))
+    As, sfas, Bs, sfbs = [], [], [], []
+    for m in sizes:
+        A, _, sfa = gen(int(m), K, rng) if m > 0 else (np.zeros((0, K // 2 if kind == 0 else K), np.uint8), None, np.zeros(0, np.uint8))
+        B, _, sfb = gen(N, K, rng)
+        As.append(A); sfas.append(sfa); Bs.append(B); sfbs.append(sfb)
+    Cb = G.bf16_normal((total, N), rng) if beta != 0 else None
+    A_all = np.concatenate(As, axis=0)
+    want = np.zeros((total, N), np.uint16)
+    row = 0
+    for g, m in enumerate(sizes):
+        m = int(m)
+        if m:
+            cg = Cb[row:row + m] if Cb is not None else None
+            want[row:row + m] = oracle_bf16(kind, m, N, K, As[g], sfas[g], Bs[g], sfbs[g], cg, alpha, beta)
+        row += m
+    lib = L.load()
+    dA, dB = dev(A_all), dev(np.stack(Bs))
+    dSFA = dev(np.concatenate(sfas) if total else np.zeros(16, np.uint8))
+    dSFB = dev(np.concatenate(sfbs))
+    dC = dev(Cb) if Cb is not None else None
+    offs = torch.tensor(np.cumsum(sizes), dtype=torch.int32, device="cuda")
+    dD = torch.full((max(total, 1), N), 0x7FC0, dtype=torch.int16, device="cuda")
+    a = L.GroupedArgs()
+    a.kind, a.out_kind, a.num_groups = kind, 0, len(sizes)
+    a.total_M, a.N, a.K = total, N, K
+    a.A, a.B, a.SFA, a.SFB, a.D = dA.data_ptr(), dB.data_ptr(), dSFA.data_ptr(), dSFB.data_ptr(), dD.data_ptr()
+    a.C = dC.data_ptr() if dC is not None else None
+    a.offsets = offs.data_ptr()
+    a.alpha, a.beta = alpha, beta
+    a.tile_n, a.cta_group = tile_n, cta_group
+    ws = torch.zeros(16, dtype=torch.uint8, device="cuda")
+    L.check(lib.bsg_grouped_run(C.byref(a), ws.data_ptr(), 16, None))
+    L.check(lib.bsg_read_device_status(ws.data_ptr(), None))
+    torch.cuda.synchronize()
+    return dD.cpu().numpy().view(np.uint16)[:total], want

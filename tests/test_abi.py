@@ -1,0 +1,106 @@
+"""The C-ABI shared library: builds, loads without a GPU, exports every declared symbol,
+and answers the calls that need no device."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from cutlass_b200 import build as B
+from cutlass_b200 import lib as L
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    B.build()
+    return L.load()
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "bsgemm.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(bsg_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_symbols_are_all_exported(lib):
+    names = _declared_symbols()
+    assert len(names) >= 9
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/bsgemm.h but not exported"
+    assert sorted(L.SYMBOLS) == names, "cutlass_b200.lib.SYMBOLS must list exactly the header's entry points"
+
+
+def test_version_and_error_string(lib):
+    assert lib.bsg_version() >= 100
+    assert isinstance(lib.bsg_last_error_string(), bytes)
+
+
+def test_struct_sizes_match_header_layout():
+    # 4 int32, 3 int64, 7 pointers, 2 int64, 2 float, 3 pointers, 4 int32
+    assert C.sizeof(L.GemmArgs) == 16 + 24 + 56 + 16 + 8 + 24 + 16
+    assert C.sizeof(L.GroupedArgs) == 16 + 24 + 56 + 16 + 8 + 16
+    assert C.sizeof(L.Caps) == 32
+
+
+def _args(**kw):
+    a = L.GemmArgs()
+    a.kind, a.out_kind, a.batch = 0, 0, 1
+    a.M, a.N, a.K = 256, 256, 256
+    for f in ("A", "B", "SFA", "SFB", "D"):
+        setattr(a, f, 0x10000)      # never dereferenced by the query
+    a.alpha = 1.0
+    for k, v in kw.items():
+        setattr(a, k, v)
+    return a
+
+
+def test_query_accepts_valid_problem_and_reports_plan(lib):
+    caps = L.Caps()
+    assert lib.bsg_gemm_query(C.byref(_args()), C.byref(caps)) == 0
+    assert (caps.tile_m, caps.tile_n, caps.tile_k, caps.cta_group) == (256, 256, 256, 2)
+    assert caps.stages >= 4 and caps.smem_bytes <= 232448 and caps.num_tiles == 1
+    assert lib.bsg_gemm_query(C.byref(_args(kind=1, tile_n=128, cta_group=1)), C.byref(caps)) == 0
+    assert (caps.tile_m, caps.tile_n, caps.tile_k) == (128, 128, 128) and caps.num_tiles == 4
+
+
+@pytest.mark.parametrize("kw,code", [
+    (dict(K=48), 1),                 # K not a multiple of 32 for NVFP4
+    (dict(kind=1, K=40), 1),         # K not a multiple of 16 for MXFP8
+    (dict(A=0x10001), 1),            # misaligned pointer
+    (dict(N=100), 1),                # bf16 rows not 16-byte multiples
+    (dict(kind=7), 3),
+    (dict(tile_n=192), 3),
+    (dict(cta_group=3), 3),
+    (dict(N=0), 2),
+    (dict(A=None), 2),
+    (dict(beta=0.5), 2),             # beta without C
+    (dict(out_kind=1), 2),           # NVFP4 output without SFD / norm constant
+    (dict(batch=1000), 2),
+])
+def test_query_rejects_bad_problems(lib, kw, code):
+    assert lib.bsg_gemm_query(C.byref(_args(**kw)), None) == code
+    assert len(L.last_error()) > 0
+
+
+def test_workspace_size_and_null_workspace(lib):
+    n = C.c_size_t(0)
+    assert lib.bsg_gemm_workspace_size(C.byref(_args()), C.byref(n)) == 0 and n.value == 16
+    # run() validates before touching the device: a null workspace is reported, not dereferenced
+    assert lib.bsg_gemm_run(C.byref(_args()), None, 0, None) == 4
+
+
+def test_grouped_query(lib):
+    g = L.GroupedArgs()
+    g.kind, g.num_groups, g.total_M, g.N, g.K = 0, 4, 1000, 256, 512
+    for f in ("A", "B", "SFA", "SFB", "D", "offsets"):
+        setattr(g, f, 0x10000)
+    g.alpha = 1.0
+    caps = L.Caps()
+    assert lib.bsg_grouped_query(C.byref(g), C.byref(caps)) == 0 and caps.num_tiles == -1
+    g.num_groups = 1000
+    assert lib.bsg_grouped_query(C.byref(g), None) == 2
+    g.num_groups = 4
+    g.offsets = None
+    assert lib.bsg_grouped_query(C.byref(g), None) == 2

@@ -1,0 +1,112 @@
+"""Pins the oracles (plain-C restatement and numpy restatement) to the reference:
+against golden vectors produced by the reference's own host GEMM
+(tests/golden/make_golden.py) and, where the compiled reference driver is present
+(oracle/_ref), against it directly on fresh seeded inputs."""
+import numpy as np
+import pytest
+
+import oracle
+from cutlass_b200 import formats as F
+from cutlass_b200 import generators as G
+from oracle import ref_numpy as R
+
+GEMM_CASES = ["nvfp4_a", "nvfp4_b", "mxfp8_a", "mxfp8_b"]
+
+
+def _case(golden, name):
+    kind, M, N, K = (int(v) for v in golden[f"{name}_dims"])
+    return kind, M, N, K, golden[f"{name}_A"], golden[f"{name}_SFA"], golden[f"{name}_B"], golden[f"{name}_SFB"], golden[f"{name}_C"]
+
+
+@pytest.mark.parametrize("name", GEMM_CASES)
+def test_c_oracle_bit_exact_on_golden_gemm(golden, name):
+    kind, M, N, K, A, sfa, B, sfb, Cb = _case(golden, name)
+    alpha, beta = (float(v) for v in golden[f"{name}_ab"])
+    got = oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K, Cb, alpha, beta)
+    assert np.array_equal(got.view(np.uint32), golden[f"{name}_D32"].view(np.uint32))
+    assert np.array_equal(oracle.to_bf16(got), golden[f"{name}_Dbf16"])
+
+
+@pytest.mark.parametrize("name", GEMM_CASES)
+def test_numpy_oracle_close_on_golden_gemm(golden, name):
+    kind, M, N, K, A, sfa, B, sfb, Cb = _case(golden, name)
+    alpha, beta = (float(v) for v in golden[f"{name}_ab"])
+    got = R.gemm_fp32(kind, A, sfa, B, sfb, M, N, K, Cb, alpha, beta)
+    want = golden[f"{name}_D32"]
+    assert np.max(np.abs(got - want)) <= 1e-5 * np.max(np.abs(want))
+
+
+def test_row_slab_equals_full(golden):
+    kind, M, N, K, A, sfa, B, sfb, Cb = _case(golden, "nvfp4_b")
+    alpha, beta = (float(v) for v in golden["nvfp4_b_ab"])
+    slab = oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K, Cb, alpha, beta, m_begin=64, m_count=50)
+    assert np.array_equal(slab, golden["nvfp4_b_D32"][64:114])
+
+
+def test_quantisation_bit_exact_on_golden(golden):
+    kind, M, N, K, A, sfa, B, sfb, Cb = _case(golden, "quant_a")
+    st = float(golden["quant_a_st"][0])
+    d32 = oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K, Cb, 1.0, 0.5)
+    assert np.array_equal(d32, golden["quant_a_D32"])
+    idx = R.sf_index(M, N // 16)
+    for D, SFD in (oracle.quant_nvfp4(d32, st), R.quantize_rows_nvfp4(d32, st)):
+        assert np.array_equal(D, golden["quant_a_D"])
+        assert np.array_equal(SFD[idx], golden["quant_a_SFD"][idx])
+
+
+def test_quantisation_edge_values():
+    x = np.zeros((3, 32), np.float32)
+    x[1, :16] = 1e-30          # underflows the scale factor to zero
+    x[2, 5] = -6.0
+    x[2, 20] = 448.0 * 6.0 * 4
+    for D, SFD in (oracle.quant_nvfp4(x, 1.0), R.quantize_rows_nvfp4(x, 1.0)):
+        sf = SFD[R.sf_index(3, 2)]
+        assert sf[0].tolist() == [0, 0] and not D[0].any()
+        # scale factor 0 -> reciprocal inf -> clamped to FLT_MAX: tiny values blow up and saturate at 6
+        assert sf[1, 0] == 0 and (D[1, :8] == 0x77).all() and not D[1, 8:].any()
+        assert sf[2, 0] == F.encode_ue4m3(np.float32(1.0)) and sf[2, 1] == 0x7E        # saturates at 448
+        codes = F.unpack_e2m1(D[2])
+        assert codes[5] == 15 and codes[20] == 7
+
+
+ref_missing = oracle.load_ref() is None
+
+
+@pytest.mark.skipif(ref_missing, reason="compiled reference driver (oracle/_ref) not present")
+@pytest.mark.parametrize("kind,M,N,K,alpha,beta", [(0, 200, 264, 416, 1.5, 0.5), (1, 129, 72, 224, 1.0, 0.0), (0, 64, 64, 1024, 1.0, 0.5)])
+def test_c_oracle_equals_compiled_reference(kind, M, N, K, alpha, beta):
+    rng = np.random.default_rng(M * 7 + N)
+    gen = G.nvfp4_operand if kind == 0 else G.mxfp8_operand
+    A, _, sfa = gen(M, K, rng)
+    B, _, sfb = gen(N, K, rng)
+    Cb = G.bf16_normal((M, N), rng)
+    o = oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K, Cb, alpha, beta)
+    r = oracle.ref_gemm(kind, 0, A, sfa, B, sfb, M, N, K, Cb, alpha, beta)
+    assert np.array_equal(o.view(np.uint32), r.view(np.uint32))
+
+
+@pytest.mark.skipif(ref_missing, reason="compiled reference driver (oracle/_ref) not present")
+def test_quantisation_equals_compiled_reference():
+    rng = np.random.default_rng(5)
+    M, N, K = 130, 160, 256
+    A, _, sfa = G.nvfp4_operand(M, K, rng)
+    B, _, sfb = G.nvfp4_operand(N, K, rng)
+    d32 = oracle.gemm_fp32(0, A, sfa, B, sfb, M, N, K)
+    st = np.float32(448 * 6 / np.abs(d32).max())
+    D, SFD = oracle.quant_nvfp4(d32, st)
+    Dr, SFDr = oracle.ref_gemm(0, 2, A, sfa, B, sfb, M, N, K, None, 1.0, 0.0, st)
+    idx = R.sf_index(M, N // 16)
+    assert np.array_equal(D, Dr) and np.array_equal(SFD[idx], SFDr[idx])
+
+
+@pytest.mark.skipif(ref_missing, reason="compiled reference driver (oracle/_ref) not present")
+def test_codecs_exhaustive_against_compiled_reference():
+    ref = oracle.load_ref()
+    lib = oracle.load_oracle()
+    rng = np.random.default_rng(9)
+    xs = np.concatenate([rng.standard_normal(3000).astype(np.float32) * s for s in (1e-3, 1, 50, 1000)])
+    for fmt in range(4):
+        for c in range(16 if fmt == 0 else 256):
+            a, b = ref.bsg_ref_decode(fmt, c), lib.bsg_oracle_decode(fmt, c)
+            assert a == b or (np.isnan(a) and np.isnan(b)), (fmt, c)
+        assert all(ref.bsg_ref_encode(fmt, float(x)) == lib.bsg_oracle_encode(fmt, float(x)) for x in xs), fmt
