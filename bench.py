@@ -211,6 +211,7 @@ def run_single(args) -> dict:
         op.run(e2e_args, compiled_artifact=artifact, stream=stream, workspace=ws)
         hD.copy_(dD, non_blocking=True)
 
+    e2e_keep = e2e_args
     e2e_steps = max(3, min(args.steps, 20))
     for _ in range(2):
         e2e_step()
@@ -240,11 +241,25 @@ def run_single(args) -> dict:
     gf, wf = F.bf16_to_f32(got), F.bf16_to_f32(want)
     rel = float(np.max(np.abs(gf - wf)) / max(float(np.max(np.abs(wf))), 1e-30))
 
+    # ---- the tensor-parallel workload on this one GPU: the base of the 1/2/4/8-GPU scaling series
+    tp_base = None
+    if not args.no_tp_base:
+        del sets, abi_args
+        torch.cuda.empty_cache()
+        for k, v in (("RANK", "0"), ("WORLD_SIZE", "1"), ("LOCAL_RANK", "0"), ("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", "29533")):
+            os.environ.setdefault(k, v)
+        from cutlass_b200 import tp_bench
+        tp_args = argparse.Namespace(steps=max(3, min(args.steps, 30)), warmup=3)
+        r = tp_bench.run(tp_args)
+        tp_base = {"metric": r["metric"], "value": r["value"], "unit": r["unit"], "ms_per_step": r["ms_per_step"],
+                   "workload": r["config"]["workload"], "parity_max_rel_err": r["parity"]["max_rel_err_vs_cpu_oracle"]}
+
     peaks = measured_peaks()
     bf16_burst = peaks.get("bf16_tflops")
     peak = 4.0 * bf16_burst if bf16_burst else 4.0 * 1590.0
     caps = L.Caps()
-    lib.bsg_gemm_query(C.byref(abi_args[0]), C.byref(caps))
+    abi0 = op.build_args(e2e_keep)
+    lib.bsg_gemm_query(C.byref(abi0), C.byref(caps))
     return {
         "metric": "nvfp4_gemm_8192_tflops", "value": round(tflops, 1), "unit": "TFLOP/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 5), "higher_is_better": True,
@@ -266,6 +281,7 @@ def run_single(args) -> dict:
                      "traffic": None},
         "cpu_baseline": {k: (round(v, 5) if isinstance(v, float) else v) for k, v in cpu.items()},
         "parity": {"slab_rows": slab, "max_rel_err_vs_cpu_reference": rel},
+        "scaling_base": tp_base,
     }
 
 
@@ -303,7 +319,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--cpu-rows", type=int, default=256, help="rows of M in the CPU baseline sample")
+    ap.add_argument("--cpu-rows", type=int, default=4096, help="rows of M in the CPU baseline sample")
+    ap.add_argument("--no-tp-base", action="store_true", help="skip the 1-GPU run of the tensor-parallel workload")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     if args.impl == "reference":

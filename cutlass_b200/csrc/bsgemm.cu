@@ -11,6 +11,7 @@
 #include <cstdio>
 #include <cstring>
 #include <cstdlib>
+#include <new>
 
 #include "../../include/bsgemm.h"
 #include "gemm_kernel.cuh"
@@ -110,6 +111,15 @@ struct Problem {
   int32_t rows_per_flag;
   uint32_t flag_target;
   int32_t tile_m_rotate;
+  // tensor parallel (TP kernel variant)
+  bool tp;
+  int32_t tp_world, tp_rank, tp_rows_per_shard, tp_ksplit;
+  uint32_t tp_epoch, tp_done_target;
+  int64_t tp_row_bytes, tp_sfa_rowatom_bytes;
+  const uint8_t* tp_peer_a[8];
+  const uint8_t* tp_peer_sfa[8];
+  uint32_t* tp_peer_sync[8];
+  int32_t* grid_ctas_out;     // receives the number of CTAs launched
 };
 
 struct Plan {
@@ -154,7 +164,7 @@ int32_t validate(const Problem& q, Plan* plan) {
   return BSG_OK;
 }
 
-template <int KIND, int CG, int BN>
+template <int KIND, int CG, int BN, bool TP = false>
 int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_t stream, int sm_count, bool dry) {
   using Cf = bsg::Cfg<KIND, CG, BN>;
   if (dry) return BSG_OK;
@@ -204,11 +214,17 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   p.rows_per_flag = q.rows_per_flag;
   p.flag_target = q.flag_target;
   p.tile_m_rotate = q.tile_m_rotate;
+  if (TP) {
+    p.tp_world = q.tp_world; p.tp_rank = q.tp_rank; p.tp_rows_per_shard = q.tp_rows_per_shard; p.tp_ksplit = q.tp_ksplit;
+    p.tp_epoch = q.tp_epoch; p.tp_done_target = q.tp_done_target;
+    p.tp_row_bytes = q.tp_row_bytes; p.tp_sfa_rowatom_bytes = q.tp_sfa_rowatom_bytes;
+    for (int i = 0; i < 8; ++i) { p.tp_peer_a[i] = q.tp_peer_a[i]; p.tp_peer_sfa[i] = q.tp_peer_sfa[i]; p.tp_peer_sync[i] = q.tp_peer_sync[i]; }
+  }
 #ifdef BSG_PROFILE
   { const char* dbg = getenv("BSG_DEBUG_FLAGS"); p.debug_flags = dbg ? atoi(dbg) : 0; }
 #endif
 
-  auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN>;
+  auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN, TP>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::kSmemBytes);
   if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
 
@@ -219,7 +235,8 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(unsigned(clusters * CG), 1, 1);
-  cfg.blockDim = dim3(192, 1, 1);
+  cfg.blockDim = dim3(TP ? 320 : 192, 1, 1);
+  if (q.grid_ctas_out) *q.grid_ctas_out = int32_t(clusters * CG);
   cfg.dynamicSmemBytes = Cf::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -236,6 +253,10 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
 
 template <int KIND>
 int32_t dispatch_shape(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_t s, int sm, bool dry) {
+  if (q.tp) {
+    if (plan.cta_group != 2) return fail(BSG_ERR_NOT_SUPPORTED, "the tensor-parallel GEMM needs cta_group 2");
+    return plan.tile_n == 256 ? launch<KIND, 2, 256, true>(q, plan, status, s, sm, dry) : launch<KIND, 2, 128, true>(q, plan, status, s, sm, dry);
+  }
   if (plan.cta_group == 2) {
     return plan.tile_n == 256 ? launch<KIND, 2, 256>(q, plan, status, s, sm, dry) : launch<KIND, 2, 128>(q, plan, status, s, sm, dry);
   }
@@ -329,6 +350,21 @@ Problem from_grouped(const bsg_grouped_args* a) {
 
 }  // namespace
 
+// Per-rank state of the tensor-parallel GEMM: one device allocation that holds the full-size A and
+// SFA buffers (this rank's shard in place, the others filled in by the kernel) and the sync words.
+struct bsg_tp_comm {
+  int32_t rank, world, kind;
+  int64_t M, K, rows_per_shard;
+  int64_t row_bytes, k_atoms, sfa_rowatom_bytes;
+  size_t a_off, sfa_off, sync_off, total_bytes;
+  uint8_t* base;
+  uint8_t* peer_base[8];
+  bool opened[8];
+  bool connected;
+  uint32_t epoch;
+  uint32_t done_total;
+};
+
 extern "C" {
 
 int32_t bsg_version(void) { return 100; }
@@ -403,6 +439,132 @@ int32_t bsg_read_device_status(void* workspace, void* cuda_stream) {
   if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "clearing status: %s", cudaGetErrorString(e));
   if (st & bsg::kStBadOffsets) return fail(BSG_ERR_INVALID_PROBLEM, "group offsets are not monotone or exceed total_M (device status 0x%x)", st);
   return fail(BSG_ERR_TIMEOUT, "a bounded device-side wait ran out (device status 0x%x)", st);
+}
+
+int32_t bsg_tp_create(int32_t rank, int32_t world, int32_t kind, int64_t M, int64_t K, bsg_tp_comm** out, void* ipc_handle_out) {
+  if (!out || !ipc_handle_out) return fail(BSG_ERR_INVALID_PROBLEM, "null argument");
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(BSG_ERR_INVALID_PROBLEM, "rank %d / world %d outside [0, 8]", rank, world);
+  if (kind != BSG_KIND_NVFP4 && kind != BSG_KIND_MXFP8) return fail(BSG_ERR_NOT_SUPPORTED, "unknown operand kind %d", kind);
+  if (M < 1 || K < 1 || M % (int64_t(world) * 256) != 0) return fail(BSG_ERR_INVALID_PROBLEM, "M=%lld must be a multiple of 256 * world", (long long)M);
+  const int64_t vec = kind == BSG_KIND_NVFP4 ? 16 : 32;
+  const int64_t row_bytes = kind == BSG_KIND_NVFP4 ? K / 2 : K;
+  if (K % (kind == BSG_KIND_NVFP4 ? 32 : 16) != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "K=%lld is not 16-byte aligned per row", (long long)K);
+  bsg_tp_comm* c = new (std::nothrow) bsg_tp_comm();
+  if (!c) return fail(BSG_ERR_INTERNAL, "out of host memory");
+  memset(c, 0, sizeof(*c));
+  c->rank = rank; c->world = world; c->kind = kind; c->M = M; c->K = K; c->rows_per_shard = M / world;
+  c->row_bytes = row_bytes;
+  c->k_atoms = ((K + vec - 1) / vec + 3) / 4;
+  c->sfa_rowatom_bytes = 512 * c->k_atoms;
+  const size_t a_bytes = size_t(M) * size_t(row_bytes);
+  const size_t sfa_bytes = size_t(M / 128) * size_t(c->sfa_rowatom_bytes);
+  const size_t sync_bytes = (size_t(bsg::kTpSyncFlags) + size_t(M / 256)) * 4;
+  auto up = [](size_t v) { return (v + 1023) & ~size_t(1023); };
+  c->a_off = 0;
+  c->sfa_off = up(a_bytes);
+  c->sync_off = c->sfa_off + up(sfa_bytes);
+  c->total_bytes = c->sync_off + up(sync_bytes);
+  cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->base), c->total_bytes);
+  if (e != cudaSuccess) { delete c; return fail(BSG_ERR_CUDA, "cudaMalloc(%zu): %s", c->total_bytes, cudaGetErrorString(e)); }
+  e = cudaMemset(c->base + c->sync_off, 0, up(sync_bytes));
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, c->base);
+  if (e != cudaSuccess) { cudaFree(c->base); delete c; return fail(BSG_ERR_CUDA, "tensor-parallel buffer set-up: %s", cudaGetErrorString(e)); }
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  memcpy(ipc_handle_out, &h, 64);
+  c->peer_base[rank] = c->base;
+  c->connected = world == 1;
+  *out = c;
+  return BSG_OK;
+}
+
+int32_t bsg_tp_connect(bsg_tp_comm* c, const void* all_handles) {
+  if (!c || !all_handles) return fail(BSG_ERR_INVALID_PROBLEM, "null argument");
+  for (int q = 0; q < c->world; ++q) {
+    if (q == c->rank || c->opened[q]) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, static_cast<const uint8_t*>(all_handles) + size_t(q) * 64, 64);
+    void* ptr = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "cudaIpcOpenMemHandle(rank %d): %s", q, cudaGetErrorString(e));
+    c->peer_base[q] = static_cast<uint8_t*>(ptr);
+    c->opened[q] = true;
+  }
+  c->connected = true;
+  return BSG_OK;
+}
+
+int32_t bsg_tp_buffers(bsg_tp_comm* c, void** a_full, void** sfa_full, void** a_shard, void** sfa_shard) {
+  if (!c) return fail(BSG_ERR_INVALID_PROBLEM, "null communicator");
+  uint8_t* a = c->base + c->a_off;
+  uint8_t* sf = c->base + c->sfa_off;
+  if (a_full) *a_full = a;
+  if (sfa_full) *sfa_full = sf;
+  if (a_shard) *a_shard = a + size_t(c->rank) * size_t(c->rows_per_shard) * size_t(c->row_bytes);
+  if (sfa_shard) *sfa_shard = sf + size_t(c->rank) * size_t(c->rows_per_shard / 128) * size_t(c->sfa_rowatom_bytes);
+  return BSG_OK;
+}
+
+int32_t bsg_tp_gemm_run(bsg_tp_comm* c, const bsg_gemm_args* args, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  if (!c || !args) return fail(BSG_ERR_INVALID_PROBLEM, "null argument");
+  if (!c->connected) return fail(BSG_ERR_INVALID_PROBLEM, "bsg_tp_connect has not been called");
+  if (args->M != c->M || args->K != c->K || args->kind != c->kind) return fail(BSG_ERR_INVALID_PROBLEM, "M, K and kind must match the communicator");
+  if (args->batch > 1) return fail(BSG_ERR_NOT_SUPPORTED, "the tensor-parallel GEMM is not batched");
+  bsg_gemm_args local = *args;
+  local.batch = 1;
+  local.A = c->base + c->a_off;
+  local.SFA = c->base + c->sfa_off;
+  local.cta_group = 2;
+  Problem q = from_dense(&local);
+  q.tp = true;
+  q.tp_world = c->world; q.tp_rank = c->rank; q.tp_rows_per_shard = int32_t(c->rows_per_shard);
+  int ks = 8;
+  while (ks > 1 && (c->row_bytes % (16 * ks) != 0 || c->k_atoms % ks != 0)) ks >>= 1;
+  q.tp_ksplit = ks;
+  q.tp_row_bytes = c->row_bytes; q.tp_sfa_rowatom_bytes = c->sfa_rowatom_bytes;
+  for (int i = 0; i < c->world; ++i) {
+    q.tp_peer_a[i] = c->peer_base[i] + c->a_off;
+    q.tp_peer_sfa[i] = c->peer_base[i] + c->sfa_off;
+    q.tp_peer_sync[i] = reinterpret_cast<uint32_t*>(c->peer_base[i] + c->sync_off);
+  }
+  // The M sweep starts at this rank's own rows and follows the order in which the shards arrive.
+  const int32_t blocks = int32_t(c->rows_per_shard / 256);
+  int32_t band = 8;
+  while (blocks % band != 0) band >>= 1;
+  q.raster_band = band;
+  q.tile_m_rotate = c->rank * blocks;
+  q.ready_flags = c->world > 1 ? q.tp_peer_sync[c->rank] + bsg::kTpSyncFlags : nullptr;
+  q.rows_per_flag = 256;
+  // Every rank launches the same grid, so the cumulative number of "finished copying" arrivals is known.
+  Plan plan;
+  int32_t rc = validate(q, &plan);
+  if (rc != BSG_OK) return rc;
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (q.sm_count > 0 && q.sm_count < sms) sms = q.sm_count;
+  int64_t clusters = sms / 2;
+  if (plan.num_tiles >= 0 && plan.num_tiles < clusters) clusters = plan.num_tiles;
+  q.tp_epoch = c->epoch + 1;
+  q.tp_done_target = c->done_total + uint32_t(clusters * 2);
+  q.flag_target = q.tp_epoch * uint32_t(ks);
+  rc = run_problem(q, workspace, workspace_bytes, cuda_stream);
+  if (rc != BSG_OK) return rc;
+  c->epoch += 1;
+  c->done_total += uint32_t(clusters * 2);
+  return BSG_OK;
+}
+
+int32_t bsg_tp_destroy(bsg_tp_comm* c) {
+  if (!c) return BSG_OK;
+  cudaDeviceSynchronize();
+  for (int q = 0; q < c->world; ++q) {
+    if (c->opened[q]) cudaIpcCloseMemHandle(c->peer_base[q]);
+  }
+  if (c->base) cudaFree(c->base);
+  delete c;
+  return BSG_OK;
 }
 
 }  // extern "C"

@@ -75,6 +75,11 @@ SYMBOLS = {
     "bsg_grouped_run": (C.c_int32, [C.POINTER(GroupedArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "bsg_workspace_init": (C.c_int32, [C.c_void_p, C.c_size_t, C.c_void_p]),
     "bsg_read_device_status": (C.c_int32, [C.c_void_p, C.c_void_p]),
+    "bsg_tp_create": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.POINTER(C.c_void_p), C.c_void_p]),
+    "bsg_tp_connect": (C.c_int32, [C.c_void_p, C.c_void_p]),
+    "bsg_tp_buffers": (C.c_int32, [C.c_void_p] + [C.POINTER(C.c_void_p)] * 4),
+    "bsg_tp_gemm_run": (C.c_int32, [C.c_void_p, C.POINTER(GemmArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "bsg_tp_destroy": (C.c_int32, [C.c_void_p]),
 }
 
 _lib = None

@@ -1,0 +1,161 @@
+"""Tensor-parallel block-scaled GEMM: A row-sharded and all-gathered inside the kernel,
+B and D sharded over N.  One process per GPU (``torch.distributed`` for the bootstrap only).
+
+Plays the role of the reference's distributed all-gather GEMM
+(``include/cutlass/experimental/distributed/schedules/dist_gemm_1d_schedules.hpp``,
+``AllGather1D_TilingCD_RotatingA``; host orchestration in
+``examples/python/CuTeDSL/cute/blackwell/kernel/distributed/distributed_all_gather_gemm_blackwell.py:2166-2273``).
+There the copy engine moves the peer shards and per-stage GEMM launches are gated by flags; here a
+single kernel per rank does both: copy warps pull the peers' rows over NVLink and publish
+per-row-block flags, the tensor-core warps start on the local rows and follow the arrival order.
+
+The planning helpers at the top are pure Python (they restate the kernel's schedule) and are
+what the CPU multi-process tests exercise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+ROW_BLOCK = 256          # rows per readiness flag = rows of one MMA tile (two CTAs x 128)
+MAX_WORLD = 8
+
+
+def shard_rows(M: int, world: int, rank: int) -> tuple[int, int]:
+    """Row range [begin, end) of A that ``rank`` owns."""
+    if M % (world * ROW_BLOCK) != 0:
+        raise ValueError(f"M={M} must be a multiple of {ROW_BLOCK} * world ({world})")
+    ms = M // world
+    return rank * ms, (rank + 1) * ms
+
+
+def shard_cols(N: int, world: int, rank: int) -> tuple[int, int]:
+    """Column range [begin, end) of B / D that ``rank`` owns."""
+    if N % (world * 8) != 0:
+        raise ValueError(f"N={N} must be a multiple of 8 * world ({world})")
+    ns = N // world
+    return rank * ns, (rank + 1) * ns
+
+
+def choose_ksplit(row_bytes: int, k_atoms: int) -> int:
+    """Pieces a 256-row block is cut into along K (each piece is one flag increment)."""
+    ks = 8
+    while ks > 1 and (row_bytes % (16 * ks) != 0 or k_atoms % ks != 0):
+        ks //= 2
+    return ks
+
+
+def consumption_order(world: int, rank: int) -> list[int]:
+    """Shards in the order the GEMM of ``rank`` consumes them: its own first, then rank+1, ..."""
+    return [(rank + j) % world for j in range(world)]
+
+
+@dataclass(frozen=True)
+class CopyPiece:
+    src_rank: int
+    row_block: int       # global index of the 256-row block
+    k_piece: int
+
+
+def copy_schedule(world: int, rank: int, M: int, ksplit: int, cta: int, grid: int) -> list[CopyPiece]:
+    """Pieces of remote A that CTA ``cta`` of ``grid`` copies, in order (restates the kernel loop)."""
+    ms = M // world
+    blocks = ms // ROW_BLOCK
+    per_shard = blocks * ksplit
+    out = []
+    for c in range(cta, (world - 1) * per_shard, grid):
+        j = c // per_shard + 1
+        rem = c - (j - 1) * per_shard
+        rb, ks = divmod(rem, ksplit)
+        src = (rank + j) % world
+        out.append(CopyPiece(src, src * blocks + rb, ks))
+    return out
+
+
+def exchange_handles(handle: bytes, group=None) -> list[bytes]:
+    """All-gather one opaque per-rank blob (the CUDA IPC handle) over ``torch.distributed``."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    out: list = [None] * world
+    dist.all_gather_object(out, handle, group=group)
+    return out
+
+
+class _DevicePointer:
+    """Exposes raw device memory through ``__cuda_array_interface__`` so torch can view it."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class TpGemm:
+    """Per-rank handle of the tensor-parallel GEMM for a fixed (kind, M, K).
+
+    ``a_shard`` / ``sfa_shard`` are uint8 views of where this rank's rows of A and their
+    interleaved scale factors live; fill them, then call ``run`` on every rank."""
+
+    def __init__(self, kind: int, M: int, K: int, group=None):
+        import torch
+        import torch.distributed as dist
+        from . import lib as L
+        self._L = L
+        self._lib = L.load()
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        if self.world > MAX_WORLD:
+            raise ValueError(f"at most {MAX_WORLD} ranks are supported")
+        self.kind, self.M, self.K = kind, M, K
+        self.row_begin, self.row_end = shard_rows(M, self.world, self.rank)
+        self._comm = C.c_void_p()
+        handle = (C.c_uint8 * 64)()
+        L.check(self._lib.bsg_tp_create(self.rank, self.world, kind, M, K, C.byref(self._comm), handle))
+        if self.world > 1:
+            handles = exchange_handles(bytes(handle), group)
+            blob = (C.c_uint8 * (64 * self.world)).from_buffer_copy(b"".join(handles))
+            L.check(self._lib.bsg_tp_connect(self._comm, blob))
+            dist.barrier(group)
+        ptrs = [C.c_void_p() for _ in range(4)]
+        L.check(self._lib.bsg_tp_buffers(self._comm, *[C.byref(p) for p in ptrs]))
+        row_bytes = K // 2 if kind == L.KIND_NVFP4 else K
+        vec = 16 if kind == L.KIND_NVFP4 else 32
+        k_atoms = -(-(-(-K // vec)) // 4)
+        ms = M // self.world
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.a_full = torch.as_tensor(_DevicePointer(ptrs[0].value, M * row_bytes), device=dev).view(M, row_bytes)
+        self.sfa_full = torch.as_tensor(_DevicePointer(ptrs[1].value, (M // 128) * 512 * k_atoms), device=dev)
+        self.a_shard = torch.as_tensor(_DevicePointer(ptrs[2].value, ms * row_bytes), device=dev).view(ms, row_bytes)
+        self.sfa_shard = torch.as_tensor(_DevicePointer(ptrs[3].value, (ms // 128) * 512 * k_atoms), device=dev)
+        self.workspace = torch.zeros(16, dtype=torch.uint8, device=dev)
+
+    def build_args(self, B, SFB, out, C_=None, alpha: float = 1.0, beta: float = 0.0, tile_n: int = 0):
+        """B: (N_local, K bytes) K-major uint8/e4m3 tensor; SFB its interleaved scales; out: (M, N_local) bf16."""
+        L = self._L
+        a = L.GemmArgs()
+        a.kind, a.out_kind, a.batch = self.kind, L.OUT_BF16, 1
+        a.M, a.N, a.K = self.M, out.shape[-1], self.K
+        a.B, a.SFB, a.D = B.data_ptr(), SFB.data_ptr(), out.data_ptr()
+        a.C = C_.data_ptr() if C_ is not None else None
+        a.alpha, a.beta = alpha, beta
+        a.tile_n, a.cta_group = tile_n, 2
+        return a
+
+    def run(self, B, SFB, out, C_=None, alpha: float = 1.0, beta: float = 0.0, stream=None, abi_args=None) -> None:
+        from .operator import to_cuda_stream
+        a = abi_args if abi_args is not None else self.build_args(B, SFB, out, C_, alpha, beta)
+        self._L.check(self._lib.bsg_tp_gemm_run(self._comm, C.byref(a), self.workspace.data_ptr(), 16, to_cuda_stream(stream)))
+
+    def check_device_status(self, stream=None) -> None:
+        from .operator import to_cuda_stream
+        self._L.check(self._lib.bsg_read_device_status(self.workspace.data_ptr(), to_cuda_stream(stream)))
+
+    def close(self) -> None:
+        if self._comm:
+            self.a_full = self.sfa_full = self.a_shard = self.sfa_shard = None
+            self._lib.bsg_tp_destroy(self._comm)
+            self._comm = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001
+            pass

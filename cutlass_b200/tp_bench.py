@@ -1,0 +1,179 @@
+"""Multi-GPU leg of ``bench.py``: the tensor-parallel MXFP8 GEMM (M=16384, N=28672, K=8192),
+A row-sharded and gathered inside the kernel, B / D column-sharded.  Strong scaling: the whole
+problem is fixed, every rank computes D[:, its columns]; time = max over ranks (device events)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+M_TP, N_TP, K_TP = 16384, 28672, 8192
+
+
+def _shard_operand(rows: int, K: int, seed: int, device):
+    """Seeded MXFP8 operand rows (same values on whichever rank generates them)."""
+    import torch
+    import bench
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    return bench.gpu_mxfp8_operand(rows, K, gen, device)
+
+
+def run(args) -> dict:
+    import torch
+    import torch.distributed as dist
+    import bench
+    from cutlass_b200 import formats as F
+    from cutlass_b200 import lib as L
+    from cutlass_b200 import tp as TP
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+    M, N, K = M_TP, N_TP, K_TP
+    ms, ns = M // world, N // world
+    kind = L.KIND_MXFP8
+
+    tp = TP.TpGemm(kind, M, K)
+    A, SFA = _shard_operand(ms, K, 1000 + rank, dev)
+    tp.a_shard.copy_(A)
+    tp.sfa_shard.copy_(SFA)
+    B, SFB = _shard_operand(ns, K, 2000 + rank, dev)
+    n_out = 2
+    outs = [torch.empty((M, ns), dtype=torch.bfloat16, device=dev) for _ in range(n_out)]
+    abi = [tp.build_args(B, SFB, o) for o in outs]
+    stream = torch.cuda.current_stream()
+    torch.cuda.synchronize()
+    dist.barrier()
+
+    def step(i):
+        tp.run(B, SFB, outs[i % n_out], stream=stream, abi_args=abi[i % n_out])
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with bench.ClockSampler(local) as clk:
+        e0.record(stream)
+        for i in range(args.steps):
+            step(i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+    tp.check_device_status(stream)
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    flops = 2.0 * M * N * K
+    tflops = flops / ms_step / 1e9
+
+    # ---- parity: a few rows of a REMOTE shard (gathered over NVLink) against the CPU oracle
+    import oracle
+    check_shard = (rank + 1) % world
+    rows = 32
+    A_chk, SFA_chk = _shard_operand(ms, K, 1000 + check_shard, dev)
+    got = outs[(args.steps - 1) % n_out][check_shard * ms: check_shard * ms + rows, :256].contiguous()
+    want = oracle.to_bf16(oracle.gemm_fp32(kind, A_chk[:128].cpu().numpy(), SFA_chk[: 512 * (K // 128)].cpu().numpy(),
+                                           B[:256].cpu().numpy(), SFB[: 2 * 512 * (K // 128)].cpu().numpy(), 128, 256, K))[:rows]
+    gf = F.bf16_to_f32(got.view(torch.int16).cpu().numpy().view(np.uint16))
+    wf = F.bf16_to_f32(want)
+    rel = float(np.max(np.abs(gf - wf)) / max(float(np.max(np.abs(wf))), 1e-30))
+    relt = torch.tensor([rel], dtype=torch.float64, device=dev)
+    dist.all_reduce(relt, op=dist.ReduceOp.MAX)
+
+    # ---- unfused baseline: NCCL all-gather of A and SFA, then the plain dense kernel
+    lib = L.load()
+    a_full, sfa_full = torch.empty_like(tp.a_full), torch.empty_like(tp.sfa_full)
+    dense = L.GemmArgs()
+    dense.kind, dense.batch, dense.M, dense.N, dense.K = kind, 1, M, ns, K
+    dense.A, dense.SFA, dense.B, dense.SFB, dense.D = a_full.data_ptr(), sfa_full.data_ptr(), B.data_ptr(), SFB.data_ptr(), outs[0].data_ptr()
+    dense.alpha = 1.0
+    ws = torch.zeros(16, dtype=torch.uint8, device=dev)
+
+    def unfused():
+        if world > 1:
+            dist.all_gather_into_tensor(a_full.view(-1), A.view(-1))
+            dist.all_gather_into_tensor(sfa_full, SFA)
+        rc = lib.bsg_gemm_run(C.byref(dense), ws.data_ptr(), 16, stream.cuda_stream)
+        assert rc == 0, L.last_error()
+
+    if world == 1:
+        a_full.copy_(A)
+        sfa_full.copy_(SFA)
+    for _ in range(3):
+        unfused()
+    torch.cuda.synchronize()
+    dist.barrier()
+    n_unf = max(3, min(args.steps, 20))
+    e0.record(stream)
+    for _ in range(n_unf):
+        unfused()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    tu = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    dist.all_reduce(tu, op=dist.ReduceOp.MAX)
+    unfused_ms = float(tu.item()) / n_unf
+
+    # ---- end to end with host buffers: this rank's A shard and B shard in, its D shard out
+    hA, hSFA, hB, hSFB = (x.cpu().pin_memory() for x in (A, SFA, B, SFB))
+    hD = torch.empty((M, ns), dtype=torch.bfloat16).pin_memory()
+    h2d = sum(x.numel() * x.element_size() for x in (hA, hSFA, hB, hSFB))
+    d2h = hD.numel() * hD.element_size()
+
+    def e2e_step():
+        tp.a_shard.copy_(hA, non_blocking=True)
+        tp.sfa_shard.copy_(hSFA, non_blocking=True)
+        B.copy_(hB, non_blocking=True)
+        SFB.copy_(hSFB, non_blocking=True)
+        tp.run(B, SFB, outs[0], stream=stream, abi_args=abi[0])
+        hD.copy_(outs[0], non_blocking=True)
+
+    e2e_step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    n_e2e = max(3, min(args.steps, 10))
+    e0.record(stream)
+    for _ in range(n_e2e):
+        e2e_step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    te = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_ms = float(te.item()) / n_e2e
+    tp.check_device_status(stream)
+
+    peaks = bench.measured_peaks()
+    bf16 = peaks.get("bf16_tflops_sustained") or peaks.get("bf16_tflops")
+    peak = (2.0 * bf16 if bf16 else 2.0 * 1400.0) * world
+    link_bytes = (world - 1) * (ms * K + SFA.numel())                     # received per rank per step
+    out = {
+        "metric": "tp_mxfp8_gemm_tflops", "value": round(tflops, 1), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "mxfp8 (e4m3 x ue8m0/32), fp32 accumulate, bf16 out", "data": "synthetic",
+        "config": {"workload": f"tensor-parallel MXFP8 GEMM M={M} N={N} K={K}: A row-sharded, gathered in-kernel over NVLink; B, D column-sharded",
+                   "M": M, "N": N, "K": K, "parallelism": f"tp{world}",
+                   "l2_policy": f"operands per rank {(ms * K + ns * K) >> 20} MiB + gathered A {(M * K) >> 20} MiB > L2; {n_out} output buffers rotated",
+                   "nvlink_bytes_received_per_rank_per_step": link_bytes,
+                   "pct_of_nominal_fp8_peak": round(100.0 * tflops / (bench.NOMINAL_FP8_TFLOPS * world), 1)},
+        "e2e": {"value": round(flops / e2e_ms / 1e9, 1), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d * world,
+                "d2h_bytes_per_step": d2h * world, "ms_per_step": round(e2e_ms, 4), "steps": n_e2e},
+        "gpu_launches": args.steps * world,
+        "clocks": clk.summary(),
+        "roofline": {"bound": "tensor", "achieved": round(tflops, 1), "peak": round(peak, 1), "unit": "TFLOP/s",
+                     "frac": round(tflops / peak, 4),
+                     "peak_source": "n_gpus x 2 x bf16_tflops_sustained of MEASURED_PEAKS.json (no fp8 figure is measured)",
+                     "frac_of_nominal": round(tflops / (bench.NOMINAL_FP8_TFLOPS * world), 4),
+                     "nvlink_time_floor_ms": round(link_bytes / 770e9 * 1e3, 4), "traffic": None},
+        "unfused_nccl": {"value": round(flops / unfused_ms / 1e9, 1), "unit": "TFLOP/s", "ms_per_step": round(unfused_ms, 4),
+                         "what": "ncclAllGather(A), ncclAllGather(SFA), then the same dense kernel"},
+        "parity": {"rows_checked_per_rank": rows, "from_shard": "rank+1 (remote)", "max_rel_err_vs_cpu_oracle": float(relt.item())},
+    }
+    tp.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    return out

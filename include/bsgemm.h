@@ -160,6 +160,33 @@ int32_t bsg_grouped_run(const bsg_grouped_args* args, void* workspace, size_t wo
  * clear it. */
 int32_t bsg_read_device_status(void* workspace, void* cuda_stream);
 
+/*
+ * Tensor-parallel GEMM: D[:, local N shard] = alpha * A B_local^T + beta * C, with A (and SFA)
+ * sharded by rows over `world` ranks (one process per GPU of one node) and B / D sharded over N.
+ * The kernel itself gathers the other ranks' A shards over NVLink (peer-memory loads by
+ * dedicated copy warps) while its tensor-core warps already work on the rows that have arrived.
+ * Takes the role of the reference's all-gather distributed GEMM
+ * (include/cutlass/experimental/distributed/device/dist_gemm_universal_wrapper.hpp:53,
+ * schedule AllGather1D_TilingCD_RotatingA in schedules/dist_gemm_1d_schedules.hpp; device barrier
+ * kernel/full_barrier.hpp:47), with bounded waits instead of unbounded spins.
+ *
+ * bsg_tp_create   allocates this rank's buffers (full-size A and SFA plus sync words; the only
+ *                 allocating call) and returns a 64-byte CUDA IPC handle to hand to the peers.
+ * bsg_tp_connect  takes the `world` handles (64 bytes each, indexed by rank) and maps the peers.
+ * bsg_tp_buffers  returns where this rank writes its own A / SFA shard (inside the full buffers).
+ * bsg_tp_gemm_run enqueues one GEMM; args->A / SFA are ignored, args->M is the full M, args->N
+ *                 the local N shard.  All ranks must call it the same number of times with the
+ *                 same shapes.  A rank's call completes only after every peer has read its shard.
+ */
+typedef struct bsg_tp_comm bsg_tp_comm;
+int32_t bsg_tp_create(int32_t rank, int32_t world, int32_t kind, int64_t M, int64_t K, bsg_tp_comm** out,
+                      void* ipc_handle_out);
+int32_t bsg_tp_connect(bsg_tp_comm* comm, const void* all_handles);
+int32_t bsg_tp_buffers(bsg_tp_comm* comm, void** a_full, void** sfa_full, void** a_shard, void** sfa_shard);
+int32_t bsg_tp_gemm_run(bsg_tp_comm* comm, const bsg_gemm_args* args, void* workspace, size_t workspace_bytes,
+                        void* cuda_stream);
+int32_t bsg_tp_destroy(bsg_tp_comm* comm);
+
 #ifdef __cplusplus
 }
 #endif
