@@ -114,7 +114,7 @@ struct Problem {
   // tensor parallel (TP kernel variant)
   bool tp;
   int32_t tp_world, tp_rank, tp_rows_per_shard, tp_ksplit;
-  uint32_t tp_epoch, tp_done_target;
+  uint32_t tp_epoch;
   int64_t tp_row_bytes, tp_sfa_rowatom_bytes;
   const uint8_t* tp_peer_a[8];
   const uint8_t* tp_peer_sfa[8];
@@ -216,7 +216,7 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   p.tile_m_rotate = q.tile_m_rotate;
   if (TP) {
     p.tp_world = q.tp_world; p.tp_rank = q.tp_rank; p.tp_rows_per_shard = q.tp_rows_per_shard; p.tp_ksplit = q.tp_ksplit;
-    p.tp_epoch = q.tp_epoch; p.tp_done_target = q.tp_done_target;
+    p.tp_epoch = q.tp_epoch;
     p.tp_row_bytes = q.tp_row_bytes; p.tp_sfa_rowatom_bytes = q.tp_sfa_rowatom_bytes;
     for (int i = 0; i < 8; ++i) { p.tp_peer_a[i] = q.tp_peer_a[i]; p.tp_peer_sfa[i] = q.tp_peer_sfa[i]; p.tp_peer_sync[i] = q.tp_peer_sync[i]; }
   }
@@ -362,7 +362,6 @@ struct bsg_tp_comm {
   bool opened[8];
   bool connected;
   uint32_t epoch;
-  uint32_t done_total;
 };
 
 extern "C" {
@@ -536,23 +535,11 @@ int32_t bsg_tp_gemm_run(bsg_tp_comm* c, const bsg_gemm_args* args, void* workspa
   q.tile_m_rotate = c->rank * blocks;
   q.ready_flags = c->world > 1 ? q.tp_peer_sync[c->rank] + bsg::kTpSyncFlags : nullptr;
   q.rows_per_flag = 256;
-  // Every rank launches the same grid, so the cumulative number of "finished copying" arrivals is known.
-  Plan plan;
-  int32_t rc = validate(q, &plan);
-  if (rc != BSG_OK) return rc;
-  int dev = 0, sms = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (q.sm_count > 0 && q.sm_count < sms) sms = q.sm_count;
-  int64_t clusters = sms / 2;
-  if (plan.num_tiles >= 0 && plan.num_tiles < clusters) clusters = plan.num_tiles;
   q.tp_epoch = c->epoch + 1;
-  q.tp_done_target = c->done_total + uint32_t(clusters * 2);
   q.flag_target = q.tp_epoch * uint32_t(ks);
-  rc = run_problem(q, workspace, workspace_bytes, cuda_stream);
+  int32_t rc = run_problem(q, workspace, workspace_bytes, cuda_stream);
   if (rc != BSG_OK) return rc;
   c->epoch += 1;
-  c->done_total += uint32_t(clusters * 2);
   return BSG_OK;
 }
 

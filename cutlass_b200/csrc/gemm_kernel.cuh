@@ -76,22 +76,20 @@ struct GemmParams {
   uint32_t flag_target;
   int32_t tile_m_rotate;      // dense only: start the M sweep at this tile row
   int32_t debug_flags;        // only read when built with -DBSG_PROFILE (ablation switches, timeline capture)
-  // Tensor-parallel all-gather of A (kernel template TP == true): the copy warps pull the other
-  // ranks' row shards of A and SFA from peer memory into this GPU's full-size buffers.
+  // Tensor-parallel all-gather of A (kernel template TP == true): the copy warps push this rank's
+  // row shard of A and SFA into every peer's full-size buffers.
   int32_t tp_world, tp_rank;
   int32_t tp_rows_per_shard;  // multiple of 256
   int32_t tp_ksplit;          // pieces a 256-row block is cut into along K (one flag increment each)
   uint32_t tp_epoch;          // call counter, starts at 1; the peers use the same value
-  uint32_t tp_done_target;    // cumulative number of CTAs that will have finished copying after this call
   int64_t tp_row_bytes;       // bytes of one row of A
   int64_t tp_sfa_rowatom_bytes;   // bytes of one 128-row atom row of SFA (512 * k_atoms)
   const uint8_t* tp_peer_a[8];    // full-size A buffer of every rank (own entry = local buffer)
   const uint8_t* tp_peer_sfa[8];
-  uint32_t* tp_peer_sync[8];      // sync words of every rank: [0,8) ready, [8,16) done, [32, ...) row-block flags
+  uint32_t* tp_peer_sync[8];      // sync words of every rank: [0,8) "buffer free for call n", [32, ...) row-block flags
 };
 
 constexpr int kTpSyncReady = 0;
-constexpr int kTpSyncDone = 8;
 constexpr int kTpSyncFlags = 32;
 constexpr uint32_t kStTimeoutPeer = 64u;      // tensor parallel: a peer never published / finished
 
@@ -380,7 +378,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const int32_t group_atoms = (ti.row_end - ti.group_row0 + 127) >> 7;
       const int32_t sfa_atom = bcast(min(ti.sf_atom + int32_t(cta_rank), ti.group_atom0 + max(group_atoms, 1) - 1));
       const int32_t sfb_atom = bcast(ti.g * p.sfb_atoms_per_group + ti.tn * (BN / 128));
-      if (p.ready_flags != nullptr && (!TP || ti.row0 / p.tp_rows_per_shard != p.tp_rank)) {
+      if (p.ready_flags != nullptr && (!TP || ti.row0 / p.tp_rows_per_shard != p.tp_rank) && !BSG_FLAG(p, 1024)) {
         const uint32_t* flag = p.ready_flags + ti.row0 / p.rows_per_flag;
         const long long t0 = clock64();
         while (ptx::ld_acquire_sys_u32(flag) < p.flag_target) {
@@ -505,13 +503,17 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
   } else if (TP && warp >= 6) {
     // ---------------------------------------------------------------- all-gather copy warps (6-9)
-    if (p.tp_world > 1) {
+    // Push: this rank's own rows of A / SFA are read locally and written into every peer's full-size
+    // buffer (posted stores over NVLink), nearest consumer first; each finished piece bumps the
+    // row-block flag in the peer's memory that the peer's TMA producer waits on.
+    if (p.tp_world > 1 && !BSG_FLAG(p, 2048)) {
       const int tid = int(threadIdx.x) - 192;
       uint32_t* sync = p.tp_peer_sync[p.tp_rank];
-      uint8_t* a_full = const_cast<uint8_t*>(p.tp_peer_a[p.tp_rank]);
-      uint8_t* sfa_full = const_cast<uint8_t*>(p.tp_peer_sfa[p.tp_rank]);
+      const uint8_t* a_own = p.tp_peer_a[p.tp_rank];
+      const uint8_t* sfa_own = p.tp_peer_sfa[p.tp_rank];
       bool peer_ok = true;
-      // This rank's shard was complete before the kernel was launched: publish it to every peer.
+      // Launching this call means the previous one has finished reading this rank's gathered buffer:
+      // tell every peer that it may now be overwritten with the data of this call.
       if (blockIdx.x == 0 && tid == 0) {
         __threadfence_system();
         for (int q = 0; q < p.tp_world; ++q) {
@@ -525,19 +527,19 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const int sfa_piece16 = int(p.tp_sfa_rowatom_bytes / p.tp_ksplit / 16);  // per 128-row atom per piece
       int checked = -1;
       for (int c = blockIdx.x; c < total; c += gridDim.x) {
-        const int j = c / per_shard + 1;                       // shards are taken in the order the GEMM consumes them
+        const int j = c / per_shard + 1;
         const int rem = c - (j - 1) * per_shard;
         const int rb = rem / p.tp_ksplit, ks = rem - rb * p.tp_ksplit;
-        const int src_rank = (p.tp_rank + j) % p.tp_world;
-        if (src_rank != checked) {
-          if (!wait_flag_ge(sync + kTpSyncReady + src_rank, p.tp_epoch, ctl)) peer_ok = false;
-          checked = src_rank;
+        const int dst_rank = (p.tp_rank - j + p.tp_world) % p.tp_world;   // rank-1 consumes this shard first
+        if (dst_rank != checked) {
+          if (!wait_flag_ge(sync + kTpSyncReady + dst_rank, p.tp_epoch, ctl)) peer_ok = false;
+          checked = dst_rank;
         }
-        const int64_t row0 = int64_t(src_rank) * p.tp_rows_per_shard + int64_t(rb) * 256;
-        const uint8_t* src_a = p.tp_peer_a[src_rank];
-        const uint8_t* src_sfa = p.tp_peer_sfa[src_rank];
-        // A: 256 rows x (row_bytes / ksplit) bytes, 8 independent 16-byte loads in flight per thread
-        {
+        const int64_t row0 = int64_t(p.tp_rank) * p.tp_rows_per_shard + int64_t(rb) * 256;
+        uint8_t* dst_a = const_cast<uint8_t*>(p.tp_peer_a[dst_rank]);
+        uint8_t* dst_sfa = const_cast<uint8_t*>(p.tp_peer_sfa[dst_rank]);
+        if (peer_ok) {
+          // A: 256 rows x (row_bytes / ksplit) bytes, 8 independent 16-byte loads in flight per thread
           const int n16 = 256 * row_piece16;
           for (int base = 0; base < n16; base += 128 * 8) {
             uint4 v[8];
@@ -547,40 +549,23 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               const int i = base + u * 128 + tid;
               const int rr = i / row_piece16, cc = i - rr * row_piece16;
               off[u] = (row0 + rr) * p.tp_row_bytes + (int64_t(ks) * row_piece16 + cc) * 16;
-              if (i < n16) v[u] = ld_global_v4(src_a + off[u]);
+              if (i < n16) v[u] = ld_global_v4(a_own + off[u]);
             }
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
               const int i = base + u * 128 + tid;
-              if (i < n16) *reinterpret_cast<uint4*>(a_full + off[u]) = v[u];
+              if (i < n16) *reinterpret_cast<uint4*>(dst_a + off[u]) = v[u];
             }
           }
+          // SFA: two 128-row atoms, a contiguous run of k-atoms each
+          for (int ra = 0; ra < 2; ++ra) {
+            const int64_t o = (row0 / 128 + ra) * p.tp_sfa_rowatom_bytes + int64_t(ks) * sfa_piece16 * 16;
+            tp_copy16(dst_sfa + o, sfa_own + o, sfa_piece16, tid);
+          }
+          __threadfence_system();
         }
-        // SFA: two 128-row atoms, a contiguous run of k-atoms each
-        for (int ra = 0; ra < 2; ++ra) {
-          const int64_t o = (row0 / 128 + ra) * p.tp_sfa_rowatom_bytes + int64_t(ks) * sfa_piece16 * 16;
-          tp_copy16(sfa_full + o, src_sfa + o, sfa_piece16, tid);
-        }
-        __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (tid == 0) {
-          asm volatile("fence.proxy.async;" ::: "memory");
-          atomicAdd(sync + kTpSyncFlags + int(row0 / 256), 1u);
-        }
-      }
-      // All loads of this CTA from peer memory have returned: tell every peer.
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (tid == 0) {
-        __threadfence_system();
-        for (int q = 0; q < p.tp_world; ++q) {
-          if (q != p.tp_rank) atomicAdd_system(p.tp_peer_sync[q] + kTpSyncDone + p.tp_rank, 1u);
-        }
-      }
-      // The kernel may only complete once every peer has finished reading this rank's shard.
-      if (blockIdx.x == 0 && tid == 0) {
-        for (int q = 0; q < p.tp_world; ++q) {
-          if (q != p.tp_rank && !wait_flag_ge(sync + kTpSyncDone + q, p.tp_done_target, ctl)) peer_ok = false;
-        }
+        if (tid == 0 && peer_ok) atomicAdd_system(p.tp_peer_sync[dst_rank] + kTpSyncFlags + int(row0 / 256), 1u);
       }
       if (!peer_ok) atomicOr(p.status, kStTimeoutPeer);
     }

@@ -6,8 +6,9 @@ Plays the role of the reference's distributed all-gather GEMM
 ``AllGather1D_TilingCD_RotatingA``; host orchestration in
 ``examples/python/CuTeDSL/cute/blackwell/kernel/distributed/distributed_all_gather_gemm_blackwell.py:2166-2273``).
 There the copy engine moves the peer shards and per-stage GEMM launches are gated by flags; here a
-single kernel per rank does both: copy warps pull the peers' rows over NVLink and publish
-per-row-block flags, the tensor-core warps start on the local rows and follow the arrival order.
+single kernel per rank does both: copy warps push this rank's rows into every peer's buffer over
+NVLink (posted stores) and bump per-row-block flags in the peer's memory; the tensor-core warps
+start on the local rows and follow the arrival order.
 
 The planning helpers at the top are pure Python (they restate the kernel's schedule) and are
 what the CPU multi-process tests exercise.
@@ -50,15 +51,20 @@ def consumption_order(world: int, rank: int) -> list[int]:
     return [(rank + j) % world for j in range(world)]
 
 
+def push_order(world: int, rank: int) -> list[int]:
+    """Peers in the order ``rank`` pushes its shard to them: rank-1 needs it first, then rank-2, ..."""
+    return [(rank - j) % world for j in range(1, world)]
+
+
 @dataclass(frozen=True)
 class CopyPiece:
-    src_rank: int
-    row_block: int       # global index of the 256-row block
+    dst_rank: int
+    row_block: int       # global index of the 256-row block (always inside the pushing rank's shard)
     k_piece: int
 
 
 def copy_schedule(world: int, rank: int, M: int, ksplit: int, cta: int, grid: int) -> list[CopyPiece]:
-    """Pieces of remote A that CTA ``cta`` of ``grid`` copies, in order (restates the kernel loop)."""
+    """Pieces of its own shard that CTA ``cta`` of ``grid`` pushes, in order (restates the kernel loop)."""
     ms = M // world
     blocks = ms // ROW_BLOCK
     per_shard = blocks * ksplit
@@ -67,8 +73,7 @@ def copy_schedule(world: int, rank: int, M: int, ksplit: int, cta: int, grid: in
         j = c // per_shard + 1
         rem = c - (j - 1) * per_shard
         rb, ks = divmod(rem, ksplit)
-        src = (rank + j) % world
-        out.append(CopyPiece(src, src * blocks + rb, ks))
+        out.append(CopyPiece((rank - j) % world, rank * blocks + rb, ks))
     return out
 
 

@@ -31,21 +31,27 @@ def test_ksplit_choice():
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_copy_schedule_covers_every_remote_piece_once_in_consumption_order(world):
+def test_push_schedule_delivers_every_piece_once_and_nearest_consumer_first(world):
     M, ksplit, grid = 16384, 8, 148
     blocks = M // world // TP.ROW_BLOCK
+    received = {}                                   # (dst, row_block, k_piece) -> count, over all ranks
     for rank in range(world):
-        seen = {}
+        order = TP.push_order(world, rank)
+        assert order[0] == (rank - 1) % world and rank not in order and len(set(order)) == world - 1
         for cta in range(grid):
             sched = TP.copy_schedule(world, rank, M, ksplit, cta, grid)
-            order = TP.consumption_order(world, rank)
-            pos = [order.index(p.src_rank) for p in sched]
-            assert pos == sorted(pos), "a CTA must copy shards in the order the GEMM consumes them"
+            pos = [order.index(p.dst_rank) for p in sched]
+            assert pos == sorted(pos), "a CTA must serve the peers in the order they consume this shard"
             for p in sched:
-                assert p.src_rank != rank
-                assert p.src_rank * blocks <= p.row_block < (p.src_rank + 1) * blocks
-                seen[(p.row_block, p.k_piece)] = seen.get((p.row_block, p.k_piece), 0) + 1
-        assert len(seen) == (world - 1) * blocks * ksplit and set(seen.values()) == {1}
+                assert rank * blocks <= p.row_block < (rank + 1) * blocks
+                key = (p.dst_rank, p.row_block, p.k_piece)
+                received[key] = received.get(key, 0) + 1
+    # every rank ends up with every remote row block, each of its ksplit pieces exactly once
+    assert len(received) == world * (world - 1) * blocks * ksplit and set(received.values()) == {1}
+    for dst in range(world):
+        # the first shard a rank consumes after its own is rank+1's, which rank+1 pushes to it first
+        assert TP.consumption_order(world, dst)[1] == (dst + 1) % world
+        assert TP.push_order(world, (dst + 1) % world)[0] == dst
 
 
 def _free_port():
