@@ -10,7 +10,8 @@ import sys
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
-OUT = os.path.join(_HERE, "lib", "libbsgemm.so")
+PROFILE = os.environ.get("BSG_PROFILE") == "1"      # ablation switches + timeline capture, separate file
+OUT = os.path.join(_HERE, "lib", "libbsgemm_profile.so" if PROFILE else "libbsgemm.so")
 SOURCES = ["bsgemm.cu"]
 HEADERS = ["gemm_kernel.cuh", "ptx.cuh", os.path.join("..", "..", "include", "bsgemm.h")]
 NVCC_FLAGS = [
@@ -33,7 +34,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return OUT
     nvcc = os.environ.get("NVCC", "nvcc")
     os.makedirs(os.path.dirname(OUT), exist_ok=True)
-    extra = ["-DBSG_PROFILE"] if os.environ.get("BSG_PROFILE") == "1" else []   # ablation switches + timeline capture
+    extra = ["-DBSG_PROFILE"] if PROFILE else []
     cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-o", OUT] + [os.path.join(CSRC, f) for f in SOURCES]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
