@@ -11,6 +11,7 @@
 #include <cstdio>
 #include <cstring>
 #include <cstdlib>
+#include <mutex>
 #include <new>
 
 #include "../../include/bsgemm.h"
@@ -350,6 +351,37 @@ Problem from_grouped(const bsg_grouped_args* a) {
 
 }  // namespace
 
+// ---------------------------------------------------------------------------------------------
+// Scratch for bsg_gemm_run_static: the kernel's workspace (today a 16-byte status word) lives in
+// this fixed device array instead of caller-provided memory.  Every GPU that loads the library
+// holds these 256 bytes until the process exits.  In host code the name below is only a stand-in
+// for the symbol; the device address is looked up once per device with cudaGetSymbolAddress.
+constexpr size_t kStaticScratchBytes = 256;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {};
+std::mutex g_static_scratch_mutex;
+
+// Device address of g_static_scratch on the current device (resolved on first use, then cached).
+int32_t static_scratch_for_current_device(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(BSG_ERR_NOT_SUPPORTED, "device ordinal %d is outside [0, %d)", dev, kMaxDevices);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) return fail(BSG_ERR_CUDA, "cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return BSG_OK;
+}
+}  // namespace
+
 // Per-rank state of the tensor-parallel GEMM: one device allocation that holds the full-size A and
 // SFA buffers (this rank's shard in place, the others filled in by the kernel) and the sync words.
 struct bsg_tp_comm {
@@ -438,6 +470,35 @@ int32_t bsg_read_device_status(void* workspace, void* cuda_stream) {
   if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "clearing status: %s", cudaGetErrorString(e));
   if (st & bsg::kStBadOffsets) return fail(BSG_ERR_INVALID_PROBLEM, "group offsets are not monotone or exceed total_M (device status 0x%x)", st);
   return fail(BSG_ERR_TIMEOUT, "a bounded device-side wait ran out (device status 0x%x)", st);
+}
+
+int32_t bsg_gemm_run_static(const bsg_gemm_args* args, void* cuda_stream, uint32_t* device_status_out) {
+  if (!args) return fail(BSG_ERR_INVALID_PROBLEM, "args is null");
+  if (args->M < 0 || args->batch < 0) return fail(BSG_ERR_INVALID_PROBLEM, "negative extent");
+  size_t need = 0;
+  int32_t rc = bsg_gemm_workspace_size(args, &need);
+  if (rc != BSG_OK) return rc;
+  if (need > kStaticScratchBytes)
+    return fail(BSG_ERR_NOT_SUPPORTED, "this problem needs %zu bytes of scratch but the built-in scratch holds %zu; use bsg_gemm_run with a caller-provided workspace",
+                need, kStaticScratchBytes);
+  void* scratch = nullptr;
+  rc = static_scratch_for_current_device(&scratch);
+  if (rc != BSG_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  // The array still holds what the previous call left there: the status word must start at zero.
+  cudaError_t e = cudaMemsetAsync(scratch, 0, need, stream);
+  if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "clearing the static scratch: %s", cudaGetErrorString(e));
+  Problem q = from_dense(args);
+  rc = run_problem(q, scratch, kStaticScratchBytes, cuda_stream);
+  if (rc != BSG_OK) return rc;
+  if (device_status_out) {
+    uint32_t st = 0;
+    e = cudaMemcpyAsync(&st, scratch, sizeof(st), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "reading the static scratch: %s", cudaGetErrorString(e));
+    *device_status_out = st;
+  }
+  return BSG_OK;
 }
 
 int32_t bsg_tp_create(int32_t rank, int32_t world, int32_t kind, int64_t M, int64_t K, bsg_tp_comm** out, void* ipc_handle_out) {

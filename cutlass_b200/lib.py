@@ -10,7 +10,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libbsgemm.so")
+# BSG_PROFILE=1 selects the instrumented build (python -m cutlass_b200.build with the same variable set).
+LIB_PATH = os.path.join(_HERE, "lib", "libbsgemm_profile.so" if os.environ.get("BSG_PROFILE") == "1" else "libbsgemm.so")
 
 BSG_OK = 0
 STATUS_NAMES = {
@@ -75,6 +76,7 @@ SYMBOLS = {
     "bsg_grouped_run": (C.c_int32, [C.POINTER(GroupedArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "bsg_workspace_init": (C.c_int32, [C.c_void_p, C.c_size_t, C.c_void_p]),
     "bsg_read_device_status": (C.c_int32, [C.c_void_p, C.c_void_p]),
+    "bsg_gemm_run_static": (C.c_int32, [C.POINTER(GemmArgs), C.c_void_p, C.POINTER(C.c_uint32)]),
     "bsg_tp_create": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.POINTER(C.c_void_p), C.c_void_p]),
     "bsg_tp_connect": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "bsg_tp_buffers": (C.c_int32, [C.c_void_p] + [C.POINTER(C.c_void_p)] * 4),

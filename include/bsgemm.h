@@ -161,6 +161,28 @@ int32_t bsg_grouped_run(const bsg_grouped_args* args, void* workspace, size_t wo
 int32_t bsg_read_device_status(void* workspace, void* cuda_stream);
 
 /*
+ * The same dense / batched GEMM as bsg_gemm_run for callers that have no device memory to hand over
+ * as workspace and are not allowed to create any: code running under a framework that has frozen or
+ * pre-reserved all device memory (an inference server after warm-up, a plug-in whose enqueue hook
+ * may not call the allocator), or code sitting inside a region where cudaMalloc is forbidden.
+ * Nothing is allocated, by this call or by anything it calls.  The kernel's scratch (its status
+ * word) lives in a 256-byte array that is part of the library image on every GPU that loads it;
+ * a problem whose scratch need exceeds those 256 bytes is refused with BSG_ERR_NOT_SUPPORTED.
+ *
+ *  - The first call on each device looks the array's address up (one-time set-up, with that device
+ *    current).  Make that first call outside any stream capture.
+ *  - All calls on a device share the one array.  Each call clears the part it uses before its
+ *    kernel runs, so results do not depend on earlier calls; but two calls whose kernels can overlap
+ *    on the GPU (different streams) race on it -- keep calls to this entry point on one stream, or
+ *    otherwise ordered.
+ *  - device_status_out may be NULL.  If it is not, the call waits for the stream and stores the
+ *    kernel's status word there (0 = every device-side wait completed).
+ *
+ * This entry point has no counterpart in the reference; it exists for such callers only.
+ */
+int32_t bsg_gemm_run_static(const bsg_gemm_args* args, void* cuda_stream, uint32_t* device_status_out);
+
+/*
  * Tensor-parallel GEMM: D[:, local N shard] = alpha * A B_local^T + beta * C, with A (and SFA)
  * sharded by rows over `world` ranks (one process per GPU of one node) and B / D sharded over N.
  * The kernel itself gathers the other ranks' A shards over NVLink (peer-memory loads by
