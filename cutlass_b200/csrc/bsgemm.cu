@@ -114,7 +114,7 @@ struct Problem {
   int32_t tile_m_rotate;
   // tensor parallel (TP kernel variant)
   bool tp;
-  int32_t tp_world, tp_rank, tp_rows_per_shard, tp_ksplit;
+  int32_t tp_world, tp_rank, tp_rows_per_shard, tp_ksplit, tp_push_in_kernel;
   uint32_t tp_epoch;
   int64_t tp_row_bytes, tp_sfa_rowatom_bytes;
   const uint8_t* tp_peer_a[8];
@@ -167,7 +167,7 @@ int32_t validate(const Problem& q, Plan* plan) {
 
 template <int KIND, int CG, int BN, bool TP = false>
 int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_t stream, int sm_count, bool dry) {
-  using Cf = bsg::Cfg<KIND, CG, BN>;
+  using Cf = bsg::Cfg<KIND, CG, BN, TP>;
   if (dry) return BSG_OK;
   const int64_t k_bytes = KIND == bsg::kKindNvfp4 ? q.K / 2 : q.K;
   const int64_t k_atoms = ((q.K + Cf::kSfVec - 1) / Cf::kSfVec + 3) / 4;
@@ -216,7 +216,7 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   p.flag_target = q.flag_target;
   p.tile_m_rotate = q.tile_m_rotate;
   if (TP) {
-    p.tp_world = q.tp_world; p.tp_rank = q.tp_rank; p.tp_rows_per_shard = q.tp_rows_per_shard; p.tp_ksplit = q.tp_ksplit;
+    p.tp_world = q.tp_world; p.tp_rank = q.tp_rank; p.tp_rows_per_shard = q.tp_rows_per_shard; p.tp_ksplit = q.tp_ksplit; p.tp_push_in_kernel = q.tp_push_in_kernel;
     p.tp_epoch = q.tp_epoch;
     p.tp_row_bytes = q.tp_row_bytes; p.tp_sfa_rowatom_bytes = q.tp_sfa_rowatom_bytes;
     for (int i = 0; i < 8; ++i) { p.tp_peer_a[i] = q.tp_peer_a[i]; p.tp_peer_sfa[i] = q.tp_peer_sfa[i]; p.tp_peer_sync[i] = q.tp_peer_sync[i]; }
@@ -236,7 +236,7 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(unsigned(clusters * CG), 1, 1);
-  cfg.blockDim = dim3(TP ? 320 : 192, 1, 1);
+  cfg.blockDim = dim3(TP ? 224 : 192, 1, 1);
   if (q.grid_ctas_out) *q.grid_ctas_out = int32_t(clusters * CG);
   cfg.dynamicSmemBytes = Cf::kSmemBytes;
   cfg.stream = stream;
@@ -394,6 +394,10 @@ struct bsg_tp_comm {
   bool opened[8];
   bool connected;
   uint32_t epoch;
+  int32_t mode;            // BSG_TP_PUSH_KERNEL / BSG_TP_PUSH_COPY_ENGINE
+  cudaStream_t side;       // set-up work; copy-engine mode: first of the transfer streams
+  cudaStream_t lanes[4];   // copy-engine mode: parallel transfer streams (lanes[0] == side)
+  cudaEvent_t ev_start, ev_done, ev_lane[4];
 };
 
 extern "C" {
@@ -534,6 +538,16 @@ int32_t bsg_tp_create(int32_t rank, int32_t world, int32_t kind, int64_t M, int6
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
   memcpy(ipc_handle_out, &h, 64);
   c->peer_base[rank] = c->base;
+  c->mode = BSG_TP_PUSH_KERNEL;
+  e = cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_start, cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_done, cudaEventDisableTiming);
+  c->lanes[0] = c->side;
+  for (int i = 0; i < 4 && e == cudaSuccess; ++i) {
+    if (i > 0) e = cudaStreamCreateWithFlags(&c->lanes[i], cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_lane[i], cudaEventDisableTiming);
+  }
+  if (e != cudaSuccess) { cudaFree(c->base); delete c; return fail(BSG_ERR_CUDA, "tensor-parallel stream set-up: %s", cudaGetErrorString(e)); }
   c->connected = world == 1;
   *out = c;
   return BSG_OK;
@@ -551,6 +565,18 @@ int32_t bsg_tp_connect(bsg_tp_comm* c, const void* all_handles) {
     c->peer_base[q] = static_cast<uint8_t*>(ptr);
     c->opened[q] = true;
   }
+  // First use of a kernel or of a peer mapping can need work in the driver that does not overlap a running
+  // persistent GEMM: do it now, once, on the side stream (unused sync words 16..31 serve as targets).
+  uint32_t* own_sync = reinterpret_cast<uint32_t*>(c->base + c->sync_off);
+  bsg::tp_wait_peers_kernel<<<1, 32, 0, c->side>>>(own_sync, 1, 0, 0, nullptr);
+  bsg::tp_announce_kernel<<<1, 32, 0, c->side>>>(own_sync + 16, 0, 0, 0);
+  cudaError_t e = cudaGetLastError();
+  for (int q = 0; q < c->world && e == cudaSuccess; ++q) {
+    if (q == c->rank) continue;
+    e = cudaMemcpyAsync(c->peer_base[q] + c->sync_off + size_t(16 + c->rank) * 4, own_sync + 31, 4, cudaMemcpyDeviceToDevice, c->side);
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(c->side);
+  if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "tensor-parallel warm-up: %s", cudaGetErrorString(e));
   c->connected = true;
   return BSG_OK;
 }
@@ -579,8 +605,8 @@ int32_t bsg_tp_gemm_run(bsg_tp_comm* c, const bsg_gemm_args* args, void* workspa
   Problem q = from_dense(&local);
   q.tp = true;
   q.tp_world = c->world; q.tp_rank = c->rank; q.tp_rows_per_shard = int32_t(c->rows_per_shard);
-  int ks = 8;
-  while (ks > 1 && (c->row_bytes % (16 * ks) != 0 || c->k_atoms % ks != 0)) ks >>= 1;
+  int ks = 32;   // pieces per 256-row block: A by rows (256 / ks each), SFA by k-atoms
+  while (ks > 1 && c->k_atoms % ks != 0) ks >>= 1;
   q.tp_ksplit = ks;
   q.tp_row_bytes = c->row_bytes; q.tp_sfa_rowatom_bytes = c->sfa_rowatom_bytes;
   for (int i = 0; i < c->world; ++i) {
@@ -598,9 +624,60 @@ int32_t bsg_tp_gemm_run(bsg_tp_comm* c, const bsg_gemm_args* args, void* workspa
   q.rows_per_flag = 256;
   q.tp_epoch = c->epoch + 1;
   q.flag_target = q.tp_epoch * uint32_t(ks);
+  q.tp_push_in_kernel = c->mode == BSG_TP_PUSH_KERNEL ? 1 : 0;
+  const bool copy_engine = c->world > 1 && c->mode == BSG_TP_PUSH_COPY_ENGINE;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (copy_engine) {
+    if (!workspace || workspace_bytes < 16) return fail(BSG_ERR_WORKSPACE_NULL, "workspace is null or smaller than 16 bytes");
+    // Side stream: once everything enqueued so far on the caller's stream is done (the shard is final)
+    // and every peer has launched this call, push the shard to the peers, nearest consumer first, one
+    // band of row blocks per transfer, each followed by its announcement.
+    cudaError_t e = cudaEventRecord(c->ev_start, stream);
+    if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "tensor-parallel stream fork: %s", cudaGetErrorString(e));
+  }
   int32_t rc = run_problem(q, workspace, workspace_bytes, cuda_stream);
   if (rc != BSG_OK) return rc;
+  if (copy_engine) {
+    // A band of row blocks can be cut into slices that travel on parallel streams; measured on two GPUs,
+    // four streams made the host-side enqueue the bottleneck (12 operations per band), so one is used.
+    uint32_t* own_sync = q.tp_peer_sync[c->rank];
+    const int n_lanes = 1;
+    const int32_t slice = band / n_lanes;                     // row blocks per transfer
+    const int64_t first_block = int64_t(c->rank) * blocks;
+    cudaError_t e = cudaSuccess;
+    for (int l = 0; l < n_lanes && e == cudaSuccess; ++l) {
+      cudaStream_t ls = c->lanes[l];
+      e = cudaStreamWaitEvent(ls, c->ev_start, 0);
+      if (e != cudaSuccess) break;
+      bsg::tp_wait_peers_kernel<<<1, 32, 0, ls>>>(own_sync, c->world, c->rank, q.tp_epoch, static_cast<uint32_t*>(workspace));
+      for (int j = 1; j < c->world && e == cudaSuccess; ++j) {
+        const int dst = (c->rank - j + c->world) % c->world;
+        for (int32_t b0 = l * slice; b0 < blocks && e == cudaSuccess; b0 += band) {
+          const size_t a_off = c->a_off + size_t(first_block + b0) * 256 * size_t(c->row_bytes);
+          const size_t a_bytes = size_t(slice) * 256 * size_t(c->row_bytes);
+          const size_t s_off = c->sfa_off + size_t(first_block + b0) * 2 * size_t(c->sfa_rowatom_bytes);
+          const size_t s_bytes = size_t(slice) * 2 * size_t(c->sfa_rowatom_bytes);
+          e = cudaMemcpyAsync(c->peer_base[dst] + a_off, c->base + a_off, a_bytes, cudaMemcpyDeviceToDevice, ls);
+          if (e == cudaSuccess) e = cudaMemcpyAsync(c->peer_base[dst] + s_off, c->base + s_off, s_bytes, cudaMemcpyDeviceToDevice, ls);
+          if (e != cudaSuccess) break;
+          bsg::tp_announce_kernel<<<1, 32, 0, ls>>>(q.tp_peer_sync[dst] + bsg::kTpSyncFlags, int(first_block + b0), slice, uint32_t(ks));
+        }
+      }
+      // The call is complete on the caller's stream only when the transfers are: the shard may then be rewritten.
+      if (e == cudaSuccess) e = cudaGetLastError();
+      if (e == cudaSuccess) e = cudaEventRecord(c->ev_lane[l], ls);
+      if (e == cudaSuccess) e = cudaStreamWaitEvent(stream, c->ev_lane[l], 0);
+    }
+    if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "tensor-parallel peer transfers: %s", cudaGetErrorString(e));
+  }
   c->epoch += 1;
+  return BSG_OK;
+}
+
+int32_t bsg_tp_set_mode(bsg_tp_comm* c, int32_t mode) {
+  if (!c) return fail(BSG_ERR_INVALID_PROBLEM, "null communicator");
+  if (mode != BSG_TP_PUSH_KERNEL && mode != BSG_TP_PUSH_COPY_ENGINE) return fail(BSG_ERR_NOT_SUPPORTED, "unknown tensor-parallel mode %d", mode);
+  c->mode = mode;
   return BSG_OK;
 }
 
@@ -610,6 +687,11 @@ int32_t bsg_tp_destroy(bsg_tp_comm* c) {
   for (int q = 0; q < c->world; ++q) {
     if (c->opened[q]) cudaIpcCloseMemHandle(c->peer_base[q]);
   }
+  for (int i = 1; i < 4; ++i) if (c->lanes[i]) cudaStreamDestroy(c->lanes[i]);
+  for (int i = 0; i < 4; ++i) if (c->ev_lane[i]) cudaEventDestroy(c->ev_lane[i]);
+  if (c->side) cudaStreamDestroy(c->side);
+  if (c->ev_start) cudaEventDestroy(c->ev_start);
+  if (c->ev_done) cudaEventDestroy(c->ev_done);
   if (c->base) cudaFree(c->base);
   delete c;
   return BSG_OK;

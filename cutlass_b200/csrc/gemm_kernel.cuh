@@ -80,7 +80,8 @@ struct GemmParams {
   // row shard of A and SFA into every peer's full-size buffers.
   int32_t tp_world, tp_rank;
   int32_t tp_rows_per_shard;  // multiple of 256
-  int32_t tp_ksplit;          // pieces a 256-row block is cut into along K (one flag increment each)
+  int32_t tp_ksplit;          // pieces a 256-row block is cut into (one flag increment each)
+  int32_t tp_push_in_kernel;  // 1: the push warp moves the data; 0: the host's copy-engine transfers do
   uint32_t tp_epoch;          // call counter, starts at 1; the peers use the same value
   int64_t tp_row_bytes;       // bytes of one row of A
   int64_t tp_sfa_rowatom_bytes;   // bytes of one 128-row atom row of SFA (512 * k_atoms)
@@ -99,7 +100,7 @@ constexpr uint32_t kStTimeoutPeer = 64u;      // tensor parallel: a peer never p
 #define BSG_FLAG(p, bit) false
 #endif
 
-template <int KIND, int CG, int BN>
+template <int KIND, int CG, int BN, bool TP = false>
 struct Cfg {
   static_assert(KIND == kKindNvfp4 || KIND == kKindMxfp8, "kind");
   static_assert(CG == 1 || CG == 2, "cta group");
@@ -120,9 +121,13 @@ struct Cfg {
   static constexpr int kCtlBytes = 8192;
   static constexpr int kEpiBytes = 4 * 4096;              // per epilogue warp: 32 rows x 128 bytes of bf16 output
   static constexpr int kSmemLimit = 232448;               // 227 KB
-  static constexpr int kStagesRaw = (kSmemLimit - kCtlBytes - kEpiBytes - 1024) / kStageBytes;
+  static constexpr int kTpChunk = 8192;                   // tensor parallel: bytes per bulk copy of the A push
+  static constexpr int kTpBufs = 4;                       // chunks in flight
+  static constexpr int kTpLag = 3;                        // a piece is announced this many chunks after its last store
+  static constexpr int kTpBytes = TP ? kTpBufs * kTpChunk : 0;
+  static constexpr int kStagesRaw = (kSmemLimit - kCtlBytes - kEpiBytes - kTpBytes - 1024) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kCtlBytes + 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kTpBytes + kCtlBytes + 1024;
   // TMEM columns: two accumulators (overlapping by 48 columns when BN == 256), then SFA, then SFB.
   static constexpr int kAccStride = BN == 256 ? 208 : 128;
   static constexpr int kAccBars = BN == 256 ? 1 : 2;
@@ -137,6 +142,7 @@ struct alignas(8) Ctl {
   uint64_t empty[8];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t tp_full[4];      // tensor parallel: staging buffer filled
   uint32_t tmem_base;
   volatile uint32_t abort;
   int32_t total_tiles;
@@ -242,6 +248,10 @@ __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 // Bounded spin until *flag >= target (system-scope acquire).  Returns false on timeout.
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t target, Ctl* ctl) {
   if (ptx::ld_acquire_sys_u32(flag) >= target) return true;
@@ -253,35 +263,106 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t targ
   return true;
 }
 
-// Copy n16 16-byte units from src to dst with the 128 copy threads of the CTA (tid in [0,128)).
-__device__ __forceinline__ void tp_copy16(uint8_t* dst, const uint8_t* src, int n16, int tid) {
-  for (int base = 0; base < n16; base += 128 * 8) {
-    uint4 v[8];
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int i = base + u * 128 + tid;
-      if (i < n16) v[u] = ld_global_v4(src + int64_t(i) * 16);
+// Walks the chunks that one CTA pushes in a tensor-parallel call: pieces c = cta, cta + grid, ...
+// (a piece = 256 / ksplit rows of one 256-row block of this rank's shard for one destination rank;
+// the first piece of a block also carries the block's two SFA row atoms); every piece is one or
+// three contiguous spans, every span is cut into chunks of at most `chunk_bytes`.
+struct TpChunkIter {
+  int c, grid, total, per_shard, span, last_span, chunk_bytes;
+  int dst_rank, row_block;
+  int64_t span_off, span_bytes, done;
+  uint32_t bytes;
+  bool last_of_piece;
+  __device__ __forceinline__ bool valid() const { return c < total; }
+  __device__ __forceinline__ void load_piece(const GemmParams& p) {
+    if (c >= total) return;
+    const int j = c / per_shard + 1;
+    dst_rank = (p.tp_rank - j + p.tp_world) % p.tp_world;     // rank-1 consumes this shard first
+    span = 0;
+    load_span(p);
+  }
+  __device__ __forceinline__ void load_span(const GemmParams& p) {
+    const int j = c / per_shard + 1;
+    const int rem = c - (j - 1) * per_shard;
+    const int rb = rem / p.tp_ksplit, ks = rem - rb * p.tp_ksplit;
+    const int64_t row0 = int64_t(p.tp_rank) * p.tp_rows_per_shard + int64_t(rb) * 256;
+    row_block = int(row0 / 256);
+    last_span = ks == 0 ? 2 : 0;     // the first piece of a row block also carries the block's scale factors
+    if (span == 0) {
+      const int rows = 256 / p.tp_ksplit;
+      span_off = (row0 + int64_t(ks) * rows) * p.tp_row_bytes;
+      span_bytes = int64_t(rows) * p.tp_row_bytes;
+    } else {
+      span_bytes = p.tp_sfa_rowatom_bytes;
+      span_off = (row0 / 128 + (span - 1)) * p.tp_sfa_rowatom_bytes;
     }
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int i = base + u * 128 + tid;
-      if (i < n16) *reinterpret_cast<uint4*>(dst + int64_t(i) * 16) = v[u];
+    done = 0;
+    set_chunk();
+  }
+  __device__ __forceinline__ void set_chunk() {
+    const int64_t left = span_bytes - done;
+    bytes = uint32_t(left < chunk_bytes ? left : chunk_bytes);
+    last_of_piece = (span == last_span) && (done + bytes >= span_bytes);
+  }
+  __device__ __forceinline__ void init(const GemmParams& p, int cta, int grid_, int chunk_bytes_) {
+    grid = grid_;
+    chunk_bytes = chunk_bytes_;
+    per_shard = (p.tp_rows_per_shard / 256) * p.tp_ksplit;
+    total = (p.tp_world - 1) * per_shard;
+    c = cta;
+    load_piece(p);
+  }
+  __device__ __forceinline__ void next(const GemmParams& p) {
+    done += bytes;
+    if (done < span_bytes) { set_chunk(); return; }
+    if (span < last_span) { ++span; load_span(p); return; }
+    c += grid;
+    load_piece(p);
+  }
+  __device__ __forceinline__ const uint8_t* src(const GemmParams& p) const {
+    return (span == 0 ? p.tp_peer_a[p.tp_rank] : p.tp_peer_sfa[p.tp_rank]) + span_off + done;
+  }
+  __device__ __forceinline__ uint8_t* dst(const GemmParams& p) const {
+    return const_cast<uint8_t*>(span == 0 ? p.tp_peer_a[dst_rank] : p.tp_peer_sfa[dst_rank]) + span_off + done;
+  }
+};
+
+// Side-stream helpers of the copy-engine mode of the tensor-parallel GEMM.
+// Waits (bounded) until every peer has launched call `epoch`, i.e. its gathered buffer may be overwritten.
+__global__ void tp_wait_peers_kernel(const uint32_t* sync, int world, int rank, uint32_t epoch, uint32_t* status) {
+  if (threadIdx.x != 0) return;
+  const long long t0 = clock64();
+  for (int q = 0; q < world; ++q) {
+    if (q == rank) continue;
+    while (ptx::ld_acquire_sys_u32(sync + kTpSyncReady + q) < epoch) {
+      if (clock64() - t0 > 4000000000ll) { atomicOr(status, kStTimeoutPeer); return; }
+      __nanosleep(200);
     }
+  }
+}
+// Announces `blocks` row blocks (starting at `first`) as arrived in a peer's buffer: stream order puts
+// this after the copy-engine transfers that filled them.
+__global__ void tp_announce_kernel(uint32_t* peer_flags, int first, int blocks, uint32_t add) {
+  const int i = threadIdx.x;
+  if (i < blocks) {
+    __threadfence_system();
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(peer_flags + first + i), "r"(add) : "memory");
   }
 }
 
 template <int KIND, int CG, int BN, bool TP = false>
-__global__ void __launch_bounds__(TP ? 320 : 192, 1)
+__global__ void __launch_bounds__(TP ? 224 : 192, 1)
 bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
                 const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
-  using C = Cfg<KIND, CG, BN>;
+  using C = Cfg<KIND, CG, BN, TP>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = sA + C::kStages * C::kABytes;
   uint8_t* sEpi = sB + C::kStages * C::kBBytes;                 // 1024-byte aligned (swizzled TMA-store source)
-  uint8_t* sSFA = sEpi + C::kEpiBytes;
+  uint8_t* sTp = sEpi + C::kEpiBytes;                           // tensor parallel: push staging (128-byte aligned)
+  uint8_t* sSFA = sTp + C::kTpBytes;
   uint8_t* sSFB = sSFA + C::kStages * C::kSfaBytes;
   Ctl* ctl = reinterpret_cast<Ctl*>(sSFB + C::kStages * C::kSfbBytes);
 
@@ -302,6 +383,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       ptx::mbar_init(ptx::smem_u32(&ctl->tmem_full[s]), 1);
       ptx::mbar_init(ptx::smem_u32(&ctl->tmem_empty[s]), 4 * CG);
     }
+    for (int s = 0; s < 4; ++s) ptx::mbar_init(ptx::smem_u32(&ctl->tp_full[s]), 1);
     ctl->abort = 0;
     ptx::fence_mbar_init();
     ptx::fence_proxy_async();
@@ -501,73 +583,80 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
       if (dead) atomicOr(p.status, kStTimeoutFull | kStTimeoutTmemEmpty);
     }
-  } else if (TP && warp >= 6) {
-    // ---------------------------------------------------------------- all-gather copy warps (6-9)
-    // Push: this rank's own rows of A / SFA are read locally and written into every peer's full-size
-    // buffer (posted stores over NVLink), nearest consumer first; each finished piece bumps the
-    // row-block flag in the peer's memory that the peer's TMA producer waits on.
+  } else if (TP && warp == 6) {
+    // ---------------------------------------------------------------- all-gather push warp (6)
+    // This rank's own rows of A / SFA go into every peer's full-size buffer, nearest consumer first.
+    // The data moves through the bulk-copy engine (global -> shared -> peer global) in chunks, with
+    // kTpBufs chunks in flight; one elected lane issues everything.  Each finished piece bumps the
+    // row-block counter in the peer's memory that the peer's TMA producer waits on.
     if (p.tp_world > 1 && !BSG_FLAG(p, 2048)) {
-      const int tid = int(threadIdx.x) - 192;
+      const uint32_t elected = ptx::elect_one_sync();
       uint32_t* sync = p.tp_peer_sync[p.tp_rank];
-      const uint8_t* a_own = p.tp_peer_a[p.tp_rank];
-      const uint8_t* sfa_own = p.tp_peer_sfa[p.tp_rank];
+      const uint32_t buf0 = ptx::smem_u32(sTp);
+      const uint32_t bar0 = ptx::smem_u32(&ctl->tp_full[0]);
       bool peer_ok = true;
       // Launching this call means the previous one has finished reading this rank's gathered buffer:
       // tell every peer that it may now be overwritten with the data of this call.
-      if (blockIdx.x == 0 && tid == 0) {
+      if (blockIdx.x == 0 && elected) {
         __threadfence_system();
         for (int q = 0; q < p.tp_world; ++q) {
           if (q != p.tp_rank) st_release_sys_u32(p.tp_peer_sync[q] + kTpSyncReady + p.tp_rank, p.tp_epoch);
         }
       }
-      const int blocks_per_shard = p.tp_rows_per_shard / 256;
-      const int per_shard = blocks_per_shard * p.tp_ksplit;
-      const int total = (p.tp_world - 1) * per_shard;
-      const int row_piece16 = int(p.tp_row_bytes / p.tp_ksplit / 16);          // 16-byte units per row per piece
-      const int sfa_piece16 = int(p.tp_sfa_rowatom_bytes / p.tp_ksplit / 16);  // per 128-row atom per piece
-      int checked = -1;
-      for (int c = blockIdx.x; c < total; c += gridDim.x) {
-        const int j = c / per_shard + 1;
-        const int rem = c - (j - 1) * per_shard;
-        const int rb = rem / p.tp_ksplit, ks = rem - rb * p.tp_ksplit;
-        const int dst_rank = (p.tp_rank - j + p.tp_world) % p.tp_world;   // rank-1 consumes this shard first
-        if (dst_rank != checked) {
-          if (!wait_flag_ge(sync + kTpSyncReady + dst_rank, p.tp_epoch, ctl)) peer_ok = false;
-          checked = dst_rank;
+      TpChunkIter ld_it, st_it;                 // the load iterator runs kTpBufs chunks ahead of the store iterator
+      if (p.tp_push_in_kernel) {
+      ld_it.init(p, int(blockIdx.x), int(gridDim.x), C::kTpChunk);
+      st_it.init(p, int(blockIdx.x), int(gridDim.x), C::kTpChunk);
+      uint32_t n_ld = 0, n_st = 0;
+      for (; n_ld < uint32_t(C::kTpBufs) && ld_it.valid(); ++n_ld, ld_it.next(p)) {
+        if (elected) {
+          ptx::mbar_arrive_expect_tx(bar0 + n_ld * 8, ld_it.bytes);
+          ptx::bulk_load(buf0 + n_ld * C::kTpChunk, ld_it.src(p), ld_it.bytes, bar0 + n_ld * 8);
         }
-        const int64_t row0 = int64_t(p.tp_rank) * p.tp_rows_per_shard + int64_t(rb) * 256;
-        uint8_t* dst_a = const_cast<uint8_t*>(p.tp_peer_a[dst_rank]);
-        uint8_t* dst_sfa = const_cast<uint8_t*>(p.tp_peer_sfa[dst_rank]);
-        if (peer_ok) {
-          // A: 256 rows x (row_bytes / ksplit) bytes, 8 independent 16-byte loads in flight per thread
-          const int n16 = 256 * row_piece16;
-          for (int base = 0; base < n16; base += 128 * 8) {
-            uint4 v[8];
-            int64_t off[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-              const int i = base + u * 128 + tid;
-              const int rr = i / row_piece16, cc = i - rr * row_piece16;
-              off[u] = (row0 + rr) * p.tp_row_bytes + (int64_t(ks) * row_piece16 + cc) * 16;
-              if (i < n16) v[u] = ld_global_v4(a_own + off[u]);
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-              const int i = base + u * 128 + tid;
-              if (i < n16) *reinterpret_cast<uint4*>(dst_a + off[u]) = v[u];
-            }
-          }
-          // SFA: two 128-row atoms, a contiguous run of k-atoms each
-          for (int ra = 0; ra < 2; ++ra) {
-            const int64_t o = (row0 / 128 + ra) * p.tp_sfa_rowatom_bytes + int64_t(ks) * sfa_piece16 * 16;
-            tp_copy16(dst_sfa + o, sfa_own + o, sfa_piece16, tid);
-          }
-          __threadfence_system();
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (tid == 0 && peer_ok) atomicAdd_system(p.tp_peer_sync[dst_rank] + kTpSyncFlags + int(row0 / 256), 1u);
       }
-      if (!peer_ok) atomicOr(p.status, kStTimeoutPeer);
+      int checked = -1;
+      // A finished piece is announced a few chunks later, once its stores are known to be complete,
+      // so that the copy pipeline never drains: pend_* hold the piece waiting for its announcement.
+      int pend_rank = -1, pend_block = 0;
+      uint32_t pend_at = 0;                      // announce once this many chunks have been committed
+      for (; st_it.valid(); st_it.next(p), ++n_st) {
+        const uint32_t b = n_st % C::kTpBufs;
+        if (st_it.dst_rank != checked) {
+          if (!wait_flag_ge(sync + kTpSyncReady + st_it.dst_rank, p.tp_epoch, ctl)) peer_ok = false;
+          checked = st_it.dst_rank;
+        }
+        wait_barrier(bar0 + b * 8, (n_st / C::kTpBufs) & 1u, ctl, dead);
+        if (elected) {
+          if (pend_rank >= 0 && (n_st >= pend_at || st_it.last_of_piece)) {
+            if (n_st >= pend_at) ptx::bulk_wait_group<C::kTpLag>(); else ptx::bulk_wait_group<0>();
+            asm volatile("fence.proxy.async;" ::: "memory");
+            red_release_sys_add(p.tp_peer_sync[pend_rank] + kTpSyncFlags + pend_block, 1u);
+            pend_rank = -1;
+          }
+          if (peer_ok) ptx::bulk_store(st_it.dst(p), buf0 + b * C::kTpChunk, st_it.bytes);
+          ptx::bulk_commit_group();
+          if (st_it.last_of_piece && peer_ok) {
+            pend_rank = st_it.dst_rank;
+            pend_block = st_it.row_block;
+            pend_at = n_st + 1 + C::kTpLag;       // by then at most kTpLag newer groups are outstanding
+          }
+          if (ld_it.valid()) {
+            ptx::bulk_wait_group_read<0>();           // the store just issued has read this buffer
+            ptx::mbar_arrive_expect_tx(bar0 + b * 8, ld_it.bytes);
+            ptx::bulk_load(buf0 + b * C::kTpChunk, ld_it.src(p), ld_it.bytes, bar0 + b * 8);
+          }
+        }
+        if (ld_it.valid()) ld_it.next(p);
+        __syncwarp();
+      }
+      if (elected && pend_rank >= 0) {
+        ptx::bulk_wait_group<0>();
+        asm volatile("fence.proxy.async;" ::: "memory");
+        red_release_sys_add(p.tp_peer_sync[pend_rank] + kTpSyncFlags + pend_block, 1u);
+      }
+      if (elected) ptx::bulk_wait_group<0>();
+      }
+      if (!peer_ok || dead) atomicOr(p.status, kStTimeoutPeer);
     }
   } else if (warp < 4) {
     // ---------------------------------------------------------------- epilogue (warps 0-3)

@@ -81,6 +81,7 @@ SYMBOLS = {
     "bsg_tp_connect": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "bsg_tp_buffers": (C.c_int32, [C.c_void_p] + [C.POINTER(C.c_void_p)] * 4),
     "bsg_tp_gemm_run": (C.c_int32, [C.c_void_p, C.POINTER(GemmArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "bsg_tp_set_mode": (C.c_int32, [C.c_void_p, C.c_int32]),
     "bsg_tp_destroy": (C.c_int32, [C.c_void_p]),
 }
 

@@ -38,10 +38,11 @@ def shard_cols(N: int, world: int, rank: int) -> tuple[int, int]:
     return rank * ns, (rank + 1) * ns
 
 
-def choose_ksplit(row_bytes: int, k_atoms: int) -> int:
-    """Pieces a 256-row block is cut into along K (each piece is one flag increment)."""
-    ks = 8
-    while ks > 1 and (row_bytes % (16 * ks) != 0 or k_atoms % ks != 0):
+def choose_ksplit(k_atoms: int) -> int:
+    """Pieces a 256-row block is cut into (each piece is one flag increment): A by rows
+    (256 / ksplit each), SFA by k-atoms (k_atoms / ksplit each)."""
+    ks = 32
+    while ks > 1 and k_atoms % ks != 0:
         ks //= 2
     return ks
 
@@ -99,7 +100,8 @@ class TpGemm:
     ``a_shard`` / ``sfa_shard`` are uint8 views of where this rank's rows of A and their
     interleaved scale factors live; fill them, then call ``run`` on every rank."""
 
-    def __init__(self, kind: int, M: int, K: int, group=None):
+    def __init__(self, kind: int, M: int, K: int, group=None, mode: str | None = None):
+        import os
         import torch
         import torch.distributed as dist
         from . import lib as L
@@ -119,6 +121,10 @@ class TpGemm:
             blob = (C.c_uint8 * (64 * self.world)).from_buffer_copy(b"".join(handles))
             L.check(self._lib.bsg_tp_connect(self._comm, blob))
             dist.barrier(group)
+        mode = mode or os.environ.get("BSG_TP_MODE")          # "kernel" | "copy_engine" | None (library default)
+        if mode is not None:
+            L.check(self._lib.bsg_tp_set_mode(self._comm, {"kernel": 0, "copy_engine": 1}[mode]))
+        self.mode = mode or "kernel"
         ptrs = [C.c_void_p() for _ in range(4)]
         L.check(self._lib.bsg_tp_buffers(self._comm, *[C.byref(p) for p in ptrs]))
         row_bytes = K // 2 if kind == L.KIND_NVFP4 else K

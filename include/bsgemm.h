@@ -198,9 +198,17 @@ int32_t bsg_gemm_run_static(const bsg_gemm_args* args, void* cuda_stream, uint32
  * bsg_tp_buffers  returns where this rank writes its own A / SFA shard (inside the full buffers).
  * bsg_tp_gemm_run enqueues one GEMM; args->A / SFA are ignored, args->M is the full M, args->N
  *                 the local N shard.  All ranks must call it the same number of times with the
- *                 same shapes.  A rank's call completes only after every peer has read its shard.
+ *                 same shapes.
+ * bsg_tp_set_mode  chooses who moves the shard: BSG_TP_PUSH_KERNEL -- a warp of the GEMM kernel itself, through
+ *                 the SM's bulk-copy engine (one launch per GEMM); or
+ *                 BSG_TP_PUSH_COPY_ENGINE -- the GPU's copy engines on an internal side stream, one transfer per
+ *                 band of row blocks followed by its announcement, joined back into the caller's stream
+ *                 (the scheme of dist_gemm_universal_wrapper.hpp:578-593).  Default: kernel.  On 8 B200s both
+ *                 deliver about 270 GB/s per GPU while the GEMM runs.  All ranks must use the same mode.
  */
+enum { BSG_TP_PUSH_KERNEL = 0, BSG_TP_PUSH_COPY_ENGINE = 1 };
 typedef struct bsg_tp_comm bsg_tp_comm;
+int32_t bsg_tp_set_mode(bsg_tp_comm* comm, int32_t mode);
 int32_t bsg_tp_create(int32_t rank, int32_t world, int32_t kind, int64_t M, int64_t K, bsg_tp_comm** out,
                       void* ipc_handle_out);
 int32_t bsg_tp_connect(bsg_tp_comm* comm, const void* all_handles);

@@ -24,15 +24,15 @@ def test_shard_ranges_cover_the_problem():
 
 
 def test_ksplit_choice():
-    assert TP.choose_ksplit(8192, 64) == 8        # MXFP8 K=8192
-    assert TP.choose_ksplit(4096, 128) == 8       # NVFP4 K=8192
-    assert TP.choose_ksplit(48, 1) == 1
-    assert TP.choose_ksplit(256, 2) == 2
+    assert TP.choose_ksplit(64) == 32         # MXFP8 K=8192
+    assert TP.choose_ksplit(128) == 32        # NVFP4 K=8192
+    assert TP.choose_ksplit(1) == 1
+    assert TP.choose_ksplit(6) == 2
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_push_schedule_delivers_every_piece_once_and_nearest_consumer_first(world):
-    M, ksplit, grid = 16384, 8, 148
+    M, ksplit, grid = 16384, 32, 148
     blocks = M // world // TP.ROW_BLOCK
     received = {}                                   # (dst, row_block, k_piece) -> count, over all ranks
     for rank in range(world):
