@@ -37,6 +37,8 @@ NOMINAL_FP4_TFLOPS = 9000.0
 NOMINAL_FP8_TFLOPS = 4500.0
 # Algorithmic DRAM bytes of one NVFP4 8192^3 launch: A + B (33.5 MB each), SFA + SFB (4.2 MB each), D bf16 (134 MB).
 L2_BYTES = 126 * 1024 * 1024
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the N=1 workload (ncu capture; 167.5 MB + 105.1 MB)
+NCU_TRAFFIC_BYTES = 272_558_848
 
 
 def measured_peaks() -> dict:
@@ -192,6 +194,16 @@ def run_single(args) -> dict:
     flops = 2.0 * M * N * K
     tflops = flops / ms / 1e9
 
+    # ---- the same launches as a short burst after an idle second (before the power cap pulls the clock down)
+    time.sleep(1.0)
+    n_burst = 20
+    e0.record(stream)
+    for i in range(n_burst):
+        launch(i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    burst_ms = e0.elapsed_time(e1) / n_burst
+
     # ---- end to end through the operator API with host buffers
     hA = [t.cpu().pin_memory() for t in (sets[0].A.quantized.tensor, sets[0].A.scale.tensor)]
     hB = [t.cpu().pin_memory() for t in (sets[0].B.quantized.tensor.t().contiguous(), sets[0].B.scale.tensor)]
@@ -278,7 +290,10 @@ def run_single(args) -> dict:
                      "peak_source": ("4 x bf16_tflops of MEASURED_PEAKS.json (burst; no fp4 figure is measured)" if bf16_burst
                                      else "4 x fallback bf16 1590"),
                      "frac_of_nominal_9000": round(tflops / NOMINAL_FP4_TFLOPS, 4),
-                     "traffic": None},
+                     "burst": {"value": round(flops / burst_ms / 1e9, 1), "steps": n_burst, "ms_per_step": round(burst_ms, 5),
+                               "frac": round(flops / burst_ms / 1e9 / peak, 4)},
+                     "traffic": NCU_TRAFFIC_BYTES, "traffic_source": "ncu --set full capture of this workload, dram read + write per launch",
+                     "algorithmic_bytes": bytes_per_set},
         "cpu_baseline": {k: (round(v, 5) if isinstance(v, float) else v) for k, v in cpu.items()},
         "parity": {"slab_rows": slab, "max_rel_err_vs_cpu_reference": rel},
         "scaling_base": tp_base,

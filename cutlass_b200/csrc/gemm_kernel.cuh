@@ -122,8 +122,10 @@ struct Cfg {
   static constexpr int kEpiBytes = 4 * 4096;              // per epilogue warp: 32 rows x 128 bytes of bf16 output
   static constexpr int kSmemLimit = 232448;               // 227 KB
   static constexpr int kTpChunk = 8192;                   // tensor parallel: bytes per bulk copy of the A push
-  static constexpr int kTpBufs = 4;                       // chunks in flight
-  static constexpr int kTpLag = 3;                        // a piece is announced this many chunks after its last store
+  static constexpr int kTpBufs = 4;                       // staging buffers (ring)
+  static constexpr int kTpReadLag = 2;                    // stores whose shared-memory read may still be pending
+  static constexpr int kTpLag = 6;                        // a piece is announced this many chunks after its last store
+  static constexpr int kTpPend = 4;                       // pieces that may wait for their announcement
   static constexpr int kTpBytes = TP ? kTpBufs * kTpChunk : 0;
   static constexpr int kStagesRaw = (kSmemLimit - kCtlBytes - kEpiBytes - kTpBytes - 1024) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
@@ -142,7 +144,7 @@ struct alignas(8) Ctl {
   uint64_t empty[8];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
-  uint64_t tp_full[4];      // tensor parallel: staging buffer filled
+  uint64_t tp_full[8];      // tensor parallel: staging buffer filled
   uint32_t tmem_base;
   volatile uint32_t abort;
   int32_t total_tiles;
@@ -248,9 +250,13 @@ __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
-  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+#ifdef BSG_PROFILE
+__device__ __forceinline__ unsigned long long gtimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
 }
+#endif
 
 // Bounded spin until *flag >= target (system-scope acquire).  Returns false on timeout.
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t target, Ctl* ctl) {
@@ -284,7 +290,9 @@ struct TpChunkIter {
   __device__ __forceinline__ void load_span(const GemmParams& p) {
     const int j = c / per_shard + 1;
     const int rem = c - (j - 1) * per_shard;
-    const int rb = rem / p.tp_ksplit, ks = rem - rb * p.tp_ksplit;
+    // The piece that also carries the scale factors (ks == 0) sits at a different place in every row
+    // block, so that those larger pieces spread over the CTAs whatever the grid size.
+    const int rb = rem / p.tp_ksplit, ks = (rem + rb) % p.tp_ksplit;
     const int64_t row0 = int64_t(p.tp_rank) * p.tp_rows_per_shard + int64_t(rb) * 256;
     row_block = int(row0 / 256);
     last_span = ks == 0 ? 2 : 0;     // the first piece of a row block also carries the block's scale factors
@@ -326,6 +334,15 @@ struct TpChunkIter {
     return const_cast<uint8_t*>(span == 0 ? p.tp_peer_a[dst_rank] : p.tp_peer_sfa[dst_rank]) + span_off + done;
   }
 };
+
+// Waits until all but the newest `n` bulk stores of this thread have read their shared-memory source.
+__device__ __forceinline__ void tp_wait_read(uint32_t n) {
+  if (n == 0u) ptx::bulk_wait_group_read<0>();
+  else if (n == 1u) ptx::bulk_wait_group_read<1>();
+  else if (n == 2u) ptx::bulk_wait_group_read<2>();
+  else if (n == 4u) ptx::bulk_wait_group_read<4>();
+  else ptx::bulk_wait_group_read<6>();
+}
 
 // Side-stream helpers of the copy-engine mode of the tensor-parallel GEMM.
 // Waits (bounded) until every peer has launched call `epoch`, i.e. its gathered buffer may be overwritten.
@@ -383,7 +400,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       ptx::mbar_init(ptx::smem_u32(&ctl->tmem_full[s]), 1);
       ptx::mbar_init(ptx::smem_u32(&ctl->tmem_empty[s]), 4 * CG);
     }
-    for (int s = 0; s < 4; ++s) ptx::mbar_init(ptx::smem_u32(&ctl->tp_full[s]), 1);
+    for (int s = 0; s < 8; ++s) ptx::mbar_init(ptx::smem_u32(&ctl->tp_full[s]), 1);
     ctl->abort = 0;
     ptx::fence_mbar_init();
     ptx::fence_proxy_async();
@@ -432,6 +449,8 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const int32_t k_tiles = (p.K + C::kTileK - 1) / C::kTileK;
   uint32_t dead = 0;
 #ifdef BSG_PROFILE
+  const bool tp_trace = BSG_FLAG(p, 16384) && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1);
+  const unsigned long long trace_t0 = gtimer();
   // Timeline capture: the workspace holds, after its first 1024 bytes, 3 regions of 4096 events
   // (producer, MMA, epilogue) of (code << 48 | SM clock), written by the first cluster only.
   unsigned long long* dbg = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(p.status) + 1024);
@@ -462,6 +481,9 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const int32_t sfb_atom = bcast(ti.g * p.sfb_atoms_per_group + ti.tn * (BN / 128));
       if (p.ready_flags != nullptr && (!TP || ti.row0 / p.tp_rows_per_shard != p.tp_rank) && !BSG_FLAG(p, 1024)) {
         const uint32_t* flag = p.ready_flags + ti.row0 / p.rows_per_flag;
+#ifdef BSG_PROFILE
+        const unsigned long long tw0 = gtimer();
+#endif
         const long long t0 = clock64();
         while (ptx::ld_acquire_sys_u32(flag) < p.flag_target) {
           if (dead || ctl->abort || clock64() - t0 > 4000000000ll) {
@@ -474,11 +496,19 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         asm volatile("fence.proxy.async;" ::: "memory");
         __syncwarp();
+#ifdef BSG_PROFILE
+        if (tp_trace && lane == 0) {
+          const unsigned long long tw1 = gtimer();
+          if (tw1 - tw0 > 2000) printf("r%d cta%d flagwait tile %d rowblk %d: from %.1f us for %.1f us\n", p.tp_rank, int(blockIdx.x), t,
+                                       ti.row0 / p.rows_per_flag, (tw0 - trace_t0) * 1e-3, (tw1 - tw0) * 1e-3);
+        }
+#endif
       }
       for (int32_t kt = 0; kt < k_tiles; ++kt) {
         wait_barrier(empty0 + stage * 8, phase ^ 1u, ctl, dead);
         BSG_DBG(0, 1);
-        if (elected) {
+        // After a timeout nothing more is issued: free-running loads would overrun the barriers' byte counts.
+        if (elected && !dead) {
           const uint32_t full_local = full0 + stage * 8;
           uint32_t txb = 0;
           if (!BSG_FLAG(p, 2)) txb += C::kABytes + C::kBBytes;
@@ -542,7 +572,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           const int32_t k_left = p.K - kt * C::kTileK;
           const int n_mma = k_left >= C::kTileK ? 4 : (k_left + C::kMmaK - 1) / C::kMmaK;
           const uint32_t acc_flag = kt > 0 ? 1u : 0u;
-          if (elected) {
+          if (elected && !dead) {     // after a timeout no further tensor-core work or barrier arrival is issued
             if (!BSG_FLAG(p, 1)) {
 #pragma unroll
               for (int ka = 0; ka < C::kKAtoms; ++ka) {
@@ -579,7 +609,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           stage = next_stage;
           phase = next_phase;
         }
-        if (elected) ptx::umma_commit<CG>(tfull0 + acc_bar * 8);
+        if (elected && !dead) ptx::umma_commit<CG>(tfull0 + acc_bar * 8);
       }
       if (dead) atomicOr(p.status, kStTimeoutFull | kStTimeoutTmemEmpty);
     }
@@ -603,58 +633,99 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           if (q != p.tp_rank) st_release_sys_u32(p.tp_peer_sync[q] + kTpSyncReady + p.tp_rank, p.tp_epoch);
         }
       }
-      TpChunkIter ld_it, st_it;                 // the load iterator runs kTpBufs chunks ahead of the store iterator
+      TpChunkIter ld_it, st_it;                 // the load iterator runs ahead of the store iterator
       if (p.tp_push_in_kernel) {
-      ld_it.init(p, int(blockIdx.x), int(gridDim.x), C::kTpChunk);
-      st_it.init(p, int(blockIdx.x), int(gridDim.x), C::kTpChunk);
+#ifdef BSG_PROFILE
+      // Ablation variants of the ring (bits 4096 / 8192): buffers x chunk bytes, read lag.
+      const uint32_t variant = (uint32_t(p.debug_flags) >> 12) & 3u;
+      const uint32_t nb = variant == 2u ? 8u : variant == 3u ? 2u : 4u;
+      const uint32_t ch = variant == 2u ? 4096u : variant == 3u ? 16384u : 8192u;
+      const uint32_t rlag = variant == 1u ? 0u : variant == 2u ? 4u : variant == 3u ? 1u : 2u;
+      long long acc_full = 0, acc_read = 0, acc_ann = 0, acc_ready = 0;
+      const long long loop_t0 = clock64();
+#define BSG_ACC(var, stmt) do { const long long a0_ = clock64(); stmt; var += clock64() - a0_; } while (0)
+#else
+      constexpr uint32_t nb = C::kTpBufs, ch = C::kTpChunk, rlag = C::kTpReadLag;
+#define BSG_ACC(var, stmt) do { stmt; } while (0)
+#endif
+      ld_it.init(p, int(blockIdx.x), int(gridDim.x), int(ch));
+      st_it.init(p, int(blockIdx.x), int(gridDim.x), int(ch));
       uint32_t n_ld = 0, n_st = 0;
-      for (; n_ld < uint32_t(C::kTpBufs) && ld_it.valid(); ++n_ld, ld_it.next(p)) {
+      for (; n_ld < nb && ld_it.valid(); ++n_ld, ld_it.next(p)) {
         if (elected) {
           ptx::mbar_arrive_expect_tx(bar0 + n_ld * 8, ld_it.bytes);
-          ptx::bulk_load(buf0 + n_ld * C::kTpChunk, ld_it.src(p), ld_it.bytes, bar0 + n_ld * 8);
+          ptx::bulk_load(buf0 + n_ld * ch, ld_it.src(p), ld_it.bytes, bar0 + n_ld * 8);
         }
       }
       int checked = -1;
-      // A finished piece is announced a few chunks later, once its stores are known to be complete,
-      // so that the copy pipeline never drains: pend_* hold the piece waiting for its announcement.
-      int pend_rank = -1, pend_block = 0;
-      uint32_t pend_at = 0;                      // announce once this many chunks have been committed
+      // Ring of staging buffers: chunk n goes through buffer n % nb.  A buffer is refilled `rlag` stores
+      // after its own store was issued (by then that store has read it), so neither the load latency nor
+      // the store's read latency is waited for in line.  A finished piece is announced kTpLag chunks
+      // later, once its stores are known to be complete; up to kTpPend pieces wait in pend_*.
+      int pend_rank[C::kTpPend], pend_block[C::kTpPend];
+      uint32_t pend_due[C::kTpPend];
+      int pend_head = 0, pend_cnt = 0;
+      // The announcement is a relaxed system-scope add issued after wait_group has reported the piece's
+      // stores complete, i.e. acknowledged by the peer's memory: the counter update leaves this GPU only
+      // after the data is in place, and the consumer reads both from its own memory.  (A release here
+      // would also wait for the newer stores still in flight, several microseconds per piece.)
+      auto announce_head = [&]() {
+        uint32_t* flag = p.tp_peer_sync[pend_rank[pend_head]] + kTpSyncFlags + pend_block[pend_head];
+        asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(flag), "r"(1u) : "memory");
+        pend_head = (pend_head + 1) % C::kTpPend;
+        --pend_cnt;
+      };
       for (; st_it.valid(); st_it.next(p), ++n_st) {
-        const uint32_t b = n_st % C::kTpBufs;
+        const uint32_t b = n_st % nb;
         if (st_it.dst_rank != checked) {
-          if (!wait_flag_ge(sync + kTpSyncReady + st_it.dst_rank, p.tp_epoch, ctl)) peer_ok = false;
+          BSG_ACC(acc_ready, if (!wait_flag_ge(sync + kTpSyncReady + st_it.dst_rank, p.tp_epoch, ctl)) peer_ok = false);
           checked = st_it.dst_rank;
         }
-        wait_barrier(bar0 + b * 8, (n_st / C::kTpBufs) & 1u, ctl, dead);
+        BSG_ACC(acc_full, wait_barrier(bar0 + b * 8, (n_st / nb) & 1u, ctl, dead));
+        if (dead) break;             // a staging load never landed: push and announce nothing more
+        const bool refill = n_st >= rlag && ld_it.valid();
         if (elected) {
-          if (pend_rank >= 0 && (n_st >= pend_at || st_it.last_of_piece)) {
-            if (n_st >= pend_at) ptx::bulk_wait_group<C::kTpLag>(); else ptx::bulk_wait_group<0>();
-            asm volatile("fence.proxy.async;" ::: "memory");
-            red_release_sys_add(p.tp_peer_sync[pend_rank] + kTpSyncFlags + pend_block, 1u);
-            pend_rank = -1;
+          while (pend_cnt > 0 && n_st >= pend_due[pend_head]) {
+            BSG_ACC(acc_ann, ptx::bulk_wait_group<C::kTpLag>());
+            announce_head();
           }
-          if (peer_ok) ptx::bulk_store(st_it.dst(p), buf0 + b * C::kTpChunk, st_it.bytes);
+          if (peer_ok) ptx::bulk_store(st_it.dst(p), buf0 + b * ch, st_it.bytes);
           ptx::bulk_commit_group();
           if (st_it.last_of_piece && peer_ok) {
-            pend_rank = st_it.dst_rank;
-            pend_block = st_it.row_block;
-            pend_at = n_st + 1 + C::kTpLag;       // by then at most kTpLag newer groups are outstanding
+            if (pend_cnt == C::kTpPend) {
+              BSG_ACC(acc_ann, ptx::bulk_wait_group<1>());   // everything but the store just issued
+              announce_head();
+            }
+            const int slot = (pend_head + pend_cnt) % C::kTpPend;
+            pend_rank[slot] = st_it.dst_rank;
+            pend_block[slot] = st_it.row_block;
+            pend_due[slot] = n_st + 1 + C::kTpLag;    // by then at most kTpLag newer groups are outstanding
+            ++pend_cnt;
           }
-          if (ld_it.valid()) {
-            ptx::bulk_wait_group_read<0>();           // the store just issued has read this buffer
-            ptx::mbar_arrive_expect_tx(bar0 + b * 8, ld_it.bytes);
-            ptx::bulk_load(buf0 + b * C::kTpChunk, ld_it.src(p), ld_it.bytes, bar0 + b * 8);
+          if (refill) {
+            BSG_ACC(acc_read, tp_wait_read(rlag));      // the store issued `rlag` chunks ago has read its buffer
+            const uint32_t rb = (n_st - rlag) % nb;
+            ptx::mbar_arrive_expect_tx(bar0 + rb * 8, ld_it.bytes);
+            ptx::bulk_load(buf0 + rb * ch, ld_it.src(p), ld_it.bytes, bar0 + rb * 8);
           }
         }
-        if (ld_it.valid()) ld_it.next(p);
+        if (refill) ld_it.next(p);
         __syncwarp();
       }
-      if (elected && pend_rank >= 0) {
+      if (elected && pend_cnt > 0) {
         ptx::bulk_wait_group<0>();
-        asm volatile("fence.proxy.async;" ::: "memory");
-        red_release_sys_add(p.tp_peer_sync[pend_rank] + kTpSyncFlags + pend_block, 1u);
+        while (pend_cnt > 0) announce_head();
       }
       if (elected) ptx::bulk_wait_group<0>();
+#ifdef BSG_PROFILE
+      if (tp_trace && elected) {
+        const long long loop = clock64() - loop_t0;
+        printf("r%d cta%d push: %u chunks of %u B rlag %u, loop %lld kcyc ending %.1f us after entry: wait full %lld, read %lld, announce %lld, ready %lld kcyc\n",
+               p.tp_rank, int(blockIdx.x), n_st, ch, rlag, loop / 1000, (gtimer() - trace_t0) * 1e-3,
+               acc_full / 1000, acc_read / 1000, acc_ann / 1000, acc_ready / 1000);
+      }
+#endif
+#undef BSG_ACC
       }
       if (!peer_ok || dead) atomicOr(p.status, kStTimeoutPeer);
     }
@@ -830,6 +901,9 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
     }
     if (lane == 0) ptx::bulk_wait_group<0>();
+#ifdef BSG_PROFILE
+    if (tp_trace && warp == 0 && lane == 0) printf("r%d cta%d epilogue done at %.1f us\n", p.tp_rank, int(blockIdx.x), (gtimer() - trace_t0) * 1e-3);
+#endif
     if (dead) atomicOr(p.status, kStTimeoutTmemFull);
   }
 

@@ -73,7 +73,8 @@ def copy_schedule(world: int, rank: int, M: int, ksplit: int, cta: int, grid: in
     for c in range(cta, (world - 1) * per_shard, grid):
         j = c // per_shard + 1
         rem = c - (j - 1) * per_shard
-        rb, ks = divmod(rem, ksplit)
+        rb = rem // ksplit
+        ks = (rem + rb) % ksplit          # rotated per row block: the piece that carries the scale factors moves around
         out.append(CopyPiece((rank - j) % world, rank * blocks + rb, ks))
     return out
 

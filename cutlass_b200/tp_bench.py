@@ -119,6 +119,33 @@ def run(args) -> dict:
     dist.all_reduce(tu, op=dist.ReduceOp.MAX)
     unfused_ms = float(tu.item()) / n_unf
 
+    # ---- the whole problem (all N columns) on ONE GPU: the base of the strong-scaling series,
+    # measured on every rank's GPU at the same time (max over ranks), A already resident
+    base = None
+    if world > 1:
+        Bf, SFBf = _shard_operand(N, K, 3000, dev)
+        Df = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        full = L.GemmArgs()
+        full.kind, full.batch, full.M, full.N, full.K = kind, 1, M, N, K
+        full.A, full.SFA, full.B, full.SFB, full.D = a_full.data_ptr(), sfa_full.data_ptr(), Bf.data_ptr(), SFBf.data_ptr(), Df.data_ptr()
+        full.alpha = 1.0
+        n_base = max(3, min(args.steps, 10))
+        for i in range(3 + n_base):
+            if i == 3:
+                torch.cuda.synchronize()
+                dist.barrier()
+                e0.record(stream)
+            rc = lib.bsg_gemm_run(C.byref(full), ws.data_ptr(), 16, stream.cuda_stream)
+            assert rc == 0, L.last_error()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        tb = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        dist.all_reduce(tb, op=dist.ReduceOp.MAX)
+        base_ms = float(tb.item()) / n_base
+        base = {"value": round(flops / base_ms / 1e9, 1), "unit": "TFLOP/s", "ms_per_step": round(base_ms, 4), "n_gpus": 1,
+                "what": "the same M x N x K problem, all N columns, on one GPU with A resident (slowest of this run's GPUs)"}
+        del Bf, SFBf, Df
+
     # ---- end to end with host buffers: this rank's A shard and B shard in, its D shard out
     hA, hSFA, hB, hSFB = (x.cpu().pin_memory() for x in (A, SFA, B, SFB))
     hD = torch.empty((M, ns), dtype=torch.bfloat16).pin_memory()
@@ -171,6 +198,7 @@ def run(args) -> dict:
                      "nvlink_time_floor_ms": round(link_bytes / 770e9 * 1e3, 4), "traffic": None},
         "unfused_nccl": {"value": round(flops / unfused_ms / 1e9, 1), "unit": "TFLOP/s", "ms_per_step": round(unfused_ms, 4),
                          "what": "ncclAllGather(A), ncclAllGather(SFA), then the same dense kernel"},
+        "scaling_base": base,
         "parity": {"rows_checked_per_rank": rows, "from_shard": "rank+1 (remote)", "max_rel_err_vs_cpu_oracle": float(relt.item())},
     }
     tp.close()

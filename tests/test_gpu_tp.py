@@ -1,0 +1,101 @@
+"""Tensor-parallel GEMM on real GPUs through the C ABI (bsg_tp_*), one process per GPU.
+
+Every call uses a different A, so a rank that read a peer's rows before they had arrived (or rows
+of the previous call) cannot pass: the operands are the exact-arithmetic fixtures and the result
+must equal the oracle's bit for bit.  NVLS is switched off for the NCCL bootstrap."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _problem(kind, M, N, K, seed):
+    from cutlass_b200 import generators as G
+    rng = np.random.default_rng(seed)
+    gen = G.exact_nvfp4_operand if kind == 0 else G.exact_mxfp8_operand
+    A, _, sfa = gen(M, K, rng)
+    B, _, sfb = gen(N, K, rng)
+    return A, sfa, B, sfb
+
+
+def _run_rank(tp, rank, world, kind, M, N, K, calls):
+    import oracle
+    vec = 16 if kind == 0 else 32
+    atom_bytes = 512 * (-(-(K // vec) // 4))
+    ms, ns = M // world, N // world
+    for call in range(calls):
+        A, sfa, B, sfb = _problem(kind, M, N, K, 100 + call)
+        tp.a_shard.copy_(torch.from_numpy(A[rank * ms:(rank + 1) * ms]).cuda())
+        tp.sfa_shard.copy_(torch.from_numpy(sfa[(rank * ms // 128) * atom_bytes:((rank + 1) * ms // 128) * atom_bytes]).cuda())
+        Bl = np.ascontiguousarray(B[rank * ns:(rank + 1) * ns])
+        sfbl = np.ascontiguousarray(sfb[(rank * ns // 128) * atom_bytes:((rank + 1) * ns // 128) * atom_bytes])
+        dB, dSFB = torch.from_numpy(Bl).cuda(), torch.from_numpy(sfbl).cuda()
+        out = torch.full((M, ns), 0x7FC0, dtype=torch.int16, device="cuda")          # NaN pattern: unwritten cells show up
+        tp.run(dB, dSFB, out)
+        tp.check_device_status()
+        torch.cuda.synchronize()
+        want = oracle.to_bf16(oracle.gemm_fp32(kind, A, sfa, Bl, sfbl, M, ns, K))
+        got = out.cpu().numpy().view(np.uint16)
+        bad = int((got != want).sum())
+        assert bad == 0, f"call {call}: {bad} of {got.size} outputs differ from the oracle (rank {rank})"
+
+
+def _worker(rank, world, port, kind, M, N, K, calls, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                          LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+        import torch.distributed as dist
+        from cutlass_b200 import tp as TP
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        tp = TP.TpGemm(kind, M, K)
+        try:
+            _run_rank(tp, rank, world, kind, M, N, K, calls)
+        finally:
+            torch.cuda.synchronize()
+            dist.barrier()
+            tp.close()
+            dist.barrier()
+            dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        q.put((rank, repr(e)))
+
+
+@pytest.mark.parametrize("kind", [0, 1])
+def test_tp_single_rank_matches_oracle(kind):
+    """world = 1: the tensor-parallel kernel with every row local (no peers, no push)."""
+    from cutlass_b200 import tp as TP
+    tp = TP.TpGemm(kind, 512, 1024)
+    try:
+        _run_rank(tp, 0, 1, kind, 512, 384, 1024, calls=2)
+    finally:
+        tp.close()
+
+
+@pytest.mark.parametrize("kind,world,M,N,K", [(1, 2, 1024, 512, 2048), (0, 2, 1024, 512, 2048), (1, 2, 4096, 1024, 4096),
+                                              (1, 4, 2048, 1024, 2048)])
+def test_tp_gathers_a_inside_the_kernel(kind, world, M, N, K):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, kind, M, N, K, 3, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+    assert results == [(r, "ok") for r in range(world)], results
