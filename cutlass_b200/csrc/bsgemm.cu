@@ -116,6 +116,8 @@ struct Problem {
   bool tp;
   int32_t tp_world, tp_rank, tp_rows_per_shard, tp_ksplit, tp_push_in_kernel;
   uint32_t tp_epoch;
+  uint32_t tp_ready_target; // a peer's buffer may be filled once the peer has launched this call number
+  int32_t tp_parity;        // which of the two gathered buffers this call fills and reads (own rows always sit in buffer 0)
   int64_t tp_row_bytes, tp_sfa_rowatom_bytes;
   const uint8_t* tp_peer_a[8];
   const uint8_t* tp_peer_sfa[8];
@@ -182,9 +184,10 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   if (q.out_kind == BSG_OUT_BF16) rc = make_out_map(&tmD, q.D, true, uint64_t(q.N), uint64_t(q.total_rows), uint64_t(q.ldd) * 2);
   else rc = make_out_map(&tmD, q.D, false, uint64_t(q.N / 2), uint64_t(q.total_rows), uint64_t(q.ldd) / 2);   // not used by the kernel
   if (rc != BSG_OK) return rc;
-  if ((rc = make_operand_map(&tmA, q.A, k_bytes, q.total_rows, Cf::kCtaM)) != BSG_OK) return rc;
+  // Tensor parallel: the two gathered buffers lie back to back, one map covers both.
+  if ((rc = make_operand_map(&tmA, q.A, k_bytes, TP ? 2 * q.total_rows : q.total_rows, Cf::kCtaM)) != BSG_OK) return rc;
   if ((rc = make_operand_map(&tmB, q.B, k_bytes, b_groups * q.N, Cf::kBRowsCta)) != BSG_OK) return rc;
-  if ((rc = make_sf_map(&tmSFA, q.SFA, k_atoms, sfa_row_atoms, Cf::kKAtoms, 1)) != BSG_OK) return rc;
+  if ((rc = make_sf_map(&tmSFA, q.SFA, k_atoms, TP ? 2 * sfa_row_atoms : sfa_row_atoms, Cf::kKAtoms, 1)) != BSG_OK) return rc;
   if ((rc = make_sf_map(&tmSFB, q.SFB, k_atoms, b_groups * n_atoms, Cf::kKAtoms, BN / 128)) != BSG_OK) return rc;
 
   bsg::GemmParams p;
@@ -218,6 +221,8 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   if (TP) {
     p.tp_world = q.tp_world; p.tp_rank = q.tp_rank; p.tp_rows_per_shard = q.tp_rows_per_shard; p.tp_ksplit = q.tp_ksplit; p.tp_push_in_kernel = q.tp_push_in_kernel;
     p.tp_epoch = q.tp_epoch;
+    p.tp_ready_target = q.tp_ready_target;
+    p.tp_remote_row_offset = q.tp_parity ? int32_t(q.total_rows) : 0;
     p.tp_row_bytes = q.tp_row_bytes; p.tp_sfa_rowatom_bytes = q.tp_sfa_rowatom_bytes;
     for (int i = 0; i < 8; ++i) { p.tp_peer_a[i] = q.tp_peer_a[i]; p.tp_peer_sfa[i] = q.tp_peer_sfa[i]; p.tp_peer_sync[i] = q.tp_peer_sync[i]; }
   }
@@ -389,6 +394,7 @@ struct bsg_tp_comm {
   int64_t M, K, rows_per_shard;
   int64_t row_bytes, k_atoms, sfa_rowatom_bytes;
   size_t a_off, sfa_off, sync_off, total_bytes;
+  size_t a_bytes, sfa_bytes;   // one gathered buffer each; two of each lie back to back
   uint8_t* base;
   uint8_t* peer_base[8];
   bool opened[8];
@@ -524,9 +530,13 @@ int32_t bsg_tp_create(int32_t rank, int32_t world, int32_t kind, int64_t M, int6
   const size_t sfa_bytes = size_t(M / 128) * size_t(c->sfa_rowatom_bytes);
   const size_t sync_bytes = (size_t(bsg::kTpSyncFlags) + size_t(M / 256)) * 4;
   auto up = [](size_t v) { return (v + 1023) & ~size_t(1023); };
+  // Two gathered buffers of each kind, back to back: call n fills and reads buffer n & 1, so a peer may
+  // already push the data of the next call while this rank still computes on the current one.  This
+  // rank's own rows always stay in buffer 0 (where the caller writes them).
+  c->a_bytes = a_bytes; c->sfa_bytes = sfa_bytes;
   c->a_off = 0;
-  c->sfa_off = up(a_bytes);
-  c->sync_off = c->sfa_off + up(sfa_bytes);
+  c->sfa_off = up(2 * a_bytes);
+  c->sync_off = c->sfa_off + up(2 * sfa_bytes);
   c->total_bytes = c->sync_off + up(sync_bytes);
   cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->base), c->total_bytes);
   if (e != cudaSuccess) { delete c; return fail(BSG_ERR_CUDA, "cudaMalloc(%zu): %s", c->total_bytes, cudaGetErrorString(e)); }
@@ -609,9 +619,15 @@ int32_t bsg_tp_gemm_run(bsg_tp_comm* c, const bsg_gemm_args* args, void* workspa
   while (ks > 1 && c->k_atoms % ks != 0) ks >>= 1;
   q.tp_ksplit = ks;
   q.tp_row_bytes = c->row_bytes; q.tp_sfa_rowatom_bytes = c->sfa_rowatom_bytes;
+  q.tp_epoch = c->epoch + 1;
+  const bool single_buffer = (c->mode & BSG_TP_SINGLE_BUFFER) != 0;
+  q.tp_parity = single_buffer ? 0 : int32_t(q.tp_epoch & 1u);
+  // The buffer this call fills was last read by the peer's previous call (single buffer) or the one before.
+  q.tp_ready_target = single_buffer ? q.tp_epoch : q.tp_epoch - 1;
   for (int i = 0; i < c->world; ++i) {
-    q.tp_peer_a[i] = c->peer_base[i] + c->a_off;
-    q.tp_peer_sfa[i] = c->peer_base[i] + c->sfa_off;
+    const bool remote = i != c->rank;     // own entry: the source of the push, always buffer 0
+    q.tp_peer_a[i] = c->peer_base[i] + c->a_off + (remote && q.tp_parity ? c->a_bytes : 0);
+    q.tp_peer_sfa[i] = c->peer_base[i] + c->sfa_off + (remote && q.tp_parity ? c->sfa_bytes : 0);
     q.tp_peer_sync[i] = reinterpret_cast<uint32_t*>(c->peer_base[i] + c->sync_off);
   }
   // The M sweep starts at this rank's own rows and follows the order in which the shards arrive.
@@ -622,10 +638,9 @@ int32_t bsg_tp_gemm_run(bsg_tp_comm* c, const bsg_gemm_args* args, void* workspa
   q.tile_m_rotate = c->rank * blocks;
   q.ready_flags = c->world > 1 ? q.tp_peer_sync[c->rank] + bsg::kTpSyncFlags : nullptr;
   q.rows_per_flag = 256;
-  q.tp_epoch = c->epoch + 1;
   q.flag_target = q.tp_epoch * uint32_t(ks);
-  q.tp_push_in_kernel = c->mode == BSG_TP_PUSH_KERNEL ? 1 : 0;
-  const bool copy_engine = c->world > 1 && c->mode == BSG_TP_PUSH_COPY_ENGINE;
+  const bool copy_engine = c->world > 1 && (c->mode & BSG_TP_PUSH_COPY_ENGINE) != 0;
+  q.tp_push_in_kernel = copy_engine ? 0 : 1;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (copy_engine) {
     if (!workspace || workspace_bytes < 16) return fail(BSG_ERR_WORKSPACE_NULL, "workspace is null or smaller than 16 bytes");
@@ -649,7 +664,7 @@ int32_t bsg_tp_gemm_run(bsg_tp_comm* c, const bsg_gemm_args* args, void* workspa
       cudaStream_t ls = c->lanes[l];
       e = cudaStreamWaitEvent(ls, c->ev_start, 0);
       if (e != cudaSuccess) break;
-      bsg::tp_wait_peers_kernel<<<1, 32, 0, ls>>>(own_sync, c->world, c->rank, q.tp_epoch, static_cast<uint32_t*>(workspace));
+      bsg::tp_wait_peers_kernel<<<1, 32, 0, ls>>>(own_sync, c->world, c->rank, q.tp_ready_target, static_cast<uint32_t*>(workspace));
       for (int j = 1; j < c->world && e == cudaSuccess; ++j) {
         const int dst = (c->rank - j + c->world) % c->world;
         for (int32_t b0 = l * slice; b0 < blocks && e == cudaSuccess; b0 += band) {
@@ -657,8 +672,9 @@ int32_t bsg_tp_gemm_run(bsg_tp_comm* c, const bsg_gemm_args* args, void* workspa
           const size_t a_bytes = size_t(slice) * 256 * size_t(c->row_bytes);
           const size_t s_off = c->sfa_off + size_t(first_block + b0) * 2 * size_t(c->sfa_rowatom_bytes);
           const size_t s_bytes = size_t(slice) * 2 * size_t(c->sfa_rowatom_bytes);
-          e = cudaMemcpyAsync(c->peer_base[dst] + a_off, c->base + a_off, a_bytes, cudaMemcpyDeviceToDevice, ls);
-          if (e == cudaSuccess) e = cudaMemcpyAsync(c->peer_base[dst] + s_off, c->base + s_off, s_bytes, cudaMemcpyDeviceToDevice, ls);
+          const size_t a_par = q.tp_parity ? c->a_bytes : 0, s_par = q.tp_parity ? c->sfa_bytes : 0;
+          e = cudaMemcpyAsync(c->peer_base[dst] + a_off + a_par, c->base + a_off, a_bytes, cudaMemcpyDeviceToDevice, ls);
+          if (e == cudaSuccess) e = cudaMemcpyAsync(c->peer_base[dst] + s_off + s_par, c->base + s_off, s_bytes, cudaMemcpyDeviceToDevice, ls);
           if (e != cudaSuccess) break;
           bsg::tp_announce_kernel<<<1, 32, 0, ls>>>(q.tp_peer_sync[dst] + bsg::kTpSyncFlags, int(first_block + b0), slice, uint32_t(ks));
         }
@@ -676,7 +692,7 @@ int32_t bsg_tp_gemm_run(bsg_tp_comm* c, const bsg_gemm_args* args, void* workspa
 
 int32_t bsg_tp_set_mode(bsg_tp_comm* c, int32_t mode) {
   if (!c) return fail(BSG_ERR_INVALID_PROBLEM, "null communicator");
-  if (mode != BSG_TP_PUSH_KERNEL && mode != BSG_TP_PUSH_COPY_ENGINE) return fail(BSG_ERR_NOT_SUPPORTED, "unknown tensor-parallel mode %d", mode);
+  if (mode < 0 || mode > (BSG_TP_PUSH_COPY_ENGINE | BSG_TP_SINGLE_BUFFER)) return fail(BSG_ERR_NOT_SUPPORTED, "unknown tensor-parallel mode %d", mode);
   c->mode = mode;
   return BSG_OK;
 }

@@ -83,6 +83,8 @@ struct GemmParams {
   int32_t tp_ksplit;          // pieces a 256-row block is cut into (one flag increment each)
   int32_t tp_push_in_kernel;  // 1: the push warp moves the data; 0: the host's copy-engine transfers do
   uint32_t tp_epoch;          // call counter, starts at 1; the peers use the same value
+  uint32_t tp_ready_target;       // a peer's buffer may be filled once its "launched call" word has reached this
+  int32_t tp_remote_row_offset;   // rows between the buffer this call gathers into and buffer 0 (0 or M)
   int64_t tp_row_bytes;       // bytes of one row of A
   int64_t tp_sfa_rowatom_bytes;   // bytes of one 128-row atom row of SFA (512 * k_atoms)
   const uint8_t* tp_peer_a[8];    // full-size A buffer of every rank (own entry = local buffer)
@@ -472,14 +474,18 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     uint32_t phase = 0;
     for (int32_t t = cluster_idx; t < total_tiles; t += num_clusters) {
       const TileInfo ti = decode_tile(ctl, p, t, C::kTileM);
-      const int32_t a_row = bcast(ti.row0 + int32_t(cta_rank) * C::kCtaM);
+      // Tensor parallel: rows of other ranks are read from the gathered buffer of this call, which lies
+      // tp_remote_row_offset rows behind buffer 0 in the same tensor map; own rows always from buffer 0.
+      const bool tp_remote = TP && ti.row0 / p.tp_rows_per_shard != p.tp_rank;
+      const int32_t tp_row_off = tp_remote ? p.tp_remote_row_offset : 0;
+      const int32_t a_row = bcast(ti.row0 + int32_t(cta_rank) * C::kCtaM + tp_row_off);
       const int32_t b_row = bcast(ti.g * p.b_rows_per_group + ti.tn * BN + int32_t(cta_rank) * C::kBRowsCta);
       // The second CTA of a pair may lie wholly past the group's last row: keep its
       // scale-factor fetch inside the group's own atoms (its rows are never stored).
       const int32_t group_atoms = (ti.row_end - ti.group_row0 + 127) >> 7;
-      const int32_t sfa_atom = bcast(min(ti.sf_atom + int32_t(cta_rank), ti.group_atom0 + max(group_atoms, 1) - 1));
+      const int32_t sfa_atom = bcast(min(ti.sf_atom + int32_t(cta_rank), ti.group_atom0 + max(group_atoms, 1) - 1) + (tp_row_off >> 7));
       const int32_t sfb_atom = bcast(ti.g * p.sfb_atoms_per_group + ti.tn * (BN / 128));
-      if (p.ready_flags != nullptr && (!TP || ti.row0 / p.tp_rows_per_shard != p.tp_rank) && !BSG_FLAG(p, 1024)) {
+      if (p.ready_flags != nullptr && (!TP || tp_remote) && !BSG_FLAG(p, 1024)) {
         const uint32_t* flag = p.ready_flags + ti.row0 / p.rows_per_flag;
 #ifdef BSG_PROFILE
         const unsigned long long tw0 = gtimer();
@@ -625,8 +631,8 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const uint32_t buf0 = ptx::smem_u32(sTp);
       const uint32_t bar0 = ptx::smem_u32(&ctl->tp_full[0]);
       bool peer_ok = true;
-      // Launching this call means the previous one has finished reading this rank's gathered buffer:
-      // tell every peer that it may now be overwritten with the data of this call.
+      // Launching this call means the previous one has finished reading its gathered buffer: tell every
+      // peer, which may then fill that buffer again (with the data of the call after this one).
       if (blockIdx.x == 0 && elected) {
         __threadfence_system();
         for (int q = 0; q < p.tp_world; ++q) {
@@ -678,7 +684,8 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       for (; st_it.valid(); st_it.next(p), ++n_st) {
         const uint32_t b = n_st % nb;
         if (st_it.dst_rank != checked) {
-          BSG_ACC(acc_ready, if (!wait_flag_ge(sync + kTpSyncReady + st_it.dst_rank, p.tp_epoch, ctl)) peer_ok = false);
+          // The peer's buffer is free once the peer has launched the call after the one that last read it.
+          BSG_ACC(acc_ready, if (!wait_flag_ge(sync + kTpSyncReady + st_it.dst_rank, p.tp_ready_target, ctl)) peer_ok = false);
           checked = st_it.dst_rank;
         }
         BSG_ACC(acc_full, wait_barrier(bar0 + b * 8, (n_st / nb) & 1u, ctl, dead));
@@ -689,7 +696,9 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             BSG_ACC(acc_ann, ptx::bulk_wait_group<C::kTpLag>());
             announce_head();
           }
-          if (peer_ok) ptx::bulk_store(st_it.dst(p), buf0 + b * ch, st_it.bytes);
+          if (BSG_FLAG(p, 65536)) BSG_ACC(acc_ann, ptx::bulk_wait_group<1>());      // ablation: at most 2 stores in flight
+          if (BSG_FLAG(p, 131072)) BSG_ACC(acc_ann, ptx::bulk_wait_group<0>());     // ablation: at most 1 store in flight
+          if (peer_ok && !BSG_FLAG(p, 32768)) ptx::bulk_store(st_it.dst(p), buf0 + b * ch, st_it.bytes);
           ptx::bulk_commit_group();
           if (st_it.last_of_piece && peer_ok) {
             if (pend_cnt == C::kTpPend) {

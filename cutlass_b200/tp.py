@@ -122,9 +122,10 @@ class TpGemm:
             blob = (C.c_uint8 * (64 * self.world)).from_buffer_copy(b"".join(handles))
             L.check(self._lib.bsg_tp_connect(self._comm, blob))
             dist.barrier(group)
-        mode = mode or os.environ.get("BSG_TP_MODE")          # "kernel" | "copy_engine" | None (library default)
+        # "kernel" | "copy_engine", optionally with "+single" (one gathered buffer instead of two); None: library default
+        mode = mode or os.environ.get("BSG_TP_MODE")
         if mode is not None:
-            L.check(self._lib.bsg_tp_set_mode(self._comm, {"kernel": 0, "copy_engine": 1}[mode]))
+            self.set_mode(mode)
         self.mode = mode or "kernel"
         ptrs = [C.c_void_p() for _ in range(4)]
         L.check(self._lib.bsg_tp_buffers(self._comm, *[C.byref(p) for p in ptrs]))
@@ -138,6 +139,13 @@ class TpGemm:
         self.a_shard = torch.as_tensor(_DevicePointer(ptrs[2].value, ms * row_bytes), device=dev).view(ms, row_bytes)
         self.sfa_shard = torch.as_tensor(_DevicePointer(ptrs[3].value, (ms // 128) * 512 * k_atoms), device=dev)
         self.workspace = torch.zeros(16, dtype=torch.uint8, device=dev)
+
+    def set_mode(self, mode: str) -> None:
+        """Only between calls, with every rank idle (device synchronised and a barrier passed), and the same on all ranks."""
+        base, _, opt = mode.partition("+")
+        code = {"kernel": 0, "copy_engine": 1}[base] | ({"": 0, "single": 2}[opt])
+        self._L.check(self._lib.bsg_tp_set_mode(self._comm, code))
+        self.mode = mode
 
     def build_args(self, B, SFB, out, C_=None, alpha: float = 1.0, beta: float = 0.0, tile_n: int = 0):
         """B: (N_local, K bytes) K-major uint8/e4m3 tensor; SFB its interleaved scales; out: (M, N_local) bf16."""

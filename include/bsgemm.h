@@ -185,17 +185,23 @@ int32_t bsg_gemm_run_static(const bsg_gemm_args* args, void* cuda_stream, uint32
 /*
  * Tensor-parallel GEMM: D[:, local N shard] = alpha * A B_local^T + beta * C, with A (and SFA)
  * sharded by rows over `world` ranks (one process per GPU of one node) and B / D sharded over N.
- * The kernel itself gathers the other ranks' A shards over NVLink (peer-memory loads by
- * dedicated copy warps) while its tensor-core warps already work on the rows that have arrived.
+ * The kernel itself gathers A over NVLink: a push warp in every CTA sends this rank's rows into the
+ * peers' buffers (bulk copies through shared memory, nearest consumer first) and bumps a per-row-block
+ * counter there, while the tensor-core warps already work on the rows that have arrived.
  * Takes the role of the reference's all-gather distributed GEMM
  * (include/cutlass/experimental/distributed/device/dist_gemm_universal_wrapper.hpp:53,
  * schedule AllGather1D_TilingCD_RotatingA in schedules/dist_gemm_1d_schedules.hpp; device barrier
  * kernel/full_barrier.hpp:47), with bounded waits instead of unbounded spins.
  *
- * bsg_tp_create   allocates this rank's buffers (full-size A and SFA plus sync words; the only
- *                 allocating call) and returns a 64-byte CUDA IPC handle to hand to the peers.
+ * bsg_tp_create   allocates this rank's buffers (two full-size gathered A and SFA buffers, used by
+ *                 alternate calls so that a peer may already send the next call's rows while this rank
+ *                 still computes, plus sync words; the only allocating call) and returns a 64-byte
+ *                 CUDA IPC handle to hand to the peers.
  * bsg_tp_connect  takes the `world` handles (64 bytes each, indexed by rank) and maps the peers.
- * bsg_tp_buffers  returns where this rank writes its own A / SFA shard (inside the full buffers).
+ * bsg_tp_buffers  returns where this rank writes its own A / SFA shard (a_shard, sfa_shard: inside the
+ *                 first gathered buffer, whose start is a_full / sfa_full; the other ranks' rows of that
+ *                 buffer are filled by every second call only, so read a_full for
+ *                 diagnosis, not as an output).
  * bsg_tp_gemm_run enqueues one GEMM; args->A / SFA are ignored, args->M is the full M, args->N
  *                 the local N shard.  All ranks must call it the same number of times with the
  *                 same shapes.
@@ -203,10 +209,9 @@ int32_t bsg_gemm_run_static(const bsg_gemm_args* args, void* cuda_stream, uint32
  *                 the SM's bulk-copy engine (one launch per GEMM); or
  *                 BSG_TP_PUSH_COPY_ENGINE -- the GPU's copy engines on an internal side stream, one transfer per
  *                 band of row blocks followed by its announcement, joined back into the caller's stream
- *                 (the scheme of dist_gemm_universal_wrapper.hpp:578-593).  Default: kernel.  On 8 B200s both
- *                 deliver about 270 GB/s per GPU while the GEMM runs.  All ranks must use the same mode.
+ *                 (the scheme of dist_gemm_universal_wrapper.hpp:578-593).  Default: kernel.  All ranks must use the same mode.
  */
-enum { BSG_TP_PUSH_KERNEL = 0, BSG_TP_PUSH_COPY_ENGINE = 1 };
+enum { BSG_TP_PUSH_KERNEL = 0, BSG_TP_PUSH_COPY_ENGINE = 1, BSG_TP_SINGLE_BUFFER = 2 /* or-ed in: every call uses the first gathered buffer */ };
 typedef struct bsg_tp_comm bsg_tp_comm;
 int32_t bsg_tp_set_mode(bsg_tp_comm* comm, int32_t mode);
 int32_t bsg_tp_create(int32_t rank, int32_t world, int32_t kind, int64_t M, int64_t K, bsg_tp_comm** out,
