@@ -52,7 +52,7 @@ def measured_peaks() -> dict:
 class ClockSampler:
     """Samples SM clock and throttle reasons through NVML while the timed region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.01):
+    def __init__(self, index: int, period_s: float = 0.002):
         self.index, self.period = index, period_s
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
@@ -103,25 +103,7 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- operands
-def gpu_nvfp4_operand(rows: int, K: int, gen, device):
-    """Seeded NVFP4 operand generated on the device: 15 distinct e2m1 values (no -0), ue4m3 scales in {0.25..4}."""
-    import torch
-    from cutlass_b200 import formats as F
-    lut = torch.tensor([0, 1, 2, 3, 4, 5, 6, 7, 9, 10, 11, 12, 13, 14, 15], dtype=torch.uint8, device=device)
-    codes = lut[torch.randint(0, 15, (rows, K), device=device, generator=gen)]
-    packed = (codes[:, 0::2] | (codes[:, 1::2] << 4)).contiguous()
-    sfl = torch.tensor([0x28, 0x30, 0x38, 0x40, 0x48], dtype=torch.uint8, device=device)
-    sf = sfl[torch.randint(0, 5, (F.numel_scale(rows, K, 16),), device=device, generator=gen)]
-    return packed, sf
-
-
-def gpu_mxfp8_operand(rows: int, K: int, gen, device):
-    """Seeded MXFP8 operand: N(0,1) rounded to e4m3, ue8m0 scale exponents uniform in [-3, 3]."""
-    import torch
-    from cutlass_b200 import formats as F
-    data = torch.randn((rows, K), device=device, generator=gen).to(torch.float8_e4m3fn).view(torch.uint8)
-    sf = torch.randint(124, 131, (F.numel_scale(rows, K, 32),), dtype=torch.uint8, device=device, generator=gen)
-    return data, sf
+from cutlass_b200.generators import gpu_mxfp8_operand, gpu_nvfp4_operand  # noqa: E402,F401  (seeded, generated on the device)
 
 
 # --------------------------------------------------------------------------- CPU baseline
@@ -253,6 +235,27 @@ def run_single(args) -> dict:
     gf, wf = F.bf16_to_f32(got), F.bf16_to_f32(want)
     rel = float(np.max(np.abs(gf - wf)) / max(float(np.max(np.abs(wf))), 1e-30))
 
+    # ---- the quantiser in front of the GEMM on an operand of the same size (HBM-bound; reported beside the headline)
+    quant = None
+    try:
+        xs = [torch.randn((M, K), device=dev, generator=gen).to(torch.bfloat16) for _ in range(3)]   # 3 x 134 MB > L2
+        qo = [ops.quantize_blockscaled(x, mode) for x in xs]
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for i in range(30):
+            ops.quantize_blockscaled(xs[i % 3], mode, out=qo[i % 3].quantized.tensor, scale_out=qo[i % 3].scale.tensor, stream=stream)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        q_ms = e0.elapsed_time(e1) / 30
+        q_bytes = M * K * 2 + M * K // 2 + M * K // 16
+        hbm = measured_peaks().get("hbm_gbs") or 6650.0
+        quant = {"workload": f"bf16 {M}x{K} -> NVFP4 values + interleaved ue4m3 scale factors", "ms": round(q_ms, 4),
+                 "achieved_gbs": round(q_bytes / q_ms / 1e6, 1), "peak_gbs": hbm, "frac": round(q_bytes / q_ms / 1e6 / hbm, 4),
+                 "algorithmic_bytes": q_bytes, "bound": "hbm"}
+        del xs, qo
+    except Exception as exc:  # noqa: BLE001
+        quant = {"error": str(exc)}
+
     # ---- the tensor-parallel workload on this one GPU: the base of the 1/2/4/8-GPU scaling series
     tp_base = None
     if not args.no_tp_base:
@@ -297,6 +300,7 @@ def run_single(args) -> dict:
         "cpu_baseline": {k: (round(v, 5) if isinstance(v, float) else v) for k, v in cpu.items()},
         "parity": {"slab_rows": slab, "max_rel_err_vs_cpu_reference": rel},
         "scaling_base": tp_base,
+        "quantiser": quant,
     }
 
 

@@ -8,12 +8,13 @@ from .arguments import (DenseTensor, EpilogueDescriptor, GemmArguments, GemmProb
 from .operator import (AllocationRequirement, BlockScaledGemmOperator, CompiledArtifact,
                        GroupedBlockScaledGemmOperator, Operator, OperatorMetadata, Workspace, all_operators,
                        get_operators, to_cuda_stream)
+from .quantize import quantize_blockscaled
 from .status import Status
 
 __all__ = [
     "AllocationRequirement", "BlockScaledGemmOperator", "CompiledArtifact", "DenseTensor", "EpilogueDescriptor",
     "GemmArguments", "GemmProblemSize", "GroupedBlockScaledGemmOperator", "GroupedGemmArguments", "Nvfp4Quant",
     "Operator", "OperatorMetadata", "ScaleMode", "ScaleSwizzleMode", "ScaledOperand", "Status", "Workspace",
-    "all_operators", "get_operators", "to_cuda_stream",
+    "all_operators", "get_operators", "quantize_blockscaled", "to_cuda_stream",
 ]
 __version__ = "0.1.0"

@@ -13,7 +13,7 @@ CSRC = os.path.join(_HERE, "csrc")
 PROFILE = os.environ.get("BSG_PROFILE") == "1"      # ablation switches + timeline capture, separate file
 OUT = os.path.join(_HERE, "lib", "libbsgemm_profile.so" if PROFILE else "libbsgemm.so")
 SOURCES = ["bsgemm.cu"]
-HEADERS = ["gemm_kernel.cuh", "ptx.cuh", os.path.join("..", "..", "include", "bsgemm.h")]
+HEADERS = ["gemm_kernel.cuh", "quant_kernel.cuh", "ptx.cuh", os.path.join("..", "..", "include", "bsgemm.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--shared", "-Xcompiler", "-fPIC", "-cudart", "static",

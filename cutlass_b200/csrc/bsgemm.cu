@@ -16,6 +16,7 @@
 
 #include "../../include/bsgemm.h"
 #include "gemm_kernel.cuh"
+#include "quant_kernel.cuh"
 
 namespace {
 
@@ -508,6 +509,30 @@ int32_t bsg_gemm_run_static(const bsg_gemm_args* args, void* cuda_stream, uint32
     if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "reading the static scratch: %s", cudaGetErrorString(e));
     *device_status_out = st;
   }
+  return BSG_OK;
+}
+
+int32_t bsg_quantize(const bsg_quant_args* a, void* cuda_stream) {
+  if (!a) return fail(BSG_ERR_INVALID_PROBLEM, "args is null");
+  if (a->kind != BSG_KIND_NVFP4 && a->kind != BSG_KIND_MXFP8) return fail(BSG_ERR_NOT_SUPPORTED, "unknown operand kind %d", a->kind);
+  if (a->rows < 0 || a->K < 1) return fail(BSG_ERR_INVALID_PROBLEM, "extents must be positive (rows=%lld K=%lld)", (long long)a->rows, (long long)a->K);
+  if (a->rows > int64_t(65535) * bsg::kQuantTileRows || a->K > 0x3FFFFFFF) return fail(BSG_ERR_INVALID_PROBLEM, "extent too large");
+  if (a->K % 32 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "K=%lld must be a multiple of 32", (long long)a->K);
+  if (a->ldx < a->K || a->ldx % 8 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "ldx=%lld must be >= K and a multiple of 8 elements", (long long)a->ldx);
+  if (a->rows == 0) return BSG_OK;
+  if (!a->X || !a->Q || !a->SF) return fail(BSG_ERR_INVALID_PROBLEM, "X, Q and SF must not be null");
+  if (!aligned16(a->X) || !aligned16(a->Q) || !aligned16(a->SF)) return fail(BSG_ERR_MISALIGNED_OPERAND, "X, Q and SF must be 16-byte aligned");
+  const int64_t vec = a->kind == BSG_KIND_NVFP4 ? 16 : 32;
+  bsg::QuantParams p{};
+  p.X = static_cast<const uint16_t*>(a->X); p.Q = static_cast<uint8_t*>(a->Q); p.SF = static_cast<uint8_t*>(a->SF);
+  p.norm_ptr = a->norm_constant; p.ldx = a->ldx; p.rows = int32_t(a->rows); p.K = int32_t(a->K);
+  p.k_atoms = int32_t((a->K / vec + 3) / 4);
+  dim3 grid(unsigned((a->K + bsg::kQuantTileK - 1) / bsg::kQuantTileK), unsigned((a->rows + bsg::kQuantTileRows - 1) / bsg::kQuantTileRows));
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (a->kind == BSG_KIND_NVFP4) bsg::bsg_quant_kernel<0><<<grid, bsg::kQuantThreads, 0, stream>>>(p);
+  else bsg::bsg_quant_kernel<1><<<grid, bsg::kQuantThreads, 0, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "quantiser launch: %s", cudaGetErrorString(e));
   return BSG_OK;
 }
 

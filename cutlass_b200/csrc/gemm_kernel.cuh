@@ -522,8 +522,16 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           if (is_leader) { if (txb) ptx::mbar_arrive_expect_tx(full_local, txb * CG); else ptx::mbar_arrive(full_local); }
           const uint32_t bar = full0_leader + stage * 8;
           if (!BSG_FLAG(p, 2)) {
+#ifdef BSG_PROFILE
+            // Ablation: L2 eviction priorities (1 << 20: A evict-first, 1 << 19: B evict-last).
+            if (BSG_FLAG(p, 1 << 20)) ptx::tma_load_2d_hint<CG>(sA0 + stage * C::kABytes, &tmA, bar, kt * C::kRowBytes, a_row, ptx::l2_policy_evict_first());
+            else ptx::tma_load_2d<CG>(sA0 + stage * C::kABytes, &tmA, bar, kt * C::kRowBytes, a_row);
+            if (BSG_FLAG(p, 1 << 19)) ptx::tma_load_2d_hint<CG>(sB0 + stage * C::kBBytes, &tmB, bar, kt * C::kRowBytes, b_row, ptx::l2_policy_evict_last());
+            else ptx::tma_load_2d<CG>(sB0 + stage * C::kBBytes, &tmB, bar, kt * C::kRowBytes, b_row);
+#else
             ptx::tma_load_2d<CG>(sA0 + stage * C::kABytes, &tmA, bar, kt * C::kRowBytes, a_row);
             ptx::tma_load_2d<CG>(sB0 + stage * C::kBBytes, &tmB, bar, kt * C::kRowBytes, b_row);
+#endif
           }
           if (!BSG_FLAG(p, 16)) {
             ptx::tma_load_3d<CG>(sSFA0 + stage * C::kSfaBytes, &tmSFA, bar, 0, kt * C::kKAtoms, sfa_atom);
@@ -903,6 +911,10 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           ptx::fence_proxy_async();
           __syncwarp();
           if (lane == 0) {
+#ifdef BSG_PROFILE
+            if (BSG_FLAG(p, 1 << 18)) ptx::tma_store_2d_hint(&tmD, stage_addr, ti.tn * BN + pr * 64, cta_row0 + warp * 32, ptx::l2_policy_evict_first());
+            else
+#endif
             ptx::tma_store_2d(&tmD, stage_addr, ti.tn * BN + pr * 64, cta_row0 + warp * 32);
             ptx::bulk_commit_group();
           }

@@ -1,0 +1,136 @@
+// Block-scaled quantiser: bf16 (rows x K, row-major) -> NVFP4 or MXFP8 values plus scale factors
+// in the interleaved layout the GEMM reads (512-byte atoms of 128 rows x 4 K-blocks).
+//
+// The arithmetic is the reference's block-scale computation
+// (tools/util/include/cutlass/util/reference/host/gett.hpp:436-478): per row and K-block of V elements
+//   amax -> SF = cvt(amax * (st * (1 / fp_max))) -> q = cvt(x * min(st * (1 / float(SF)), FLT_MAX)),
+// every product separately rounded.  NVFP4: V = 16, SF ue4m3, q e2m1 (fp_max 6);  MXFP8: V = 32,
+// SF ue8m0 (the conversion rounds up), q e4m3 (fp_max 448).
+//
+// HBM-bound.  One CTA owns a tile of 128 rows x 256 elements: a warp reads one row of the tile per
+// step as 32 x 16 bytes (fully coalesced), the lanes that share a K-block combine their maxima with
+// shuffles, and every lane stores its own 8 quantised values (4 or 8 bytes, coalesced).  The tile's
+// scale factors are collected in shared memory in atom order and leave as whole 512-byte atoms.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cfloat>
+#include <cstdint>
+
+#include "ptx.cuh"
+
+namespace bsg {
+
+struct QuantParams {
+  const uint16_t* X;      // bf16 bits
+  uint8_t* Q;
+  uint8_t* SF;
+  const float* norm_ptr;  // device scalar st, or null for 1.0
+  int64_t ldx;            // elements between rows of X
+  int32_t rows, K;
+  int32_t k_atoms;        // ceil(K / V / 4)
+};
+
+constexpr int kQuantTileRows = 128;
+constexpr int kQuantTileK = 256;
+constexpr int kQuantThreads = 256;
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t b) { return __uint_as_float(b << 16); }
+
+// fp32 (>= 0) -> ue8m0 code, rounding up (float8.h:1174 of the reference uses the same instruction).
+__device__ __forceinline__ uint32_t cvt_ue8m0_rp(float x) {
+  uint16_t out;
+  asm volatile("cvt.rp.satfinite.ue8m0x2.f32 %0, %1, %2;" : "=h"(out) : "f"(0.0f), "f"(x));
+  return out & 0xFFu;
+}
+__device__ __forceinline__ float ue8m0_to_f32(uint32_t code) {
+  if (code == 0xFFu) return __uint_as_float(0x7FC00000u);
+  return code == 0u ? __uint_as_float(0x00400000u) : __uint_as_float(code << 23);   // 2^(code - 127)
+}
+__device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
+  uint16_t lo, hi;
+  asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+  asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+  return uint32_t(lo) | (uint32_t(hi) << 16);
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(kQuantThreads) bsg_quant_kernel(const QuantParams p) {
+  constexpr int V = KIND == 0 ? 16 : 32;
+  constexpr int kLanesPerBlock = V / 8;                     // lanes that share one K-block
+  constexpr int kBlocksPerTile = kQuantTileK / V;           // K-blocks of one row of the tile: 16 or 8
+  constexpr int kAtomsPerTile = kBlocksPerTile / 4;         // 4 or 2
+  __shared__ __align__(16) uint8_t s_sf[kAtomsPerTile * 512];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = blockIdx.y * kQuantTileRows;
+  const int k0 = blockIdx.x * kQuantTileK;
+  for (int i = threadIdx.x; i < kAtomsPerTile * 512 / 4; i += kQuantThreads) reinterpret_cast<uint32_t*>(s_sf)[i] = 0u;
+  __syncthreads();
+
+  const float st = p.norm_ptr ? *p.norm_ptr : 1.0f;
+  const float st_scaled = __fmul_rn(st, __fdiv_rn(1.0f, KIND == 0 ? 6.0f : 448.0f));
+  const int k = k0 + lane * 8;
+  const bool k_ok = k < p.K;
+  const int blk = lane / kLanesPerBlock;                    // K-block of this lane inside the tile row
+
+  constexpr int kUnroll = 4;
+  for (int r = warp; r < kQuantTileRows; r += 8 * kUnroll) {
+    uint4 raw[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int row = row0 + r + 8 * u;
+      raw[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (k_ok && row < p.rows) raw[u] = *reinterpret_cast<const uint4*>(p.X + int64_t(row) * p.ldx + k);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int rt = r + 8 * u, row = row0 + rt;
+      float x[8];
+      x[0] = bf16_bits_to_f32(raw[u].x & 0xFFFFu); x[1] = bf16_bits_to_f32(raw[u].x >> 16);
+      x[2] = bf16_bits_to_f32(raw[u].y & 0xFFFFu); x[3] = bf16_bits_to_f32(raw[u].y >> 16);
+      x[4] = bf16_bits_to_f32(raw[u].z & 0xFFFFu); x[5] = bf16_bits_to_f32(raw[u].z >> 16);
+      x[6] = bf16_bits_to_f32(raw[u].w & 0xFFFFu); x[7] = bf16_bits_to_f32(raw[u].w >> 16);
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(x[j]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      if constexpr (kLanesPerBlock == 4) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const float pv = __fmul_rn(amax, st_scaled);
+      uint32_t sf_code;
+      float sf_val;
+      if constexpr (KIND == 0) {
+        sf_code = ptx::cvt_ue4m3(pv);
+        sf_val = ptx::cvt_e4m3_to_f32(sf_code);
+      } else {
+        sf_code = cvt_ue8m0_rp(pv);
+        sf_val = ue8m0_to_f32(sf_code);
+      }
+      float sc = __fmul_rn(st, __fdiv_rn(1.0f, sf_val));
+      if (sc > FLT_MAX) sc = FLT_MAX;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(x[j], sc);
+      if (k_ok && row < p.rows) {
+        if constexpr (KIND == 0) {
+          *reinterpret_cast<uint32_t*>(p.Q + int64_t(row) * (p.K / 2) + k / 2) = ptx::cvt_e2m1x8(x);
+        } else {
+          uint2 q;
+          q.x = cvt_e4m3x4(x[0], x[1], x[2], x[3]);
+          q.y = cvt_e4m3x4(x[4], x[5], x[6], x[7]);
+          *reinterpret_cast<uint2*>(p.Q + int64_t(row) * p.K + k) = q;
+        }
+        if ((lane % kLanesPerBlock) == 0)
+          s_sf[(blk >> 2) * 512 + 16 * (rt & 31) + 4 * (rt >> 5) + (blk & 3)] = uint8_t(sf_code);
+      }
+    }
+  }
+  __syncthreads();
+  // Whole atoms leave in one piece: atom (row0 / 128, k0 / (4 V) + a), 512 bytes each, consecutive in memory.
+  const int atom0 = k0 / (4 * V);
+  const int n_atoms = min(kAtomsPerTile, p.k_atoms - atom0);
+  uint8_t* dst = p.SF + (int64_t(blockIdx.y) * p.k_atoms + atom0) * 512;
+  for (int i = threadIdx.x; i < n_atoms * 32; i += kQuantThreads)
+    reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(s_sf)[i];
+}
+
+}  // namespace bsg

@@ -69,3 +69,26 @@ def moe_group_sizes(num_experts: int, tokens: int, top_k: int, rng: np.random.Ge
 def grouped_sfa(sf_per_group) -> np.ndarray:
     """Concatenate per-group interleaved scale-factor buffers (each padded to 128 rows)."""
     return np.concatenate([F.swizzle_sf(sf) if sf.shape[0] > 0 else np.zeros(0, np.uint8) for sf in sf_per_group])
+
+
+# --------------------------------------------------------------------------- generated on the device
+def gpu_nvfp4_operand(rows: int, K: int, gen, device):
+    """Seeded NVFP4 operand generated on the device (full-size benchmark inputs): the 15 distinct e2m1
+    values (no -0), ue4m3 scales in {0.25, 0.5, 1, 2, 4}.  -> (packed (rows, K/2) uint8, interleaved scales)."""
+    import torch
+    from . import formats as F
+    lut = torch.tensor([0, 1, 2, 3, 4, 5, 6, 7, 9, 10, 11, 12, 13, 14, 15], dtype=torch.uint8, device=device)
+    codes = lut[torch.randint(0, 15, (rows, K), device=device, generator=gen)]
+    packed = (codes[:, 0::2] | (codes[:, 1::2] << 4)).contiguous()
+    sfl = torch.tensor([0x28, 0x30, 0x38, 0x40, 0x48], dtype=torch.uint8, device=device)
+    sf = sfl[torch.randint(0, 5, (F.numel_scale(rows, K, 16),), device=device, generator=gen)]
+    return packed, sf
+
+
+def gpu_mxfp8_operand(rows: int, K: int, gen, device):
+    """Seeded MXFP8 operand generated on the device: N(0,1) rounded to e4m3, ue8m0 scale exponents uniform in [-3, 3]."""
+    import torch
+    from . import formats as F
+    data = torch.randn((rows, K), device=device, generator=gen).to(torch.float8_e4m3fn).view(torch.uint8)
+    sf = torch.randint(124, 131, (F.numel_scale(rows, K, 32),), dtype=torch.uint8, device=device, generator=gen)
+    return data, sf

@@ -65,6 +65,12 @@ class Caps(C.Structure):
 
 
 # name -> (restype, argtypes); every symbol include/bsgemm.h declares.
+class QuantArgs(C.Structure):
+    """``bsg_quant_args`` of include/bsgemm.h, field for field."""
+    _fields_ = [("kind", C.c_int32), ("reserved0", C.c_int32), ("rows", C.c_int64), ("K", C.c_int64), ("X", C.c_void_p),
+                ("ldx", C.c_int64), ("Q", C.c_void_p), ("SF", C.c_void_p), ("norm_constant", C.c_void_p)]
+
+
 SYMBOLS = {
     "bsg_version": (C.c_int32, []),
     "bsg_last_error_string": (C.c_char_p, []),
@@ -77,6 +83,7 @@ SYMBOLS = {
     "bsg_workspace_init": (C.c_int32, [C.c_void_p, C.c_size_t, C.c_void_p]),
     "bsg_read_device_status": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "bsg_gemm_run_static": (C.c_int32, [C.POINTER(GemmArgs), C.c_void_p, C.POINTER(C.c_uint32)]),
+    "bsg_quantize": (C.c_int32, [C.POINTER(QuantArgs), C.c_void_p]),
     "bsg_tp_create": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.POINTER(C.c_void_p), C.c_void_p]),
     "bsg_tp_connect": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "bsg_tp_buffers": (C.c_int32, [C.c_void_p] + [C.POINTER(C.c_void_p)] * 4),

@@ -183,6 +183,34 @@ int32_t bsg_read_device_status(void* workspace, void* cuda_stream);
 int32_t bsg_gemm_run_static(const bsg_gemm_args* args, void* cuda_stream, uint32_t* device_status_out);
 
 /*
+ * Block-scaled quantiser: the step in front of the GEMM that turns a bf16 matrix X (rows x K,
+ * row-major) into a GEMM operand -- quantised values plus scale factors already in the interleaved
+ * layout (512-byte atoms of 128 rows x 4 K-blocks) that bsg_gemm_args.SFA / SFB expect.
+ * The reference leaves this step to the caller ("a quantization step or an earlier kernel",
+ * operators/examples/006_block_scaled_gemm.ipynb; layout contract
+ * operators/cutlass/operators/arguments/operand.py:353-367); the arithmetic is the one of its
+ * block-scale epilogue (tools/util/include/cutlass/util/reference/host/gett.hpp:436-478): per row and
+ * K-block, amax -> SF = cvt(amax * (st / fp_max)) -> q = cvt(x * min(st / float(SF), FLT_MAX)).
+ *   kind BSG_KIND_NVFP4: K-blocks of 16, SF ue4m3, values e2m1 packed two per byte (Q is rows x K/2 bytes);
+ *   kind BSG_KIND_MXFP8: K-blocks of 32, SF ue8m0 (conversion rounds up), values e4m3 (Q is rows x K bytes).
+ * SF receives whole atoms: ceil(rows/128) * ceil(K/V/4) * 512 bytes, zero where no row / K-block exists.
+ * norm_constant: device fp32 scalar st (NVFP4: typically 448 * 6 / amax of X; MXFP8: 1), NULL = 1.0.
+ * K must be a multiple of 32, ldx (in elements, >= K) a multiple of 8, all pointers 16-byte aligned.
+ * Asynchronous on cuda_stream; allocates nothing.
+ */
+typedef struct bsg_quant_args {
+  int32_t kind;
+  int32_t reserved0;
+  int64_t rows, K;
+  const void* X;
+  int64_t ldx;
+  void* Q;
+  void* SF;
+  const float* norm_constant;
+} bsg_quant_args;
+int32_t bsg_quantize(const bsg_quant_args* args, void* cuda_stream);
+
+/*
  * Tensor-parallel GEMM: D[:, local N shard] = alpha * A B_local^T + beta * C, with A (and SFA)
  * sharded by rows over `world` ranks (one process per GPU of one node) and B / D sharded over N.
  * The kernel itself gathers A over NVLink: a push warp in every CTA sends this rank's rows into the

@@ -53,6 +53,8 @@ def load_oracle() -> C.CDLL:
         [C.c_int64, C.c_float, C.c_float, C.c_int64, C.c_int64, C.c_void_p]
     lib.bsg_oracle_quant_nvfp4.restype = None
     lib.bsg_oracle_quant_nvfp4.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_void_p, C.c_void_p]
+    lib.bsg_oracle_quant.restype = None
+    lib.bsg_oracle_quant.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_void_p, C.c_void_p]
     lib.bsg_oracle_to_bf16.restype = None
     lib.bsg_oracle_to_bf16.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
     lib.bsg_oracle_threads.restype = C.c_int
@@ -116,6 +118,20 @@ def quant_nvfp4(x: np.ndarray, st: float):
     return D, SFD
 
 
+def quant(kind: int, x: np.ndarray, st: float = 1.0):
+    """C oracle: block-scaled quantisation of an fp32 matrix along its rows -> (values, interleaved scale factors).
+    kind 0: packed e2m1 + ue4m3 per 16; kind 1: e4m3 + ue8m0 per 32."""
+    lib = load_oracle()
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    M, N = x.shape
+    vec = 16 if kind == 0 else 32
+    nb = N // vec
+    D = np.zeros((M, N // 2 if kind == 0 else N), dtype=np.uint8)
+    SFD = np.zeros(-(-M // 128) * 128 * (-(-nb // 4)) * 4, dtype=np.uint8)
+    lib.bsg_oracle_quant(int(kind), _ptr(x), M, N, float(st), _ptr(D), _ptr(SFD))
+    return D, SFD
+
+
 def to_bf16(x: np.ndarray) -> np.ndarray:
     lib = load_oracle()
     x = np.ascontiguousarray(x, dtype=np.float32)
@@ -125,7 +141,7 @@ def to_bf16(x: np.ndarray) -> np.ndarray:
 
 
 def ref_gemm(kind: int, out_mode: int, A, SFA, B, SFB, M: int, N: int, K: int, C_bits=None, alpha=1.0, beta=0.0, st=0.0):
-    """Compiled reference: out_mode 0 fp32, 1 bf16 bits, 2 (packed e2m1, SFD)."""
+    """Compiled reference: out_mode 0 fp32, 1 bf16 bits, 2 (packed e2m1, ue4m3 SFD per 16), 3 (e4m3, ue8m0 SFD per 32)."""
     lib = load_ref()
     if lib is None:
         raise FileNotFoundError("oracle/_ref/libbsg_ref.so has not been built")
@@ -139,9 +155,13 @@ def ref_gemm(kind: int, out_mode: int, A, SFA, B, SFB, M: int, N: int, K: int, C
         D = np.zeros((M, N), dtype=np.float32)
     elif out_mode == 1:
         D = np.zeros((M, N), dtype=np.uint16)
-    else:
+    elif out_mode == 2:
         D = np.zeros((M, N // 2), dtype=np.uint8)
         nb = N // 16
+        sfd = np.zeros(-(-M // 128) * 128 * (-(-nb // 4)) * 4, dtype=np.uint8)
+    else:
+        D = np.zeros((M, N), dtype=np.uint8)
+        nb = N // 32
         sfd = np.zeros(-(-M // 128) * 128 * (-(-nb // 4)) * 4, dtype=np.uint8)
     rc = lib.bsg_ref_gemm(kind, out_mode, M, N, K, _ptr(A), _ptr(B), _ptr(SFA), _ptr(SFB), _ptr(Cb), alpha, beta, _ptr(D),
                           _ptr(sfd), float(st))

@@ -199,34 +199,52 @@ int bsg_oracle_gemm_rows(int kind, int64_t M, int64_t N, int64_t K, const uint8_
   return 0;
 }
 
-/* NVFP4 re-quantisation of an fp32 (M x N) matrix: packed e2m1 D (M x N/2) and interleaved ue4m3 SFD. */
-void bsg_oracle_quant_nvfp4(const float* x, int64_t M, int64_t N, float st, uint8_t* D, uint8_t* SFD) {
-  const float scale_down = 1.0f / 6.0f;
+/* Block-scaled quantisation of an fp32 (M x N) matrix along N, as the reference's epilogue and any
+ * quantiser in front of the GEMM do it (tools/util/include/cutlass/util/reference/host/gett.hpp:364-481,
+ * row-major branch :436-478): per row and per block of V elements, amax -> scale factor
+ * SF = cvt(amax * (st * (1 / fp_max))) -> values cvt(x * min(st * (1 / float(SF)), FLT_MAX)).
+ * kind 0: V = 16, SF ue4m3, values e2m1 packed two per byte (fp_max 6);
+ * kind 1: V = 32, SF ue8m0 (conversion rounds up), values e4m3 (fp_max 448).
+ * D is M x N/2 or M x N bytes; SFD is the interleaved scale-factor buffer (zero where nothing is written). */
+void bsg_oracle_quant(int kind, const float* x, int64_t M, int64_t N, float st, uint8_t* D, uint8_t* SFD) {
+  const int V = kind == 0 ? 16 : 32;
+  const int sf_fmt = kind == 0 ? 2 : 3, d_fmt = kind == 0 ? 0 : 1;
+  const float fp_max = kind == 0 ? 6.0f : 448.0f;
+  const float scale_down = 1.0f / fp_max;
   const float st_scaled = st * scale_down;
-  const int64_t nblocks = N / 16, k_atoms = (nblocks + 3) / 4;
+  const int64_t nblocks = N / V, k_atoms = (nblocks + 3) / 4;
   int64_t m;
 #pragma omp parallel for schedule(static)
   for (m = 0; m < M; ++m) {
     int64_t nb;
     for (nb = 0; nb < nblocks; ++nb) {
-      const float* v = x + m * N + nb * 16;
+      const float* v = x + m * N + nb * V;
       float amax = 0.f, pv, qf, rcp, sc;
       uint32_t q;
       int j;
-      for (j = 0; j < 16; ++j) { const float a = fabsf(v[j]); if (a > amax) amax = a; }
+      for (j = 0; j < V; ++j) { const float a = fabsf(v[j]); if (a > amax) amax = a; }
       pv = amax * st_scaled;
-      q = bsg_oracle_encode(2, pv);
+      q = bsg_oracle_encode(sf_fmt, pv);
       SFD[bsg_oracle_sf_offset(m, nb, k_atoms)] = (uint8_t)q;
-      qf = bsg_oracle_decode(2, q);
+      qf = bsg_oracle_decode(sf_fmt, q);
       rcp = 1.0f / qf;
       sc = st * rcp;
       if (sc > FLT_MAX) sc = FLT_MAX;
-      for (j = 0; j < 16; j += 2) {
-        const uint32_t lo = bsg_oracle_encode(0, v[j] * sc), hi = bsg_oracle_encode(0, v[j + 1] * sc);
-        D[m * (N / 2) + nb * 8 + j / 2] = (uint8_t)(lo | (hi << 4));
+      if (kind == 0) {
+        for (j = 0; j < V; j += 2) {
+          const uint32_t lo = bsg_oracle_encode(d_fmt, v[j] * sc), hi = bsg_oracle_encode(d_fmt, v[j + 1] * sc);
+          D[m * (N / 2) + nb * 8 + j / 2] = (uint8_t)(lo | (hi << 4));
+        }
+      } else {
+        for (j = 0; j < V; ++j) D[m * N + nb * V + j] = (uint8_t)bsg_oracle_encode(d_fmt, v[j] * sc);
       }
     }
   }
+}
+
+/* NVFP4 re-quantisation of an fp32 (M x N) matrix: packed e2m1 D (M x N/2) and interleaved ue4m3 SFD. */
+void bsg_oracle_quant_nvfp4(const float* x, int64_t M, int64_t N, float st, uint8_t* D, uint8_t* SFD) {
+  bsg_oracle_quant(0, x, M, N, st, D, SFD);
 }
 
 void bsg_oracle_to_bf16(const float* x, int64_t n, uint16_t* out) {

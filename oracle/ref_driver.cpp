@@ -27,7 +27,7 @@ using SfCfg = cutlass::detail::Sm1xxBlockScaledConfig<Vec>;
 template <int Vec>
 using SfOutCfg = cutlass::detail::Sm1xxBlockScaledOutputConfig<Vec>;
 
-template <class ElemAB, class ElemSF, int Vec, class ElemD, bool GenSfd>
+template <class ElemAB, class ElemSF, int Vec, class ElemD, bool GenSfd, int SfdVec = 16, class ElemSFD = cutlass::float_ue4m3_t>
 void run_gemm(int M, int N, int K, const void* A, const void* B, const void* SFA, const void* SFB,
               const cutlass::bfloat16_t* C, float alpha, float beta, void* D, void* SFD, float st) {
   auto layout_A = make_layout(make_shape(M, K, 1), make_stride(int64_t(K), _1{}, int64_t(M) * K));
@@ -46,10 +46,10 @@ void run_gemm(int M, int N, int K, const void* A, const void* B, const void* SFA
   Tensor tC = make_tensor(const_cast<cutlass::bfloat16_t*>(C), layout_C);
   Tensor tD = make_tensor(recast_ptr<ElemD>(D), layout_C);
   if constexpr (GenSfd) {
-    auto layout_SFD = SfOutCfg<16>::tile_atom_to_shape_SFD(make_shape(M, N, K, 1));
-    Tensor tSFD = make_tensor(reinterpret_cast<cutlass::float_ue4m3_t*>(SFD), layout_SFD);
+    auto layout_SFD = SfOutCfg<SfdVec>::tile_atom_to_shape_SFD(make_shape(M, N, K, 1));
+    Tensor tSFD = make_tensor(reinterpret_cast<ElemSFD*>(SFD), layout_SFD);
     cutlass::reference::host::GettBlockScalingEpilogueParams<float, float, float, decltype(tC), decltype(tD), decltype(tSFD),
-                                                             cute::Int<16>, cutlass::reference::host::SfStrategy::SfDGen>
+                                                             cute::Int<SfdVec>, cutlass::reference::host::SfStrategy::SfDGen>
         epi{alpha, beta, tC, tD, tSFD, st};
     cutlass::reference::host::Gemm3x(mainloop, epi);
   } else {
@@ -96,7 +96,8 @@ int64_t bsg_ref_sf_size(int vec, int rows, int K) {
   return int64_t(size(filter_zeros(SfCfg<32>::tile_atom_to_shape_SFA(make_shape(rows, 1, K, 1)))));
 }
 
-// kind 0 NVFP4 / 1 MXFP8.  out_mode 0: D fp32, 1: D bf16, 2: D e2m1 + SFD ue4m3 (NVFP4 re-quantisation with norm constant st).
+// kind 0 NVFP4 / 1 MXFP8.  out_mode 0: D fp32, 1: D bf16, 2: D e2m1 + SFD ue4m3 per 16 (NVFP4 re-quantisation with norm
+// constant st), 3: D e4m3 + SFD ue8m0 per 32 (MXFP8 re-quantisation).
 // C is bf16 (may be null when beta == 0).  Returns 0 on success.
 int bsg_ref_gemm(int kind, int out_mode, int M, int N, int K, const void* A, const void* B, const void* SFA, const void* SFB,
                  const void* C, float alpha, float beta, void* D, void* SFD, float st) {
@@ -107,6 +108,7 @@ int bsg_ref_gemm(int kind, int out_mode, int M, int N, int K, const void* A, con
     if (out_mode == 0) run_gemm<E, S, 16, float, false>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, nullptr, 0.f);
     else if (out_mode == 1) run_gemm<E, S, 16, cutlass::bfloat16_t, false>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, nullptr, 0.f);
     else if (out_mode == 2) run_gemm<E, S, 16, cutlass::float_e2m1_t, true>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, SFD, st);
+    else if (out_mode == 3) run_gemm<E, S, 16, cutlass::float_e4m3_t, true, 32, cutlass::float_ue8m0_t>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, SFD, st);
     else return 1;
   } else if (kind == 1) {
     using E = cutlass::float_e4m3_t;
@@ -114,6 +116,7 @@ int bsg_ref_gemm(int kind, int out_mode, int M, int N, int K, const void* A, con
     if (out_mode == 0) run_gemm<E, S, 32, float, false>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, nullptr, 0.f);
     else if (out_mode == 1) run_gemm<E, S, 32, cutlass::bfloat16_t, false>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, nullptr, 0.f);
     else if (out_mode == 2) run_gemm<E, S, 32, cutlass::float_e2m1_t, true>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, SFD, st);
+    else if (out_mode == 3) run_gemm<E, S, 32, cutlass::float_e4m3_t, true, 32, cutlass::float_ue8m0_t>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, SFD, st);
     else return 1;
   } else {
     return 1;

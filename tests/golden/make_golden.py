@@ -45,7 +45,7 @@ def main() -> None:
         tab = np.array([[ref.bsg_ref_sf_offset(vec, rows, K, r, k * vec) for k in range(kb)] for r in range(rows)], dtype=np.int64)
         out[f"sf_offset_{vec}_{rows}_{K}"] = tab
         out[f"sf_size_{vec}_{rows}_{K}"] = np.array([ref.bsg_ref_sf_size(vec, rows, K)], dtype=np.int64)
-    # --- GEMMs (fp32 and bf16 outputs) and the fused NVFP4 output quantisation
+    # --- GEMMs (fp32 and bf16 outputs) and the block-scaled output quantisation (NVFP4 and MXFP8)
     cases = [("nvfp4_a", 0, 96, 80, 128, 1.0, 0.5), ("nvfp4_b", 0, 130, 48, 320, 0.75, 0.0),
              ("mxfp8_a", 1, 96, 80, 128, 1.0, 0.5), ("mxfp8_b", 1, 40, 136, 96, -1.25, 2.0)]
     for name, kind, M, N, K, alpha, beta in cases:
@@ -71,6 +71,10 @@ def main() -> None:
     out.update({f"{name}_A": A, f"{name}_B": B, f"{name}_SFA": sfa, f"{name}_SFB": sfb, f"{name}_C": Cb,
                 f"{name}_dims": np.array([0, M, N, K], dtype=np.int64), f"{name}_st": np.array([st], dtype=np.float32),
                 f"{name}_D": Dq, f"{name}_SFD": SFD, f"{name}_D32": d32})
+    # the same accumulators quantised to MXFP8 (e4m3 values, ue8m0 scale per 32, conversion rounds up)
+    for tag, st_mx in (("mx1", np.float32(1.0)), ("mx2", np.float32(448.0 / np.abs(d32).max()))):
+        Dm, SFm = oracle.ref_gemm(0, 3, A, sfa, B, sfb, M, N, K, Cb, 1.0, 0.5, st_mx)
+        out.update({f"{name}_st_{tag}": np.array([st_mx], dtype=np.float32), f"{name}_D_{tag}": Dm, f"{name}_SFD_{tag}": SFm})
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "blockscaled_golden.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes,", len(out), "arrays")

@@ -104,3 +104,31 @@ def test_grouped_query(lib):
     g.num_groups = 4
     g.offsets = None
     assert lib.bsg_grouped_query(C.byref(g), None) == 2
+
+
+def _quant_args(**kw):
+    a = L.QuantArgs()
+    a.kind, a.rows, a.K, a.ldx = 0, 256, 256, 256
+    a.X = a.Q = a.SF = 0x10000          # rejected before anything is dereferenced or launched
+    for k, v in kw.items():
+        setattr(a, k, v)
+    return a
+
+
+@pytest.mark.parametrize("kw,code", [
+    (dict(kind=7), 3),
+    (dict(K=48, ldx=48), 1),        # K must be a multiple of 32
+    (dict(ldx=250), 1),             # shorter than K
+    (dict(ldx=260), 1),             # rows not 16-byte aligned
+    (dict(rows=-1), 2),
+    (dict(X=None), 2),
+    (dict(SF=0x10004), 1),
+])
+def test_quantiser_rejects_bad_arguments_before_launching(lib, kw, code):
+    assert C.sizeof(L.QuantArgs) == 8 + 16 + 8 + 8 + 24
+    assert lib.bsg_quantize(C.byref(_quant_args(**kw)), None) == code
+    assert lib.bsg_last_error_string()
+
+
+def test_quantiser_accepts_an_empty_matrix(lib):
+    assert lib.bsg_quantize(C.byref(_quant_args(rows=0)), None) == L.BSG_OK

@@ -54,6 +54,21 @@ def test_quantisation_bit_exact_on_golden(golden):
         assert np.array_equal(SFD[idx], golden["quant_a_SFD"][idx])
 
 
+def test_mxfp8_quantisation_bit_exact_on_golden(golden):
+    """e4m3 values + ue8m0 scale per 32 (round-up conversion), from the reference's own epilogue."""
+    kind, M, N, K, A, sfa, B, sfb, Cb = _case(golden, "quant_a")
+    d32 = oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K, Cb, 1.0, 0.5)
+    idx = R.sf_index(M, N // 32)
+    for tag in ("mx1", "mx2"):
+        st = float(golden[f"quant_a_st_{tag}"][0])
+        D, SFD = oracle.quant(1, d32, st)
+        assert np.array_equal(D, golden[f"quant_a_D_{tag}"])
+        assert np.array_equal(SFD[idx], golden[f"quant_a_SFD_{tag}"][idx])
+    # kind 0 of the general entry point is the NVFP4 routine
+    D0, S0 = oracle.quant(0, d32, float(golden["quant_a_st"][0]))
+    assert np.array_equal(D0, golden["quant_a_D"])
+
+
 def test_quantisation_edge_values():
     x = np.zeros((3, 32), np.float32)
     x[1, :16] = 1e-30          # underflows the scale factor to zero
