@@ -4,7 +4,7 @@ tensor-parallel forms.  The Python surface keeps the shape of the CUTLASS Python
 Operator API; the work is done by hand-written CUDA behind a C ABI
 (``include/bsgemm.h``, loaded by ``cutlass_b200.lib``)."""
 from .arguments import (DenseTensor, EpilogueDescriptor, GemmArguments, GemmProblemSize, GroupedGemmArguments,
-                        Nvfp4Quant, ScaledOperand, ScaleMode, ScaleSwizzleMode)
+                        Mxfp8Quant, Nvfp4Quant, ScaledOperand, ScaleMode, ScaleSwizzleMode)
 from .operator import (AllocationRequirement, BlockScaledGemmOperator, CompiledArtifact,
                        GroupedBlockScaledGemmOperator, Operator, OperatorMetadata, Workspace, all_operators,
                        get_operators, to_cuda_stream)
@@ -13,7 +13,7 @@ from .status import Status
 
 __all__ = [
     "AllocationRequirement", "BlockScaledGemmOperator", "CompiledArtifact", "DenseTensor", "EpilogueDescriptor",
-    "GemmArguments", "GemmProblemSize", "GroupedBlockScaledGemmOperator", "GroupedGemmArguments", "Nvfp4Quant",
+    "GemmArguments", "GemmProblemSize", "GroupedBlockScaledGemmOperator", "GroupedGemmArguments", "Mxfp8Quant", "Nvfp4Quant",
     "Operator", "OperatorMetadata", "ScaleMode", "ScaleSwizzleMode", "ScaledOperand", "Status", "Workspace",
     "all_operators", "get_operators", "quantize_blockscaled", "to_cuda_stream",
 ]

@@ -163,6 +163,17 @@ class Nvfp4Quant:
 
 
 @dataclass
+class Mxfp8Quant:
+    """Fused MXFP8 re-quantisation of the output: per row and per 32 columns,
+    ``SF = ue8m0(amax * norm_constant / 448)`` (the conversion rounds up) and
+    ``D = e4m3(x * norm_constant / SF)``.  ``scale`` receives the scale factors in the
+    Swizzle32x4x4 layout over (M, N/32); ``norm_constant`` is a one-element fp32 CUDA tensor or None (1)."""
+
+    scale: torch.Tensor
+    norm_constant: torch.Tensor | None = None
+
+
+@dataclass
 class EpilogueDescriptor:
     """``out = alpha * acc + beta * C`` followed by the output conversion.
     ``alpha`` / ``beta`` are Python floats or one-element fp32 CUDA tensors."""
@@ -170,7 +181,7 @@ class EpilogueDescriptor:
     alpha: float | torch.Tensor = 1.0
     beta: float | torch.Tensor = 0.0
     C: torch.Tensor | None = None
-    out_quant: Nvfp4Quant | None = None
+    out_quant: Nvfp4Quant | Mxfp8Quant | None = None
 
 
 def _logical_k(op, axis: int) -> int:
@@ -202,7 +213,7 @@ class GemmArguments:
 
     @property
     def out_is_packed_fp4(self) -> bool:
-        return self.epilogue is not None and self.epilogue.out_quant is not None
+        return self.epilogue is not None and isinstance(self.epilogue.out_quant, Nvfp4Quant)
 
     @property
     def problem_size(self) -> GemmProblemSize:

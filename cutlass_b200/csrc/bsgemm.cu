@@ -133,7 +133,7 @@ struct Plan {
 
 int32_t validate(const Problem& q, Plan* plan) {
   if (q.kind != BSG_KIND_NVFP4 && q.kind != BSG_KIND_MXFP8) return fail(BSG_ERR_NOT_SUPPORTED, "unknown operand kind %d", q.kind);
-  if (q.out_kind != BSG_OUT_BF16 && q.out_kind != BSG_OUT_NVFP4) return fail(BSG_ERR_NOT_SUPPORTED, "unknown output kind %d", q.out_kind);
+  if (q.out_kind != BSG_OUT_BF16 && q.out_kind != BSG_OUT_NVFP4 && q.out_kind != BSG_OUT_MXFP8) return fail(BSG_ERR_NOT_SUPPORTED, "unknown output kind %d", q.out_kind);
   if (q.num_groups < 1 || q.num_groups > BSG_MAX_GROUPS) return fail(BSG_ERR_INVALID_PROBLEM, "group / batch count %d outside [1, %d]", q.num_groups, BSG_MAX_GROUPS);
   if (q.N < 1 || q.K < 1 || q.total_rows < 0) return fail(BSG_ERR_INVALID_PROBLEM, "extents must be positive (rows=%lld N=%lld K=%lld)", (long long)q.total_rows, (long long)q.N, (long long)q.K);
   if (q.total_rows > 0x7FFFFFFF / 2 || q.N > 0x7FFFFFFF / 2 || q.K > 0x7FFFFFFF / 2) return fail(BSG_ERR_INVALID_PROBLEM, "extent exceeds 2^30");
@@ -145,6 +145,10 @@ int32_t validate(const Problem& q, Plan* plan) {
   if (!aligned16(q.SFA) || !aligned16(q.SFB)) return fail(BSG_ERR_MISALIGNED_OPERAND, "scale-factor tensors must be 16-byte aligned");
   if (q.out_kind == BSG_OUT_BF16) {
     if (q.N % 8 != 0 || q.ldd % 8 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "bf16 output needs N and ldd to be multiples of 8");
+  } else if (q.out_kind == BSG_OUT_MXFP8) {
+    if (!q.SFD) return fail(BSG_ERR_INVALID_PROBLEM, "MXFP8 output needs SFD");
+    if (q.N % 32 != 0 || q.ldd % 16 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "MXFP8 output needs N %% 32 == 0 and ldd %% 16 == 0");
+    if (q.offsets) return fail(BSG_ERR_NOT_SUPPORTED, "MXFP8 output is not available for grouped GEMM");
   } else {
     if (!q.SFD || !q.norm_ptr) return fail(BSG_ERR_INVALID_PROBLEM, "NVFP4 output needs SFD and norm_constant");
     if (q.N % 16 != 0 || q.ldd % 32 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "NVFP4 output needs N %% 16 == 0 and ldd %% 32 == 0");
@@ -183,6 +187,7 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   CUtensorMap tmA, tmB, tmSFA, tmSFB, tmD;
   int32_t rc;
   if (q.out_kind == BSG_OUT_BF16) rc = make_out_map(&tmD, q.D, true, uint64_t(q.N), uint64_t(q.total_rows), uint64_t(q.ldd) * 2);
+  else if (q.out_kind == BSG_OUT_MXFP8) rc = make_out_map(&tmD, q.D, false, uint64_t(q.N), uint64_t(q.total_rows), uint64_t(q.ldd));   // not used by the kernel
   else rc = make_out_map(&tmD, q.D, false, uint64_t(q.N / 2), uint64_t(q.total_rows), uint64_t(q.ldd) / 2);   // not used by the kernel
   if (rc != BSG_OK) return rc;
   // Tensor parallel: the two gathered buffers lie back to back, one map covers both.

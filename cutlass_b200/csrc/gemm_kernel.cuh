@@ -40,6 +40,7 @@ constexpr int kKindNvfp4 = 0;
 constexpr int kKindMxfp8 = 1;
 constexpr int kOutBf16 = 0;
 constexpr int kOutNvfp4 = 1;
+constexpr int kOutMxfp8 = 2;
 
 // Bits of the device status word.
 constexpr uint32_t kStTimeoutFull = 1u;       // MMA warp: operands never arrived
@@ -752,11 +753,12 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const float beta = p.beta_ptr ? *p.beta_ptr : p.beta;
     const bool use_c = (p.C != nullptr) && (beta != 0.0f);
     float st = 0.f, st_scaled = 0.f;
-    if (p.out_kind == kOutNvfp4) {
-      st = *p.norm_ptr;
-      st_scaled = __fmul_rn(st, __fdiv_rn(1.0f, 6.0f));
+    if (p.out_kind != kOutBf16) {
+      st = p.norm_ptr ? *p.norm_ptr : 1.0f;
+      st_scaled = __fmul_rn(st, __fdiv_rn(1.0f, p.out_kind == kOutNvfp4 ? 6.0f : 448.0f));
     }
-    const int32_t sfd_k_atoms = ((p.N + 15) / 16 + 3) / 4;
+    const int32_t sfd_vec = p.out_kind == kOutMxfp8 ? 32 : 16;
+    const int32_t sfd_k_atoms = ((p.N + sfd_vec - 1) / sfd_vec + 3) / 4;
     const uint32_t tfull0 = ptx::smem_u32(&ctl->tmem_full[0]);
     const uint32_t tempty0 = ptx::smem_u32(&ctl->tmem_empty[0]);
     uint8_t* stage_buf = sEpi + warp * 4096;                     // this warp's 32 x 128-byte staging tile
@@ -868,6 +870,30 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                   if (j < cols_valid) drow[j] = __float2bfloat16_rn(x[j]);
                 }
               }
+            }
+          } else if (p.out_kind == kOutMxfp8) {
+            // MXFP8 re-quantisation: one ue8m0 scale factor (round-up conversion) for the 32 columns of
+            // this row held here, e4m3 values; same routine of the reference host GEMM as below.
+            uint8_t* drow = reinterpret_cast<uint8_t*>(p.D) + int64_t(grow) * p.ldd + col0;
+            float amax = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(x[j]));
+            const float pv = __fmul_rn(amax, st_scaled);
+            const uint32_t q = ptx::cvt_ue8m0_rp(pv);
+            float sc = __fmul_rn(st, __fdiv_rn(1.0f, ptx::ue8m0_to_f32(q)));
+            sc = fminf(sc, FLT_MAX);
+            uint32_t w[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              w[e] = ptx::cvt_e4m3x4(__fmul_rn(x[e * 4 + 0], sc), __fmul_rn(x[e * 4 + 1], sc), __fmul_rn(x[e * 4 + 2], sc),
+                                     __fmul_rn(x[e * 4 + 3], sc));
+            const int32_t nb = col0 >> 5;
+            uint8_t* sfp = p.SFD + (int64_t(ti.group_atom0) + lrow / 128) * (512ll * sfd_k_atoms) + (nb >> 2) * 512 +
+                           16 * (lrow & 31) + 4 * ((lrow & 127) >> 5) + (nb & 3);
+            if (cols_valid >= 32) {
+              reinterpret_cast<uint4*>(drow)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+              reinterpret_cast<uint4*>(drow)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+              *sfp = uint8_t(q);
             }
           } else {
             // NVFP4 re-quantisation, one scale factor per 16 columns of this row; same

@@ -387,6 +387,23 @@ __device__ __forceinline__ float cvt_e4m3_to_f32(uint32_t code) {
   return __half2float(__low2half(h));
 }
 
+// fp32 (>= 0) -> ue8m0 code, rounding up (float8.h:1174 of the reference uses the same instruction).
+__device__ __forceinline__ uint32_t cvt_ue8m0_rp(float x) {
+  uint16_t out;
+  asm volatile("cvt.rp.satfinite.ue8m0x2.f32 %0, %1, %2;" : "=h"(out) : "f"(0.0f), "f"(x));
+  return out & 0xFFu;
+}
+__device__ __forceinline__ float ue8m0_to_f32(uint32_t code) {
+  if (code == 0xFFu) return __uint_as_float(0x7FC00000u);
+  return code == 0u ? __uint_as_float(0x00400000u) : __uint_as_float(code << 23);   // 2^(code - 127)
+}
+__device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
+  uint16_t lo, hi;
+  asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+  asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+  return uint32_t(lo) | (uint32_t(hi) << 16);
+}
+
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");

@@ -37,23 +37,6 @@ constexpr int kQuantThreads = 256;
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t b) { return __uint_as_float(b << 16); }
 
-// fp32 (>= 0) -> ue8m0 code, rounding up (float8.h:1174 of the reference uses the same instruction).
-__device__ __forceinline__ uint32_t cvt_ue8m0_rp(float x) {
-  uint16_t out;
-  asm volatile("cvt.rp.satfinite.ue8m0x2.f32 %0, %1, %2;" : "=h"(out) : "f"(0.0f), "f"(x));
-  return out & 0xFFu;
-}
-__device__ __forceinline__ float ue8m0_to_f32(uint32_t code) {
-  if (code == 0xFFu) return __uint_as_float(0x7FC00000u);
-  return code == 0u ? __uint_as_float(0x00400000u) : __uint_as_float(code << 23);   // 2^(code - 127)
-}
-__device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
-  uint16_t lo, hi;
-  asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
-  asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
-  return uint32_t(lo) | (uint32_t(hi) << 16);
-}
-
 template <int KIND>
 __global__ void __launch_bounds__(kQuantThreads) bsg_quant_kernel(const QuantParams p) {
   constexpr int V = KIND == 0 ? 16 : 32;
@@ -103,8 +86,8 @@ __global__ void __launch_bounds__(kQuantThreads) bsg_quant_kernel(const QuantPar
         sf_code = ptx::cvt_ue4m3(pv);
         sf_val = ptx::cvt_e4m3_to_f32(sf_code);
       } else {
-        sf_code = cvt_ue8m0_rp(pv);
-        sf_val = ue8m0_to_f32(sf_code);
+        sf_code = ptx::cvt_ue8m0_rp(pv);
+        sf_val = ptx::ue8m0_to_f32(sf_code);
       }
       float sc = __fmul_rn(st, __fdiv_rn(1.0f, sf_val));
       if (sc > FLT_MAX) sc = FLT_MAX;
@@ -115,8 +98,8 @@ __global__ void __launch_bounds__(kQuantThreads) bsg_quant_kernel(const QuantPar
           *reinterpret_cast<uint32_t*>(p.Q + int64_t(row) * (p.K / 2) + k / 2) = ptx::cvt_e2m1x8(x);
         } else {
           uint2 q;
-          q.x = cvt_e4m3x4(x[0], x[1], x[2], x[3]);
-          q.y = cvt_e4m3x4(x[4], x[5], x[6], x[7]);
+          q.x = ptx::cvt_e4m3x4(x[0], x[1], x[2], x[3]);
+          q.y = ptx::cvt_e4m3x4(x[4], x[5], x[6], x[7]);
           *reinterpret_cast<uint2*>(p.Q + int64_t(row) * p.K + k) = q;
         }
         if ((lane % kLanesPerBlock) == 0)

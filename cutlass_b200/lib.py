@@ -29,6 +29,7 @@ KIND_NVFP4 = 0
 KIND_MXFP8 = 1
 OUT_BF16 = 0
 OUT_NVFP4 = 1
+OUT_MXFP8 = 2
 MAX_GROUPS = 256
 
 

@@ -19,7 +19,7 @@ from typing import Callable
 import torch
 
 from . import lib as L
-from .arguments import (DenseTensor, EpilogueDescriptor, GemmArguments, GroupedGemmArguments, ScaledOperand,
+from .arguments import (DenseTensor, EpilogueDescriptor, GemmArguments, GroupedGemmArguments, Mxfp8Quant, ScaledOperand,
                         ScaleMode, ScaleSwizzleMode, _E8M0, _FP4X2, _logical_k)
 from .status import Status
 
@@ -245,6 +245,19 @@ class BlockScaledGemmOperator(Operator):
                 return Status.fail(f"out dtype {out.dtype} is not supported (bf16, or packed fp4 with out_quant)")
             if ps.N % 8 != 0:
                 return Status.fail("N must be a multiple of 8 for bf16 output")
+        elif isinstance(epi.out_quant, Mxfp8Quant):
+            if out.dtype not in (torch.uint8, torch.float8_e4m3fn):
+                return Status.fail("MXFP8 output needs a uint8 / float8_e4m3fn out tensor")
+            if ps.L != 1:
+                return Status.fail("MXFP8 output is not batched")
+            if ps.N % 32 != 0:
+                return Status.fail("N must be a multiple of 32 for MXFP8 output")
+            want = ScaledOperand.numel_scale((ps.L, ps.M, ps.N), ScaleMode.Blockwise1x32, ScaleSwizzleMode.Swizzle32x4x4)
+            if epi.out_quant.scale.numel() != want or not epi.out_quant.scale.is_contiguous():
+                return Status.fail(f"out_quant.scale must be contiguous with {want} elements")
+            nc = epi.out_quant.norm_constant
+            if nc is not None and (nc.numel() != 1 or nc.dtype != torch.float32):
+                return Status.fail("out_quant.norm_constant must be a one-element float32 tensor")
         else:
             if not (out.dtype == torch.uint8 or (_FP4X2 is not None and out.dtype == _FP4X2)):
                 return Status.fail("NVFP4 output needs a packed fp4 (uint8 / float4_e2m1fn_x2) out tensor")
@@ -273,7 +286,7 @@ class BlockScaledGemmOperator(Operator):
         epi = args.epilogue or EpilogueDescriptor()
         a = L.GemmArgs()
         a.kind = md.kind
-        a.out_kind = L.OUT_NVFP4 if epi.out_quant is not None else L.OUT_BF16
+        a.out_kind = L.OUT_BF16 if epi.out_quant is None else (L.OUT_MXFP8 if isinstance(epi.out_quant, Mxfp8Quant) else L.OUT_NVFP4)
         a.batch = ps.L
         a.M, a.N, a.K = ps.M, ps.N, ps.K
         a.A = args.A.quantized.data_ptr()
@@ -290,7 +303,8 @@ class BlockScaledGemmOperator(Operator):
         a.beta_ptr = beta_ptr
         if epi.out_quant is not None:
             a.SFD = epi.out_quant.scale.data_ptr()
-            a.norm_constant = epi.out_quant.norm_constant.data_ptr()
+            nc = epi.out_quant.norm_constant
+            a.norm_constant = nc.data_ptr() if nc is not None else None
         a.tile_n = md.tile_n
         a.cta_group = md.cta_group
         return a

@@ -41,7 +41,8 @@ enum {
 /* Output formats. */
 enum {
   BSG_OUT_BF16 = 0,         /* D = bf16(alpha*acc + beta*C) */
-  BSG_OUT_NVFP4 = 1         /* D = e2m1 packed + SFD ue4m3 per 16 N-elements, interleaved layout */
+  BSG_OUT_NVFP4 = 1,        /* D = e2m1 packed + SFD ue4m3 per 16 N-elements, interleaved layout */
+  BSG_OUT_MXFP8 = 2         /* D = e4m3 + SFD ue8m0 (round-up conversion) per 32 N-elements, interleaved layout */
 };
 
 /*
@@ -67,15 +68,15 @@ typedef struct bsg_gemm_args {
   const void* SFA;
   const void* SFB;
   const void* C;            /* bf16, may be NULL when beta == 0 */
-  void* D;                  /* bf16, or packed e2m1 when out_kind == BSG_OUT_NVFP4 */
-  void* SFD;                /* ue4m3, interleaved over (M, N/16); BSG_OUT_NVFP4 only */
+  void* D;                  /* bf16; packed e2m1 (BSG_OUT_NVFP4); e4m3 (BSG_OUT_MXFP8) */
+  void* SFD;                /* scale factors of D, interleaved over (M, N/16) or (M, N/32); quantised outputs only */
   int64_t ldc;              /* C row pitch in elements (0 = N) */
   int64_t ldd;              /* D row pitch in elements (0 = N) */
   float alpha;
   float beta;
   const float* alpha_ptr;   /* optional device scalars, override alpha / beta */
   const float* beta_ptr;
-  const float* norm_constant; /* device fp32 scalar, BSG_OUT_NVFP4 only */
+  const float* norm_constant; /* device fp32 scalar: required for BSG_OUT_NVFP4, optional (NULL = 1) for BSG_OUT_MXFP8 */
   int32_t tile_n;           /* 0 = library default, else 128 or 256 */
   int32_t cta_group;        /* 0 = default, else 1 or 2 (CTAs per MMA) */
   int32_t sm_count;         /* 0 = all SMs of the current device */

@@ -28,7 +28,7 @@ def make_operands(kind: int, M: int, N: int, K: int, seed: int, exact: bool):
 
 def run_dense(kind, M, N, K, A, sfa, B, sfb, Cb=None, alpha=1.0, beta=0.0, out_kind=0, st=None, tile_n=0, cta_group=0,
               batch=1, check_status=True):
-    """-> bf16 bits (batch*M, N), or (packed e2m1, SFD buffer) for out_kind 1."""
+    """-> bf16 bits (batch*M, N), or (quantised values, SFD buffer) for out_kind 1 (NVFP4) / 2 (MXFP8)."""
     lib = L.load()
     dA, dB, dSFA, dSFB = dev(A), dev(B), dev(sfa), dev(sfb)
     dC = dev(Cb) if Cb is not None else None
@@ -44,11 +44,14 @@ def run_dense(kind, M, N, K, A, sfa, B, sfb, Cb=None, alpha=1.0, beta=0.0, out_k
     if out_kind == 0:
         dD = torch.full((rows, N), 0x7FC0, dtype=torch.int16, device="cuda")      # NaN pattern: unwritten cells show up
     else:
-        dD = torch.full((rows, N // 2), 0x77, dtype=torch.uint8, device="cuda")
-        dSFD = torch.full((batch * F.numel_scale(M, N, 16),), 0x7F, dtype=torch.uint8, device="cuda")
-        dst = torch.tensor([st], dtype=torch.float32, device="cuda")
-        a.SFD, a.norm_constant = dSFD.data_ptr(), dst.data_ptr()
-        keep += [dSFD, dst]
+        dD = torch.full((rows, N // 2 if out_kind == 1 else N), 0x77, dtype=torch.uint8, device="cuda")
+        dSFD = torch.full((batch * F.numel_scale(M, N, 16 if out_kind == 1 else 32),), 0x7F, dtype=torch.uint8, device="cuda")
+        a.SFD = dSFD.data_ptr()
+        keep += [dSFD]
+        if st is not None:
+            dst = torch.tensor([st], dtype=torch.float32, device="cuda")
+            a.norm_constant = dst.data_ptr()
+            keep += [dst]
     a.D = dD.data_ptr()
     ws = torch.zeros(16, dtype=torch.uint8, device="cuda")
     L.check(lib.bsg_gemm_run(C.byref(a), ws.data_ptr(), 16, None))

@@ -101,6 +101,26 @@ def test_fused_nvfp4_output_bit_exact(cuda_lib, exact, beta):
     assert np.array_equal(SFD[idx], SFDw[idx])
 
 
+@pytest.mark.parametrize("kind,exact,beta,st", [(0, True, 0.0, None), (0, False, 0.5, 3.0), (1, True, 0.0, 0.25), (1, False, 0.5, None)])
+def test_fused_mxfp8_output_bit_exact(cuda_lib, kind, exact, beta, st):
+    """e4m3 data and ue8m0 scale factors (round-up conversion) of the fused MXFP8 re-quantisation against the oracle.
+    With exact-arithmetic operands the accumulators are exact and every byte must agree; with realistic MXFP8
+    operands the fp32 accumulation order differs, so a value that sits on a rounding boundary may move one code."""
+    M, N, K = 384, 768, 512
+    rng, A, sfa, B, sfb = make_operands(kind, M, N, K, seed=21, exact=exact)
+    Cb = G.bf16_normal((M, N), rng) if beta else None
+    pre = oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K, Cb, 1.0, beta)
+    D, SFD = run_dense(kind, M, N, K, A, sfa, B, sfb, Cb, 1.0, beta, out_kind=2, st=st)
+    Dw, SFDw = oracle.quant(1, pre, 1.0 if st is None else st)
+    idx = R.sf_index(M, N // 32)
+    if exact or kind == 0:
+        assert np.array_equal(SFD[idx], SFDw[idx])
+        assert np.array_equal(D, Dw)
+    else:
+        assert (SFD[idx] != SFDw[idx]).mean() < 1e-3
+        assert (D != Dw).mean() < 2e-2
+
+
 def test_quantisation_stage_in_isolation(cuda_lib):
     """K = 32 with identity-like operands turns the GEMM into a copy of chosen fp32 values, so the
     kernel's quantisation arithmetic is compared with the oracle on arbitrary magnitudes."""

@@ -112,7 +112,7 @@ def test_quantised_operands_feed_the_gemm(kind):
     U.assert_close_bf16(got, want)
     exact = (x.float() @ w.float().t()).cpu().numpy()
     err = np.abs(F.bf16_to_f32(got) - exact)
-    assert float(err.max()) <= (0.25 if kind == 0 else 0.08) * float(np.abs(exact).max())
+    assert float(err.max()) <= (0.3 if kind == 0 else 0.15) * float(np.abs(exact).max())
 
 
 @pytest.mark.parametrize("kind", [0, 1])
