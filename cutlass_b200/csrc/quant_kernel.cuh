@@ -57,18 +57,26 @@ __global__ void __launch_bounds__(kQuantThreads) bsg_quant_kernel(const QuantPar
   const bool k_ok = k < p.K;
   const int blk = lane / kLanesPerBlock;                    // K-block of this lane inside the tile row
 
-  constexpr int kUnroll = 4;
-  for (int r = warp; r < kQuantTileRows; r += 8 * kUnroll) {
-    uint4 raw[kUnroll];
+  // A warp owns rows warp + 8 u + 32 g of the tile (u < 4, g < 4).  The four loads of group g + 1 are issued
+  // before group g is processed, so that every warp always has loads in flight (the kernel is bound by
+  // memory latency x bytes in flight, not by arithmetic).
+  constexpr int kUnroll = 4, kGroups = kQuantTileRows / (8 * kUnroll);
+  auto load_group = [&](uint4 (&raw)[kUnroll], int g) {
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const int row = row0 + r + 8 * u;
+      const int row = row0 + warp + 8 * u + 32 * g;
       raw[u] = make_uint4(0u, 0u, 0u, 0u);
       if (k_ok && row < p.rows) raw[u] = *reinterpret_cast<const uint4*>(p.X + int64_t(row) * p.ldx + k);
     }
+  };
+  uint4 raw[kUnroll], nxt[kUnroll];
+  load_group(raw, 0);
+#pragma unroll
+  for (int g = 0; g < kGroups; ++g) {
+    if (g + 1 < kGroups) load_group(nxt, g + 1);
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const int rt = r + 8 * u, row = row0 + rt;
+      const int rt = warp + 8 * u + 32 * g, row = row0 + rt;
       float x[8];
       x[0] = bf16_bits_to_f32(raw[u].x & 0xFFFFu); x[1] = bf16_bits_to_f32(raw[u].x >> 16);
       x[2] = bf16_bits_to_f32(raw[u].y & 0xFFFFu); x[3] = bf16_bits_to_f32(raw[u].y >> 16);
@@ -89,7 +97,7 @@ __global__ void __launch_bounds__(kQuantThreads) bsg_quant_kernel(const QuantPar
         sf_code = ptx::cvt_ue8m0_rp(pv);
         sf_val = ptx::ue8m0_to_f32(sf_code);
       }
-      float sc = __fmul_rn(st, __fdiv_rn(1.0f, sf_val));
+      float sc = __fmul_rn(st, __frcp_rn(sf_val));      // correctly rounded reciprocal == 1.0f / sf_val
       if (sc > FLT_MAX) sc = FLT_MAX;
 #pragma unroll
       for (int j = 0; j < 8; ++j) x[j] = __fmul_rn(x[j], sc);
@@ -106,6 +114,8 @@ __global__ void __launch_bounds__(kQuantThreads) bsg_quant_kernel(const QuantPar
           s_sf[(blk >> 2) * 512 + 16 * (rt & 31) + 4 * (rt >> 5) + (blk & 3)] = uint8_t(sf_code);
       }
     }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) raw[u] = nxt[u];
   }
   __syncthreads();
   // Whole atoms leave in one piece: atom (row0 / 128, k0 / (4 V) + a), 512 bytes each, consecutive in memory.
