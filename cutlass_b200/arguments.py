@@ -175,13 +175,22 @@ class Mxfp8Quant:
 
 @dataclass
 class EpilogueDescriptor:
-    """``out = alpha * acc + beta * C`` followed by the output conversion.
-    ``alpha`` / ``beta`` are Python floats or one-element fp32 CUDA tensors."""
+    """``out = activation(alpha * acc + bias + beta * C)`` followed by the output conversion (the order of the
+    reference's host epilogue, tools/util/include/cutlass/util/reference/host/gett.hpp:714-761).
+    ``alpha`` / ``beta`` are Python floats or one-element fp32 CUDA tensors.  ``bias`` is an fp32 vector with one
+    entry per output column (N; grouped GEMM: (groups, N)) or, with ``bias_per_row``, per output row (M; dense only).
+    ``activation``: "identity", "relu", "gelu" (erf form) or "silu"."""
 
     alpha: float | torch.Tensor = 1.0
     beta: float | torch.Tensor = 0.0
     C: torch.Tensor | None = None
     out_quant: Nvfp4Quant | Mxfp8Quant | None = None
+    bias: torch.Tensor | None = None
+    bias_per_row: bool = False
+    activation: str = "identity"
+
+
+ACTIVATIONS = {"identity": 0, "relu": 1, "gelu": 2, "silu": 3}
 
 
 def _logical_k(op, axis: int) -> int:

@@ -117,6 +117,8 @@ struct Problem {
   bool tp;
   int32_t tp_world, tp_rank, tp_rows_per_shard, tp_ksplit, tp_push_in_kernel;
   uint32_t tp_epoch;
+  const float* bias;
+  int32_t bias_mode, bias_group_stride, activation;
   uint32_t tp_ready_target; // a peer's buffer may be filled once the peer has launched this call number
   int32_t tp_parity;        // which of the two gathered buffers this call fills and reads (own rows always sit in buffer 0)
   int64_t tp_row_bytes, tp_sfa_rowatom_bytes;
@@ -154,6 +156,14 @@ int32_t validate(const Problem& q, Plan* plan) {
     if (q.N % 16 != 0 || q.ldd % 32 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "NVFP4 output needs N %% 16 == 0 and ldd %% 32 == 0");
     if (q.offsets) return fail(BSG_ERR_NOT_SUPPORTED, "NVFP4 output is not available for grouped GEMM");
   }
+  if (q.bias_mode < BSG_BIAS_NONE || q.bias_mode > BSG_BIAS_PER_ROW) return fail(BSG_ERR_NOT_SUPPORTED, "unknown bias mode %d", q.bias_mode);
+  if (q.bias_mode != BSG_BIAS_NONE) {
+    if (!q.bias) return fail(BSG_ERR_INVALID_PROBLEM, "bias mode %d needs a bias vector", q.bias_mode);
+    if (!aligned16(q.bias)) return fail(BSG_ERR_MISALIGNED_OPERAND, "bias must be 16-byte aligned");
+    if (q.bias_mode == BSG_BIAS_PER_COLUMN && q.N % 4 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "per-column bias needs N %% 4 == 0");
+    if (q.bias_mode == BSG_BIAS_PER_ROW && q.offsets) return fail(BSG_ERR_NOT_SUPPORTED, "per-row bias is not available for grouped GEMM");
+  }
+  if (q.activation < BSG_ACT_IDENTITY || q.activation > BSG_ACT_SILU) return fail(BSG_ERR_NOT_SUPPORTED, "unknown activation %d", q.activation);
   if (q.C && (q.ldc % 8 != 0)) return fail(BSG_ERR_MISALIGNED_OPERAND, "ldc must be a multiple of 8");
   if (q.ldd < q.N || (q.C && q.ldc < q.N)) return fail(BSG_ERR_INVALID_PROBLEM, "row pitch smaller than N");
   if (q.beta != 0.0f && !q.C && !q.beta_ptr) return fail(BSG_ERR_INVALID_PROBLEM, "beta != 0 needs C");
@@ -209,6 +219,7 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   p.tiles_n = int32_t((q.N + BN - 1) / BN);
   p.raster_band = q.raster_band > 0 ? q.raster_band : 8;
   p.out_kind = q.out_kind;
+  p.bias = q.bias; p.bias_mode = q.bias_mode; p.bias_group_stride = q.bias_group_stride; p.activation = q.activation;
   p.C = static_cast<const __nv_bfloat16*>(q.C);
   p.D = q.D;
   p.SFD = static_cast<uint8_t*>(q.SFD);
@@ -337,6 +348,8 @@ Problem from_dense(const bsg_gemm_args* a) {
   q.alpha = a->alpha; q.beta = a->beta;
   q.alpha_ptr = a->alpha_ptr; q.beta_ptr = a->beta_ptr; q.norm_ptr = a->norm_constant;
   q.tile_n = a->tile_n; q.cta_group = a->cta_group; q.sm_count = a->sm_count; q.raster_band = a->raster_band;
+  q.bias = a->bias_mode != BSG_BIAS_NONE ? a->bias : nullptr;
+  q.bias_mode = a->bias_mode; q.bias_group_stride = 0; q.activation = a->activation;
   return q;
 }
 
@@ -357,6 +370,8 @@ Problem from_grouped(const bsg_grouped_args* a) {
   q.ldd = a->ldd ? a->ldd : a->N;
   q.alpha = a->alpha; q.beta = a->beta;
   q.tile_n = a->tile_n; q.cta_group = a->cta_group; q.sm_count = a->sm_count; q.raster_band = a->raster_band;
+  q.bias = a->bias; q.bias_mode = a->bias ? BSG_BIAS_PER_COLUMN : BSG_BIAS_NONE; q.bias_group_stride = int32_t(a->N);
+  q.activation = a->activation;
   return q;
 }
 

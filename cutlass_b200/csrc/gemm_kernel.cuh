@@ -41,6 +41,7 @@ constexpr int kKindMxfp8 = 1;
 constexpr int kOutBf16 = 0;
 constexpr int kOutNvfp4 = 1;
 constexpr int kOutMxfp8 = 2;
+constexpr int kActIdentity = 0, kActRelu = 1, kActGelu = 2, kActSilu = 3;
 
 // Bits of the device status word.
 constexpr uint32_t kStTimeoutFull = 1u;       // MMA warp: operands never arrived
@@ -69,6 +70,10 @@ struct GemmParams {
   const float* alpha_ptr;
   const float* beta_ptr;
   const float* norm_ptr;
+  const float* bias;          // fp32 vector added to alpha * acc before beta * C, or null
+  int32_t bias_mode;          // 1: one entry per output column; 2: one per row of the (batched) problem
+  int32_t bias_group_stride;  // mode 1: entries between the bias vectors of two groups (0: one vector for all)
+  int32_t activation;         // kAct*: applied after alpha * acc + bias + beta * C, before the output conversion
   uint32_t* status;
   // Optional gating of A rows by flags (tensor-parallel all-gather): rows
   // [i*rows_per_flag, (i+1)*rows_per_flag) may be read once ready_flags[i] >= flag_target.
@@ -367,6 +372,17 @@ __global__ void tp_announce_kernel(uint32_t* peer_flags, int first, int blocks, 
   if (i < blocks) {
     __threadfence_system();
     asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(peer_flags + first + i), "r"(add) : "memory");
+  }
+}
+
+// Element-wise activations of the reference (include/cutlass/epilogue/thread/activation.h): ReLu :145 (max with 0),
+// GELU<float> :585 ((0.5 x) (1 + erf(x / sqrt 2))), SiLu :452 (x * 1 / (1 + exp(-x))), same operation order.
+__device__ __forceinline__ float apply_activation(float x, int act) {
+  switch (act) {
+    case kActRelu: return x != x ? x : fmaxf(x, 0.0f);
+    case kActGelu: return __fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.0f, erff(__fmul_rn(x, 0.70710678118654752440f))));
+    case kActSilu: return __fmul_rn(x, __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))));
+    default: return x;
   }
 }
 
@@ -816,6 +832,26 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           float x[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) x[j] = __fmul_rn(alpha, __uint_as_float(v[h][j]));
+          if (p.bias_mode == 1) {
+            const float* b = p.bias + int64_t(ti.g) * p.bias_group_stride + col0;
+            if (cols_valid >= 32) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const float4 bv = __ldg(reinterpret_cast<const float4*>(b) + q);
+                x[q * 4 + 0] = __fadd_rn(x[q * 4 + 0], bv.x); x[q * 4 + 1] = __fadd_rn(x[q * 4 + 1], bv.y);
+                x[q * 4 + 2] = __fadd_rn(x[q * 4 + 2], bv.z); x[q * 4 + 3] = __fadd_rn(x[q * 4 + 3], bv.w);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (j < cols_valid) x[j] = __fadd_rn(x[j], __ldg(b + j));
+              }
+            }
+          } else if (p.bias_mode == 2 && row_ok) {
+            const float bv = __ldg(p.bias + lrow);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) x[j] = __fadd_rn(x[j], bv);
+          }
           if (use_c && row_ok) {
             const __nv_bfloat16* crow = p.C + int64_t(grow) * p.ldc + col0;
             if (cols_valid >= 32) {
@@ -837,6 +873,11 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (j < cols_valid) x[j] = __fadd_rn(__fmul_rn(beta, __bfloat162float(crow[j])), x[j]);
               }
             }
+          }
+
+          if (p.activation != kActIdentity) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) x[j] = apply_activation(x[j], p.activation);
           }
 
           if (p.out_kind == kOutBf16) {

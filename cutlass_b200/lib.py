@@ -30,6 +30,8 @@ KIND_MXFP8 = 1
 OUT_BF16 = 0
 OUT_NVFP4 = 1
 OUT_MXFP8 = 2
+ACT_IDENTITY, ACT_RELU, ACT_GELU, ACT_SILU = 0, 1, 2, 3
+BIAS_NONE, BIAS_PER_COLUMN, BIAS_PER_ROW = 0, 1, 2
 MAX_GROUPS = 256
 
 
@@ -43,6 +45,7 @@ class GemmArgs(C.Structure):
         ("alpha", C.c_float), ("beta", C.c_float),
         ("alpha_ptr", C.c_void_p), ("beta_ptr", C.c_void_p), ("norm_constant", C.c_void_p),
         ("tile_n", C.c_int32), ("cta_group", C.c_int32), ("sm_count", C.c_int32), ("raster_band", C.c_int32),
+        ("bias", C.c_void_p), ("bias_mode", C.c_int32), ("activation", C.c_int32),
     ]
 
 
@@ -55,6 +58,7 @@ class GroupedArgs(C.Structure):
         ("ldc", C.c_int64), ("ldd", C.c_int64),
         ("alpha", C.c_float), ("beta", C.c_float),
         ("tile_n", C.c_int32), ("cta_group", C.c_int32), ("sm_count", C.c_int32), ("raster_band", C.c_int32),
+        ("bias", C.c_void_p), ("reserved1", C.c_int32), ("activation", C.c_int32),
     ]
 
 

@@ -19,7 +19,7 @@ from typing import Callable
 import torch
 
 from . import lib as L
-from .arguments import (DenseTensor, EpilogueDescriptor, GemmArguments, GroupedGemmArguments, Mxfp8Quant, ScaledOperand,
+from .arguments import (ACTIVATIONS, DenseTensor, EpilogueDescriptor, GemmArguments, GroupedGemmArguments, Mxfp8Quant, ScaledOperand,
                         ScaleMode, ScaleSwizzleMode, _E8M0, _FP4X2, _logical_k)
 from .status import Status
 
@@ -276,6 +276,12 @@ class BlockScaledGemmOperator(Operator):
             beta = epi.beta
             if not isinstance(beta, torch.Tensor) and float(beta) != 0.0:
                 return Status.fail("beta != 0 needs C")
+        if epi.activation not in ACTIVATIONS:
+            return Status.fail(f"unknown activation {epi.activation!r}: one of {sorted(ACTIVATIONS)}")
+        if epi.bias is not None:
+            want = ps.M if epi.bias_per_row else ps.N
+            if epi.bias.dtype != torch.float32 or epi.bias.numel() != want or not epi.bias.is_contiguous():
+                return Status.fail(f"bias must be a contiguous fp32 vector of {want} entries")
         if md.tile_n not in (128, 256) or md.cta_group not in (1, 2):
             return Status.fail("invalid tile configuration")
         return Status.success()
@@ -305,6 +311,10 @@ class BlockScaledGemmOperator(Operator):
             a.SFD = epi.out_quant.scale.data_ptr()
             nc = epi.out_quant.norm_constant
             a.norm_constant = nc.data_ptr() if nc is not None else None
+        if epi.bias is not None:
+            a.bias = epi.bias.data_ptr()
+            a.bias_mode = L.BIAS_PER_ROW if epi.bias_per_row else L.BIAS_PER_COLUMN
+        a.activation = ACTIVATIONS[epi.activation]
         a.tile_n = md.tile_n
         a.cta_group = md.cta_group
         return a
@@ -363,6 +373,13 @@ class GroupedBlockScaledGemmOperator(Operator):
             return Status.fail("beta != 0 needs C")
         if not args.offsets.tensor.is_contiguous():
             return Status.fail("offsets must be contiguous")
+        if epi.activation not in ACTIVATIONS:
+            return Status.fail(f"unknown activation {epi.activation!r}: one of {sorted(ACTIVATIONS)}")
+        if epi.bias is not None:
+            if epi.bias_per_row:
+                return Status.fail("grouped GEMM takes a per-column bias only")
+            if epi.bias.dtype != torch.float32 or epi.bias.numel() != ps.L * ps.N or not epi.bias.is_contiguous():
+                return Status.fail(f"bias must be a contiguous fp32 tensor of shape ({ps.L}, {ps.N})")
         return Status.success()
 
     def build_args(self, args: GroupedGemmArguments) -> L.GroupedArgs:
@@ -385,6 +402,8 @@ class GroupedBlockScaledGemmOperator(Operator):
         a.ldd = ps.N
         a.alpha = float(epi.alpha)
         a.beta = float(epi.beta)
+        a.bias = epi.bias.data_ptr() if epi.bias is not None else None
+        a.activation = ACTIVATIONS[epi.activation]
         a.tile_n = md.tile_n
         a.cta_group = md.cta_group
         return a

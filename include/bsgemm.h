@@ -57,6 +57,13 @@ enum {
  * include/cutlass/detail/sm100_blockscaled_layout.hpp:49-114, one layout per
  * batch entry, padding included.  C and D are (batch, M, N) row-major.
  */
+/* Element-wise activation applied to alpha * acc + bias + beta * C before the output conversion / quantisation
+ * (include/cutlass/epilogue/thread/activation.h of the reference: ReLu :145, GELU<float> :585, SiLu :452). */
+typedef enum bsg_activation { BSG_ACT_IDENTITY = 0, BSG_ACT_RELU = 1, BSG_ACT_GELU = 2, BSG_ACT_SILU = 3 } bsg_activation;
+/* Which output coordinate indexes the bias vector (PerColumnBias of the reference's host epilogue,
+ * tools/util/include/cutlass/util/reference/host/gett.hpp:189,717). */
+typedef enum bsg_bias_mode { BSG_BIAS_NONE = 0, BSG_BIAS_PER_COLUMN = 1, BSG_BIAS_PER_ROW = 2 } bsg_bias_mode;
+
 typedef struct bsg_gemm_args {
   int32_t kind;             /* BSG_KIND_* */
   int32_t out_kind;         /* BSG_OUT_* */
@@ -81,6 +88,10 @@ typedef struct bsg_gemm_args {
   int32_t cta_group;        /* 0 = default, else 1 or 2 (CTAs per MMA) */
   int32_t sm_count;         /* 0 = all SMs of the current device */
   int32_t raster_band;      /* 0 = default band height in tiles */
+  /* D = act(alpha * acc + bias + beta * C), the reference's order of operations (gett.hpp:714-761). */
+  const float* bias;        /* device fp32: N entries (per column) or M entries (per row), shared by all batches; or NULL */
+  int32_t bias_mode;        /* BSG_BIAS_* (BSG_BIAS_NONE ignores bias) */
+  int32_t activation;       /* BSG_ACT_* */
 } bsg_gemm_args;
 
 /*
@@ -112,6 +123,9 @@ typedef struct bsg_grouped_args {
   int64_t ldc, ldd;
   float alpha, beta;
   int32_t tile_n, cta_group, sm_count, raster_band;
+  const float* bias;        /* device fp32 (num_groups, N): one vector per group, added per output column; or NULL */
+  int32_t reserved1;
+  int32_t activation;       /* BSG_ACT_* */
 } bsg_grouped_args;
 
 #define BSG_MAX_GROUPS 256

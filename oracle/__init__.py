@@ -51,6 +51,11 @@ def load_oracle() -> C.CDLL:
     lib.bsg_oracle_gemm_rows.restype = C.c_int
     lib.bsg_oracle_gemm_rows.argtypes = [C.c_int, C.c_int64, C.c_int64, C.c_int64] + [C.c_void_p] * 5 + \
         [C.c_int64, C.c_float, C.c_float, C.c_int64, C.c_int64, C.c_void_p]
+    lib.bsg_oracle_gemm_rows_epi.restype = C.c_int
+    lib.bsg_oracle_gemm_rows_epi.argtypes = [C.c_int, C.c_int64, C.c_int64, C.c_int64] + [C.c_void_p] * 5 + \
+        [C.c_int64, C.c_float, C.c_float, C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_void_p]
+    lib.bsg_oracle_activation.restype = C.c_float
+    lib.bsg_oracle_activation.argtypes = [C.c_int, C.c_float]
     lib.bsg_oracle_quant_nvfp4.restype = None
     lib.bsg_oracle_quant_nvfp4.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_void_p, C.c_void_p]
     lib.bsg_oracle_quant.restype = None
@@ -74,6 +79,9 @@ def load_ref() -> C.CDLL | None:
     lib.bsg_ref_decode.argtypes = [C.c_int, C.c_uint32]
     lib.bsg_ref_encode.restype = C.c_uint32
     lib.bsg_ref_encode.argtypes = [C.c_int, C.c_float]
+    if hasattr(lib, "bsg_ref_gemm_epi"):
+        lib.bsg_ref_gemm_epi.restype = C.c_int
+        lib.bsg_ref_gemm_epi.argtypes = [C.c_int] * 4 + [C.c_void_p] * 5 + [C.c_float, C.c_float, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
     lib.bsg_ref_sf_offset.restype = C.c_int64
     lib.bsg_ref_sf_offset.argtypes = [C.c_int] * 5
     lib.bsg_ref_sf_size.restype = C.c_int64
@@ -89,8 +97,9 @@ def _ptr(a: np.ndarray | None):
 
 
 def gemm_fp32(kind: int, A, SFA, B, SFB, M: int, N: int, K: int, C_bits=None, alpha: float = 1.0, beta: float = 0.0,
-              m_begin: int = 0, m_count: int | None = None) -> np.ndarray:
-    """C oracle: alpha * (A.SFA)(B.SFB)^T + beta * C in fp32 for rows [m_begin, m_begin + m_count)."""
+              m_begin: int = 0, m_count: int | None = None, bias=None, bias_per_row: bool = False, activation: int = 0) -> np.ndarray:
+    """C oracle: act(alpha * (A.SFA)(B.SFB)^T + bias + beta * C) in fp32 for rows [m_begin, m_begin + m_count).
+    activation: 0 identity, 1 ReLU, 2 GELU, 3 SiLU; bias: fp32 vector of N (per column) or M (per row) entries."""
     lib = load_oracle()
     m_count = M - m_begin if m_count is None else m_count
     A = np.ascontiguousarray(A, dtype=np.uint8)
@@ -99,8 +108,12 @@ def gemm_fp32(kind: int, A, SFA, B, SFB, M: int, N: int, K: int, C_bits=None, al
     SFB = np.ascontiguousarray(SFB, dtype=np.uint8)
     Cb = None if C_bits is None else np.ascontiguousarray(C_bits, dtype=np.uint16)
     out = np.empty((m_count, N), dtype=np.float32)
-    rc = lib.bsg_oracle_gemm_rows(kind, M, N, K, _ptr(A), _ptr(B), _ptr(SFA), _ptr(SFB), _ptr(Cb), N, alpha, beta,
-                                  m_begin, m_count, _ptr(out))
+    bv = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    if bv is not None and bv.size != (M if bias_per_row else N):
+        raise ValueError("bias has the wrong number of entries")
+    rc = lib.bsg_oracle_gemm_rows_epi(kind, M, N, K, _ptr(A), _ptr(B), _ptr(SFA), _ptr(SFB), _ptr(Cb), N, alpha, beta,
+                                      _ptr(bv), 0 if bv is None else (2 if bias_per_row else 1), int(activation),
+                                      m_begin, m_count, _ptr(out))
     if rc != 0:
         raise MemoryError("oracle GEMM could not allocate its scratch buffers")
     return out
@@ -168,3 +181,23 @@ def ref_gemm(kind: int, out_mode: int, A, SFA, B, SFB, M: int, N: int, K: int, C
     if rc != 0:
         raise ValueError("reference driver rejected the arguments")
     return D if sfd is None else (D, sfd)
+
+
+def ref_gemm_epi(kind: int, A, SFA, B, SFB, M: int, N: int, K: int, C_bits=None, alpha=1.0, beta=0.0, bias=None,
+                 bias_per_row: bool = False, activation: int = 0) -> np.ndarray:
+    """Compiled reference with its general epilogue: fp32 act(alpha * acc + bias + beta * C)."""
+    lib = load_ref()
+    if lib is None:
+        raise FileNotFoundError("oracle/_ref/libbsg_ref.so has not been built")
+    A = np.ascontiguousarray(A, dtype=np.uint8)
+    B = np.ascontiguousarray(B, dtype=np.uint8)
+    SFA = np.ascontiguousarray(SFA, dtype=np.uint8)
+    SFB = np.ascontiguousarray(SFB, dtype=np.uint8)
+    Cb = np.zeros((M, N), dtype=np.uint16) if C_bits is None else np.ascontiguousarray(C_bits, dtype=np.uint16)
+    bv = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    D = np.zeros((M, N), dtype=np.float32)
+    rc = lib.bsg_ref_gemm_epi(kind, M, N, K, _ptr(A), _ptr(B), _ptr(SFA), _ptr(SFB), _ptr(Cb), alpha, beta, _ptr(bv),
+                              0 if bv is None else (2 if bias_per_row else 1), int(activation), _ptr(D))
+    if rc != 0:
+        raise ValueError("reference driver rejected the arguments")
+    return D

@@ -146,9 +146,24 @@ static void expand_operand(int kind, const uint8_t* data, const uint8_t* sf, int
  * out[m, n] = alpha * sum_k a[m,k]*b[n,k] (+ beta * C[m,n]), fp32, for rows [m_begin, m_begin + m_count).
  * out is m_count x N.  C is bf16 bits with pitch ldc (may be NULL).  Returns 0 on success.
  */
-int bsg_oracle_gemm_rows(int kind, int64_t M, int64_t N, int64_t K, const uint8_t* A, const uint8_t* B, const uint8_t* SFA,
-                         const uint8_t* SFB, const uint16_t* C, int64_t ldc, float alpha, float beta, int64_t m_begin,
-                         int64_t m_count, float* out) {
+/* Element-wise activations as the reference defines them (include/cutlass/epilogue/thread/activation.h:
+ * ReLu :145 -- maximum with 0, NaN kept; GELU<float> :585; SiLu :452 with Sigmoid :408 and exp through the
+ * host math library).  act: 0 identity, 1 ReLU, 2 GELU (erf form), 3 SiLU. */
+float bsg_oracle_activation(int act, float x) {
+  switch (act) {
+    case 1: return x != x ? x : (x > 0.f ? x : 0.f);
+    case 2: return (0.5f * x) * (1.0f + erff(x * 0.70710678118654752440f));
+    case 3: return x * (1.0f / (1.0f + expf(-x)));
+    default: return x;
+  }
+}
+
+/* As bsg_oracle_gemm_rows, with the rest of the reference's epilogue (gett.hpp:714-761, in that order):
+ * o = alpha * acc;  o = o + bias[n or m];  o = beta * C + o;  o = act(o).
+ * bias_mode 0 none, 1 per column (N entries), 2 per row (M entries). */
+int bsg_oracle_gemm_rows_epi(int kind, int64_t M, int64_t N, int64_t K, const uint8_t* A, const uint8_t* B, const uint8_t* SFA,
+                             const uint8_t* SFB, const uint16_t* C, int64_t ldc, float alpha, float beta, const float* bias,
+                             int bias_mode, int act, int64_t m_begin, int64_t m_count, float* out) {
   float* a = (float*)malloc(sizeof(float) * (size_t)(m_count * K));
   float* b = (float*)malloc(sizeof(float) * (size_t)(N * K));
   int64_t mb, nb;
@@ -188,8 +203,10 @@ int bsg_oracle_gemm_rows(int kind, int64_t M, int64_t N, int64_t K, const uint8_
         for (j = 0; j < ncnt; ++j) {
           const int64_t n = nb * 64 + j;
           float o = alpha * acc[i][j];
+          if (bias_mode == 1) o = o + bias[n];
+          else if (bias_mode == 2) o = o + bias[m_begin + m];
           if (C) o = beta * bf16_to_f32(C[(m_begin + m) * ldc + n]) + o;
-          out[m * N + n] = o;
+          out[m * N + n] = bsg_oracle_activation(act, o);
         }
       }
     }
@@ -197,6 +214,12 @@ int bsg_oracle_gemm_rows(int kind, int64_t M, int64_t N, int64_t K, const uint8_
   free(a);
   free(b);
   return 0;
+}
+
+int bsg_oracle_gemm_rows(int kind, int64_t M, int64_t N, int64_t K, const uint8_t* A, const uint8_t* B, const uint8_t* SFA,
+                         const uint8_t* SFB, const uint16_t* C, int64_t ldc, float alpha, float beta, int64_t m_begin,
+                         int64_t m_count, float* out) {
+  return bsg_oracle_gemm_rows_epi(kind, M, N, K, A, B, SFA, SFB, C, ldc, alpha, beta, NULL, 0, 0, m_begin, m_count, out);
 }
 
 /* Block-scaled quantisation of an fp32 (M x N) matrix along N, as the reference's epilogue and any

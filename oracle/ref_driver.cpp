@@ -58,6 +58,56 @@ void run_gemm(int M, int N, int K, const void* A, const void* B, const void* SFA
   }
 }
 
+// The general host epilogue of the reference (GettEpilogueParams, gett.hpp:173-262): bias vector, beta * C and an
+// activation functor of include/cutlass/epilogue/thread/activation.h; D in fp32.
+template <class ElemAB, class ElemSF, int Vec, class Act, bool PerCol>
+void run_gemm_epi(int M, int N, int K, const void* A, const void* B, const void* SFA, const void* SFB,
+                  const cutlass::bfloat16_t* C, float alpha, float beta, const float* bias, float* D) {
+  auto layout_A = make_layout(make_shape(M, K, 1), make_stride(int64_t(K), _1{}, int64_t(M) * K));
+  auto layout_B = make_layout(make_shape(N, K, 1), make_stride(int64_t(K), _1{}, int64_t(N) * K));
+  auto layout_C = make_layout(make_shape(M, N, 1), make_stride(int64_t(N), _1{}, int64_t(M) * N));
+  auto layout_SFA = SfCfg<Vec>::tile_atom_to_shape_SFA(make_shape(M, N, K, 1));
+  auto layout_SFB = SfCfg<Vec>::tile_atom_to_shape_SFB(make_shape(M, N, K, 1));
+  Tensor tA = make_tensor(recast_ptr<ElemAB>(const_cast<void*>(A)), layout_A);
+  Tensor tB = make_tensor(recast_ptr<ElemAB>(const_cast<void*>(B)), layout_B);
+  Tensor tSFA = make_tensor(reinterpret_cast<ElemSF*>(const_cast<void*>(SFA)), layout_SFA);
+  Tensor tSFB = make_tensor(reinterpret_cast<ElemSF*>(const_cast<void*>(SFB)), layout_SFB);
+  cutlass::reference::host::GettBlockScalingMainloopParams<float, decltype(tA), decltype(tSFA), decltype(tB), decltype(tSFB)>
+      mainloop{tA, tSFA, tB, tSFB};
+  Tensor tC = make_tensor(const_cast<cutlass::bfloat16_t*>(C), layout_C);
+  Tensor tD = make_tensor(D, layout_C);
+  Tensor tBias = make_tensor(const_cast<float*>(bias), make_layout(make_shape(PerCol ? N : M, 1, 1)));
+  using Unused = decltype(make_tensor(cute::recast_ptr<float>(nullptr), typename decltype(tD)::layout_type{}));
+  using Epi = cutlass::reference::host::GettEpilogueParams<float, float, float, float, decltype(tC), decltype(tD), decltype(tBias),
+                                                           Unused, Unused, Unused, Act, decltype(tD), cute::Int<0>,
+                                                           cutlass::plus<float>, PerCol>;
+  Epi epi;
+  epi.alpha = alpha;
+  epi.beta = beta;
+  epi.C = tC;
+  epi.D = tD;
+  epi.Bias = tBias;
+  cutlass::reference::host::Gemm3x(mainloop, epi);
+}
+
+template <class ElemAB, class ElemSF, int Vec>
+int dispatch_epi(int M, int N, int K, const void* A, const void* B, const void* SFA, const void* SFB,
+                 const cutlass::bfloat16_t* C, float alpha, float beta, const float* bias, int bias_mode, int act, float* D) {
+  using namespace cutlass::epilogue::thread;
+  const bool per_col = bias_mode != 2;
+  const float* b = bias_mode == 0 ? nullptr : bias;
+#define BSG_EPI(ACT) (per_col ? run_gemm_epi<ElemAB, ElemSF, Vec, ACT<float>, true>(M, N, K, A, B, SFA, SFB, C, alpha, beta, b, D) \
+                              : run_gemm_epi<ElemAB, ElemSF, Vec, ACT<float>, false>(M, N, K, A, B, SFA, SFB, C, alpha, beta, b, D))
+  switch (act) {
+    case 0: BSG_EPI(Identity); return 0;
+    case 1: BSG_EPI(ReLu); return 0;
+    case 2: BSG_EPI(GELU); return 0;
+    case 3: BSG_EPI(SiLu); return 0;
+    default: return 1;
+  }
+#undef BSG_EPI
+}
+
 }  // namespace
 
 extern "C" {
@@ -122,6 +172,15 @@ int bsg_ref_gemm(int kind, int out_mode, int M, int N, int K, const void* A, con
     return 1;
   }
   return 0;
+}
+
+// fp32 D = act(alpha * acc + bias + beta * C).  bias_mode 0 none, 1 per column, 2 per row; act 0 identity, 1 ReLU, 2 GELU, 3 SiLU.
+int bsg_ref_gemm_epi(int kind, int M, int N, int K, const void* A, const void* B, const void* SFA, const void* SFB, const void* C,
+                     float alpha, float beta, const float* bias, int bias_mode, int act, float* D) {
+  auto Cb = static_cast<const cutlass::bfloat16_t*>(C);
+  if (kind == 0) return dispatch_epi<cutlass::float_e2m1_t, cutlass::float_ue4m3_t, 16>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, bias, bias_mode, act, D);
+  if (kind == 1) return dispatch_epi<cutlass::float_e4m3_t, cutlass::float_ue8m0_t, 32>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, bias, bias_mode, act, D);
+  return 1;
 }
 
 }  // extern "C"

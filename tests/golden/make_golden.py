@@ -60,6 +60,11 @@ def main() -> None:
         out[f"{name}_ab"] = np.array([alpha, beta], dtype=np.float32)
         out[f"{name}_D32"] = oracle.ref_gemm(kind, 0, A, sfa, B, sfb, M, N, K, Cb, alpha, beta)
         out[f"{name}_Dbf16"] = oracle.ref_gemm(kind, 1, A, sfa, B, sfb, M, N, K, Cb, alpha, beta)
+        # the reference's general epilogue: act(alpha * acc + bias + beta * C), bias per column or per row
+        bias_col, bias_row = (rng.standard_normal(n).astype(np.float32) * 3 for n in (N, M))
+        out[f"{name}_bias_col"], out[f"{name}_bias_row"] = bias_col, bias_row
+        for tag, bias, per_row, act in (("relu_col", bias_col, False, 1), ("gelu_col", bias_col, False, 2), ("silu_row", bias_row, True, 3)):
+            out[f"{name}_D32_{tag}"] = oracle.ref_gemm_epi(kind, A, sfa, B, sfb, M, N, K, Cb, alpha, beta, bias, per_row, act)
     name, M, N, K = "quant_a", 70, 96, 192
     rng = np.random.default_rng(77)
     A, _, sfa = G.nvfp4_operand(M, K, rng)

@@ -27,7 +27,7 @@ def make_operands(kind: int, M: int, N: int, K: int, seed: int, exact: bool):
 
 
 def run_dense(kind, M, N, K, A, sfa, B, sfb, Cb=None, alpha=1.0, beta=0.0, out_kind=0, st=None, tile_n=0, cta_group=0,
-              batch=1, check_status=True):
+              batch=1, check_status=True, bias=None, bias_per_row=False, activation=0):
     """-> bf16 bits (batch*M, N), or (quantised values, SFD buffer) for out_kind 1 (NVFP4) / 2 (MXFP8)."""
     lib = L.load()
     dA, dB, dSFA, dSFB = dev(A), dev(B), dev(sfa), dev(sfb)
@@ -39,6 +39,10 @@ def run_dense(kind, M, N, K, A, sfa, B, sfb, Cb=None, alpha=1.0, beta=0.0, out_k
     a.C = dC.data_ptr() if dC is not None else None
     a.alpha, a.beta = alpha, beta
     a.tile_n, a.cta_group = tile_n, cta_group
+    dbias = dev(np.asarray(bias, dtype=np.float32)) if bias is not None else None
+    if dbias is not None:
+        a.bias, a.bias_mode = dbias.data_ptr(), (L.BIAS_PER_ROW if bias_per_row else L.BIAS_PER_COLUMN)
+    a.activation = activation
     rows = batch * M
     keep = []
     if out_kind == 0:
@@ -63,8 +67,9 @@ def run_dense(kind, M, N, K, A, sfa, B, sfb, Cb=None, alpha=1.0, beta=0.0, out_k
     return dD.cpu().numpy(), keep[0].cpu().numpy()
 
 
-def oracle_bf16(kind, M, N, K, A, sfa, B, sfb, Cb=None, alpha=1.0, beta=0.0):
-    return oracle.to_bf16(oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K, Cb, alpha, beta))
+def oracle_bf16(kind, M, N, K, A, sfa, B, sfb, Cb=None, alpha=1.0, beta=0.0, bias=None, bias_per_row=False, activation=0):
+    return oracle.to_bf16(oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K, Cb, alpha, beta, bias=bias, bias_per_row=bias_per_row,
+                                           activation=activation))
 
 
 def assert_close_bf16(got_bits, want_bits, rel_tol=1e-2):
@@ -80,7 +85,7 @@ def assert_close_bf16(got_bits, want_bits, rel_tol=1e-2):
         assert float((err[big] / np.abs(want[big])).max()) <= rel_tol
 
 
-def run_grouped(kind, sizes, N, K, seed, exact=True, alpha=1.0, beta=0.0, tile_n=0, cta_group=0):
+def run_grouped(kind, sizes, N, K, seed, exact=True, alpha=1.0, beta=0.0, tile_n=0, cta_group=0, with_bias=False, activation=0):
     """Ragged grouped GEMM through the C ABI and the per-group oracle.  -> (got bits, want bits)."""
     rng = np.random.default_rng(seed)
     if kind == 0:
@@ -95,13 +100,15 @@ def run_grouped(kind, sizes, N, K, seed, exact=True, alpha=1.0, beta=0.0, tile_n
         As.append(A); sfas.append(sfa); Bs.append(B); sfbs.append(sfb)
     Cb = G.bf16_normal((total, N), rng) if beta != 0 else None
     A_all = np.concatenate(As, axis=0)
+    bias = (rng.standard_normal((len(sizes), N)) * 2).astype(np.float32) if with_bias else None
     want = np.zeros((total, N), np.uint16)
     row = 0
     for g, m in enumerate(sizes):
         m = int(m)
         if m:
             cg = Cb[row:row + m] if Cb is not None else None
-            want[row:row + m] = oracle_bf16(kind, m, N, K, As[g], sfas[g], Bs[g], sfbs[g], cg, alpha, beta)
+            want[row:row + m] = oracle_bf16(kind, m, N, K, As[g], sfas[g], Bs[g], sfbs[g], cg, alpha, beta,
+                                            bias=bias[g] if with_bias else None, activation=activation)
         row += m
     lib = L.load()
     dA, dB = dev(A_all), dev(np.stack(Bs))
@@ -118,6 +125,9 @@ def run_grouped(kind, sizes, N, K, seed, exact=True, alpha=1.0, beta=0.0, tile_n
     a.offsets = offs.data_ptr()
     a.alpha, a.beta = alpha, beta
     a.tile_n, a.cta_group = tile_n, cta_group
+    dbias = dev(bias) if with_bias else None
+    a.bias = dbias.data_ptr() if with_bias else None
+    a.activation = activation
     ws = torch.zeros(16, dtype=torch.uint8, device="cuda")
     L.check(lib.bsg_grouped_run(C.byref(a), ws.data_ptr(), 16, None))
     L.check(lib.bsg_read_device_status(ws.data_ptr(), None))

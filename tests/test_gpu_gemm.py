@@ -121,6 +121,49 @@ def test_fused_mxfp8_output_bit_exact(cuda_lib, kind, exact, beta, st):
         assert (D != Dw).mean() < 2e-2
 
 
+@pytest.mark.parametrize("kind", [0, 1])
+@pytest.mark.parametrize("act,per_row,beta", [(1, False, 0.0), (1, True, 0.5), (2, False, 0.5), (3, False, 0.0), (3, True, 0.5), (0, False, 0.5)])
+def test_bias_and_activation_epilogue(cuda_lib, kind, act, per_row, beta):
+    """act(alpha * acc + bias + beta * C): exact-arithmetic operands, so identity and ReLU must agree bit for bit
+    with the oracle; GELU / SiLU go through erf / exp of two different math libraries (rel 1e-2 on bf16)."""
+    M, N, K = 300, 456, 384          # ragged M, N not a multiple of the tile
+    rng, A, sfa, B, sfb = make_operands(kind, M, N, K, seed=31 + act, exact=True)
+    Cb = G.bf16_normal((M, N), rng) if beta else None
+    bias = (rng.standard_normal(M if per_row else N) * 4).astype(np.float32)
+    got = run_dense(kind, M, N, K, A, sfa, B, sfb, Cb, 0.5, beta, bias=bias, bias_per_row=per_row, activation=act)
+    want = oracle_bf16(kind, M, N, K, A, sfa, B, sfb, Cb, 0.5, beta, bias=bias, bias_per_row=per_row, activation=act)
+    if act in (0, 1):
+        assert np.array_equal(got, want)
+    else:
+        assert_close_bf16(got, want)
+        assert (got != want).mean() < 0.05          # at most a bf16 ulp here and there
+
+
+@pytest.mark.parametrize("kind", [0, 1])
+def test_grouped_bias_per_group_and_activation(cuda_lib, kind):
+    got, want = run_grouped(kind, [200, 0, 129, 384], 256, 256, seed=5, exact=True, alpha=1.0, beta=0.5, with_bias=True, activation=1)
+    assert np.array_equal(got, want)
+    got, want = run_grouped(kind, [64, 300], 384, 512, seed=6, exact=True, with_bias=True, activation=3)
+    assert_close_bf16(got, want)
+
+
+def test_activation_before_fused_quantisation(cuda_lib):
+    """ReLU then NVFP4 / MXFP8 re-quantisation of the output: the quantiser sees the activated values."""
+    M, N, K = 256, 512, 256
+    rng, A, sfa, B, sfb = make_operands(0, M, N, K, seed=41, exact=True)
+    bias = (rng.standard_normal(N) * 8).astype(np.float32)
+    pre = oracle.gemm_fp32(0, A, sfa, B, sfb, M, N, K, bias=bias, activation=1)
+    st = np.float32(448.0 * 6.0 / np.abs(pre).max())
+    D, SFD = run_dense(0, M, N, K, A, sfa, B, sfb, out_kind=1, st=float(st), bias=bias, activation=1)
+    Dw, SFDw = oracle.quant(0, pre, st)
+    idx = R.sf_index(M, N // 16)
+    assert np.array_equal(D, Dw) and np.array_equal(SFD[idx], SFDw[idx])
+    D, SFD = run_dense(0, M, N, K, A, sfa, B, sfb, out_kind=2, bias=bias, activation=1)
+    Dw, SFDw = oracle.quant(1, pre, 1.0)
+    idx = R.sf_index(M, N // 32)
+    assert np.array_equal(D, Dw) and np.array_equal(SFD[idx], SFDw[idx])
+
+
 def test_quantisation_stage_in_isolation(cuda_lib):
     """K = 32 with identity-like operands turns the GEMM into a copy of chosen fp32 values, so the
     kernel's quantisation arithmetic is compared with the oracle on arbitrary magnitudes."""

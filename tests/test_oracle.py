@@ -43,6 +43,22 @@ def test_row_slab_equals_full(golden):
     assert np.array_equal(slab, golden["nvfp4_b_D32"][64:114])
 
 
+@pytest.mark.parametrize("name", ["nvfp4_a", "mxfp8_a", "mxfp8_b"])
+def test_bias_and_activation_epilogue_on_golden(golden, name):
+    """act(alpha * acc + bias + beta * C) in the reference's order; ReLU bit for bit, GELU / SiLU up to the
+    host math library's erf / exp (the golden values were produced on this image: normally bit for bit too)."""
+    kind, M, N, K, A, sfa, B, sfb, Cb = _case(golden, name)
+    alpha, beta = (float(v) for v in golden[f"{name}_ab"])
+    for tag, per_row, act in (("relu_col", False, 1), ("gelu_col", False, 2), ("silu_row", True, 3)):
+        bias = golden[f"{name}_bias_row" if per_row else f"{name}_bias_col"]
+        got = oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K, Cb, alpha, beta, bias=bias, bias_per_row=per_row, activation=act)
+        want = golden[f"{name}_D32_{tag}"]
+        if act == 1:
+            assert np.array_equal(got, want)
+        else:
+            assert np.allclose(got, want, rtol=2e-6, atol=1e-30)
+
+
 def test_quantisation_bit_exact_on_golden(golden):
     kind, M, N, K, A, sfa, B, sfb, Cb = _case(golden, "quant_a")
     st = float(golden["quant_a_st"][0])
