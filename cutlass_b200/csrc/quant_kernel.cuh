@@ -36,9 +36,16 @@ constexpr int kQuantTileK = 256;
 constexpr int kQuantThreads = 256;
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t b) { return __uint_as_float(b << 16); }
+// max of two packed bf16 pairs, element-wise (NaN operands are ignored, as by fmaxf).
+__device__ __forceinline__ uint32_t bf16x2_max(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t bf16x2_absmax(uint32_t a, uint32_t b) { return bf16x2_max(a & 0x7FFF7FFFu, b & 0x7FFF7FFFu); }
 
 template <int KIND>
-__global__ void __launch_bounds__(kQuantThreads) bsg_quant_kernel(const QuantParams p) {
+__global__ void __launch_bounds__(kQuantThreads, 4) bsg_quant_kernel(const QuantParams p) {
   constexpr int V = KIND == 0 ? 16 : 32;
   constexpr int kLanesPerBlock = V / 8;                     // lanes that share one K-block
   constexpr int kBlocksPerTile = kQuantTileK / V;           // K-blocks of one row of the tile: 16 or 8
@@ -82,9 +89,10 @@ __global__ void __launch_bounds__(kQuantThreads) bsg_quant_kernel(const QuantPar
       x[2] = bf16_bits_to_f32(raw[u].y & 0xFFFFu); x[3] = bf16_bits_to_f32(raw[u].y >> 16);
       x[4] = bf16_bits_to_f32(raw[u].z & 0xFFFFu); x[5] = bf16_bits_to_f32(raw[u].z >> 16);
       x[6] = bf16_bits_to_f32(raw[u].w & 0xFFFFu); x[7] = bf16_bits_to_f32(raw[u].w >> 16);
-      float amax = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(x[j]));
+      // |x| maximum of the lane's 8 values on the packed bf16 pairs (exact: max and abs do not round)
+      const uint32_t m01 = bf16x2_absmax(raw[u].x, raw[u].y), m23 = bf16x2_absmax(raw[u].z, raw[u].w);
+      const uint32_t m = bf16x2_max(m01, m23);
+      float amax = fmaxf(bf16_bits_to_f32(m & 0xFFFFu), bf16_bits_to_f32(m >> 16));
       amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
       if constexpr (kLanesPerBlock == 4) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
       const float pv = __fmul_rn(amax, st_scaled);
