@@ -102,6 +102,66 @@ class ClockSampler:
         return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+class SmiClockSampler:
+    """Clock and throttle-reason samples from an ``nvidia-smi`` child process (one line every 10 ms), for timed regions
+    that must not be disturbed: NVML polling inside the launching process slowed the multi-GPU kernel launches.
+    ``start()`` early (the tool needs a moment), ``begin()`` / ``end()`` around the timed region, then ``summary()``."""
+
+    FIELDS = "timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.t0, self.t1 = index, None, None, None
+
+    def start(self):
+        import subprocess
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-i", str(self.index),
+                                          "-lms", "10"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def begin(self):
+        import datetime
+        self.t0 = datetime.datetime.now()
+
+    def end(self):
+        import datetime
+        self.t1 = datetime.datetime.now()
+
+    def summary(self):
+        import datetime
+        if self.proc is None:
+            return None
+        time.sleep(0.03)                       # let the sample that covers the end of the region arrive
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:  # noqa: BLE001
+            self.proc.kill()
+            return None
+        mhz, reasons, max_mhz, total = [], set(), None, 0
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) != 7:
+                continue
+            try:
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f")
+                clk, mx = float(f[1]), float(f[2])
+            except ValueError:
+                continue
+            total += 1
+            max_mhz = mx
+            if self.t0 is not None and self.t1 is not None and not (self.t0 <= ts <= self.t1 + datetime.timedelta(milliseconds=15)):
+                continue
+            mhz.append(clk)
+            reasons.update(n for n, v in zip(self.NAMES, f[3:]) if v == "Active")
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": max_mhz, "reasons": sorted(reasons),
+                "samples": len(mhz), "samples_whole_run": total, "source": "nvidia-smi child process, 10 ms period"}
+
+
 # --------------------------------------------------------------------------- operands
 from cutlass_b200.generators import gpu_mxfp8_operand, gpu_nvfp4_operand  # noqa: E402,F401  (seeded, generated on the device)
 
@@ -344,6 +404,9 @@ def main() -> None:
     rank = int(os.environ.get("RANK", "0"))
     if args.impl == "reference":
         if rank == 0:
+            # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use every core it may run on.
+            import oracle
+            oracle.set_threads(len(os.sched_getaffinity(0)))
             print(json.dumps(run_reference(args)))
         return
     if args.gpus == 1:

@@ -39,6 +39,8 @@ def run(args) -> dict:
     ms, ns = M // world, N // world
     kind = L.KIND_MXFP8
 
+    # Clocks of rank 0's GPU, sampled by a child process (nothing in this process polls during the timed region).
+    smi = bench.SmiClockSampler(local).start() if rank == 0 and os.environ.get("BSG_BENCH_CLOCKS", "1") != "0" else None
     tp = TP.TpGemm(kind, M, K)
     A, SFA = _shard_operand(ms, K, 1000 + rank, dev)
     tp.a_shard.copy_(A)
@@ -59,12 +61,16 @@ def run(args) -> dict:
     torch.cuda.synchronize()
     dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with bench.ClockSampler(local) as clk:
-        e0.record(stream)
-        for i in range(args.steps):
-            step(i)
-        e1.record(stream)
-        torch.cuda.synchronize()
+    if smi is not None:
+        smi.begin()
+    e0.record(stream)
+    for i in range(args.steps):
+        step(i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    if smi is not None:
+        smi.end()
+    clocks = smi.summary() if smi is not None else None
     tp.check_device_status(stream)
     t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -190,7 +196,7 @@ def run(args) -> dict:
         "e2e": {"value": round(flops / e2e_ms / 1e9, 1), "unit": "TFLOP/s", "h2d_bytes_per_step": h2d * world,
                 "d2h_bytes_per_step": d2h * world, "ms_per_step": round(e2e_ms, 4), "steps": n_e2e},
         "gpu_launches": args.steps * world,
-        "clocks": clk.summary(),
+        "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": round(tflops, 1), "peak": round(peak, 1), "unit": "TFLOP/s",
                      "frac": round(tflops / peak, 4),
                      "peak_source": "n_gpus x 2 x bf16_tflops_sustained of MEASURED_PEAKS.json (no fp8 figure is measured)",

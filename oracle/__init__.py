@@ -145,6 +145,15 @@ def quant(kind: int, x: np.ndarray, st: float = 1.0):
     return D, SFD
 
 
+def set_threads(n: int) -> None:
+    """Use ``n`` OpenMP threads in the oracle and the compiled reference from now on (launchers such as torchrun
+    export OMP_NUM_THREADS=1, which the runtime has already read by the time this module loads)."""
+    lib = load_oracle()
+    lib.bsg_oracle_set_threads.restype = None
+    lib.bsg_oracle_set_threads.argtypes = [C.c_int]
+    lib.bsg_oracle_set_threads(int(n))
+
+
 def to_bf16(x: np.ndarray) -> np.ndarray:
     lib = load_oracle()
     x = np.ascontiguousarray(x, dtype=np.float32)

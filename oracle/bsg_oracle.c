@@ -275,6 +275,16 @@ void bsg_oracle_to_bf16(const float* x, int64_t n, uint16_t* out) {
   for (i = 0; i < n; ++i) out[i] = bsg_oracle_f32_to_bf16(x[i]);
 }
 
+/* Number of threads for the parallel regions the calling thread starts from now on (this library's and the
+ * compiled reference's: they share the OpenMP runtime). */
+void bsg_oracle_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int bsg_oracle_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();
