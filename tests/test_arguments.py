@@ -189,3 +189,65 @@ def test_stream_conversion():
     assert ops.to_cuda_stream(S()) == 99
     with pytest.raises(TypeError):
         ops.to_cuda_stream(object())
+
+
+def test_mxfp8_output_descriptor_checks():
+    M, N, K = 256, 256, 512
+    sfd = torch.zeros(ops.ScaledOperand.numel_scale((M, N), M32, SW), dtype=torch.uint8)
+    a = nvfp4_args(M, N, K)
+    args = ops.GemmArguments(a.A, a.B, torch.zeros((M, N), dtype=torch.uint8), torch.float32,
+                             epilogue=ops.EpilogueDescriptor(out_quant=ops.Mxfp8Quant(sfd)))
+    assert not args.out_is_packed_fp4
+    op = ops.get_operators(args)[0]
+    assert op.supports(args)
+    built = op.build_args(args)
+    assert built.out_kind == L.OUT_MXFP8 and built.N == N and built.SFD == sfd.data_ptr() and not built.norm_constant
+    args.epilogue.out_quant.scale = torch.zeros(7, dtype=torch.uint8)
+    assert "out_quant.scale" in str(op.supports(args).error)
+    args.epilogue.out_quant = ops.Mxfp8Quant(sfd, norm_constant=torch.ones(2, dtype=torch.float32))
+    assert "norm_constant" in str(op.supports(args).error)
+
+
+def test_bias_and_activation_descriptor():
+    M, N, K = 256, 384, 512
+    bias_n, bias_m = torch.zeros(N, dtype=torch.float32), torch.zeros(M, dtype=torch.float32)
+    args = nvfp4_args(M, N, K, epilogue=ops.EpilogueDescriptor(bias=bias_n, activation="gelu"))
+    op = ops.get_operators(args)[0]
+    assert op.supports(args)
+    a = op.build_args(args)
+    assert (a.bias, a.bias_mode, a.activation) == (bias_n.data_ptr(), L.BIAS_PER_COLUMN, L.ACT_GELU)
+    args = nvfp4_args(M, N, K, epilogue=ops.EpilogueDescriptor(bias=bias_m, bias_per_row=True, activation="silu"))
+    a = op.build_args(args)
+    assert op.supports(args) and (a.bias_mode, a.activation) == (L.BIAS_PER_ROW, L.ACT_SILU)
+    assert op.build_args(nvfp4_args(M, N, K)).bias_mode == L.BIAS_NONE
+    bad = nvfp4_args(M, N, K, epilogue=ops.EpilogueDescriptor(bias=bias_m))            # M entries for a per-column bias
+    assert "bias" in str(op.supports(bad).error)
+    bad = nvfp4_args(M, N, K, epilogue=ops.EpilogueDescriptor(bias=bias_n.double()))
+    assert "bias" in str(op.supports(bad).error)
+    bad = nvfp4_args(M, N, K, epilogue=ops.EpilogueDescriptor(activation="tanh"))
+    assert "activation" in str(op.supports(bad).error)
+
+
+def test_abi_rejects_bad_bias_and_activation():
+    lib = L.load()
+    a = L.GemmArgs()
+    a.kind, a.batch, a.M, a.N, a.K = 0, 1, 256, 256, 256
+    a.A = a.B = a.SFA = a.SFB = a.D = 0x10000
+    a.alpha = 1.0
+    caps = L.Caps()
+    a.activation = 9
+    assert lib.bsg_gemm_query(a, caps) == 3                     # BSG_ERR_NOT_SUPPORTED
+    a.activation, a.bias_mode = 1, 1
+    assert lib.bsg_gemm_query(a, caps) == 2                     # bias mode without a bias vector
+    a.bias = 0x10004
+    assert lib.bsg_gemm_query(a, caps) == 1                     # misaligned bias
+    a.bias = 0x10000
+    assert lib.bsg_gemm_query(a, caps) == 0
+
+
+def test_quantize_blockscaled_argument_checks():
+    x = torch.zeros((64, 128), dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="CUDA"):
+        ops.quantize_blockscaled(x, M16)
+    with pytest.raises(ValueError, match="scale mode"):
+        ops.quantize_blockscaled(x, (1, 1, 64))
