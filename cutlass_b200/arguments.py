@@ -177,7 +177,8 @@ class Mxfp8Quant:
 class EpilogueDescriptor:
     """``out = activation(alpha * acc + bias + beta * C)`` followed by the output conversion (the order of the
     reference's host epilogue, tools/util/include/cutlass/util/reference/host/gett.hpp:714-761).
-    ``alpha`` / ``beta`` are Python floats or one-element fp32 CUDA tensors.  ``bias`` is an fp32 vector with one
+    ``alpha`` / ``beta`` are Python floats or one-element fp32 CUDA tensors (grouped GEMM: floats, or fp32
+    tensors with one entry per group).  ``bias`` is an fp32 vector with one
     entry per output column (N; grouped GEMM: (groups, N)) or, with ``bias_per_row``, per output row (M; dense only).
     ``activation``: "identity", "relu", "gelu" (erf form) or "silu"."""
 

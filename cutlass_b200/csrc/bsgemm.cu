@@ -118,6 +118,8 @@ struct Problem {
   int32_t tp_world, tp_rank, tp_rows_per_shard, tp_ksplit, tp_push_in_kernel;
   uint32_t tp_epoch;
   const float* bias;
+  const float* alpha_array;
+  const float* beta_array;
   int32_t bias_mode, bias_group_stride, activation;
   uint32_t tp_ready_target; // a peer's buffer may be filled once the peer has launched this call number
   int32_t tp_parity;        // which of the two gathered buffers this call fills and reads (own rows always sit in buffer 0)
@@ -167,6 +169,7 @@ int32_t validate(const Problem& q, Plan* plan) {
   if (q.C && (q.ldc % 8 != 0)) return fail(BSG_ERR_MISALIGNED_OPERAND, "ldc must be a multiple of 8");
   if (q.ldd < q.N || (q.C && q.ldc < q.N)) return fail(BSG_ERR_INVALID_PROBLEM, "row pitch smaller than N");
   if (q.beta != 0.0f && !q.C && !q.beta_ptr) return fail(BSG_ERR_INVALID_PROBLEM, "beta != 0 needs C");
+  if (q.beta_array && !q.C) return fail(BSG_ERR_INVALID_PROBLEM, "per-group beta needs C");
   int32_t cg = q.cta_group == 0 ? 2 : q.cta_group;
   int32_t tn = q.tile_n == 0 ? (q.N > 128 ? 256 : 128) : q.tile_n;
   if (cg != 1 && cg != 2) return fail(BSG_ERR_NOT_SUPPORTED, "cta_group must be 1 or 2");
@@ -219,6 +222,7 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   p.tiles_n = int32_t((q.N + BN - 1) / BN);
   p.raster_band = q.raster_band > 0 ? q.raster_band : 8;
   p.out_kind = q.out_kind;
+  p.alpha_array = q.alpha_array; p.beta_array = q.beta_array;
   p.bias = q.bias; p.bias_mode = q.bias_mode; p.bias_group_stride = q.bias_group_stride; p.activation = q.activation;
   p.C = static_cast<const __nv_bfloat16*>(q.C);
   p.D = q.D;
@@ -372,6 +376,7 @@ Problem from_grouped(const bsg_grouped_args* a) {
   q.tile_n = a->tile_n; q.cta_group = a->cta_group; q.sm_count = a->sm_count; q.raster_band = a->raster_band;
   q.bias = a->bias; q.bias_mode = a->bias ? BSG_BIAS_PER_COLUMN : BSG_BIAS_NONE; q.bias_group_stride = int32_t(a->N);
   q.activation = a->activation;
+  q.alpha_array = a->alpha_array; q.beta_array = a->beta_array;
   return q;
 }
 

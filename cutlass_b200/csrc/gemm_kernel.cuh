@@ -70,6 +70,8 @@ struct GemmParams {
   const float* alpha_ptr;
   const float* beta_ptr;
   const float* norm_ptr;
+  const float* alpha_array;   // grouped: one alpha per group (device), overrides alpha / alpha_ptr; or null
+  const float* beta_array;
   const float* bias;          // fp32 vector added to alpha * acc before beta * C, or null
   int32_t bias_mode;          // 1: one entry per output column; 2: one per row of the (batched) problem
   int32_t bias_group_stride;  // mode 1: entries between the bias vectors of two groups (0: one vector for all)
@@ -82,8 +84,8 @@ struct GemmParams {
   uint32_t flag_target;
   int32_t tile_m_rotate;      // dense only: start the M sweep at this tile row
   int32_t debug_flags;        // only read when built with -DBSG_PROFILE (ablation switches, timeline capture)
-  // Tensor-parallel all-gather of A (kernel template TP == true): the copy warps push this rank's
-  // row shard of A and SFA into every peer's full-size buffers.
+  // Tensor-parallel all-gather of A (kernel template TP == true): the push warp of every CTA sends pieces of
+  // this rank's row shard of A and SFA into every peer's gathered buffer.
   int32_t tp_world, tp_rank;
   int32_t tp_rows_per_shard;  // multiple of 256
   int32_t tp_ksplit;          // pieces a 256-row block is cut into (one flag increment each)
@@ -93,9 +95,9 @@ struct GemmParams {
   int32_t tp_remote_row_offset;   // rows between the buffer this call gathers into and buffer 0 (0 or M)
   int64_t tp_row_bytes;       // bytes of one row of A
   int64_t tp_sfa_rowatom_bytes;   // bytes of one 128-row atom row of SFA (512 * k_atoms)
-  const uint8_t* tp_peer_a[8];    // full-size A buffer of every rank (own entry = local buffer)
+  const uint8_t* tp_peer_a[8];    // gathered A buffer of every rank that this call fills (own entry = source: local buffer 0)
   const uint8_t* tp_peer_sfa[8];
-  uint32_t* tp_peer_sync[8];      // sync words of every rank: [0,8) "buffer free for call n", [32, ...) row-block flags
+  uint32_t* tp_peer_sync[8];      // sync words of every rank: [0,8) "rank q has launched call n", [32, ...) row-block counters
 };
 
 constexpr int kTpSyncReady = 0;
@@ -765,9 +767,8 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
   } else if (warp < 4) {
     // ---------------------------------------------------------------- epilogue (warps 0-3)
-    const float alpha = p.alpha_ptr ? *p.alpha_ptr : p.alpha;
-    const float beta = p.beta_ptr ? *p.beta_ptr : p.beta;
-    const bool use_c = (p.C != nullptr) && (beta != 0.0f);
+    const float alpha_all = p.alpha_ptr ? *p.alpha_ptr : p.alpha;
+    const float beta_all = p.beta_ptr ? *p.beta_ptr : p.beta;
     float st = 0.f, st_scaled = 0.f;
     if (p.out_kind != kOutBf16) {
       st = p.norm_ptr ? *p.norm_ptr : 1.0f;
@@ -782,6 +783,10 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     int32_t it = 0;
     for (int32_t t = cluster_idx; t < total_tiles; t += num_clusters, ++it) {
       const TileInfo ti = decode_tile(ctl, p, t, C::kTileM);
+      // One alpha / beta per group when the arrays are given (grouped GEMM), else the scalars.
+      const float alpha = p.alpha_array ? __ldg(p.alpha_array + ti.g) : alpha_all;
+      const float beta = p.beta_array ? __ldg(p.beta_array + ti.g) : beta_all;
+      const bool use_c = (p.C != nullptr) && (beta != 0.0f);
       const int acc_bar = it % C::kAccBars;
       const uint32_t acc_phase = uint32_t(it / C::kAccBars) & 1u;
       const uint32_t acc_col = uint32_t(it & 1) * C::kAccStride;

@@ -59,6 +59,7 @@ class GroupedArgs(C.Structure):
         ("alpha", C.c_float), ("beta", C.c_float),
         ("tile_n", C.c_int32), ("cta_group", C.c_int32), ("sm_count", C.c_int32), ("raster_band", C.c_int32),
         ("bias", C.c_void_p), ("reserved1", C.c_int32), ("activation", C.c_int32),
+        ("alpha_array", C.c_void_p), ("beta_array", C.c_void_p),
     ]
 
 

@@ -367,9 +367,10 @@ class GroupedBlockScaledGemmOperator(Operator):
         epi = args.epilogue or EpilogueDescriptor()
         if epi.out_quant is not None:
             return Status.fail("NVFP4 output is not available for grouped GEMM")
-        if isinstance(epi.alpha, torch.Tensor) or isinstance(epi.beta, torch.Tensor):
-            return Status.fail("grouped GEMM takes scalar alpha / beta")
-        if epi.C is None and float(epi.beta) != 0.0:
+        for name, v in (("alpha", epi.alpha), ("beta", epi.beta)):
+            if isinstance(v, torch.Tensor) and (v.dtype != torch.float32 or v.numel() != ps.L or not v.is_contiguous()):
+                return Status.fail(f"grouped GEMM takes a scalar {name} or a contiguous fp32 tensor with one entry per group ({ps.L})")
+        if epi.C is None and (isinstance(epi.beta, torch.Tensor) or float(epi.beta) != 0.0):
             return Status.fail("beta != 0 needs C")
         if not args.offsets.tensor.is_contiguous():
             return Status.fail("offsets must be contiguous")
@@ -400,8 +401,14 @@ class GroupedBlockScaledGemmOperator(Operator):
         a.offsets = args.offsets.data_ptr()
         a.ldc = ps.N
         a.ldd = ps.N
-        a.alpha = float(epi.alpha)
-        a.beta = float(epi.beta)
+        if isinstance(epi.alpha, torch.Tensor):
+            a.alpha, a.alpha_array = 1.0, epi.alpha.data_ptr()
+        else:
+            a.alpha = float(epi.alpha)
+        if isinstance(epi.beta, torch.Tensor):
+            a.beta, a.beta_array = 0.0, epi.beta.data_ptr()
+        else:
+            a.beta = float(epi.beta)
         a.bias = epi.bias.data_ptr() if epi.bias is not None else None
         a.activation = ACTIVATIONS[epi.activation]
         a.tile_n = md.tile_n

@@ -6,9 +6,10 @@ Plays the role of the reference's distributed all-gather GEMM
 ``AllGather1D_TilingCD_RotatingA``; host orchestration in
 ``examples/python/CuTeDSL/cute/blackwell/kernel/distributed/distributed_all_gather_gemm_blackwell.py:2166-2273``).
 There the copy engine moves the peer shards and per-stage GEMM launches are gated by flags; here a
-single kernel per rank does both: copy warps push this rank's rows into every peer's buffer over
-NVLink (posted stores) and bump per-row-block flags in the peer's memory; the tensor-core warps
-start on the local rows and follow the arrival order.
+single kernel per rank does both: one warp per CTA pushes this rank's rows into every peer's buffer
+over NVLink (bulk copies staged through shared memory) and bumps per-row-block arrival counters in the
+peer's memory; the tensor-core warps start on the local rows and follow the arrival order.  Two
+gathered buffers are used by alternate calls, so a peer may already send the next call's rows.
 
 The planning helpers at the top are pure Python (they restate the kernel's schedule) and are
 what the CPU multi-process tests exercise.

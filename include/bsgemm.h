@@ -126,6 +126,10 @@ typedef struct bsg_grouped_args {
   const float* bias;        /* device fp32 (num_groups, N): one vector per group, added per output column; or NULL */
   int32_t reserved1;
   int32_t activation;       /* BSG_ACT_* */
+  const float* alpha_array; /* device fp32[num_groups]: one alpha per group, overrides alpha; or NULL.  The reference passes
+                               per-group scalars as pointer arrays (examples/75_blackwell_grouped_gemm_block_scaled/
+                               75_blackwell_grouped_gemm_block_scaled.cu:693-719) */
+  const float* beta_array;  /* likewise for beta */
 } bsg_grouped_args;
 
 #define BSG_MAX_GROUPS 256

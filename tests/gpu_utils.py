@@ -85,7 +85,8 @@ def assert_close_bf16(got_bits, want_bits, rel_tol=1e-2):
         assert float((err[big] / np.abs(want[big])).max()) <= rel_tol
 
 
-def run_grouped(kind, sizes, N, K, seed, exact=True, alpha=1.0, beta=0.0, tile_n=0, cta_group=0, with_bias=False, activation=0):
+def run_grouped(kind, sizes, N, K, seed, exact=True, alpha=1.0, beta=0.0, tile_n=0, cta_group=0, with_bias=False, activation=0,
+                per_group_scalars=False):
     """Ragged grouped GEMM through the C ABI and the per-group oracle.  -> (got bits, want bits)."""
     rng = np.random.default_rng(seed)
     if kind == 0:
@@ -101,13 +102,20 @@ def run_grouped(kind, sizes, N, K, seed, exact=True, alpha=1.0, beta=0.0, tile_n
     Cb = G.bf16_normal((total, N), rng) if beta != 0 else None
     A_all = np.concatenate(As, axis=0)
     bias = (rng.standard_normal((len(sizes), N)) * 2).astype(np.float32) if with_bias else None
+    # per-group alpha / beta: powers of two keep the exact-arithmetic property; alpha stays positive because the oracle
+    # adds 0 * C where the kernel skips C (beta == 0), which differs in the sign of a zero result only
+    alphas = rng.choice([0.5, 1.0, 2.0, 4.0, 0.25], len(sizes)).astype(np.float32) if per_group_scalars else None
+    betas = rng.choice([0.0, 0.5, 1.0, -2.0], len(sizes)).astype(np.float32) if per_group_scalars else None
+    if per_group_scalars and Cb is None:
+        Cb = G.bf16_normal((total, N), rng)
     want = np.zeros((total, N), np.uint16)
     row = 0
     for g, m in enumerate(sizes):
         m = int(m)
         if m:
             cg = Cb[row:row + m] if Cb is not None else None
-            want[row:row + m] = oracle_bf16(kind, m, N, K, As[g], sfas[g], Bs[g], sfbs[g], cg, alpha, beta,
+            ag, bg = (float(alphas[g]), float(betas[g])) if per_group_scalars else (alpha, beta)
+            want[row:row + m] = oracle_bf16(kind, m, N, K, As[g], sfas[g], Bs[g], sfbs[g], cg, ag, bg,
                                             bias=bias[g] if with_bias else None, activation=activation)
         row += m
     lib = L.load()
@@ -127,6 +135,9 @@ def run_grouped(kind, sizes, N, K, seed, exact=True, alpha=1.0, beta=0.0, tile_n
     a.tile_n, a.cta_group = tile_n, cta_group
     dbias = dev(bias) if with_bias else None
     a.bias = dbias.data_ptr() if with_bias else None
+    dal, dbe = (dev(alphas), dev(betas)) if per_group_scalars else (None, None)
+    if per_group_scalars:
+        a.alpha_array, a.beta_array = dal.data_ptr(), dbe.data_ptr()
     a.activation = activation
     ws = torch.zeros(16, dtype=torch.uint8, device="cuda")
     L.check(lib.bsg_grouped_run(C.byref(a), ws.data_ptr(), 16, None))

@@ -40,7 +40,7 @@ def test_version_and_error_string(lib):
 def test_struct_sizes_match_header_layout():
     # 4 int32, 3 int64, 7 pointers, 2 int64, 2 float, 3 pointers, 4 int32
     assert C.sizeof(L.GemmArgs) == 16 + 24 + 56 + 16 + 8 + 24 + 16 + 16       # + bias pointer, bias_mode, activation
-    assert C.sizeof(L.GroupedArgs) == 16 + 24 + 56 + 16 + 8 + 16 + 16
+    assert C.sizeof(L.GroupedArgs) == 16 + 24 + 56 + 16 + 8 + 16 + 16 + 16     # + alpha_array, beta_array
     assert C.sizeof(L.Caps) == 32
 
 

@@ -147,6 +147,13 @@ def test_grouped_bias_per_group_and_activation(cuda_lib, kind):
     assert_close_bf16(got, want)
 
 
+@pytest.mark.parametrize("kind", [0, 1])
+def test_grouped_per_group_alpha_beta(cuda_lib, kind):
+    """One alpha and one beta per expert (device arrays), beta = 0 for some groups."""
+    got, want = run_grouped(kind, [130, 256, 0, 77, 512, 1], 256, 384, seed=8, exact=True, per_group_scalars=True)
+    assert np.array_equal(got, want)
+
+
 def test_activation_before_fused_quantisation(cuda_lib):
     """ReLU then NVFP4 / MXFP8 re-quantisation of the output: the quantiser sees the activated values."""
     M, N, K = 256, 512, 256
