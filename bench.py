@@ -323,7 +323,7 @@ def run_single(args) -> dict:
         torch.cuda.empty_cache()
         for k, v in (("RANK", "0"), ("WORLD_SIZE", "1"), ("LOCAL_RANK", "0"), ("MASTER_ADDR", "127.0.0.1"), ("MASTER_PORT", "29533")):
             os.environ.setdefault(k, v)
-        from cutlass_b200 import tp_bench
+        import bench_tp as tp_bench
         tp_args = argparse.Namespace(steps=max(3, min(args.steps, 30)), warmup=3)
         r = tp_bench.run(tp_args)
         tp_base = {"metric": r["metric"], "value": r["value"], "unit": r["unit"], "ms_per_step": r["ms_per_step"],
@@ -412,7 +412,7 @@ def main() -> None:
     if args.gpus == 1:
         print(json.dumps(run_single(args)))
         return
-    from cutlass_b200 import tp_bench
+    import bench_tp as tp_bench
     out = tp_bench.run(args)
     if rank == 0:
         print(json.dumps(out))
