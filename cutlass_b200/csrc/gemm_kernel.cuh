@@ -605,17 +605,23 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           const int32_t k_left = p.K - kt * C::kTileK;
           const int n_mma = k_left >= C::kTileK ? 4 : (k_left + C::kMmaK - 1) / C::kMmaK;
           const uint32_t acc_flag = kt > 0 ? 1u : 0u;
+          // MXFP8 needs 4 + BN/32 scale-factor columns per k-tile and has room for two sets: consecutive k-tiles
+          // alternate between them, so the copies of one k-tile do not have to wait for the MMAs of the previous
+          // one to have read theirs.  (NVFP4 fills all 48 columns with one set.)
+          const uint32_t sf_set = KIND == kKindMxfp8 ? uint32_t(kt & 1) : 0u;
+          const uint32_t sfa_col = tmem_base + C::kSfaCol + 4u * sf_set;
+          const uint32_t sfb_col = tmem_base + C::kSfbCol + uint32_t(BN / 32) * sf_set;
           if (elected && !dead) {     // after a timeout no further tensor-core work or barrier arrival is issued
             if (!BSG_FLAG(p, 1)) {
 #pragma unroll
               for (int ka = 0; ka < C::kKAtoms; ++ka) {
-                ptx::utccp_32x128b_warpx4<CG>(tmem_base + C::kSfaCol + 4 * ka, make_desc_sf(sfa_s + ka * 512));
+                ptx::utccp_32x128b_warpx4<CG>(sfa_col + 4 * ka, make_desc_sf(sfa_s + ka * 512));
               }
 #pragma unroll
               for (int ra = 0; ra < BN / 128; ++ra) {
 #pragma unroll
                 for (int ka = 0; ka < C::kKAtoms; ++ka) {
-                  ptx::utccp_32x128b_warpx4<CG>(tmem_base + C::kSfbCol + (BN / 32) * ka + 4 * ra,
+                  ptx::utccp_32x128b_warpx4<CG>(sfb_col + (BN / 32) * ka + 4 * ra,
                                                 make_desc_sf(sfb_s + (ra * C::kKAtoms + ka) * 512));
                 }
               }
@@ -625,11 +631,11 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               if (kb < n_mma && !BSG_FLAG(p, 8)) {
                 uint32_t sfa_t, sfb_t, id = idesc;
                 if constexpr (KIND == kKindNvfp4) {
-                  sfa_t = tmem_base + C::kSfaCol + 4 * kb;
-                  sfb_t = tmem_base + C::kSfbCol + (BN / 32) * kb;
+                  sfa_t = sfa_col + 4 * kb;
+                  sfb_t = sfb_col + (BN / 32) * kb;
                 } else {
-                  sfa_t = tmem_base + C::kSfaCol;
-                  sfb_t = tmem_base + C::kSfbCol;
+                  sfa_t = sfa_col;
+                  sfb_t = sfb_col;
                   id |= (uint32_t(kb) << 4) | (uint32_t(kb) << 29);   // scale-factor byte of this K block
                 }
                 ptx::umma_block_scaled<KIND, CG>(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, id, sfa_t, sfb_t,
