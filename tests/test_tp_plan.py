@@ -89,3 +89,14 @@ def test_handle_exchange_two_gloo_ranks():
         assert got == [bytes([0]) * 64, bytes([1]) * 64]          # every rank holds every handle, indexed by rank
         assert rows == (rank * 512, (rank + 1) * 512)
         assert order == [rank, 1 - rank]
+
+
+@pytest.mark.parametrize("grid", [128, 148])
+def test_scale_factor_pieces_are_spread_over_the_ctas(grid):
+    """The piece of a row block that also carries its scale factors (k_piece 0) is twice as large; the rotation of
+    k_piece from block to block must keep such pieces from piling up on one CTA, whatever the grid size."""
+    world, M, ksplit = 2, 16384, 32
+    per_cta = [sum(1 for p in TP.copy_schedule(world, 0, M, ksplit, cta, grid) if p.k_piece == 0) for cta in range(grid)]
+    blocks = M // world // TP.ROW_BLOCK
+    assert sum(per_cta) == (world - 1) * blocks
+    assert max(per_cta) <= 2
