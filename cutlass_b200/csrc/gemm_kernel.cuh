@@ -141,12 +141,24 @@ struct Cfg {
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kTpBytes + kCtlBytes + 1024;
   // TMEM columns: two accumulators (overlapping by 48 columns when BN == 256), then SFA, then SFB.
-  static constexpr int kAccStride = BN == 256 ? 208 : 128;
+  // Scale-factor sets: consecutive k-tiles alternate between kSfSets sets of columns, so that the copies of one
+  // k-tile need not wait for the MMAs of the previous one to have read theirs.  MXFP8 has room for two sets next
+  // to the standard layout.  NVFP4 fills its 48 columns with one set; building with -DBSG_NVFP4_SF_SETS=2
+  // (BN == 256 only: accumulators 160 columns apart, 96 columns of overlap, released after two drained pairs) is an
+  // experiment that has not run yet.
+#ifndef BSG_NVFP4_SF_SETS
+#define BSG_NVFP4_SF_SETS 1
+#endif
+  static constexpr bool kNvfp4TwoSets = KIND == kKindNvfp4 && BN == 256 && BSG_NVFP4_SF_SETS == 2;
+  static constexpr int kSfSets = (KIND == kKindMxfp8 || kNvfp4TwoSets) ? 2 : 1;
+  static constexpr int kSfaSetStride = KIND == kKindMxfp8 ? 4 : 48;        // columns between the SFA of two sets
+  static constexpr int kSfbSetStride = KIND == kKindMxfp8 ? BN / 32 : 48;
+  static constexpr int kAccStride = BN == 256 ? (kNvfp4TwoSets ? 160 : 208) : 128;
   static constexpr int kAccBars = BN == 256 ? 1 : 2;
-  static constexpr int kSfaCol = 464;
-  static constexpr int kSfbCol = 480;
+  static constexpr int kSfaCol = kNvfp4TwoSets ? 416 : 464;
+  static constexpr int kSfbCol = kNvfp4TwoSets ? 432 : 480;
   static constexpr int kPairs = BN / 64;                  // the epilogue drains 64 columns at a time
-  static constexpr int kReleasePair = BN == 256 ? 0 : kPairs - 1;   // pair after whose load the accumulator is released
+  static constexpr int kReleasePair = BN == 256 ? (kNvfp4TwoSets ? 1 : 0) : kPairs - 1;   // pair after whose load the accumulator is released
 };
 
 struct alignas(8) Ctl {
@@ -605,12 +617,9 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           const int32_t k_left = p.K - kt * C::kTileK;
           const int n_mma = k_left >= C::kTileK ? 4 : (k_left + C::kMmaK - 1) / C::kMmaK;
           const uint32_t acc_flag = kt > 0 ? 1u : 0u;
-          // MXFP8 needs 4 + BN/32 scale-factor columns per k-tile and has room for two sets: consecutive k-tiles
-          // alternate between them, so the copies of one k-tile do not have to wait for the MMAs of the previous
-          // one to have read theirs.  (NVFP4 fills all 48 columns with one set.)
-          const uint32_t sf_set = KIND == kKindMxfp8 ? uint32_t(kt & 1) : 0u;
-          const uint32_t sfa_col = tmem_base + C::kSfaCol + 4u * sf_set;
-          const uint32_t sfb_col = tmem_base + C::kSfbCol + uint32_t(BN / 32) * sf_set;
+          const uint32_t sf_set = C::kSfSets == 2 ? uint32_t(kt & 1) : 0u;       // see Cfg: scale-factor sets
+          const uint32_t sfa_col = tmem_base + C::kSfaCol + uint32_t(C::kSfaSetStride) * sf_set;
+          const uint32_t sfb_col = tmem_base + C::kSfbCol + uint32_t(C::kSfbSetStride) * sf_set;
           if (elected && !dead) {     // after a timeout no further tensor-core work or barrier arrival is issued
             if (!BSG_FLAG(p, 1)) {
 #pragma unroll

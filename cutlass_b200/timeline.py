@@ -29,7 +29,7 @@ def capture(kind: int, M: int, N: int, K: int, flags: int = 0, cta_group: int = 
     from . import formats as F
     from . import lib as L
     B.PROFILE = True
-    B.OUT = os.path.join(os.path.dirname(B.OUT), "libbsgemm_profile.so")
+    B.OUT = os.path.join(os.path.dirname(B.OUT), B.lib_name(True, B.SF2))
     B.build()
     L.LIB_PATH = B.OUT
     lib = L.load()
