@@ -99,3 +99,70 @@ def test_tp_gathers_a_inside_the_kernel(kind, world, M, N, K):
     for p in procs:
         p.join(timeout=120)
     assert results == [(r, "ok") for r in range(world)], results
+
+
+def _worker_peer_absent(rank, world, port, q):
+    """Rank 1 never launches its call: rank 0's kernel must come back by itself with a time-out status."""
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                          LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+        import time
+
+        import torch.distributed as dist
+        from cutlass_b200 import lib as L
+        from cutlass_b200 import tp as TP
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        kind, M, N, K = 1, 1024, 512, 1024
+        tp = TP.TpGemm(kind, M, K)
+        verdict = "ok"
+        try:
+            if rank == 0:
+                A, sfa, B, sfb = _problem(kind, M, N, K, 7)
+                ns = N // world
+                tp.a_shard.copy_(torch.from_numpy(A[:M // world]).cuda())
+                tp.sfa_shard.copy_(torch.from_numpy(sfa[:tp.sfa_shard.numel()]).cuda())
+                dB = torch.from_numpy(np.ascontiguousarray(B[:ns])).cuda()
+                dSFB = torch.from_numpy(np.ascontiguousarray(sfb[:(ns // 128) * 512 * (K // 32 // 4)])).cuda()
+                out = torch.zeros((M, ns), dtype=torch.int16, device="cuda")
+                t0 = time.time()
+                tp.run(dB, dSFB, out)
+                torch.cuda.synchronize()                      # the bounded waits run out after about two seconds
+                took = time.time() - t0
+                try:
+                    tp.check_device_status()
+                    verdict = "no time-out was reported"
+                except L.BsgError as exc:
+                    if exc.code != 7:                         # BSG_ERR_TIMEOUT
+                        verdict = f"unexpected status {exc}"
+                if took > 30:
+                    verdict = f"the kernel took {took:.1f} s to give up"
+                # the context is still usable
+                assert int((torch.ones(4, device="cuda") * 2).sum().item()) == 8
+        finally:
+            torch.cuda.synchronize()
+            dist.barrier()                                    # rank 1 waits here, with nothing of its own in flight
+            tp.close()
+            dist.barrier()
+            dist.destroy_process_group()
+        q.put((rank, verdict))
+    except Exception as e:  # noqa: BLE001
+        q.put((rank, repr(e)))
+
+
+def test_tp_rank_that_never_launches_gives_a_timeout_status_not_a_hang():
+    """Failure detection without a fault: the missing peer is a host-side event (it simply does not call run); the
+    surviving rank's device-side waits are bounded and the host reads BSG_ERR_TIMEOUT."""
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_peer_absent, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+    assert results == [(r, "ok") for r in range(world)], results
