@@ -1,7 +1,7 @@
 // Persistent warp-specialised block-scaled GEMM for sm_100a.
 //
-//   D = alpha * (A . SFA)(B . SFB)^T + beta * C          (bf16 out), or
-//   (D, SFD) = nvfp4_quantise(alpha * ... + beta * C)     (e2m1 + ue4m3 out)
+//   X = act(alpha * (A . SFA)(B . SFB)^T + bias + beta * C)
+//   D = bf16(X),  or  (D, SFD) = block-scaled quantisation of X (e2m1 + ue4m3 per 16, or e4m3 + ue8m0 per 32)
 //
 // One kernel serves the dense, batched, grouped (ragged M) and flag-gated
 // (tensor-parallel) forms: every output tile belongs to a "group" that owns a
@@ -9,9 +9,10 @@
 // layouts.
 //
 // Roles (192 threads): warps 0-3 epilogue (TMEM lane quadrant = warp id),
-// warp 4 UMMA issue + TMEM allocation, warp 5 TMA producer.  With CG == 2 two
-// CTAs of a cluster form one 256-row MMA (cta_group::2): both load their half
-// of A and B, the even CTA issues the MMA, both run their own epilogue.
+// warp 4 UMMA issue + TMEM allocation, warp 5 TMA producer; the tensor-parallel
+// variant adds warp 6, which pushes this rank's rows of A to the peers.  With
+// CG == 2 two CTAs of a cluster form one 256-row MMA (cta_group::2): both load
+// their half of A and B, the even CTA issues the MMA, both run their own epilogue.
 //
 // The producer and MMA warps run their loops with all 32 lanes (warp-uniform
 // control flow and operands; only the issuing instructions are predicated on one
@@ -22,8 +23,9 @@
 // mainloop include/cutlass/gemm/collective/sm100_blockscaled_mma_warpspecialized.hpp
 // (load :879, mma :949) and the linear-combination / block-scale-factor epilogue
 // (include/cutlass/epilogue/fusion/sm100_visitor_store_tma_warpspecialized.hpp:226-275).
-// Every wait is bounded: on a timeout the kernel records a status bit, keeps going
-// through the motions with short waits, and returns.
+// Every wait is bounded: on a timeout the role records a status bit, issues no further
+// loads, MMAs or pushes, runs through its remaining loop iterations with short waits,
+// and the kernel returns after a pause for what is still in flight.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
