@@ -131,6 +131,47 @@ def test_quantisation_equals_compiled_reference():
 
 
 @pytest.mark.skipif(ref_missing, reason="compiled reference driver (oracle/_ref) not present")
+@pytest.mark.parametrize("st", [1.0, 0.37, 1e-3, 300.0])
+def test_both_output_quantisations_on_wide_magnitudes_equal_compiled_reference(st):
+    """K = 32 with one non-zero per row turns the GEMM into a table of chosen products, so the quantisation of the
+    reference's epilogue sees magnitudes more than five decades apart, zero blocks included; both output types, bit for bit."""
+    M, N, K = 128, 256, 32
+    rng = np.random.default_rng(3)
+    codesA = np.zeros((M, K), np.uint8)
+    codesB = np.zeros((N, K), np.uint8)
+    codesA[np.arange(M), np.arange(M) % K] = rng.integers(1, 8, M)
+    codesB[np.arange(N), rng.integers(0, K, N)] = rng.integers(1, 16, N)
+    codesB[codesB == 8] = 1
+    A, B = F.pack_e2m1(codesA), F.pack_e2m1(codesB)
+    sfa = F.swizzle_sf(rng.integers(0x20, 0x60, (M, 2)).astype(np.uint8))
+    sfb = F.swizzle_sf(rng.integers(0x20, 0x60, (N, 2)).astype(np.uint8))
+    pre = oracle.gemm_fp32(0, A, sfa, B, sfb, M, N, K)
+    assert (pre == 0).any() and np.abs(pre).max() / np.abs(pre[pre != 0]).min() > 1e5
+    for mode, qkind, vec in ((2, 0, 16), (3, 1, 32)):
+        Dr, Sr = oracle.ref_gemm(0, mode, A, sfa, B, sfb, M, N, K, None, 1.0, 0.0, st)
+        Do, So = oracle.quant(qkind, pre, st)
+        idx = R.sf_index(M, N // vec)
+        assert np.array_equal(Do, Dr), (mode, st)
+        assert np.array_equal(So[idx], Sr[idx]), (mode, st)
+
+
+@pytest.mark.skipif(ref_missing, reason="compiled reference driver (oracle/_ref) not present")
+@pytest.mark.parametrize("kind", [0, 1])
+@pytest.mark.parametrize("act,per_row", [(0, False), (1, True), (2, False), (3, True)])
+def test_epilogue_with_bias_and_activation_equals_compiled_reference(kind, act, per_row):
+    rng = np.random.default_rng(17 + act)
+    gen = G.nvfp4_operand if kind == 0 else G.mxfp8_operand
+    M, N, K = 70, 136, 192
+    A, _, sfa = gen(M, K, rng)
+    B, _, sfb = gen(N, K, rng)
+    Cb = G.bf16_normal((M, N), rng)
+    bias = (rng.standard_normal(M if per_row else N) * 3).astype(np.float32)
+    r = oracle.ref_gemm_epi(kind, A, sfa, B, sfb, M, N, K, Cb, 0.75, 0.5, bias, per_row, act)
+    o = oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K, Cb, 0.75, 0.5, bias=bias, bias_per_row=per_row, activation=act)
+    assert np.array_equal(o.view(np.uint32), r.view(np.uint32))
+
+
+@pytest.mark.skipif(ref_missing, reason="compiled reference driver (oracle/_ref) not present")
 def test_codecs_exhaustive_against_compiled_reference():
     ref = oracle.load_ref()
     lib = oracle.load_oracle()
