@@ -6,14 +6,14 @@ Operator API; the work is done by hand-written CUDA behind a C ABI
 from .arguments import (DenseTensor, EpilogueDescriptor, GemmArguments, GemmProblemSize, GroupedGemmArguments,
                         Mxfp8Quant, Nvfp4Quant, ScaledOperand, ScaleMode, ScaleSwizzleMode)
 from .operator import (AllocationRequirement, BlockScaledGemmOperator, CompiledArtifact,
-                       GroupedBlockScaledGemmOperator, Operator, OperatorMetadata, Workspace, all_operators,
+                       GroupedBlockScaledGemmOperator, NativeProvider, Operator, OperatorMetadata, Workspace, all_operators,
                        get_operators, to_cuda_stream)
 from .quantize import quantize_blockscaled
 from .status import Status
 
 __all__ = [
     "AllocationRequirement", "BlockScaledGemmOperator", "CompiledArtifact", "DenseTensor", "EpilogueDescriptor",
-    "GemmArguments", "GemmProblemSize", "GroupedBlockScaledGemmOperator", "GroupedGemmArguments", "Mxfp8Quant", "Nvfp4Quant",
+    "GemmArguments", "GemmProblemSize", "GroupedBlockScaledGemmOperator", "GroupedGemmArguments", "Mxfp8Quant", "NativeProvider", "Nvfp4Quant",
     "Operator", "OperatorMetadata", "ScaleMode", "ScaleSwizzleMode", "ScaledOperand", "Status", "Workspace",
     "all_operators", "get_operators", "quantize_blockscaled", "to_cuda_stream",
 ]

@@ -440,9 +440,24 @@ def all_operators() -> list[Operator]:
     return ops
 
 
+class NativeProvider:
+    """The one source of operators here: the hand-written sm_100a library.  Takes the place of the reference's
+    provider classes (operators/cutlass/operators/providers/provider.py:43) in ``get_operators(providers=...)``."""
+
+    name = "native"
+
+    @staticmethod
+    def operators() -> list["Operator"]:
+        return all_operators()
+
+
 def get_operators(args=None, metadata_filter: Callable[[OperatorMetadata], bool] | None = None,
-                  target_sm: str | None = None) -> list[Operator]:
-    """Operators that can run ``args`` (all operators when ``args`` is None), best first."""
+                  target_sm: str | None = None, providers: list | None = None) -> list[Operator]:
+    """Operators that can run ``args`` (all operators when ``args`` is None), best first.  Same parameters as the
+    reference's ``get_operators`` (operators/cutlass/operators/__init__.py:72); ``providers`` restricts discovery to the
+    listed providers, of which this package has one (``NativeProvider``)."""
+    if providers is not None and NativeProvider not in providers and not any(isinstance(p, NativeProvider) for p in providers):
+        return []
     out = []
     for op in all_operators():
         if metadata_filter is not None and not metadata_filter(op.metadata):

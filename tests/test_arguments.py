@@ -251,3 +251,12 @@ def test_quantize_blockscaled_argument_checks():
         ops.quantize_blockscaled(x, M16)
     with pytest.raises(ValueError, match="scale mode"):
         ops.quantize_blockscaled(x, (1, 1, 64))
+
+
+def test_get_operators_takes_the_reference_parameters():
+    args = nvfp4_args()
+    everything = ops.get_operators(args)
+    assert len(ops.get_operators(args, None, "100a", [ops.NativeProvider])) == len(everything)
+    assert len(ops.get_operators(args, providers=[ops.NativeProvider])) == len(everything) > 0
+    assert ops.get_operators(args, providers=[]) == []
+    assert ops.get_operators(args, target_sm="90a") == []
