@@ -252,6 +252,12 @@ int32_t bsg_quantize(const bsg_quant_args* args, void* cuda_stream);
  * bsg_tp_gemm_run enqueues one GEMM; args->A / SFA are ignored, args->M is the full M, args->N
  *                 the local N shard.  All ranks must call it the same number of times with the
  *                 same shapes.
+ *                 The caller may rewrite its shard for the next call as soon as this call is complete on the
+ *                 stream (the push has read it by then).  With the default two gathered buffers a rank may run
+ *                 at most one call ahead of its slowest peer; the device-side waits that enforce this are
+ *                 bounded (about two seconds), after which bsg_read_device_status reports BSG_ERR_TIMEOUT.
+ * bsg_tp_destroy  frees the buffers the peers write into: call it only after every rank has finished its last
+ *                 call (synchronise the device, then a barrier across the ranks), never with a call in flight.
  * bsg_tp_set_mode  chooses who moves the shard: BSG_TP_PUSH_KERNEL -- a warp of the GEMM kernel itself, through
  *                 the SM's bulk-copy engine (one launch per GEMM); or
  *                 BSG_TP_PUSH_COPY_ENGINE -- the GPU's copy engines on an internal side stream, one transfer per
