@@ -10,15 +10,14 @@ import sys
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
-PROFILE = os.environ.get("BSG_PROFILE") == "1"      # ablation switches + timeline capture, separate file
-SF2 = os.environ.get("BSG_NVFP4_SF_SETS") == "2"    # experimental NVFP4 TMEM layout with two scale-factor sets, separate file
+PROFILE = os.environ.get("BSG_PROFILE") == "1"      # in-kernel timeline capture, separate file
 
 
-def lib_name(profile: bool, sf2: bool) -> str:
-    return "libbsgemm" + ("_profile" if profile else "") + ("_sf2" if sf2 else "") + ".so"
+def lib_name(profile: bool) -> str:
+    return "libbsgemm" + ("_profile" if profile else "") + ".so"
 
 
-OUT = os.path.join(_HERE, "lib", lib_name(PROFILE, SF2))
+OUT = os.path.join(_HERE, "lib", lib_name(PROFILE))
 SOURCES = ["bsgemm.cu"]
 HEADERS = ["gemm_kernel.cuh", "quant_kernel.cuh", "ptx.cuh", os.path.join("..", "..", "include", "bsgemm.h")]
 NVCC_FLAGS = [
@@ -41,7 +40,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return OUT
     nvcc = os.environ.get("NVCC", "nvcc")
     os.makedirs(os.path.dirname(OUT), exist_ok=True)
-    extra = (["-DBSG_PROFILE"] if PROFILE else []) + (["-DBSG_NVFP4_SF_SETS=2"] if SF2 else [])
+    extra = ["-DBSG_PROFILE"] if PROFILE else []
     cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-o", OUT] + [os.path.join(CSRC, f) for f in SOURCES]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:

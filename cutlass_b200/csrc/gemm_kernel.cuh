@@ -106,12 +106,6 @@ constexpr int kTpSyncReady = 0;
 constexpr int kTpSyncFlags = 32;
 constexpr uint32_t kStTimeoutPeer = 64u;      // tensor parallel: a peer never published / finished
 
-#ifdef BSG_PROFILE
-#define BSG_FLAG(p, bit) (((p).debug_flags & (bit)) != 0)
-#else
-#define BSG_FLAG(p, bit) false
-#endif
-
 template <int KIND, int CG, int BN, bool TP = false>
 struct Cfg {
   static_assert(KIND == kKindNvfp4 || KIND == kKindMxfp8, "kind");
@@ -130,7 +124,12 @@ struct Cfg {
   static constexpr int kSfaBytes = kKAtoms * 512;
   static constexpr int kSfbBytes = (BN / 128) * kKAtoms * 512;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
-  static constexpr int kCtlBytes = 8192;
+#ifdef BSG_PROFILE
+  static constexpr int kDbgBytes = (512 + 1024 + 256) * 4;   // instrumented build: in-kernel timeline stamps
+#else
+  static constexpr int kDbgBytes = 0;
+#endif
+  static constexpr int kCtlBytes = 8192 + kDbgBytes;
   static constexpr int kEpiBytes = 4 * 4096;              // per epilogue warp: 32 rows x 128 bytes of bf16 output
   static constexpr int kSmemLimit = 232448;               // 227 KB
   static constexpr int kTpChunk = 8192;                   // tensor parallel: bytes per bulk copy of the A push
@@ -142,25 +141,16 @@ struct Cfg {
   static constexpr int kStagesRaw = (kSmemLimit - kCtlBytes - kEpiBytes - kTpBytes - 1024) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + kTpBytes + kCtlBytes + 1024;
-  // TMEM columns: two accumulators (overlapping by 48 columns when BN == 256), then SFA, then SFB.
-  // Scale-factor sets: consecutive k-tiles alternate between kSfSets sets of columns, so that the copies of one
-  // k-tile need not wait for the MMAs of the previous one to have read theirs.  MXFP8 has room for two sets next
-  // to the standard layout.  NVFP4 fills its 48 columns with one set; building with -DBSG_NVFP4_SF_SETS=2
-  // (BN == 256 only: accumulators 160 columns apart, 96 columns of overlap, released after two drained pairs) is an
-  // experiment that has not run yet.
-#ifndef BSG_NVFP4_SF_SETS
-#define BSG_NVFP4_SF_SETS 1
-#endif
-  static constexpr bool kNvfp4TwoSets = KIND == kKindNvfp4 && BN == 256 && BSG_NVFP4_SF_SETS == 2;
-  static constexpr int kSfSets = (KIND == kKindMxfp8 || kNvfp4TwoSets) ? 2 : 1;
-  static constexpr int kSfaSetStride = KIND == kKindMxfp8 ? 4 : 48;        // columns between the SFA of two sets
-  static constexpr int kSfbSetStride = KIND == kKindMxfp8 ? BN / 32 : 48;
-  static constexpr int kAccStride = BN == 256 ? (kNvfp4TwoSets ? 160 : 208) : 128;
+  // TMEM columns: two accumulators (overlapping by 48 columns when BN == 256), then SFA (16), then SFB (32).
+  // One set of scale-factor columns: a second set, used by alternate k-tiles so that a k-tile's copies need not
+  // wait for the previous k-tile's MMAs, was measured for both kinds and gained nothing (the copies and the MMAs
+  // of one issuing thread run strictly in order in the tensor pipe).
+  static constexpr int kAccStride = BN == 256 ? 208 : 128;
   static constexpr int kAccBars = BN == 256 ? 1 : 2;
-  static constexpr int kSfaCol = kNvfp4TwoSets ? 416 : 464;
-  static constexpr int kSfbCol = kNvfp4TwoSets ? 432 : 480;
+  static constexpr int kSfaCol = 464;
+  static constexpr int kSfbCol = 480;
   static constexpr int kPairs = BN / 64;                  // the epilogue drains 64 columns at a time
-  static constexpr int kReleasePair = BN == 256 ? (kNvfp4TwoSets ? 1 : 0) : kPairs - 1;   // pair after whose load the accumulator is released
+  static constexpr int kReleasePair = BN == 256 ? 0 : kPairs - 1;   // pair after whose load the accumulator is released
 };
 
 struct alignas(8) Ctl {
@@ -273,14 +263,6 @@ __device__ __forceinline__ uint4 ld_global_v4(const void* p) {
 __device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-
-#ifdef BSG_PROFILE
-__device__ __forceinline__ unsigned long long gtimer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#endif
 
 // Bounded spin until *flag >= target (system-scope acquire).  Returns false on timeout.
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t target, Ctl* ctl) {
@@ -484,14 +466,17 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const int32_t k_tiles = (p.K + C::kTileK - 1) / C::kTileK;
   uint32_t dead = 0;
 #ifdef BSG_PROFILE
-  const bool tp_trace = BSG_FLAG(p, 16384) && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1);
-  const unsigned long long trace_t0 = gtimer();
-  // Timeline capture: the workspace holds, after its first 1024 bytes, 3 regions of 4096 events
-  // (producer, MMA, epilogue) of (code << 48 | SM clock), written by the first cluster only.
-  unsigned long long* dbg = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(p.status) + 1024);
-  const bool dbg_on = BSG_FLAG(p, 256) && cluster_idx == 0 && is_leader;
-  uint32_t dbg_n = 0;
-#define BSG_DBG(region, code) do { if (dbg_on && lane == 0 && dbg_n < 4096) { dbg[(region) * 4096 + dbg_n++] = ((unsigned long long)(code) << 48) | ((unsigned long long)clock64() & 0xFFFFFFFFFFFFull); } } while (0)
+  // Timeline capture (instrumented build only, debug_flags != 0): the first cluster's leader CTA collects stamps
+  // (code << 26 | low 26 bits of the SM clock) in shared memory, regions of 512 / 1024 / 256 entries for the
+  // producer, MMA and epilogue warps (entry 0 = count), and copies them behind the first 1024 bytes of the
+  // workspace when the kernel ends.
+  uint32_t* dbg_s = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(ctl) + 8192);
+  const bool dbg_on = p.debug_flags != 0 && cluster_idx == 0 && is_leader;
+  uint32_t dbg_n = 1;
+#define BSG_DBG(region, code) do { if (dbg_on && lane == 0) { constexpr int o_ = (region) == 0 ? 0 : (region) == 1 ? 512 : 1536; \
+    constexpr int cap_ = (region) == 0 ? 512 : (region) == 1 ? 1024 : 256; \
+    if (dbg_n < cap_) { dbg_s[o_ + dbg_n++] = (uint32_t(code) << 26) | (uint32_t(clock64()) & 0x3FFFFFFu); dbg_s[o_] = dbg_n; } } } while (0)
+  if (dbg_on && threadIdx.x < 3) dbg_s[threadIdx.x == 0 ? 0 : threadIdx.x == 1 ? 512 : 1536] = 1;
 #else
 #define BSG_DBG(region, code) do { } while (0)
 #endif
@@ -518,11 +503,8 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const int32_t group_atoms = (ti.row_end - ti.group_row0 + 127) >> 7;
       const int32_t sfa_atom = bcast(min(ti.sf_atom + int32_t(cta_rank), ti.group_atom0 + max(group_atoms, 1) - 1) + (tp_row_off >> 7));
       const int32_t sfb_atom = bcast(ti.g * p.sfb_atoms_per_group + ti.tn * (BN / 128));
-      if (p.ready_flags != nullptr && (!TP || tp_remote) && !BSG_FLAG(p, 1024)) {
+      if (p.ready_flags != nullptr && (!TP || tp_remote)) {
         const uint32_t* flag = p.ready_flags + ti.row0 / p.rows_per_flag;
-#ifdef BSG_PROFILE
-        const unsigned long long tw0 = gtimer();
-#endif
         const long long t0 = clock64();
         while (ptx::ld_acquire_sys_u32(flag) < p.flag_target) {
           if (dead || ctl->abort || clock64() - t0 > 4000000000ll) {
@@ -535,13 +517,6 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         asm volatile("fence.proxy.async;" ::: "memory");
         __syncwarp();
-#ifdef BSG_PROFILE
-        if (tp_trace && lane == 0) {
-          const unsigned long long tw1 = gtimer();
-          if (tw1 - tw0 > 2000) printf("r%d cta%d flagwait tile %d rowblk %d: from %.1f us for %.1f us\n", p.tp_rank, int(blockIdx.x), t,
-                                       ti.row0 / p.rows_per_flag, (tw0 - trace_t0) * 1e-3, (tw1 - tw0) * 1e-3);
-        }
-#endif
       }
       for (int32_t kt = 0; kt < k_tiles; ++kt) {
         wait_barrier(empty0 + stage * 8, phase ^ 1u, ctl, dead);
@@ -549,27 +524,12 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // After a timeout nothing more is issued: free-running loads would overrun the barriers' byte counts.
         if (elected && !dead) {
           const uint32_t full_local = full0 + stage * 8;
-          uint32_t txb = 0;
-          if (!BSG_FLAG(p, 2)) txb += C::kABytes + C::kBBytes;
-          if (!BSG_FLAG(p, 16)) txb += C::kSfaBytes + C::kSfbBytes;
-          if (is_leader) { if (txb) ptx::mbar_arrive_expect_tx(full_local, txb * CG); else ptx::mbar_arrive(full_local); }
+          if (is_leader) ptx::mbar_arrive_expect_tx(full_local, uint32_t(C::kStageBytes) * CG);
           const uint32_t bar = full0_leader + stage * 8;
-          if (!BSG_FLAG(p, 2)) {
-#ifdef BSG_PROFILE
-            // Ablation: L2 eviction priorities (1 << 20: A evict-first, 1 << 19: B evict-last).
-            if (BSG_FLAG(p, 1 << 20)) ptx::tma_load_2d_hint<CG>(sA0 + stage * C::kABytes, &tmA, bar, kt * C::kRowBytes, a_row, ptx::l2_policy_evict_first());
-            else ptx::tma_load_2d<CG>(sA0 + stage * C::kABytes, &tmA, bar, kt * C::kRowBytes, a_row);
-            if (BSG_FLAG(p, 1 << 19)) ptx::tma_load_2d_hint<CG>(sB0 + stage * C::kBBytes, &tmB, bar, kt * C::kRowBytes, b_row, ptx::l2_policy_evict_last());
-            else ptx::tma_load_2d<CG>(sB0 + stage * C::kBBytes, &tmB, bar, kt * C::kRowBytes, b_row);
-#else
-            ptx::tma_load_2d<CG>(sA0 + stage * C::kABytes, &tmA, bar, kt * C::kRowBytes, a_row);
-            ptx::tma_load_2d<CG>(sB0 + stage * C::kBBytes, &tmB, bar, kt * C::kRowBytes, b_row);
-#endif
-          }
-          if (!BSG_FLAG(p, 16)) {
-            ptx::tma_load_3d<CG>(sSFA0 + stage * C::kSfaBytes, &tmSFA, bar, 0, kt * C::kKAtoms, sfa_atom);
-            ptx::tma_load_3d<CG>(sSFB0 + stage * C::kSfbBytes, &tmSFB, bar, 0, kt * C::kKAtoms, sfb_atom);
-          }
+          ptx::tma_load_2d<CG>(sA0 + stage * C::kABytes, &tmA, bar, kt * C::kRowBytes, a_row);
+          ptx::tma_load_2d<CG>(sB0 + stage * C::kBBytes, &tmB, bar, kt * C::kRowBytes, b_row);
+          ptx::tma_load_3d<CG>(sSFA0 + stage * C::kSfaBytes, &tmSFA, bar, 0, kt * C::kKAtoms, sfa_atom);
+          ptx::tma_load_3d<CG>(sSFB0 + stage * C::kSfbBytes, &tmSFB, bar, 0, kt * C::kKAtoms, sfb_atom);
         }
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
       }
@@ -610,7 +570,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           int next_stage = stage + 1;
           uint32_t next_phase = phase;
           if (next_stage == C::kStages) { next_stage = 0; next_phase ^= 1u; }
-          ready = BSG_FLAG(p, 64) ? 0u : ptx::mbar_spin_test(full0 + next_stage * 8, next_phase, 1);
+          ready = ptx::mbar_spin_test(full0 + next_stage * 8, next_phase, 1);
           ptx::tc_fence_after();
           const uint32_t sfa_s = sSFA0 + stage * C::kSfaBytes;
           const uint32_t sfb_s = sSFB0 + stage * C::kSfbBytes;
@@ -619,27 +579,24 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           const int32_t k_left = p.K - kt * C::kTileK;
           const int n_mma = k_left >= C::kTileK ? 4 : (k_left + C::kMmaK - 1) / C::kMmaK;
           const uint32_t acc_flag = kt > 0 ? 1u : 0u;
-          const uint32_t sf_set = C::kSfSets == 2 ? uint32_t(kt & 1) : 0u;       // see Cfg: scale-factor sets
-          const uint32_t sfa_col = tmem_base + C::kSfaCol + uint32_t(C::kSfaSetStride) * sf_set;
-          const uint32_t sfb_col = tmem_base + C::kSfbCol + uint32_t(C::kSfbSetStride) * sf_set;
+          const uint32_t sfa_col = tmem_base + C::kSfaCol;
+          const uint32_t sfb_col = tmem_base + C::kSfbCol;
           if (elected && !dead) {     // after a timeout no further tensor-core work or barrier arrival is issued
-            if (!BSG_FLAG(p, 1)) {
+#pragma unroll
+            for (int ka = 0; ka < C::kKAtoms; ++ka) {
+              ptx::utccp_32x128b_warpx4<CG>(sfa_col + 4 * ka, make_desc_sf(sfa_s + ka * 512));
+            }
+#pragma unroll
+            for (int ra = 0; ra < BN / 128; ++ra) {
 #pragma unroll
               for (int ka = 0; ka < C::kKAtoms; ++ka) {
-                ptx::utccp_32x128b_warpx4<CG>(sfa_col + 4 * ka, make_desc_sf(sfa_s + ka * 512));
-              }
-#pragma unroll
-              for (int ra = 0; ra < BN / 128; ++ra) {
-#pragma unroll
-                for (int ka = 0; ka < C::kKAtoms; ++ka) {
-                  ptx::utccp_32x128b_warpx4<CG>(sfb_col + (BN / 32) * ka + 4 * ra,
-                                                make_desc_sf(sfb_s + (ra * C::kKAtoms + ka) * 512));
-                }
+                ptx::utccp_32x128b_warpx4<CG>(sfb_col + (BN / 32) * ka + 4 * ra,
+                                              make_desc_sf(sfb_s + (ra * C::kKAtoms + ka) * 512));
               }
             }
 #pragma unroll
             for (int kb = 0; kb < 4; ++kb) {
-              if (kb < n_mma && !BSG_FLAG(p, 8)) {
+              if (kb < n_mma) {
                 uint32_t sfa_t, sfb_t, id = idesc;
                 if constexpr (KIND == kKindNvfp4) {
                   sfa_t = sfa_col + 4 * kb;
@@ -669,7 +626,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // The data moves through the bulk-copy engine (global -> shared -> peer global) in chunks, with
     // kTpBufs chunks in flight; one elected lane issues everything.  Each finished piece bumps the
     // row-block counter in the peer's memory that the peer's TMA producer waits on.
-    if (p.tp_world > 1 && !BSG_FLAG(p, 2048)) {
+    if (p.tp_world > 1) {
       const uint32_t elected = ptx::elect_one_sync();
       uint32_t* sync = p.tp_peer_sync[p.tp_rank];
       const uint32_t buf0 = ptx::smem_u32(sTp);
@@ -685,19 +642,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
       TpChunkIter ld_it, st_it;                 // the load iterator runs ahead of the store iterator
       if (p.tp_push_in_kernel) {
-#ifdef BSG_PROFILE
-      // Ablation variants of the ring (bits 4096 / 8192): buffers x chunk bytes, read lag.
-      const uint32_t variant = (uint32_t(p.debug_flags) >> 12) & 3u;
-      const uint32_t nb = variant == 2u ? 8u : variant == 3u ? 2u : 4u;
-      const uint32_t ch = variant == 2u ? 4096u : variant == 3u ? 16384u : 8192u;
-      const uint32_t rlag = variant == 1u ? 0u : variant == 2u ? 4u : variant == 3u ? 1u : 2u;
-      long long acc_full = 0, acc_read = 0, acc_ann = 0, acc_ready = 0;
-      const long long loop_t0 = clock64();
-#define BSG_ACC(var, stmt) do { const long long a0_ = clock64(); stmt; var += clock64() - a0_; } while (0)
-#else
       constexpr uint32_t nb = C::kTpBufs, ch = C::kTpChunk, rlag = C::kTpReadLag;
-#define BSG_ACC(var, stmt) do { stmt; } while (0)
-#endif
       ld_it.init(p, int(blockIdx.x), int(gridDim.x), int(ch));
       st_it.init(p, int(blockIdx.x), int(gridDim.x), int(ch));
       uint32_t n_ld = 0, n_st = 0;
@@ -729,24 +674,22 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const uint32_t b = n_st % nb;
         if (st_it.dst_rank != checked) {
           // The peer's buffer is free once the peer has launched the call after the one that last read it.
-          BSG_ACC(acc_ready, if (!wait_flag_ge(sync + kTpSyncReady + st_it.dst_rank, p.tp_ready_target, ctl)) peer_ok = false);
+          if (!wait_flag_ge(sync + kTpSyncReady + st_it.dst_rank, p.tp_ready_target, ctl)) peer_ok = false;
           checked = st_it.dst_rank;
         }
-        BSG_ACC(acc_full, wait_barrier(bar0 + b * 8, (n_st / nb) & 1u, ctl, dead));
+        wait_barrier(bar0 + b * 8, (n_st / nb) & 1u, ctl, dead);
         if (dead) break;             // a staging load never landed: push and announce nothing more
         const bool refill = n_st >= rlag && ld_it.valid();
         if (elected) {
           while (pend_cnt > 0 && n_st >= pend_due[pend_head]) {
-            BSG_ACC(acc_ann, ptx::bulk_wait_group<C::kTpLag>());
+            ptx::bulk_wait_group<C::kTpLag>();
             announce_head();
           }
-          if (BSG_FLAG(p, 65536)) BSG_ACC(acc_ann, ptx::bulk_wait_group<1>());      // ablation: at most 2 stores in flight
-          if (BSG_FLAG(p, 131072)) BSG_ACC(acc_ann, ptx::bulk_wait_group<0>());     // ablation: at most 1 store in flight
-          if (peer_ok && !BSG_FLAG(p, 32768)) ptx::bulk_store(st_it.dst(p), buf0 + b * ch, st_it.bytes);
+          if (peer_ok) ptx::bulk_store(st_it.dst(p), buf0 + b * ch, st_it.bytes);
           ptx::bulk_commit_group();
           if (st_it.last_of_piece && peer_ok) {
             if (pend_cnt == C::kTpPend) {
-              BSG_ACC(acc_ann, ptx::bulk_wait_group<1>());   // everything but the store just issued
+              ptx::bulk_wait_group<1>();   // everything but the store just issued
               announce_head();
             }
             const int slot = (pend_head + pend_cnt) % C::kTpPend;
@@ -756,7 +699,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             ++pend_cnt;
           }
           if (refill) {
-            BSG_ACC(acc_read, tp_wait_read(rlag));      // the store issued `rlag` chunks ago has read its buffer
+            tp_wait_read(rlag);      // the store issued `rlag` chunks ago has read its buffer
             const uint32_t rb = (n_st - rlag) % nb;
             ptx::mbar_arrive_expect_tx(bar0 + rb * 8, ld_it.bytes);
             ptx::bulk_load(buf0 + rb * ch, ld_it.src(p), ld_it.bytes, bar0 + rb * 8);
@@ -770,15 +713,6 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         while (pend_cnt > 0) announce_head();
       }
       if (elected) ptx::bulk_wait_group<0>();
-#ifdef BSG_PROFILE
-      if (tp_trace && elected) {
-        const long long loop = clock64() - loop_t0;
-        printf("r%d cta%d push: %u chunks of %u B rlag %u, loop %lld kcyc ending %.1f us after entry: wait full %lld, read %lld, announce %lld, ready %lld kcyc\n",
-               p.tp_rank, int(blockIdx.x), n_st, ch, rlag, loop / 1000, (gtimer() - trace_t0) * 1e-3,
-               acc_full / 1000, acc_read / 1000, acc_ann / 1000, acc_ready / 1000);
-      }
-#endif
-#undef BSG_ACC
       }
       if (!peer_ok || dead) atomicOr(p.status, kStTimeoutPeer);
     }
@@ -821,7 +755,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const bool reverse = (BN == 256) && ((it & 1) == 0);
       const uint32_t empty_bar = tempty0 + acc_bar * 8;
       // Whole 128-row slab inside the group: bf16 output goes through shared memory and TMA stores.
-      const bool tma_out = (p.out_kind == kOutBf16) && (cta_row0 + C::kCtaM <= ti.row_end) && !BSG_FLAG(p, 128);
+      const bool tma_out = (p.out_kind == kOutBf16) && (cta_row0 + C::kCtaM <= ti.row_end);
 
 #pragma unroll 1
       for (int pi = 0; pi < C::kPairs; ++pi) {
@@ -830,16 +764,19 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         ptx::tmem_ld_32x32b_x32(lane_addr + pr * 64, v[0]);
         ptx::tmem_ld_32x32b_x32(lane_addr + pr * 64 + 32, v[1]);
         ptx::tmem_ld_wait();
+        if (warp == 0 && pi == 0) BSG_DBG(2, 22);
         if (pi == C::kReleasePair) {
           ptx::tc_fence_before();
           __syncwarp();
+          // Relaxed arrival: the reads of the accumulator columns have completed (wait::ld above), and an
+          // arrival with release semantics was measured to stall this lane until its TMA stores of the previous
+          // tile had drained (about 1 700 cycles per tile, during which the MMA warp waits for the accumulator).
           if (lane == 0) {
-            if constexpr (CG == 2) ptx::mbar_arrive_remote(ptx::mapa(empty_bar, 0));
-            else ptx::mbar_arrive(empty_bar);
+            if constexpr (CG == 2) ptx::mbar_arrive_remote_relaxed(ptx::mapa(empty_bar, 0));
+            else ptx::mbar_arrive_relaxed(empty_bar);
           }
           if (warp == 0) BSG_DBG(2, 21);
         }
-        if (BSG_FLAG(p, 4)) continue;
         if (tma_out) {
           // The previous store must have finished reading the staging tile before it is overwritten.
           if (lane == 0) ptx::bulk_wait_group_read<0>();
@@ -1000,10 +937,6 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           ptx::fence_proxy_async();
           __syncwarp();
           if (lane == 0) {
-#ifdef BSG_PROFILE
-            if (BSG_FLAG(p, 1 << 18)) ptx::tma_store_2d_hint(&tmD, stage_addr, ti.tn * BN + pr * 64, cta_row0 + warp * 32, ptx::l2_policy_evict_first());
-            else
-#endif
             ptx::tma_store_2d(&tmD, stage_addr, ti.tn * BN + pr * 64, cta_row0 + warp * 32);
             ptx::bulk_commit_group();
           }
@@ -1011,9 +944,6 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
     }
     if (lane == 0) ptx::bulk_wait_group<0>();
-#ifdef BSG_PROFILE
-    if (tp_trace && warp == 0 && lane == 0) printf("r%d cta%d epilogue done at %.1f us\n", p.tp_rank, int(blockIdx.x), (gtimer() - trace_t0) * 1e-3);
-#endif
     if (dead) atomicOr(p.status, kStTimeoutTmemFull);
   }
 
@@ -1031,6 +961,12 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     ptx::tc_fence_after();
     ptx::tmem_dealloc<CG>(tmem_base, 512);
   }
+#ifdef BSG_PROFILE
+  if (dbg_on) {
+    uint32_t* dbg_g = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(p.status) + 1024);
+    for (int i = threadIdx.x; i < 512 + 1024 + 256; i += blockDim.x) dbg_g[i] = dbg_s[i];
+  }
+#endif
 }
 
 }  // namespace bsg

@@ -10,10 +10,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# BSG_PROFILE=1 selects the instrumented build, BSG_NVFP4_SF_SETS=2 the experimental NVFP4 tensor-memory layout
-# (python -m cutlass_b200.build with the same variables set).
-LIB_PATH = os.path.join(_HERE, "lib", "libbsgemm" + ("_profile" if os.environ.get("BSG_PROFILE") == "1" else "") +
-                        ("_sf2" if os.environ.get("BSG_NVFP4_SF_SETS") == "2" else "") + ".so")
+# BSG_PROFILE=1 selects the instrumented build (python -m cutlass_b200.build with the same variable set).
+LIB_PATH = os.path.join(_HERE, "lib", "libbsgemm" + ("_profile" if os.environ.get("BSG_PROFILE") == "1" else "") + ".so")
 
 BSG_OK = 0
 STATUS_NAMES = {
