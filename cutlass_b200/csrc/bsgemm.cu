@@ -45,50 +45,110 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// K-major byte matrix (rows x row_bytes), box = 128 bytes x box_rows, 128-byte swizzle.
-int32_t make_operand_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows) {
-  EncodeTiledFn enc = get_encode_fn();
-  if (!enc) return fail(BSG_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
-  cuuint64_t dims[2] = {row_bytes, rows};
-  cuuint64_t strides[1] = {row_bytes};
-  cuuint32_t box[2] = {128, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(BSG_ERR_CUDA, "cuTensorMapEncodeTiled(operand) failed with %d", int(r));
-  return BSG_OK;
+// Tensor maps are pure descriptions (address, extents, strides, box, swizzle), so one encoded for a given
+// description stays valid for as long as that memory is used with that shape.  A small cache, guarded by a mutex,
+// keeps the most recently used ones: a steady-state run encodes nothing.  (SURVEY of the reference: it encodes its
+// descriptors in GemmUniversalAdapter::initialize and reuses them across run() calls, gemm_universal_adapter.h:313-375.)
+struct MapKey {
+  const void* base;
+  uint64_t dims[3];
+  uint64_t strides[2];
+  uint32_t box[3];
+  int32_t dtype, swizzle, l2;
+};
+
+class MapCache {
+ public:
+  int32_t get(const MapKey& k, CUtensorMap* out) {
+    {
+      std::lock_guard<std::mutex> lock(mu_);
+      for (int i = 0; i < kEntries; ++i) {
+        if (used_[i] && memcmp(&keys_[i], &k, sizeof(MapKey)) == 0) {
+          ticks_[i] = ++tick_;
+          memcpy(out, &maps_[i], sizeof(CUtensorMap));
+          return BSG_OK;
+        }
+      }
+    }
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return fail(BSG_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+    cuuint64_t dims[3] = {k.dims[0], k.dims[1], k.dims[2]};
+    cuuint64_t strides[2] = {k.strides[0], k.strides[1]};
+    cuuint32_t box[3] = {k.box[0], k.box[1], k.box[2]};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUtensorMap m;
+    CUresult r = enc(&m, static_cast<CUtensorMapDataType>(k.dtype), 3, const_cast<void*>(k.base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, static_cast<CUtensorMapSwizzle>(k.swizzle),
+                     static_cast<CUtensorMapL2promotion>(k.l2), CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+      return fail(BSG_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (dims %llu x %llu x %llu, strides %llu, %llu bytes)", int(r),
+                  (unsigned long long)k.dims[0], (unsigned long long)k.dims[1], (unsigned long long)k.dims[2],
+                  (unsigned long long)k.strides[0], (unsigned long long)k.strides[1]);
+    memcpy(out, &m, sizeof(CUtensorMap));
+    std::lock_guard<std::mutex> lock(mu_);
+    int victim = 0;
+    for (int i = 0; i < kEntries; ++i) {
+      if (!used_[i]) { victim = i; break; }
+      if (ticks_[i] < ticks_[victim]) victim = i;
+    }
+    keys_[victim] = k;
+    memcpy(&maps_[victim], &m, sizeof(CUtensorMap));
+    used_[victim] = true;
+    ticks_[victim] = ++tick_;
+    return BSG_OK;
+  }
+
+ private:
+  static constexpr int kEntries = 64;
+  std::mutex mu_;
+  MapKey keys_[kEntries];
+  CUtensorMap maps_[kEntries];
+  bool used_[kEntries] = {};
+  uint64_t ticks_[kEntries] = {};
+  uint64_t tick_ = 0;
+};
+
+MapCache g_maps;
+
+MapKey make_key(const void* base, int dtype, int swizzle, int l2, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s0, uint64_t s1,
+                uint32_t b0, uint32_t b1, uint32_t b2) {
+  MapKey k;
+  memset(&k, 0, sizeof(k));     // padding bytes take part in the comparison
+  k.base = base;
+  k.dims[0] = d0; k.dims[1] = d1; k.dims[2] = d2;
+  k.strides[0] = s0; k.strides[1] = s1;
+  k.box[0] = b0; k.box[1] = b1; k.box[2] = b2;
+  k.dtype = dtype; k.swizzle = swizzle; k.l2 = l2;
+  return k;
+}
+
+// K-major byte matrices (batches x rows x row_bytes) with a row pitch and a batch stride, box = 128 bytes x box_rows,
+// 128-byte swizzle.
+int32_t make_operand_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint64_t batches,
+                         uint64_t pitch_bytes, uint64_t batch_stride_bytes, uint32_t box_rows) {
+  return g_maps.get(make_key(base, CU_TENSOR_MAP_DATA_TYPE_UINT8, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             row_bytes, rows, batches, pitch_bytes, batch_stride_bytes, 128, box_rows, 1), map);
 }
 
 // Interleaved scale factors as (row_atoms, k_atoms, 512 bytes); box = box_row_atoms x box_k_atoms x 512 bytes.
 int32_t make_sf_map(CUtensorMap* map, const void* base, uint64_t k_atoms, uint64_t row_atoms, uint32_t box_k_atoms,
                     uint32_t box_row_atoms) {
-  EncodeTiledFn enc = get_encode_fn();
-  if (!enc) return fail(BSG_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
-  cuuint64_t dims[3] = {128, k_atoms, row_atoms};
-  cuuint64_t strides[2] = {512, 512 * k_atoms};
-  cuuint32_t box[3] = {128, box_k_atoms, box_row_atoms};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(BSG_ERR_CUDA, "cuTensorMapEncodeTiled(scale factors) failed with %d", int(r));
-  return BSG_OK;
+  return g_maps.get(make_key(base, CU_TENSOR_MAP_DATA_TYPE_UINT32, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             128, k_atoms, row_atoms, 512, 512 * k_atoms, 128, box_k_atoms, box_row_atoms), map);
 }
 
-// Output matrix for the epilogue's TMA stores: box = 64 elements x 32 rows, 128-byte swizzle.
-int32_t make_out_map(CUtensorMap* map, const void* base, bool bf16, uint64_t cols, uint64_t rows, uint64_t pitch_bytes) {
-  EncodeTiledFn enc = get_encode_fn();
-  if (!enc) return fail(BSG_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
-  cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {pitch_bytes};
-  cuuint32_t box[2] = {64, 32};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims,
-                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, bf16 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
-                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(BSG_ERR_CUDA, "cuTensorMapEncodeTiled(output) failed with %d", int(r));
-  return BSG_OK;
+// Output matrix for the epilogue's TMA stores, (batches x rows x cols); a box is 32 rows x 64 output columns:
+// bf16: 128 bytes per row, 128-byte swizzle; e4m3: 64 bytes, 64-byte swizzle; packed e2m1: 32 bytes, no swizzle.
+int32_t make_out_map(CUtensorMap* map, const void* base, int32_t out_kind, uint64_t cols, uint64_t rows, uint64_t batches,
+                     uint64_t pitch_elems, uint64_t batch_stride_elems) {
+  if (out_kind == BSG_OUT_BF16)
+    return g_maps.get(make_key(base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                               cols, rows, batches, pitch_elems * 2, batch_stride_elems * 2, 64, 32, 1), map);
+  if (out_kind == BSG_OUT_MXFP8)
+    return g_maps.get(make_key(base, CU_TENSOR_MAP_DATA_TYPE_UINT8, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                               cols, rows, batches, pitch_elems, batch_stride_elems, 64, 32, 1), map);
+  return g_maps.get(make_key(base, CU_TENSOR_MAP_DATA_TYPE_UINT8, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                             cols / 2, rows, batches, pitch_elems / 2, batch_stride_elems / 2, 32, 32, 1), map);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -105,6 +165,10 @@ struct Problem {
   const int32_t* offsets;
   bool b_per_group;
   int64_t ldc, ldd;
+  int64_t lda, ldb;                         // row pitch of A / B in elements
+  int64_t bs_a, bs_b, bs_c, bs_d;           // batch strides in elements (dense / batched form only)
+  int32_t use_pdl, scheduler;
+  int32_t cluster[4];                       // cluster_m, cluster_n, fallback m, n (0 = default)
   float alpha, beta;
   const float *alpha_ptr, *beta_ptr, *norm_ptr;
   int32_t tile_n, cta_group, sm_count, raster_band;
@@ -152,11 +216,9 @@ int32_t validate(const Problem& q, Plan* plan) {
   } else if (q.out_kind == BSG_OUT_MXFP8) {
     if (!q.SFD) return fail(BSG_ERR_INVALID_PROBLEM, "MXFP8 output needs SFD");
     if (q.N % 32 != 0 || q.ldd % 16 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "MXFP8 output needs N %% 32 == 0 and ldd %% 16 == 0");
-    if (q.offsets) return fail(BSG_ERR_NOT_SUPPORTED, "MXFP8 output is not available for grouped GEMM");
   } else {
     if (!q.SFD || !q.norm_ptr) return fail(BSG_ERR_INVALID_PROBLEM, "NVFP4 output needs SFD and norm_constant");
     if (q.N % 16 != 0 || q.ldd % 32 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "NVFP4 output needs N %% 16 == 0 and ldd %% 32 == 0");
-    if (q.offsets) return fail(BSG_ERR_NOT_SUPPORTED, "NVFP4 output is not available for grouped GEMM");
   }
   if (q.bias_mode < BSG_BIAS_NONE || q.bias_mode > BSG_BIAS_PER_ROW) return fail(BSG_ERR_NOT_SUPPORTED, "unknown bias mode %d", q.bias_mode);
   if (q.bias_mode != BSG_BIAS_NONE) {
@@ -168,12 +230,30 @@ int32_t validate(const Problem& q, Plan* plan) {
   if (q.activation < BSG_ACT_IDENTITY || q.activation > BSG_ACT_SILU) return fail(BSG_ERR_NOT_SUPPORTED, "unknown activation %d", q.activation);
   if (q.C && (q.ldc % 8 != 0)) return fail(BSG_ERR_MISALIGNED_OPERAND, "ldc must be a multiple of 8");
   if (q.ldd < q.N || (q.C && q.ldc < q.N)) return fail(BSG_ERR_INVALID_PROBLEM, "row pitch smaller than N");
+  if (q.lda < q.K || q.ldb < q.K) return fail(BSG_ERR_INVALID_PROBLEM, "lda / ldb smaller than K");
+  if (q.lda % k_align != 0 || q.ldb % k_align != 0)
+    return fail(BSG_ERR_MISALIGNED_OPERAND, "lda=%lld and ldb=%lld must be multiples of %lld (16-byte rows)", (long long)q.lda, (long long)q.ldb, (long long)k_align);
+  if (!q.offsets && q.num_groups > 1) {
+    if (q.bs_a % k_align != 0 || q.bs_b % k_align != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "batch strides of A and B must be multiples of %lld elements", (long long)k_align);
+    const int64_t d_align = q.out_kind == BSG_OUT_BF16 ? 8 : q.out_kind == BSG_OUT_MXFP8 ? 16 : 32;
+    if (q.bs_d % d_align != 0 || (q.C && q.bs_c % 8 != 0)) return fail(BSG_ERR_MISALIGNED_OPERAND, "batch strides of C and D must keep every matrix 16-byte aligned");
+    if (q.bs_a < 0 || q.bs_b < 0 || q.bs_c < 0 || q.bs_d < q.rows_per_group * q.ldd) return fail(BSG_ERR_INVALID_PROBLEM, "negative batch stride, or output matrices that overlap");
+  }
+  if (q.use_pdl != 0 && q.use_pdl != 1) return fail(BSG_ERR_INVALID_PROBLEM, "use_pdl must be 0 or 1");
+  if (q.scheduler != BSG_SCHED_STATIC && q.scheduler != BSG_SCHED_DYNAMIC) return fail(BSG_ERR_NOT_SUPPORTED, "unknown scheduler %d", q.scheduler);
   if (q.beta != 0.0f && !q.C && !q.beta_ptr) return fail(BSG_ERR_INVALID_PROBLEM, "beta != 0 needs C");
   if (q.beta_array && !q.C) return fail(BSG_ERR_INVALID_PROBLEM, "per-group beta needs C");
   int32_t cg = q.cta_group == 0 ? 2 : q.cta_group;
   int32_t tn = q.tile_n == 0 ? (q.N > 128 ? 256 : 128) : q.tile_n;
   if (cg != 1 && cg != 2) return fail(BSG_ERR_NOT_SUPPORTED, "cta_group must be 1 or 2");
   if (tn != 128 && tn != 256) return fail(BSG_ERR_NOT_SUPPORTED, "tile_n must be 128 or 256");
+  // Cluster shapes: the cluster is the CTA group of one MMA, there is nothing larger to prefer or to fall back to.
+  for (int i = 0; i < 4; i += 2) {
+    if ((q.cluster[i] != 0 || q.cluster[i + 1] != 0) && !(q.cluster[i] == cg && q.cluster[i + 1] == 1))
+      return fail(BSG_ERR_NOT_SUPPORTED, "%scluster shape %d x %d is not available: this configuration runs clusters of %d x 1",
+                  i ? "fallback " : "", q.cluster[i], q.cluster[i + 1], cg);
+  }
+  if (q.scheduler == BSG_SCHED_DYNAMIC && (q.tp || cg != 2)) return fail(BSG_ERR_NOT_SUPPORTED, "the dynamic scheduler needs cta_group 2 and is not available for the tensor-parallel GEMM");
   plan->cta_group = cg;
   plan->tile_n = tn;
   if (q.offsets) {
@@ -185,27 +265,75 @@ int32_t validate(const Problem& q, Plan* plan) {
   return BSG_OK;
 }
 
+// Per kernel instantiation and device: the dynamic shared-memory limit is raised once, and the number of clusters
+// that can be resident at the same time is asked once (the grid never exceeds it: the roles of a persistent kernel
+// wait on one another across CTAs only inside a cluster, but the tensor-parallel variant also waits for rows that
+// the push warps of OTHER CTAs of a peer deliver, so every CTA of a launch must be resident).
+struct KernelSetup {
+  std::mutex mu;
+  bool done[64] = {};
+  int max_clusters[64] = {};
+};
+
+template <int KIND, int CG, int BN, bool TP>
+int32_t kernel_setup(int dev, int* max_clusters) {
+  using Cf = bsg::Cfg<KIND, CG, BN, TP>;
+  static KernelSetup ks;
+  if (dev < 0 || dev >= 64) return fail(BSG_ERR_NOT_SUPPORTED, "device ordinal %d is outside [0, 64)", dev);
+  std::lock_guard<std::mutex> lock(ks.mu);
+  if (!ks.done[dev]) {
+    auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN, TP>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::kSmemBytes);
+    if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(unsigned(CG) * 1024u, 1, 1);
+    cfg.blockDim = dim3(TP ? 224 : 192, 1, 1);
+    cfg.dynamicSmemBytes = Cf::kSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CG; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
+    if (e != cudaSuccess || n < 1) { cudaGetLastError(); n = 0; }     // unknown: do not clamp
+    ks.max_clusters[dev] = n;
+    ks.done[dev] = true;
+  }
+  *max_clusters = ks.max_clusters[dev];
+  return BSG_OK;
+}
+
 template <int KIND, int CG, int BN, bool TP = false>
-int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_t stream, int sm_count, bool dry) {
+int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_t stream, int sm_count, int dev, bool dry) {
   using Cf = bsg::Cfg<KIND, CG, BN, TP>;
   if (dry) return BSG_OK;
-  const int64_t k_bytes = KIND == bsg::kKindNvfp4 ? q.K / 2 : q.K;
+  const bool fp4 = KIND == bsg::kKindNvfp4;
+  const int64_t k_bytes = fp4 ? q.K / 2 : q.K;
   const int64_t k_atoms = ((q.K + Cf::kSfVec - 1) / Cf::kSfVec + 3) / 4;
   const int64_t n_atoms = (q.N + 127) / 128;
   const int64_t b_groups = q.b_per_group ? q.num_groups : 1;
+  const bool batched = !q.offsets && !TP;          // dense / batched form: rows are addressed per batch entry
   int64_t sfa_row_atoms;
   if (q.offsets) sfa_row_atoms = q.total_rows / 128 + q.num_groups;   // upper bound; fetches are clamped per group
   else sfa_row_atoms = int64_t(q.num_groups) * ((q.rows_per_group + 127) / 128);
+  const int64_t lda_bytes = fp4 ? q.lda / 2 : q.lda, ldb_bytes = fp4 ? q.ldb / 2 : q.ldb;
+  const int64_t bsa_bytes = fp4 ? q.bs_a / 2 : q.bs_a, bsb_bytes = fp4 ? q.bs_b / 2 : q.bs_b;
 
   CUtensorMap tmA, tmB, tmSFA, tmSFB, tmD;
   int32_t rc;
-  if (q.out_kind == BSG_OUT_BF16) rc = make_out_map(&tmD, q.D, true, uint64_t(q.N), uint64_t(q.total_rows), uint64_t(q.ldd) * 2);
-  else if (q.out_kind == BSG_OUT_MXFP8) rc = make_out_map(&tmD, q.D, false, uint64_t(q.N), uint64_t(q.total_rows), uint64_t(q.ldd));   // not used by the kernel
-  else rc = make_out_map(&tmD, q.D, false, uint64_t(q.N / 2), uint64_t(q.total_rows), uint64_t(q.ldd) / 2);   // not used by the kernel
-  if (rc != BSG_OK) return rc;
-  // Tensor parallel: the two gathered buffers lie back to back, one map covers both.
-  if ((rc = make_operand_map(&tmA, q.A, k_bytes, TP ? 2 * q.total_rows : q.total_rows, Cf::kCtaM)) != BSG_OK) return rc;
-  if ((rc = make_operand_map(&tmB, q.B, k_bytes, b_groups * q.N, Cf::kBRowsCta)) != BSG_OK) return rc;
+  // Rows of the A and D maps: one batch entry (batched form), all groups (grouped), or the two gathered buffers of
+  // the tensor-parallel GEMM, which lie back to back.
+  const uint64_t map_rows = batched ? uint64_t(q.rows_per_group) : uint64_t(TP ? 2 * q.total_rows : q.total_rows);
+  const uint64_t map_batches = batched ? uint64_t(q.num_groups) : 1u;
+  const uint64_t d_rows = batched ? uint64_t(q.rows_per_group) : uint64_t(q.total_rows);
+  if ((rc = make_out_map(&tmD, q.D, q.out_kind, uint64_t(q.N), d_rows, map_batches, uint64_t(q.ldd),
+                         uint64_t(batched && q.num_groups > 1 ? q.bs_d : d_rows * q.ldd))) != BSG_OK) return rc;
+  if ((rc = make_operand_map(&tmA, q.A, uint64_t(k_bytes), map_rows, map_batches, uint64_t(lda_bytes),
+                             uint64_t(batched && q.num_groups > 1 ? bsa_bytes : int64_t(map_rows) * lda_bytes), Cf::kCtaM)) != BSG_OK) return rc;
+  if ((rc = make_operand_map(&tmB, q.B, uint64_t(k_bytes), uint64_t(q.N), uint64_t(b_groups), uint64_t(ldb_bytes),
+                             uint64_t(b_groups > 1 ? bsb_bytes : q.N * ldb_bytes), Cf::kBRowsCta)) != BSG_OK) return rc;
   if ((rc = make_sf_map(&tmSFA, q.SFA, k_atoms, TP ? 2 * sfa_row_atoms : sfa_row_atoms, Cf::kKAtoms, 1)) != BSG_OK) return rc;
   if ((rc = make_sf_map(&tmSFB, q.SFB, k_atoms, b_groups * n_atoms, Cf::kKAtoms, BN / 128)) != BSG_OK) return rc;
 
@@ -217,8 +345,11 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   p.N = int32_t(q.N);
   p.K = int32_t(q.K);
   p.offsets = q.offsets;
-  p.b_rows_per_group = q.b_per_group ? int32_t(q.N) : 0;
+  p.b_per_group = q.b_per_group ? 1 : 0;
   p.sfb_atoms_per_group = q.b_per_group ? int32_t(n_atoms) : 0;
+  p.batched = batched ? 1 : 0;
+  p.batch_stride_c = batched ? q.bs_c : 0;
+  p.batch_stride_d = batched ? q.bs_d : 0;
   p.tiles_n = int32_t((q.N + BN - 1) / BN);
   p.raster_band = q.raster_band > 0 ? q.raster_band : 8;
   p.out_kind = q.out_kind;
@@ -251,11 +382,12 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   { const char* dbg = getenv("BSG_DEBUG_FLAGS"); p.debug_flags = dbg ? atoi(dbg) : 0; }
 #endif
 
+  int max_clusters = 0;
+  if ((rc = kernel_setup<KIND, CG, BN, TP>(dev, &max_clusters)) != BSG_OK) return rc;
   auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN, TP>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::kSmemBytes);
-  if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
 
   int64_t clusters = sm_count / CG;
+  if (max_clusters > 0 && clusters > max_clusters) clusters = max_clusters;
   if (plan.num_tiles >= 0 && plan.num_tiles < clusters) clusters = plan.num_tiles;
   if (clusters < 1) clusters = 1;
 
@@ -266,28 +398,33 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   if (q.grid_ctas_out) *q.grid_ctas_out = int32_t(clusters * CG);
   cfg.dynamicSmemBytes = Cf::kSmemBytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CG;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmSFA, tmSFB, tmD, p);
+  if (q.use_pdl && !TP) {
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmSFA, tmSFB, tmD, p);
   if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(e));
   return BSG_OK;
 }
 
 template <int KIND>
-int32_t dispatch_shape(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_t s, int sm, bool dry) {
+int32_t dispatch_shape(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_t s, int sm, int dev, bool dry) {
   if (q.tp) {
     if (plan.cta_group != 2) return fail(BSG_ERR_NOT_SUPPORTED, "the tensor-parallel GEMM needs cta_group 2");
-    return plan.tile_n == 256 ? launch<KIND, 2, 256, true>(q, plan, status, s, sm, dry) : launch<KIND, 2, 128, true>(q, plan, status, s, sm, dry);
+    return plan.tile_n == 256 ? launch<KIND, 2, 256, true>(q, plan, status, s, sm, dev, dry) : launch<KIND, 2, 128, true>(q, plan, status, s, sm, dev, dry);
   }
   if (plan.cta_group == 2) {
-    return plan.tile_n == 256 ? launch<KIND, 2, 256>(q, plan, status, s, sm, dry) : launch<KIND, 2, 128>(q, plan, status, s, sm, dry);
+    return plan.tile_n == 256 ? launch<KIND, 2, 256>(q, plan, status, s, sm, dev, dry) : launch<KIND, 2, 128>(q, plan, status, s, sm, dev, dry);
   }
-  return plan.tile_n == 256 ? launch<KIND, 1, 256>(q, plan, status, s, sm, dry) : launch<KIND, 1, 128>(q, plan, status, s, sm, dry);
+  return plan.tile_n == 256 ? launch<KIND, 1, 256>(q, plan, status, s, sm, dev, dry) : launch<KIND, 1, 128>(q, plan, status, s, sm, dev, dry);
 }
 
 template <int KIND, int CG, int BN>
@@ -330,8 +467,8 @@ int32_t run_problem(const Problem& q, void* workspace, size_t ws_bytes, void* st
   if (q.total_rows == 0) return BSG_OK;   // nothing to compute
 
   uint32_t* status = static_cast<uint32_t*>(workspace);
-  if (q.kind == BSG_KIND_NVFP4) return dispatch_shape<0>(q, plan, status, stream, sms, false);
-  return dispatch_shape<1>(q, plan, status, stream, sms, false);
+  if (q.kind == BSG_KIND_NVFP4) return dispatch_shape<0>(q, plan, status, stream, sms, dev, false);
+  return dispatch_shape<1>(q, plan, status, stream, sms, dev, false);
 }
 
 Problem from_dense(const bsg_gemm_args* a) {
@@ -349,6 +486,14 @@ Problem from_dense(const bsg_gemm_args* a) {
   q.b_per_group = true;
   q.ldc = a->ldc ? a->ldc : a->N;
   q.ldd = a->ldd ? a->ldd : a->N;
+  q.lda = a->lda ? a->lda : a->K;
+  q.ldb = a->ldb ? a->ldb : a->K;
+  q.bs_a = a->batch_stride_A ? a->batch_stride_A : a->M * q.lda;
+  q.bs_b = a->batch_stride_B ? a->batch_stride_B : a->N * q.ldb;
+  q.bs_c = a->batch_stride_C ? a->batch_stride_C : a->M * q.ldc;
+  q.bs_d = a->batch_stride_D ? a->batch_stride_D : a->M * q.ldd;
+  q.use_pdl = a->use_pdl; q.scheduler = a->scheduler;
+  q.cluster[0] = a->cluster_m; q.cluster[1] = a->cluster_n; q.cluster[2] = a->cluster_fallback_m; q.cluster[3] = a->cluster_fallback_n;
   q.alpha = a->alpha; q.beta = a->beta;
   q.alpha_ptr = a->alpha_ptr; q.beta_ptr = a->beta_ptr; q.norm_ptr = a->norm_constant;
   q.tile_n = a->tile_n; q.cta_group = a->cta_group; q.sm_count = a->sm_count; q.raster_band = a->raster_band;
@@ -367,11 +512,15 @@ Problem from_grouped(const bsg_grouped_args* a) {
   q.total_rows = a->total_M;
   q.N = a->N;
   q.K = a->K;
-  q.A = a->A; q.B = a->B; q.SFA = a->SFA; q.SFB = a->SFB; q.C = a->C; q.D = a->D; q.SFD = nullptr;
+  q.A = a->A; q.B = a->B; q.SFA = a->SFA; q.SFB = a->SFB; q.C = a->C; q.D = a->D; q.SFD = a->SFD;
+  q.norm_ptr = a->norm_constant;
   q.offsets = a->offsets;
   q.b_per_group = true;
   q.ldc = a->ldc ? a->ldc : a->N;
   q.ldd = a->ldd ? a->ldd : a->N;
+  q.lda = a->K; q.ldb = a->K;
+  q.bs_b = a->N * a->K;
+  q.use_pdl = a->use_pdl; q.scheduler = a->scheduler;
   q.alpha = a->alpha; q.beta = a->beta;
   q.tile_n = a->tile_n; q.cta_group = a->cta_group; q.sm_count = a->sm_count; q.raster_band = a->raster_band;
   q.bias = a->bias; q.bias_mode = a->bias ? BSG_BIAS_PER_COLUMN : BSG_BIAS_NONE; q.bias_group_stride = int32_t(a->N);
@@ -511,8 +660,13 @@ int32_t bsg_read_device_status(void* workspace, void* cuda_stream) {
 int32_t bsg_gemm_run_static(const bsg_gemm_args* args, void* cuda_stream, uint32_t* device_status_out) {
   if (!args) return fail(BSG_ERR_INVALID_PROBLEM, "args is null");
   if (args->M < 0 || args->batch < 0) return fail(BSG_ERR_INVALID_PROBLEM, "negative extent");
+  // Arguments are checked first: a refused call puts nothing on the stream and leaves the shared array alone.
+  Problem q = from_dense(args);
+  Plan plan;
+  int32_t rc = validate(q, &plan);
+  if (rc != BSG_OK) return rc;
   size_t need = 0;
-  int32_t rc = bsg_gemm_workspace_size(args, &need);
+  rc = bsg_gemm_workspace_size(args, &need);
   if (rc != BSG_OK) return rc;
   if (need > kStaticScratchBytes)
     return fail(BSG_ERR_NOT_SUPPORTED, "this problem needs %zu bytes of scratch but the built-in scratch holds %zu; use bsg_gemm_run with a caller-provided workspace",
@@ -524,7 +678,6 @@ int32_t bsg_gemm_run_static(const bsg_gemm_args* args, void* cuda_stream, uint32
   // The array still holds what the previous call left there: the status word must start at zero.
   cudaError_t e = cudaMemsetAsync(scratch, 0, need, stream);
   if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "clearing the static scratch: %s", cudaGetErrorString(e));
-  Problem q = from_dense(args);
   rc = run_problem(q, scratch, kStaticScratchBytes, cuda_stream);
   if (rc != BSG_OK) return rc;
   if (device_status_out) {
@@ -533,6 +686,8 @@ int32_t bsg_gemm_run_static(const bsg_gemm_args* args, void* cuda_stream, uint32
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "reading the static scratch: %s", cudaGetErrorString(e));
     *device_status_out = st;
+    // Same translation as bsg_read_device_status: the raw word goes to the caller, the meaning into the return code.
+    if (st != 0) return fail(BSG_ERR_TIMEOUT, "a bounded device-side wait ran out (device status 0x%x)", st);
   }
   return BSG_OK;
 }

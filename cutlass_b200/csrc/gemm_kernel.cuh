@@ -59,8 +59,11 @@ struct GemmParams {
   int32_t total_rows;         // rows of A and D over all groups
   int32_t N, K;
   const int32_t* offsets;     // grouped: cumulative END row of each group (device)
-  int32_t b_rows_per_group;   // row distance between the B matrices of two groups (0: shared B)
+  int32_t b_per_group;        // 1: group g reads B[g] (third coordinate of the B map); 0: one B for all groups
   int32_t sfb_atoms_per_group;
+  int32_t batched;            // 1: A, C and D are addressed per group (row within the group; the group is the third
+                              //    tensor-map coordinate and selects the batch stride); 0: rows run over all groups
+  int64_t batch_stride_c, batch_stride_d;   // elements between the C / D matrices of two batch entries (batched only)
   int32_t tiles_n;
   int32_t raster_band;
   int32_t out_kind;
@@ -177,6 +180,8 @@ struct TileInfo {
   int32_t group_row0; // first row of the group
   int32_t sf_atom;    // SFA / SFD row-atom index of the tile's first row
   int32_t group_atom0;
+  int32_t map_row0;   // row coordinate of the tile's first row in the A / D tensor maps
+  int32_t map_l;      // third coordinate there (batch entry; 0 when rows run over all groups)
 };
 
 __device__ __forceinline__ TileInfo decode_tile(const Ctl* ctl, const GemmParams& p, int32_t t, int32_t tile_m) {
@@ -204,6 +209,8 @@ __device__ __forceinline__ TileInfo decode_tile(const Ctl* ctl, const GemmParams
   ti.row_end = ti.group_row0 + rows;
   ti.group_atom0 = ctl->atom0[lo];
   ti.sf_atom = ti.group_atom0 + tm * (tile_m / 128);
+  ti.map_row0 = p.batched ? tm * tile_m : ti.row0;
+  ti.map_l = p.batched ? lo : 0;
   return ti;
 }
 
@@ -429,6 +436,11 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     ptx::prefetch_tmap(&tmSFB);
     ptx::prefetch_tmap(&tmD);
   }
+  // Programmatic dependent launch: everything above overlaps the tail of the previous kernel on the stream; from
+  // here on global memory is touched, which needs that kernel complete.  The kernel after this one may start its
+  // own set-up as soon as SMs free up (it waits at the same place).  Both are no-ops in an ordinary launch.
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
   // Group table: end rows first (parallel), then a serial prefix by one thread.
   for (int g = threadIdx.x; g < p.num_groups; g += blockDim.x) {
     ctl->rows[g] = p.offsets ? p.offsets[g] : (g + 1) * p.rows_per_group;   // holds END rows for now
@@ -496,8 +508,10 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       // tp_remote_row_offset rows behind buffer 0 in the same tensor map; own rows always from buffer 0.
       const bool tp_remote = TP && ti.row0 / p.tp_rows_per_shard != p.tp_rank;
       const int32_t tp_row_off = tp_remote ? p.tp_remote_row_offset : 0;
-      const int32_t a_row = bcast(ti.row0 + int32_t(cta_rank) * C::kCtaM + tp_row_off);
-      const int32_t b_row = bcast(ti.g * p.b_rows_per_group + ti.tn * BN + int32_t(cta_rank) * C::kBRowsCta);
+      const int32_t a_row = bcast(ti.map_row0 + int32_t(cta_rank) * C::kCtaM + tp_row_off);
+      const int32_t a_l = bcast(ti.map_l);
+      const int32_t b_row = bcast(ti.tn * BN + int32_t(cta_rank) * C::kBRowsCta);
+      const int32_t b_l = bcast(p.b_per_group ? ti.g : 0);
       // The second CTA of a pair may lie wholly past the group's last row: keep its
       // scale-factor fetch inside the group's own atoms (its rows are never stored).
       const int32_t group_atoms = (ti.row_end - ti.group_row0 + 127) >> 7;
@@ -526,8 +540,8 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           const uint32_t full_local = full0 + stage * 8;
           if (is_leader) ptx::mbar_arrive_expect_tx(full_local, uint32_t(C::kStageBytes) * CG);
           const uint32_t bar = full0_leader + stage * 8;
-          ptx::tma_load_2d<CG>(sA0 + stage * C::kABytes, &tmA, bar, kt * C::kRowBytes, a_row);
-          ptx::tma_load_2d<CG>(sB0 + stage * C::kBBytes, &tmB, bar, kt * C::kRowBytes, b_row);
+          ptx::tma_load_3d<CG>(sA0 + stage * C::kABytes, &tmA, bar, kt * C::kRowBytes, a_row, a_l);
+          ptx::tma_load_3d<CG>(sB0 + stage * C::kBBytes, &tmB, bar, kt * C::kRowBytes, b_row, b_l);
           ptx::tma_load_3d<CG>(sSFA0 + stage * C::kSfaBytes, &tmSFA, bar, 0, kt * C::kKAtoms, sfa_atom);
           ptx::tma_load_3d<CG>(sSFB0 + stage * C::kSfbBytes, &tmSFB, bar, 0, kt * C::kKAtoms, sfb_atom);
         }
@@ -730,7 +744,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const uint32_t tfull0 = ptx::smem_u32(&ctl->tmem_full[0]);
     const uint32_t tempty0 = ptx::smem_u32(&ctl->tmem_empty[0]);
     uint8_t* stage_buf = sEpi + warp * 4096;                     // this warp's 32 x 128-byte staging tile
-    const uint32_t stage_addr = ptx::smem_u32(stage_buf);
+    uint32_t n_store = 0;                                        // TMA stores issued so far (staging rotation)
     int32_t it = 0;
     for (int32_t t = cluster_idx; t < total_tiles; t += num_clusters, ++it) {
       const TileInfo ti = decode_tile(ctl, p, t, C::kTileM);
@@ -748,14 +762,24 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       ptx::tc_fence_after();
 
       const int32_t cta_row0 = ti.row0 + int32_t(cta_rank) * C::kCtaM;
-      const int32_t grow = cta_row0 + warp * 32 + lane;
+      const int32_t grow = cta_row0 + warp * 32 + lane;          // row over all groups
       const bool row_ok = grow < ti.row_end;
-      const int32_t lrow = grow - ti.group_row0;
+      const int32_t lrow = grow - ti.group_row0;                 // row within the group
+      const int32_t warp_map_row0 = ti.map_row0 + int32_t(cta_rank) * C::kCtaM + warp * 32;
+      // Element offsets of this lane's row in C and D (the batch entry selects the batch stride).
+      const int64_t c_row_off = int64_t(ti.map_l) * p.batch_stride_c + int64_t(warp_map_row0 + lane) * p.ldc;
+      const int64_t d_row_off = int64_t(ti.map_l) * p.batch_stride_d + int64_t(warp_map_row0 + lane) * p.ldd;
       const uint32_t lane_addr = tmem_base + (uint32_t(warp * 32) << 16) + acc_col;
       const bool reverse = (BN == 256) && ((it & 1) == 0);
       const uint32_t empty_bar = tempty0 + acc_bar * 8;
-      // Whole 128-row slab inside the group: bf16 output goes through shared memory and TMA stores.
-      const bool tma_out = (p.out_kind == kOutBf16) && (cta_row0 + C::kCtaM <= ti.row_end);
+      // This warp's 32 rows lie inside the group: the output goes through shared memory and TMA stores.  (A TMA
+      // store clips at the end of the matrix, not at the end of a group: the warp that holds a group's last rows
+      // stores them row by row.)
+      const bool tma_out = cta_row0 + warp * 32 + 32 <= ti.row_end;
+      const int out_kind = p.out_kind;
+      // Staging sub-buffers a warp cycles through (4 KB per warp): bf16 uses all of it per 64 columns, e4m3 half,
+      // e2m1 a quarter; a sub-buffer is rewritten once all but the newest n_bufs - 1 stores have read theirs.
+      const int n_bufs = out_kind == kOutBf16 ? 1 : out_kind == kOutMxfp8 ? 2 : 4;
 
 #pragma unroll 1
       for (int pi = 0; pi < C::kPairs; ++pi) {
@@ -777,11 +801,18 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
           if (warp == 0) BSG_DBG(2, 21);
         }
+        uint8_t* sub_buf = stage_buf + (n_store % n_bufs) * (4096 / n_bufs);
+        if (tma_out) ++n_store;      // counts the stores actually issued: the wait below is in units of those
         if (tma_out) {
-          // The previous store must have finished reading the staging tile before it is overwritten.
-          if (lane == 0) ptx::bulk_wait_group_read<0>();
+          // The store that last used this sub-buffer must have finished reading it before it is overwritten.
+          if (lane == 0) {
+            if (n_bufs == 1) ptx::bulk_wait_group_read<0>();
+            else if (n_bufs == 2) ptx::bulk_wait_group_read<1>();
+            else ptx::bulk_wait_group_read<3>();
+          }
           __syncwarp();
         }
+        uint32_t sf_pair = 0;       // quantised outputs: the scale-factor codes of this lane's row for these 64 columns
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int32_t col0 = ti.tn * BN + pr * 64 + h * 32;
@@ -812,7 +843,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int j = 0; j < 32; ++j) x[j] = __fadd_rn(x[j], bv);
           }
           if (use_c && row_ok) {
-            const __nv_bfloat16* crow = p.C + int64_t(grow) * p.ldc + col0;
+            const __nv_bfloat16* crow = p.C + c_row_off + col0;
             if (cols_valid >= 32) {
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
@@ -839,7 +870,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int j = 0; j < 32; ++j) x[j] = apply_activation(x[j], p.activation);
           }
 
-          if (p.out_kind == kOutBf16) {
+          if (out_kind == kOutBf16) {
             if (tma_out) {
               // 128-byte-swizzled staging tile: 16-byte chunk c of row r lives at chunk (c ^ (r & 7)).
 #pragma unroll
@@ -853,7 +884,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 *reinterpret_cast<uint4*>(stage_buf + lane * 128 + chunk * 16) = o;
               }
             } else {
-              __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D) + int64_t(grow) * p.ldd + col0;
+              __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D) + d_row_off + col0;
               if (cols_valid >= 32) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
@@ -871,10 +902,9 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
               }
             }
-          } else if (p.out_kind == kOutMxfp8) {
+          } else if (out_kind == kOutMxfp8) {
             // MXFP8 re-quantisation: one ue8m0 scale factor (round-up conversion) for the 32 columns of
             // this row held here, e4m3 values; same routine of the reference host GEMM as below.
-            uint8_t* drow = reinterpret_cast<uint8_t*>(p.D) + int64_t(grow) * p.ldd + col0;
             float amax = 0.f;
 #pragma unroll
             for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(x[j]));
@@ -887,21 +917,22 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int e = 0; e < 8; ++e)
               w[e] = ptx::cvt_e4m3x4(__fmul_rn(x[e * 4 + 0], sc), __fmul_rn(x[e * 4 + 1], sc), __fmul_rn(x[e * 4 + 2], sc),
                                      __fmul_rn(x[e * 4 + 3], sc));
-            const int32_t nb = col0 >> 5;
-            uint8_t* sfp = p.SFD + (int64_t(ti.group_atom0) + lrow / 128) * (512ll * sfd_k_atoms) + (nb >> 2) * 512 +
-                           16 * (lrow & 31) + 4 * ((lrow & 127) >> 5) + (nb & 3);
-            if (cols_valid >= 32) {
+            if (cols_valid >= 32) sf_pair |= q << (8 * h);
+            if (tma_out) {
+              // 64-byte rows, 64-byte swizzle: 16-byte chunk c of row r lives at chunk c ^ ((r >> 1) & 3).
+              const int sw = (lane >> 1) & 3;
+              *reinterpret_cast<uint4*>(sub_buf + lane * 64 + (((h * 2 + 0) ^ sw) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+              *reinterpret_cast<uint4*>(sub_buf + lane * 64 + (((h * 2 + 1) ^ sw) * 16)) = make_uint4(w[4], w[5], w[6], w[7]);
+            } else if (cols_valid >= 32) {
+              uint8_t* drow = reinterpret_cast<uint8_t*>(p.D) + d_row_off + col0;
               reinterpret_cast<uint4*>(drow)[0] = make_uint4(w[0], w[1], w[2], w[3]);
               reinterpret_cast<uint4*>(drow)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-              *sfp = uint8_t(q);
             }
           } else {
             // NVFP4 re-quantisation, one scale factor per 16 columns of this row; same
             // operation order as compute_1d_scaling_factor_and_quantized_output of the
             // reference host GEMM (tools/util/include/cutlass/util/reference/host/gett.hpp:364-481).
-            uint8_t* drow = reinterpret_cast<uint8_t*>(p.D) + (int64_t(grow) * p.ldd + col0) / 2;
             uint32_t packed[4];
-            uint32_t sf_codes = 0;
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
               float amax = 0.f;
@@ -912,7 +943,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               const float qf = ptx::cvt_e4m3_to_f32(q);
               float sc = __fmul_rn(st, __fdiv_rn(1.0f, qf));
               sc = fminf(sc, FLT_MAX);
-              sf_codes |= q << (8 * b);
+              if (cols_valid >= 16 * (b + 1)) sf_pair |= q << (16 * h + 8 * b);
 #pragma unroll
               for (int e = 0; e < 2; ++e) {
                 float y[8];
@@ -921,23 +952,42 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 packed[b * 2 + e] = ptx::cvt_e2m1x8(y);
               }
             }
-            const int32_t nb = col0 >> 4;
-            uint8_t* sfp = p.SFD + (int64_t(ti.group_atom0) + lrow / 128) * (512ll * sfd_k_atoms) + (nb >> 2) * 512 +
-                           16 * (lrow & 31) + 4 * ((lrow & 127) >> 5) + (nb & 3);
-            if (cols_valid >= 32) {
-              *reinterpret_cast<uint4*>(drow) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-              *reinterpret_cast<uint16_t*>(sfp) = uint16_t(sf_codes);
-            } else if (cols_valid >= 16) {
-              *reinterpret_cast<uint2*>(drow) = make_uint2(packed[0], packed[1]);
-              *sfp = uint8_t(sf_codes);
+            if (tma_out) {
+              // 32-byte rows, no swizzle: a warp's 32 rows fill 1 KB back to back.
+              *reinterpret_cast<uint4*>(sub_buf + lane * 32 + h * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            } else {
+              uint8_t* drow = reinterpret_cast<uint8_t*>(p.D) + (d_row_off + col0) / 2;
+              if (cols_valid >= 32) *reinterpret_cast<uint4*>(drow) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              else if (cols_valid >= 16) *reinterpret_cast<uint2*>(drow) = make_uint2(packed[0], packed[1]);
             }
+          }
+        }
+        if (out_kind != kOutBf16 && row_ok && ti.tn * BN + pr * 64 < p.N) {
+          // Scale factors of this row for the 64 columns: consecutive bytes of one 512-byte atom of the interleaved
+          // layout (4 per row for 16-wide blocks, 2 for 32-wide ones).
+          const int32_t pair_col0 = ti.tn * BN + pr * 64;
+          const int32_t cols_left = p.N - pair_col0;
+          const int32_t nb = pair_col0 / sfd_vec;
+          uint8_t* sfp = p.SFD + (int64_t(ti.group_atom0) + lrow / 128) * (512ll * sfd_k_atoms) + (nb >> 2) * 512 +
+                         16 * (lrow & 31) + 4 * ((lrow & 127) >> 5) + (nb & 3);
+          if (out_kind == kOutNvfp4) {
+            if (cols_left >= 64) *reinterpret_cast<uint32_t*>(sfp) = sf_pair;
+            else {
+#pragma unroll
+              for (int b = 0; b < 4; ++b) if (cols_left >= 16 * (b + 1)) sfp[b] = uint8_t(sf_pair >> (8 * b));
+            }
+          } else {
+            if (cols_left >= 64) *reinterpret_cast<uint16_t*>(sfp) = uint16_t(sf_pair);
+            else if (cols_left >= 32) sfp[0] = uint8_t(sf_pair);
           }
         }
         if (tma_out) {
           ptx::fence_proxy_async();
           __syncwarp();
           if (lane == 0) {
-            ptx::tma_store_2d(&tmD, stage_addr, ti.tn * BN + pr * 64, cta_row0 + warp * 32);
+            // Column coordinate in bytes / elements of the D map: bf16 elements, e4m3 bytes, two e2m1 per byte.
+            const int32_t col = ti.tn * BN + pr * 64;
+            ptx::tma_store_3d(&tmD, ptx::smem_u32(sub_buf), out_kind == kOutNvfp4 ? col / 2 : col, warp_map_row0, ti.map_l);
             ptx::bulk_commit_group();
           }
         }

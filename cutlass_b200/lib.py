@@ -33,6 +33,7 @@ OUT_MXFP8 = 2
 ACT_IDENTITY, ACT_RELU, ACT_GELU, ACT_SILU = 0, 1, 2, 3
 BIAS_NONE, BIAS_PER_COLUMN, BIAS_PER_ROW = 0, 1, 2
 MAX_GROUPS = 256
+SCHED_STATIC, SCHED_DYNAMIC = 0, 1
 
 
 class GemmArgs(C.Structure):
@@ -46,6 +47,10 @@ class GemmArgs(C.Structure):
         ("alpha_ptr", C.c_void_p), ("beta_ptr", C.c_void_p), ("norm_constant", C.c_void_p),
         ("tile_n", C.c_int32), ("cta_group", C.c_int32), ("sm_count", C.c_int32), ("raster_band", C.c_int32),
         ("bias", C.c_void_p), ("bias_mode", C.c_int32), ("activation", C.c_int32),
+        ("lda", C.c_int64), ("ldb", C.c_int64),
+        ("batch_stride_A", C.c_int64), ("batch_stride_B", C.c_int64), ("batch_stride_C", C.c_int64), ("batch_stride_D", C.c_int64),
+        ("use_pdl", C.c_int32), ("scheduler", C.c_int32),
+        ("cluster_m", C.c_int32), ("cluster_n", C.c_int32), ("cluster_fallback_m", C.c_int32), ("cluster_fallback_n", C.c_int32),
     ]
 
 
@@ -60,6 +65,7 @@ class GroupedArgs(C.Structure):
         ("tile_n", C.c_int32), ("cta_group", C.c_int32), ("sm_count", C.c_int32), ("raster_band", C.c_int32),
         ("bias", C.c_void_p), ("reserved1", C.c_int32), ("activation", C.c_int32),
         ("alpha_array", C.c_void_p), ("beta_array", C.c_void_p),
+        ("SFD", C.c_void_p), ("norm_constant", C.c_void_p), ("use_pdl", C.c_int32), ("scheduler", C.c_int32),
     ]
 
 

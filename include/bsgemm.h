@@ -51,11 +51,13 @@ enum {
  * Field-for-field stand-in for cutlass::library::BlockScaledGemmArguments
  * (tools/library/include/cutlass/library/library.h:354-397).
  *
- * A is (batch, M, K) and B is (batch, N, K), both K-major and densely packed
- * (two e2m1 per byte, even K index in the low nibble).  SFA / SFB use the
- * 128-row x 4-K-block interleaved layout of
+ * A is (batch, M, K) and B is (batch, N, K), both K-major (two e2m1 per byte,
+ * even K index in the low nibble); rows may carry a pitch (lda / ldb) and batch
+ * entries a stride, so a slice of a larger buffer can be passed as it is.
+ * SFA / SFB use the 128-row x 4-K-block interleaved layout of
  * include/cutlass/detail/sm100_blockscaled_layout.hpp:49-114, one layout per
- * batch entry, padding included.  C and D are (batch, M, N) row-major.
+ * batch entry, padding included (the reference derives that layout from the
+ * shape alone: it has no strides).  C and D are (batch, M, N) row-major.
  */
 /* Element-wise activation applied to alpha * acc + bias + beta * C before the output conversion / quantisation
  * (include/cutlass/epilogue/thread/activation.h of the reference: ReLu :145, GELU<float> :585, SiLu :452). */
@@ -92,7 +94,32 @@ typedef struct bsg_gemm_args {
   const float* bias;        /* device fp32: N entries (per column) or M entries (per row), shared by all batches; or NULL */
   int32_t bias_mode;        /* BSG_BIAS_* (BSG_BIAS_NONE ignores bias) */
   int32_t activation;       /* BSG_ACT_* */
+  /* Strides in ELEMENTS, 0 = densely packed (library.h:374-383: lda, ldb, batch_stride_A..D).  lda / ldb must keep
+   * every row 16-byte aligned (multiples of 32 for e2m1, of 16 for e4m3). */
+  int64_t lda;              /* A row pitch (0 = K) */
+  int64_t ldb;              /* B row pitch (0 = K) */
+  int64_t batch_stride_A;   /* elements between A[l] and A[l+1] (0 = M * lda) */
+  int64_t batch_stride_B;   /* (0 = N * ldb) */
+  int64_t batch_stride_C;   /* (0 = M * ldc) */
+  int64_t batch_stride_D;   /* (0 = M * ldd) */
+  int32_t use_pdl;          /* 1: launch with programmatic stream serialisation (library.h:396 use_pdl): the kernel's
+                               set-up overlaps the tail of the previous kernel on the stream and it waits
+                               (griddepcontrol.wait) before its first global access */
+  int32_t scheduler;        /* BSG_SCHED_* */
+  /* cluster_shape / cluster_shape_fallback of the reference (library.h:357-358).  The kernels here use no TMA
+   * multicast, so the cluster is exactly the CTA group of one MMA and there is no larger preferred shape to fall
+   * back from: 0 (default) or {cta_group, 1} are accepted, anything else is BSG_ERR_NOT_SUPPORTED. */
+  int32_t cluster_m, cluster_n;
+  int32_t cluster_fallback_m, cluster_fallback_n;
 } bsg_gemm_args;
+
+/* Tile schedulers.  STATIC: persistent grid of one cluster per SM pair, tile index += cluster count (the
+ * reference's StaticPersistentTileScheduler, python/CuTeDSL/cutlass/utils/static_persistent_tile_scheduler.py:376).
+ * DYNAMIC: one cluster per output tile is launched and every running cluster, when it has finished a tile, cancels a
+ * not-yet-started cluster and takes over its tile (clusterlaunchcontrol.try_cancel; the reference's
+ * PersistentTileSchedulerSm100, include/cutlass/gemm/kernel/sm100_tile_scheduler.hpp:400-423), so tiles are handed
+ * out in the order clusters become free and the GPU can be shared with other kernels. */
+enum { BSG_SCHED_STATIC = 0, BSG_SCHED_DYNAMIC = 1 };
 
 /*
  * Arguments of a grouped (MoE) GEMM with ragged M: the rows of all groups are
@@ -108,7 +135,7 @@ typedef struct bsg_gemm_args {
  */
 typedef struct bsg_grouped_args {
   int32_t kind;
-  int32_t out_kind;         /* BSG_OUT_BF16 only */
+  int32_t out_kind;         /* BSG_OUT_*; quantised outputs need SFD (and norm_constant for NVFP4) below */
   int32_t num_groups;       /* 1..BSG_MAX_GROUPS */
   int32_t reserved0;
   int64_t total_M;          /* rows of A and D (sum of group sizes) */
@@ -118,7 +145,7 @@ typedef struct bsg_grouped_args {
   const void* SFA;
   const void* SFB;
   const void* C;            /* (total_M, N) bf16 or NULL */
-  void* D;                  /* (total_M, N) bf16 */
+  void* D;                  /* (total_M, N): bf16, packed e2m1 or e4m3 */
   const int32_t* offsets;   /* device int32[num_groups], cumulative END rows */
   int64_t ldc, ldd;
   float alpha, beta;
@@ -130,6 +157,14 @@ typedef struct bsg_grouped_args {
                                per-group scalars as pointer arrays (examples/75_blackwell_grouped_gemm_block_scaled/
                                75_blackwell_grouped_gemm_block_scaled.cu:693-719) */
   const float* beta_array;  /* likewise for beta */
+  /* Quantised output per group (the reference's grouped block-scaled example emits SFD per group,
+   * examples/75_blackwell_grouped_gemm/75_blackwell_grouped_gemm_block_scaled.cu:551-566): SFD holds one interleaved
+   * layout over (M_g, N/16 or N/32) per group, back to back, each padded to 128 rows -- the form SFA has, so the
+   * output feeds the next grouped GEMM (K := N) as it is.  Pad rows of a group's last atom are not written. */
+  void* SFD;
+  const float* norm_constant; /* device fp32 scalar shared by all groups */
+  int32_t use_pdl;
+  int32_t scheduler;        /* BSG_SCHED_* */
 } bsg_grouped_args;
 
 #define BSG_MAX_GROUPS 256
@@ -194,8 +229,13 @@ int32_t bsg_read_device_status(void* workspace, void* cuda_stream);
  *    kernel runs, so results do not depend on earlier calls; but two calls whose kernels can overlap
  *    on the GPU (different streams) race on it -- keep calls to this entry point on one stream, or
  *    otherwise ordered.
- *  - device_status_out may be NULL.  If it is not, the call waits for the stream and stores the
- *    kernel's status word there (0 = every device-side wait completed).
+ *  - device_status_out may be NULL.  If it is not, the call waits for the stream, stores the kernel's status
+ *    word there (0 = every device-side wait completed) and returns BSG_ERR_TIMEOUT when it is not 0, as
+ *    bsg_read_device_status does; a waiting call like that does not belong inside a stream capture.  With NULL
+ *    nobody reads the word: the next call's clearing erases it, so a time-out goes unnoticed (the sticky word of
+ *    a caller-provided workspace has no such gap).
+ *  - Arguments are checked before anything is enqueued: a refused call leaves the stream and the array untouched.
+ *  - The address that was looked up belongs to the device's current context; it does not survive cudaDeviceReset.
  *
  * This entry point has no counterpart in the reference; it exists for such callers only.
  */

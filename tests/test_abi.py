@@ -38,9 +38,11 @@ def test_version_and_error_string(lib):
 
 
 def test_struct_sizes_match_header_layout():
-    # 4 int32, 3 int64, 7 pointers, 2 int64, 2 float, 3 pointers, 4 int32
-    assert C.sizeof(L.GemmArgs) == 16 + 24 + 56 + 16 + 8 + 24 + 16 + 16       # + bias pointer, bias_mode, activation
-    assert C.sizeof(L.GroupedArgs) == 16 + 24 + 56 + 16 + 8 + 16 + 16 + 16     # + alpha_array, beta_array
+    # 4 int32, 3 int64, 7 pointers, 2 int64, 2 float, 3 pointers, 4 int32; bias pointer, bias_mode, activation;
+    # lda, ldb and four batch strides (int64); use_pdl, scheduler and four cluster extents (int32)
+    assert C.sizeof(L.GemmArgs) == 16 + 24 + 56 + 16 + 8 + 24 + 16 + 16 + 48 + 24
+    # ... alpha_array, beta_array; SFD, norm_constant, use_pdl, scheduler
+    assert C.sizeof(L.GroupedArgs) == 16 + 24 + 56 + 16 + 8 + 16 + 16 + 16 + 24
     assert C.sizeof(L.Caps) == 32
 
 
@@ -78,6 +80,12 @@ def test_query_accepts_valid_problem_and_reports_plan(lib):
     (dict(beta=0.5), 2),             # beta without C
     (dict(out_kind=1), 2),           # NVFP4 output without SFD / norm constant
     (dict(batch=1000), 2),
+    (dict(lda=128), 2),              # row pitch smaller than K
+    (dict(lda=272), 1),              # row pitch that breaks the 16-byte row alignment (e2m1: multiples of 32)
+    (dict(batch=2, batch_stride_A=256 * 256 + 8), 1),
+    (dict(scheduler=5), 3),
+    (dict(use_pdl=2), 2),
+    (dict(cluster_m=2, cluster_n=4), 3),     # the reference's multicast cluster: nothing here uses it
 ])
 def test_query_rejects_bad_problems(lib, kw, code):
     assert lib.bsg_gemm_query(C.byref(_args(**kw)), None) == code

@@ -1,0 +1,164 @@
+"""-m gpu tests of the argument surface that mirrors cutlass::library::BlockScaledGemmArguments beyond the plain
+dense call: row pitches and batch strides, programmatic dependent launch, cluster-shape fields, and quantised
+output of the grouped GEMM.  Everything goes through the C ABI and is compared bit for bit with the oracle
+(exact-arithmetic operands)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from cutlass_b200 import formats as F
+from cutlass_b200 import generators as G
+from cutlass_b200 import lib as L
+from oracle import ref_numpy as R
+
+from gpu_utils import dev, make_operands, oracle_bf16
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(a):
+    lib = L.load()
+    ws = torch.zeros(16, dtype=torch.uint8, device="cuda")
+    L.check(lib.bsg_gemm_run(C.byref(a), ws.data_ptr(), 16, None))
+    L.check(lib.bsg_read_device_status(ws.data_ptr(), None))
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("kind", [0, 1])
+def test_pitched_k_major_views_and_strided_batches(cuda_lib, kind):
+    """A and B are slices of larger buffers (row pitch > K, batch entries further apart than one matrix) and C / D
+    carry their own pitch and batch stride: the result must equal the oracle's on the packed copies."""
+    Lb, M, N, K = 3, 320, 384, 512
+    kb = K // 2 if kind == 0 else K                       # bytes of K per row
+    pa, pb = kb + 64, kb + 160                            # row pitches in bytes (16-byte multiples)
+    unit = 2 if kind == 0 else 1                          # elements per byte
+    bsa, bsb = (M + 5) * pa, (N + 3) * pb                 # batch strides in bytes
+    ldc, ldd = N + 8, N + 24
+    bsc, bsd = (M + 2) * ldc, (M + 1) * ldd
+    rng = np.random.default_rng(5)
+    bufA = rng.integers(0, 256, Lb * bsa, dtype=np.uint8)
+    bufB = rng.integers(0, 256, Lb * bsb, dtype=np.uint8)
+    bufC = G.bf16_normal((Lb * bsc,), rng)
+    want, sfas, sfbs = [], [], []
+    for l in range(Lb):
+        _, A, sfa, B, sfb = make_operands(kind, M, N, K, seed=200 + l, exact=True)
+        bufA[l * bsa: l * bsa + M * pa].reshape(M, pa)[:, :kb] = A
+        bufB[l * bsb: l * bsb + N * pb].reshape(N, pb)[:, :kb] = B
+        Cl = bufC[l * bsc: l * bsc + M * ldc].reshape(M, ldc)[:, :N]
+        sfas.append(sfa); sfbs.append(sfb)
+        want.append(oracle_bf16(kind, M, N, K, A, sfa, B, sfb, np.ascontiguousarray(Cl), 2.0, 0.5))
+    dA, dB, dC = dev(bufA), dev(bufB), dev(bufC)
+    dSFA, dSFB = dev(np.concatenate(sfas)), dev(np.concatenate(sfbs))
+    dD = torch.full((Lb * bsd,), 0x7FC0, dtype=torch.int16, device="cuda")
+    a = L.GemmArgs()
+    a.kind, a.batch, a.M, a.N, a.K = kind, Lb, M, N, K
+    a.A, a.B, a.SFA, a.SFB, a.C, a.D = (x.data_ptr() for x in (dA, dB, dSFA, dSFB, dC, dD))
+    a.alpha, a.beta = 2.0, 0.5
+    a.lda, a.ldb, a.ldc, a.ldd = pa * unit, pb * unit, ldc, ldd
+    a.batch_stride_A, a.batch_stride_B, a.batch_stride_C, a.batch_stride_D = bsa * unit, bsb * unit, bsc, bsd
+    _run(a)
+    got = dD.cpu().numpy().view(np.uint16)
+    for l in range(Lb):
+        blk = got[l * bsd: l * bsd + M * ldd].reshape(M, ldd)
+        assert np.array_equal(blk[:, :N], want[l]), f"batch entry {l}"
+        assert np.all(blk[:, N:] == 0x7FC0), "the pitch padding of D must stay untouched"
+    assert np.all(got[(Lb - 1) * bsd + M * ldd:] == 0x7FC0)
+
+
+@pytest.mark.parametrize("use_pdl", [0, 1])
+def test_back_to_back_launches_with_programmatic_dependent_launch(cuda_lib, use_pdl):
+    """A chain in which every GEMM reads what the previous one wrote as its C: with use_pdl the kernels' set-up
+    overlaps the predecessor's tail, and the results must still be those of the serial chain."""
+    M, N, K = 512, 512, 256
+    rng, A, sfa, B, sfb = make_operands(0, M, N, K, seed=77, exact=True)
+    dA, dB, dSFA, dSFB = dev(A), dev(B), dev(sfa), dev(sfb)
+    bufs = [torch.zeros((M, N), dtype=torch.int16, device="cuda") for _ in range(2)]
+    lib = L.load()
+    ws = torch.zeros(16, dtype=torch.uint8, device="cuda")
+    steps = 6
+    for i in range(steps):
+        a = L.GemmArgs()
+        a.kind, a.batch, a.M, a.N, a.K = 0, 1, M, N, K
+        a.A, a.B, a.SFA, a.SFB = dA.data_ptr(), dB.data_ptr(), dSFA.data_ptr(), dSFB.data_ptr()
+        a.C, a.D = bufs[i % 2].data_ptr(), bufs[(i + 1) % 2].data_ptr()
+        a.alpha, a.beta = 1.0, 0.5
+        a.use_pdl = use_pdl
+        L.check(lib.bsg_gemm_run(C.byref(a), ws.data_ptr(), 16, None))
+    L.check(lib.bsg_read_device_status(ws.data_ptr(), None))
+    torch.cuda.synchronize()
+    cur = np.zeros((M, N), np.uint16)
+    for i in range(steps):
+        cur = oracle_bf16(0, M, N, K, A, sfa, B, sfb, cur, 1.0, 0.5)
+    assert np.array_equal(bufs[steps % 2].cpu().numpy().view(np.uint16), cur)
+
+
+def test_cluster_shape_fields(cuda_lib):
+    """The reference's cluster_shape / cluster_shape_fallback fields: the CTA pair of one MMA is the only cluster here."""
+    M, N, K = 256, 256, 256
+    _, A, sfa, B, sfb = make_operands(0, M, N, K, seed=3, exact=True)
+    t = [dev(x) for x in (A, B, sfa, sfb)]
+    D = torch.zeros((M, N), dtype=torch.int16, device="cuda")
+    a = L.GemmArgs()
+    a.kind, a.batch, a.M, a.N, a.K = 0, 1, M, N, K
+    a.A, a.B, a.SFA, a.SFB, a.D = (x.data_ptr() for x in (*t, D))
+    a.alpha = 1.0
+    a.cluster_m, a.cluster_n, a.cluster_fallback_m, a.cluster_fallback_n = 2, 1, 2, 1
+    _run(a)
+    assert np.array_equal(D.cpu().numpy().view(np.uint16), oracle_bf16(0, M, N, K, A, sfa, B, sfb))
+    a.cluster_n = 4
+    assert L.load().bsg_gemm_query(C.byref(a), None) == 3          # BSG_ERR_NOT_SUPPORTED
+
+
+@pytest.mark.parametrize("out_kind", [1, 2])
+@pytest.mark.parametrize("sizes", [[256, 384], [100, 0, 300, 1, 515], [700]])
+def test_grouped_quantised_output_per_group(cuda_lib, out_kind, sizes):
+    """Grouped GEMM with fused NVFP4 / MXFP8 output: every group's values and scale factors (one interleaved layout
+    per group, padded to 128 rows -- what the next grouped GEMM takes as A / SFA) equal the oracle's quantisation of
+    that group's GEMM, bit for bit; rows of other groups and the bytes past a group's last row stay untouched."""
+    kind, N, K = 0, 640, 512
+    vec = 16 if out_kind == 1 else 32
+    rng = np.random.default_rng(9)
+    total = int(np.sum(sizes))
+    As, sfas, Bs, sfbs = [], [], [], []
+    for m in sizes:
+        A, _, sfa = G.exact_nvfp4_operand(int(m), K, rng) if m > 0 else (np.zeros((0, K // 2), np.uint8), None, np.zeros(0, np.uint8))
+        B, _, sfb = G.exact_nvfp4_operand(N, K, rng)
+        As.append(A); sfas.append(sfa); Bs.append(B); sfbs.append(sfb)
+    pres = [oracle.gemm_fp32(kind, As[g], sfas[g], Bs[g], sfbs[g], int(m), N, K) if m > 0 else None for g, m in enumerate(sizes)]
+    amax = max(float(np.abs(x).max()) for x in pres if x is not None)
+    st = np.float32(448.0 * 6.0 / amax) if out_kind == 1 else np.float32(0.5)
+    dA, dB = dev(np.concatenate(As, axis=0)), dev(np.stack(Bs))
+    dSFA, dSFB = dev(np.concatenate(sfas)), dev(np.concatenate(sfbs))
+    offs = torch.tensor(np.cumsum(sizes), dtype=torch.int32, device="cuda")
+    row_bytes = N // 2 if out_kind == 1 else N
+    dD = torch.full((total, row_bytes), 0x77, dtype=torch.uint8, device="cuda")
+    atoms = [-(-int(m) // 128) for m in sizes]
+    katoms = F.sf_k_atoms(N, vec)
+    dSFD = torch.full((sum(atoms) * 512 * katoms,), 0x7F, dtype=torch.uint8, device="cuda")
+    nc = torch.tensor([st], dtype=torch.float32, device="cuda")
+    a = L.GroupedArgs()
+    a.kind, a.out_kind, a.num_groups = kind, out_kind, len(sizes)
+    a.total_M, a.N, a.K = total, N, K
+    a.A, a.B, a.SFA, a.SFB, a.D = dA.data_ptr(), dB.data_ptr(), dSFA.data_ptr(), dSFB.data_ptr(), dD.data_ptr()
+    a.offsets, a.SFD, a.norm_constant = offs.data_ptr(), dSFD.data_ptr(), nc.data_ptr()
+    a.alpha = 1.0
+    lib = L.load()
+    ws = torch.zeros(16, dtype=torch.uint8, device="cuda")
+    L.check(lib.bsg_grouped_run(C.byref(a), ws.data_ptr(), 16, None))
+    L.check(lib.bsg_read_device_status(ws.data_ptr(), None))
+    torch.cuda.synchronize()
+    gotD, gotSFD = dD.cpu().numpy(), dSFD.cpu().numpy()
+    row, atom = 0, 0
+    for g, m in enumerate(sizes):
+        m = int(m)
+        if m:
+            Dw, SFDw = oracle.quant(0 if out_kind == 1 else 1, pres[g], float(st))
+            assert np.array_equal(gotD[row:row + m], Dw), f"group {g}: values"
+            sfd_g = gotSFD[atom * 512 * katoms:(atom + atoms[g]) * 512 * katoms]
+            idx = R.sf_index(m, N // vec)
+            assert np.array_equal(sfd_g[idx], SFDw[idx]), f"group {g}: scale factors"
+        row += m
+        atom += atoms[g]
