@@ -18,8 +18,8 @@ three streams); ``roofline`` compares against the tensor-core peak; ``cpu_baseli
 reference's host GEMM timed on this machine's CPU cores on a row slab of the same problem.
 
 ``--impl reference`` times that CPU implementation alone on the same configuration (at N > 1:
-on the tensor-parallel configuration) and, where the reference's own sm_100 kernels have been
-built (baseline/Makefile), reports their time on the same operands beside it.
+on the tensor-parallel configuration) and, at N = 1 where the reference's own sm_100 kernel has been
+built (baseline/Makefile), reports its time on operands of the same distribution beside it.
 """
 from __future__ import annotations
 
@@ -653,46 +653,6 @@ def run_single(args) -> dict:
 
 
 # --------------------------------------------------------------------------- reference arm
-def reference_gpu_kernel(name: str, kind: int, M: int, N: int, K: int, steps: int) -> dict | None:
-    """Time of the reference's own sm_100 kernel (baseline/_ref/libref_gpu_<name>.so, built from the reference's
-    headers by baseline/Makefile) on seeded operands of the same distribution, by the same event loop."""
-    path = os.path.join(ROOT, "baseline", "_ref", f"libref_gpu_{name}.so")
-    if not os.path.exists(path):
-        return None
-    try:
-        import torch
-        if not torch.cuda.is_available():
-            return None
-        dev = torch.device("cuda", 0)
-        rl = C.CDLL(path)
-        rl.ref_gpu_describe.restype = C.c_char_p
-        rl.ref_gpu_workspace_size.restype = C.c_int64
-        rl.ref_gpu_init.argtypes = [C.c_void_p] * 8 + [C.c_int] * 3 + [C.c_float] * 2 + [C.c_int, C.c_void_p, C.c_void_p]
-        rl.ref_gpu_launch.argtypes = [C.c_void_p]
-        gen = torch.Generator(device=dev)
-        gen.manual_seed(0)
-        make = gpu_nvfp4_operand if kind == 0 else gpu_mxfp8_operand
-        kb = K // 2 if kind == 0 else K
-        n_sets = max(2, -(-2 * L2_BYTES // ((M + N) * kb + M * N * 2)))
-        sets = [(*make(M, K, gen, dev), *make(N, K, gen, dev), torch.empty((M, N), dtype=torch.bfloat16, device=dev)) for _ in range(n_sets)]
-        rws = torch.zeros(max(int(rl.ref_gpu_workspace_size(M, N, K)), 16), dtype=torch.uint8, device=dev)
-        stream = torch.cuda.current_stream()
-
-        def launch(i):
-            A, SFA, B, SFB, D = sets[i % n_sets]
-            rc = rl.ref_gpu_init(A.data_ptr(), B.data_ptr(), SFA.data_ptr(), SFB.data_ptr(), None, D.data_ptr(), None, None, M, N, K,
-                                 1.0, 0.0, 0, rws.data_ptr(), stream.cuda_stream)
-            if rc == 0:
-                rc = rl.ref_gpu_launch(stream.cuda_stream)
-            if rc != 0:
-                raise RuntimeError(f"reference kernel status {rc}")
-        ms = time_steps(launch, steps, 3, stream)
-        return {"ms_per_step": round(ms, 5), "value": round(2.0 * M * N * K / ms / 1e9, 1), "unit": "TFLOP/s", "steps": steps,
-                "kernel": rl.ref_gpu_describe().decode(), "what": "the reference's CollectiveBuilder kernel for its example tile / cluster shape"}
-    except Exception as exc:  # noqa: BLE001
-        return {"error": repr(exc)}
-
-
 def run_reference(args) -> dict:
     """The reference's host GEMM on this machine's CPU cores, same configuration, a bounded row slab per step."""
     import oracle
@@ -749,13 +709,14 @@ def run_reference(args) -> dict:
         "e2e": {"value": round(tflops, 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    if not args.no_reference_gpu:
-        if tp:
-            g = reference_gpu_kernel("mxfp8", 1, M, N // world, K, 10)
-            if g is not None:
-                g["what"] += f"; one rank's shape at tp{world} (M={M}, N={N // world}), A resident: no all-gather in it"
-        else:
-            g = reference_gpu_kernel("nvfp4", 0, M, N, K, 20)
+    if not args.no_reference_gpu and not tp:
+        # The reference's own GPU kernel on the same shape, where it has been built (baseline/; single-GPU runs only:
+        # that directory does not travel with multi-GPU runs).
+        try:
+            from baseline import ref_gpu_bench
+            g = ref_gpu_bench.time_kernel("nvfp4", 0, M, N, K, 20)
+        except ImportError:
+            g = None
         if g is not None:
             out["reference_gpu_kernel"] = g
     return out

@@ -135,20 +135,19 @@ class ScaledOperand:
 
     @staticmethod
     def numel_scale(quantized_shape: tuple[int, ...], mode, swizzle: ScaleSwizzleMode) -> int:
-        """Elements the scale tensor must hold for a logical operand shape (L, outer, K) or (outer, K)."""
-        if len(quantized_shape) == 3:
-            L, outer, K = quantized_shape
-        elif len(quantized_shape) == 2:
-            L = 1
-            outer, K = quantized_shape
-        else:
-            raise ValueError(f"quantized_shape must be rank 2 or 3, got rank {len(quantized_shape)}: {quantized_shape}")
-        k_blocks = ceil_div(K, ScaleMode.numel(mode))
-        if swizzle == ScaleSwizzleMode.SwizzleNone:
-            return L * outer * k_blocks
-        if swizzle == ScaleSwizzleMode.Swizzle32x4x4:
-            return L * round_up(outer, 128) * round_up(k_blocks, 4)
-        raise ValueError(f"Unrecognised ScaleSwizzleMode: {swizzle}")
+        """Number of scale factors that belong to an operand of logical shape (L, rows, K) or (rows, K): one per
+        ``mode`` block along K, and for the Swizzle32x4x4 layout whole 128-row x 4-block atoms (padding included).
+        Same contract as the reference's ``ScaledOperand.numel_scale`` (operand.py:212-231)."""
+        dims = tuple(int(d) for d in quantized_shape)
+        if len(dims) not in (2, 3):
+            raise ValueError(f"the operand shape must be (rows, K) or (L, rows, K); got {dims}")
+        batch = dims[0] if len(dims) == 3 else 1
+        rows, k_blocks = dims[-2], ceil_div(dims[-1], ScaleMode.numel(mode))
+        layouts = {ScaleSwizzleMode.SwizzleNone: (1, 1), ScaleSwizzleMode.Swizzle32x4x4: (128, 4)}
+        if swizzle not in layouts:
+            raise ValueError(f"{swizzle!r} is not a scale layout of this library")
+        row_unit, block_unit = layouts[swizzle]
+        return batch * round_up(rows, row_unit) * round_up(k_blocks, block_unit)
 
 
 @dataclass
@@ -234,23 +233,23 @@ class GemmArguments:
         return GemmProblemSize(M=M, N=N, K=K, L=L)
 
     def _validate(self) -> None:
-        for name, t in (("A", self.A), ("B", self.B), ("out", self.out)):
-            if len(t.shape) < 2 or len(t.shape) > 3:
-                raise ValueError(f"{name} must be a tensor of rank 2 or 3, got {t.shape}")
-        a_k = _logical_k(self.A, -1)
-        b_k = _logical_k(self.B, -2)
-        if a_k != b_k:
-            raise ValueError(f"A's K dimension ({a_k}) must be equal to B's K dimension ({b_k}). "
-                             f"A shape (L, M, K): {self.A.shape}, B shape (L, K, N): {self.B.shape}")
-        out_n = self.out.shape[-1] * (2 if self.out_is_packed_fp4 else 1)
-        if self.out.shape[-2] != self.A.shape[-2]:
-            raise ValueError(f"out's M dimension ({self.out.shape[-2]}) must be equal to A's M dimension ({self.A.shape[-2]})")
-        if out_n != self.B.shape[-1]:
-            raise ValueError(f"out's N dimension ({out_n}) must be equal to B's N dimension ({self.B.shape[-1]})")
-        if self.A.shape[:-2] != self.B.shape[:-2]:
-            raise ValueError(f"A & B must have the same rank and batch dimension (if any). A: {self.A.shape}, B: {self.B.shape}")
-        if self.out.shape[:-2] != self.A.shape[:-2]:
-            raise ValueError(f"out & A must have the same rank and batch dimension (if any). out: {self.out.shape}, A: {self.A.shape}")
+        """Shape agreement of A (.., M, K), B (.., K, N) and out (.., M, N); raises ValueError naming the mismatch.
+        Same checks as the reference's ``GemmArguments`` (gemm.py:163-199)."""
+        shapes = {"A": self.A.shape, "B": self.B.shape, "out": self.out.shape}
+        for name, shp in shapes.items():
+            if len(shp) not in (2, 3):
+                raise ValueError(f"{name} has rank {len(shp)} ({shp}); operands are matrices (rank 2) or batches of matrices (rank 3)")
+        batch = {name: tuple(shp[:-2]) for name, shp in shapes.items()}
+        if batch["B"] != batch["A"] or batch["out"] != batch["A"]:
+            raise ValueError(f"A, B and out must agree in rank and batch count: A {shapes['A']}, B {shapes['B']}, out {shapes['out']}")
+        M, k_of_a = self.A.shape[-2], _logical_k(self.A, -1)
+        k_of_b, N = _logical_k(self.B, -2), self.B.shape[-1]
+        if k_of_a != k_of_b:
+            raise ValueError(f"contraction extents differ: A (.., M, K) has K = {k_of_a}, B (.., K, N) has K = {k_of_b} "
+                             f"(shapes {shapes['A']} and {shapes['B']}; packed fp4 counts two elements per byte)")
+        out_m, out_n = self.out.shape[-2], self.out.shape[-1] * (2 if self.out_is_packed_fp4 else 1)
+        if (out_m, out_n) != (M, N):
+            raise ValueError(f"out is {out_m} x {out_n} but A @ B is {M} x {N}")
 
 
 class GroupedGemmArguments:

@@ -179,7 +179,7 @@ struct Problem {
   int32_t tile_m_rotate;
   // tensor parallel (TP kernel variant)
   bool tp;
-  int32_t tp_world, tp_rank, tp_rows_per_shard, tp_ksplit, tp_push_in_kernel;
+  int32_t tp_world, tp_rank, tp_rows_per_shard, tp_ksplit, tp_push_in_kernel, tp_release_announce;
   uint32_t tp_epoch;
   const float* bias;
   const float* alpha_array;
@@ -275,14 +275,14 @@ struct KernelSetup {
   int max_clusters[64] = {};
 };
 
-template <int KIND, int CG, int BN, bool TP>
+template <int KIND, int CG, int BN, bool TP, bool DYN>
 int32_t kernel_setup(int dev, int* max_clusters) {
   using Cf = bsg::Cfg<KIND, CG, BN, TP>;
   static KernelSetup ks;
   if (dev < 0 || dev >= 64) return fail(BSG_ERR_NOT_SUPPORTED, "device ordinal %d is outside [0, 64)", dev);
   std::lock_guard<std::mutex> lock(ks.mu);
   if (!ks.done[dev]) {
-    auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN, TP>;
+    auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN, TP, DYN>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::kSmemBytes);
     if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg;
@@ -305,7 +305,7 @@ int32_t kernel_setup(int dev, int* max_clusters) {
   return BSG_OK;
 }
 
-template <int KIND, int CG, int BN, bool TP = false>
+template <int KIND, int CG, int BN, bool TP = false, bool DYN = false>
 int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_t stream, int sm_count, int dev, bool dry) {
   using Cf = bsg::Cfg<KIND, CG, BN, TP>;
   if (dry) return BSG_OK;
@@ -351,7 +351,7 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   p.batch_stride_c = batched ? q.bs_c : 0;
   p.batch_stride_d = batched ? q.bs_d : 0;
   p.tiles_n = int32_t((q.N + BN - 1) / BN);
-  p.raster_band = q.raster_band > 0 ? q.raster_band : 8;
+  p.raster_band = q.raster_band > 0 ? q.raster_band : 16;
   p.out_kind = q.out_kind;
   p.alpha_array = q.alpha_array; p.beta_array = q.beta_array;
   p.bias = q.bias; p.bias_mode = q.bias_mode; p.bias_group_stride = q.bias_group_stride; p.activation = q.activation;
@@ -370,9 +370,11 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   p.rows_per_flag = q.rows_per_flag;
   p.flag_target = q.flag_target;
   p.tile_m_rotate = q.tile_m_rotate;
+  p.split_tail = 1;
   if (TP) {
     p.tp_world = q.tp_world; p.tp_rank = q.tp_rank; p.tp_rows_per_shard = q.tp_rows_per_shard; p.tp_ksplit = q.tp_ksplit; p.tp_push_in_kernel = q.tp_push_in_kernel;
     p.tp_epoch = q.tp_epoch;
+    p.tp_release_announce = q.tp_release_announce;
     p.tp_ready_target = q.tp_ready_target;
     p.tp_remote_row_offset = q.tp_parity ? int32_t(q.total_rows) : 0;
     p.tp_row_bytes = q.tp_row_bytes; p.tp_sfa_rowatom_bytes = q.tp_sfa_rowatom_bytes;
@@ -383,12 +385,20 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
 #endif
 
   int max_clusters = 0;
-  if ((rc = kernel_setup<KIND, CG, BN, TP>(dev, &max_clusters)) != BSG_OK) return rc;
-  auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN, TP>;
+  if ((rc = kernel_setup<KIND, CG, BN, TP, DYN>(dev, &max_clusters)) != BSG_OK) return rc;
+  auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN, TP, DYN>;
 
   int64_t clusters = sm_count / CG;
   if (max_clusters > 0 && clusters > max_clusters) clusters = max_clusters;
   if (plan.num_tiles >= 0 && plan.num_tiles < clusters) clusters = plan.num_tiles;
+  if (DYN) {
+    // One cluster per output tile: the hardware starts as many as fit, and every running cluster takes over the
+    // tiles of clusters that have not started (the launch itself is the work queue).  Grouped problems only know an
+    // upper bound of their tile count here; the kernel skips the surplus ids.
+    const int64_t tile_m = 128 * CG;
+    clusters = plan.num_tiles >= 0 ? plan.num_tiles : (q.total_rows / tile_m + q.num_groups) * ((q.N + BN - 1) / BN);
+    if (clusters > 0x3FFFFFFF / CG) return fail(BSG_ERR_INVALID_PROBLEM, "too many tiles for one launch");
+  }
   if (clusters < 1) clusters = 1;
 
   cudaLaunchConfig_t cfg;
@@ -420,6 +430,10 @@ int32_t dispatch_shape(const Problem& q, const Plan& plan, uint32_t* status, cud
   if (q.tp) {
     if (plan.cta_group != 2) return fail(BSG_ERR_NOT_SUPPORTED, "the tensor-parallel GEMM needs cta_group 2");
     return plan.tile_n == 256 ? launch<KIND, 2, 256, true>(q, plan, status, s, sm, dev, dry) : launch<KIND, 2, 128, true>(q, plan, status, s, sm, dev, dry);
+  }
+  if (plan.cta_group == 2 && q.scheduler == BSG_SCHED_DYNAMIC) {
+    return plan.tile_n == 256 ? launch<KIND, 2, 256, false, true>(q, plan, status, s, sm, dev, dry)
+                              : launch<KIND, 2, 128, false, true>(q, plan, status, s, sm, dev, dry);
   }
   if (plan.cta_group == 2) {
     return plan.tile_n == 256 ? launch<KIND, 2, 256>(q, plan, status, s, sm, dev, dry) : launch<KIND, 2, 128>(q, plan, status, s, sm, dev, dry);
@@ -846,6 +860,7 @@ int32_t bsg_tp_gemm_run(bsg_tp_comm* c, const bsg_gemm_args* args, void* workspa
   q.flag_target = q.tp_epoch * uint32_t(ks);
   const bool copy_engine = c->world > 1 && (c->mode & BSG_TP_PUSH_COPY_ENGINE) != 0;
   q.tp_push_in_kernel = copy_engine ? 0 : 1;
+  q.tp_release_announce = (c->mode & BSG_TP_RELEASE_ANNOUNCE) ? 1 : 0;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (copy_engine) {
     if (!workspace || workspace_bytes < 16) return fail(BSG_ERR_WORKSPACE_NULL, "workspace is null or smaller than 16 bytes");
@@ -897,7 +912,7 @@ int32_t bsg_tp_gemm_run(bsg_tp_comm* c, const bsg_gemm_args* args, void* workspa
 
 int32_t bsg_tp_set_mode(bsg_tp_comm* c, int32_t mode) {
   if (!c) return fail(BSG_ERR_INVALID_PROBLEM, "null communicator");
-  if (mode < 0 || mode > (BSG_TP_PUSH_COPY_ENGINE | BSG_TP_SINGLE_BUFFER)) return fail(BSG_ERR_NOT_SUPPORTED, "unknown tensor-parallel mode %d", mode);
+  if (mode < 0 || mode > (BSG_TP_PUSH_COPY_ENGINE | BSG_TP_SINGLE_BUFFER | BSG_TP_RELEASE_ANNOUNCE)) return fail(BSG_ERR_NOT_SUPPORTED, "unknown tensor-parallel mode %d", mode);
   c->mode = mode;
   return BSG_OK;
 }

@@ -88,6 +88,9 @@ struct GemmParams {
   int32_t rows_per_flag;
   uint32_t flag_target;
   int32_t tile_m_rotate;      // dense only: start the M sweep at this tile row
+  int32_t split_tail;         // 1: the tiles of the last wave of the persistent walk, when they fill at most half of the
+                              // clusters, are computed as two halves of BN / 2 columns each, by twice as many clusters
+                              // (BN == 256 only)
   int32_t debug_flags;        // only read when built with -DBSG_PROFILE (ablation switches, timeline capture)
   // Tensor-parallel all-gather of A (kernel template TP == true): the push warp of every CTA sends pieces of
   // this rank's row shard of A and SFA into every peer's gathered buffer.
@@ -95,6 +98,7 @@ struct GemmParams {
   int32_t tp_rows_per_shard;  // multiple of 256
   int32_t tp_ksplit;          // pieces a 256-row block is cut into (one flag increment each)
   int32_t tp_push_in_kernel;  // 1: the push warp moves the data; 0: the host's copy-engine transfers do
+  int32_t tp_release_announce; // 1: a batch of announcements is preceded by a proxy fence and a system-scope release fence
   uint32_t tp_epoch;          // call counter, starts at 1; the peers use the same value
   uint32_t tp_ready_target;       // a peer's buffer may be filled once its "launched call" word has reached this
   int32_t tp_remote_row_offset;   // rows between the buffer this call gathers into and buffer 0 (0 or M)
@@ -156,12 +160,22 @@ struct Cfg {
   static constexpr int kReleasePair = BN == 256 ? 0 : kPairs - 1;   // pair after whose load the accumulator is released
 };
 
-struct alignas(8) Ctl {
+constexpr int kSchedSlots = 4;
+
+struct alignas(16) Ctl {
   uint64_t full[8];
   uint64_t empty[8];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t tp_full[8];      // tensor parallel: staging buffer filled
+  // Dynamic scheduler: ring of kSchedSlots work ids.  sched_full[s] (every CTA): slot s holds the next work id;
+  // sched_empty[s] (leader CTA): every consumer warp of the cluster has read it; clc_bar[s] (leader): the
+  // answer of the cancellation request for slot s has landed in clc_response[s].
+  uint64_t sched_full[4];
+  uint64_t sched_empty[4];
+  uint64_t clc_bar[4];
+  alignas(16) uint32_t clc_response[4][4];
+  int32_t sched_w[4];
   uint32_t tmem_base;
   volatile uint32_t abort;
   int32_t total_tiles;
@@ -246,12 +260,27 @@ __device__ __forceinline__ uint64_t make_desc_sf(uint32_t smem_addr) {
   return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (8ull << 32) | (1ull << 46);
 }
 
-template <int KIND, int CG, int BN>
-__device__ __forceinline__ constexpr uint32_t make_idesc() {
+template <int KIND, int CG>
+__device__ __forceinline__ constexpr uint32_t make_idesc(uint32_t n) {
   constexpr uint32_t fmt = KIND == kKindNvfp4 ? 1u : 0u;       // E2M1 (mxf4) / E4M3 (mxf8f6f4)
   constexpr uint32_t sf_fmt = KIND == kKindNvfp4 ? 0u : 1u;    // UE4M3 / UE8M0
   constexpr uint32_t m = 128u * CG;
-  return (fmt << 7) | (fmt << 10) | ((uint32_t(BN) >> 3) << 17) | (sf_fmt << 23) | ((m >> 4) << 24);
+  return (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | (sf_fmt << 23) | ((m >> 4) << 24);
+}
+
+// Work item w of the persistent walk -> (tile, half): items below split_from are whole tiles; above it every tile
+// appears twice, once per half of its columns.
+struct WorkItem {
+  int32_t t;       // tile index
+  int32_t half;    // 0 or 1: which BN / 2 columns (split items only)
+  bool split;
+};
+__device__ __forceinline__ WorkItem decode_work(int32_t w, int32_t split_from) {
+  WorkItem wi;
+  wi.split = w >= split_from;
+  wi.t = wi.split ? split_from + ((w - split_from) >> 1) : w;
+  wi.half = wi.split ? ((w - split_from) & 1) : 0;
+  return wi;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -391,7 +420,24 @@ __device__ __forceinline__ float apply_activation(float x, int act) {
   }
 }
 
-template <int KIND, int CG, int BN, bool TP = false>
+// Consumer side of the dynamic scheduler's ring: step k of the walk -> the work id published for it (-1: no more
+// work).  Called by a whole warp; lane 0 reports the slot as read to the leader CTA.
+template <int CG>
+__device__ __forceinline__ int32_t sched_consume(Ctl* ctl, uint32_t k, uint32_t& dead) {
+  const uint32_t slot = k % kSchedSlots, phase = (k / kSchedSlots) & 1u;
+  wait_barrier(ptx::smem_u32(&ctl->sched_full[slot]), phase, ctl, dead);
+  asm volatile("fence.acq_rel.cluster;" ::: "memory");      // the id may have been written by the other CTA of the pair
+  const int32_t w = *reinterpret_cast<volatile int32_t*>(&ctl->sched_w[slot]);
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) {
+    const uint32_t bar = ptx::smem_u32(&ctl->sched_empty[slot]);
+    if constexpr (CG == 2) ptx::mbar_arrive_remote(ptx::mapa(bar, 0));
+    else ptx::mbar_arrive(bar);
+  }
+  return dead ? -1 : w;
+}
+
+template <int KIND, int CG, int BN, bool TP = false, bool DYN = false>
 __global__ void __launch_bounds__(TP ? 224 : 192, 1)
 bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
@@ -425,6 +471,11 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       ptx::mbar_init(ptx::smem_u32(&ctl->tmem_empty[s]), 4 * CG);
     }
     for (int s = 0; s < 8; ++s) ptx::mbar_init(ptx::smem_u32(&ctl->tp_full[s]), 1);
+    for (int s = 0; s < kSchedSlots; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&ctl->sched_full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctl->sched_empty[s]), 5 * CG);   // leader: MMA + 4 epilogue warps; other CTA: producer + 4
+      ptx::mbar_init(ptx::smem_u32(&ctl->clc_bar[s]), 1);
+    }
     ctl->abort = 0;
     ptx::fence_mbar_init();
     ptx::fence_proxy_async();
@@ -475,6 +526,20 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   const uint32_t tmem_base = bcast(ctl->tmem_base);
   const int32_t total_tiles = bcast(ctl->total_tiles);
+  // Tail of the walk: with T tiles on G clusters the last wave holds T mod G tiles; if that is at most G / 2 its tiles
+  // are split (see split_tail), which shortens the last wave to half a tile time.
+  int32_t split_from = total_tiles;
+  if (BN == 256 && !DYN && p.split_tail != 0 && total_tiles > num_clusters) {
+    const int32_t tail = total_tiles % num_clusters;
+    if (tail > 0 && 2 * tail <= num_clusters) split_from = total_tiles - tail;
+  }
+  const int32_t total_work = split_from + 2 * (total_tiles - split_from);
+  // Walk of the work items.  Static: cluster c takes items c, c + G, c + 2G, ...  Dynamic: one cluster per work item
+  // was launched; a running cluster starts with its own id and, after each item, takes over the id of a cluster that
+  // has not started yet by cancelling it (work ids beyond total_work are skipped: the launch only knows an upper bound
+  // when the group sizes live on the device).  -1 ends the walk.
+  const int32_t first_work = (DYN || cluster_idx < total_work) ? cluster_idx : -1;
+  auto static_next = [&](int32_t w) { w += num_clusters; return w < total_work ? w : -1; };
   const int32_t k_tiles = (p.K + C::kTileK - 1) / C::kTileK;
   uint32_t dead = 0;
 #ifdef BSG_PROFILE
@@ -502,21 +567,38 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const uint32_t full0_leader = CG == 2 ? ptx::mapa(full0, 0) : full0;
     int stage = 0;
     uint32_t phase = 0;
-    for (int32_t t = cluster_idx; t < total_tiles; t += num_clusters) {
-      const TileInfo ti = decode_tile(ctl, p, t, C::kTileM);
+    uint32_t step = 0;
+    for (int32_t w = first_work; w >= 0; ++step) {
+      if constexpr (DYN) {
+        if (is_leader) {
+          // Ask for the work item after this one now; the answer is read once this item's loads are issued.
+          const uint32_t slot = step % kSchedSlots, sphase = (step / kSchedSlots) & 1u;
+          wait_barrier(ptx::smem_u32(&ctl->sched_empty[slot]), sphase ^ 1u, ctl, dead);
+          if (elected && !dead) {
+            const uint32_t bar = ptx::smem_u32(&ctl->clc_bar[slot]);
+            ptx::mbar_arrive_expect_tx(bar, 16);
+            ptx::clc_try_cancel(ptx::smem_u32(&ctl->clc_response[slot][0]), bar);
+          }
+        }
+      }
+      if (w < total_work) {
+      const WorkItem wi = decode_work(w, split_from);
+      const TileInfo ti = decode_tile(ctl, p, wi.t, C::kTileM);
       // Tensor parallel: rows of other ranks are read from the gathered buffer of this call, which lies
       // tp_remote_row_offset rows behind buffer 0 in the same tensor map; own rows always from buffer 0.
       const bool tp_remote = TP && ti.row0 / p.tp_rows_per_shard != p.tp_rank;
       const int32_t tp_row_off = tp_remote ? p.tp_remote_row_offset : 0;
       const int32_t a_row = bcast(ti.map_row0 + int32_t(cta_rank) * C::kCtaM + tp_row_off);
       const int32_t a_l = bcast(ti.map_l);
-      const int32_t b_row = bcast(ti.tn * BN + int32_t(cta_rank) * C::kBRowsCta);
+      // A half tile needs BN / 4 rows of B per CTA; the box still brings kBRowsCta rows, of which the MMA reads the first.
+      const int32_t b_row = bcast(ti.tn * BN + (wi.split ? wi.half * (BN / 2) + int32_t(cta_rank) * (C::kBRowsCta / 2)
+                                                         : int32_t(cta_rank) * C::kBRowsCta));
       const int32_t b_l = bcast(p.b_per_group ? ti.g : 0);
       // The second CTA of a pair may lie wholly past the group's last row: keep its
       // scale-factor fetch inside the group's own atoms (its rows are never stored).
       const int32_t group_atoms = (ti.row_end - ti.group_row0 + 127) >> 7;
       const int32_t sfa_atom = bcast(min(ti.sf_atom + int32_t(cta_rank), ti.group_atom0 + max(group_atoms, 1) - 1) + (tp_row_off >> 7));
-      const int32_t sfb_atom = bcast(ti.g * p.sfb_atoms_per_group + ti.tn * (BN / 128));
+      const int32_t sfb_atom = bcast(ti.g * p.sfb_atoms_per_group + ti.tn * (BN / 128) + wi.half);
       if (p.ready_flags != nullptr && (!TP || tp_remote)) {
         const uint32_t* flag = p.ready_flags + ti.row0 / p.rows_per_flag;
         const long long t0 = clock64();
@@ -547,6 +629,36 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
       }
+      }
+      if constexpr (DYN) {
+        if (is_leader) {
+          // Publish the next work id to every consumer warp of the cluster.
+          const uint32_t slot = step % kSchedSlots, sphase = (step / kSchedSlots) & 1u;
+          wait_barrier(ptx::smem_u32(&ctl->clc_bar[slot]), sphase, ctl, dead);
+          int32_t next = -1;
+          if (!dead) {
+            const uint32_t first_cta = ptx::clc_query_first_ctaid_x(ptx::smem_u32(&ctl->clc_response[slot][0]));
+            next = first_cta == 0xFFFFFFFFu ? -1 : int32_t(first_cta / CG);
+          }
+          ptx::fence_proxy_async();      // the slot's next request overwrites the answer just read
+          __syncwarp();
+          if (lane == 0) {
+            const uint32_t wslot = ptx::smem_u32(&ctl->sched_w[slot]);
+            const uint32_t fbar = ptx::smem_u32(&ctl->sched_full[slot]);
+            ctl->sched_w[slot] = next;
+            ptx::mbar_arrive(fbar);
+            if constexpr (CG == 2) {
+              ptx::st_shared_cluster_u32(ptx::mapa(wslot, 1), uint32_t(next));
+              ptx::mbar_arrive_remote(ptx::mapa(fbar, 1));
+            }
+          }
+          w = next;
+        } else {
+          w = sched_consume<CG>(ctl, step, dead);
+        }
+      } else {
+        w = static_next(w);
+      }
     }
     // Tail: every stage must have been released, so that no commit-arrive is still
     // in flight towards this CTA's shared memory when it exits.
@@ -558,7 +670,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   } else if (warp == 4) {
     // ---------------------------------------------------------------- UMMA issue
     if (is_leader) {
-      constexpr uint32_t idesc = make_idesc<KIND, CG, BN>();
+      constexpr uint32_t idesc_full = make_idesc<KIND, CG>(BN), idesc_half = make_idesc<KIND, CG>(BN / 2);
       const uint32_t elected = ptx::elect_one_sync();
       const uint32_t sA0 = ptx::smem_u32(sA), sB0 = ptx::smem_u32(sB);
       const uint32_t sSFA0 = ptx::smem_u32(sSFA), sSFB0 = ptx::smem_u32(sSFB);
@@ -570,7 +682,10 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       // `ready` holds the result of a non-blocking look at the NEXT stage's barrier, taken before the
       // current stage's instructions are issued, so that the barrier round trip overlaps the issue.
       uint32_t ready = 0;
-      for (int32_t t = cluster_idx; t < total_tiles; t += num_clusters, ++it) {
+      uint32_t step = 0;
+      for (int32_t w = first_work; w >= 0; w = DYN ? sched_consume<CG>(ctl, step++, dead) : static_next(w)) {
+        if (w >= total_work) continue;
+        const uint32_t idesc = w >= split_from ? idesc_half : idesc_full;    // a half tile: the same operands, N = BN / 2
         const int acc_bar = it % C::kAccBars;
         const uint32_t acc_phase = uint32_t(it / C::kAccBars) & 1u;
         const uint32_t d_tmem = tmem_base + uint32_t(it & 1) * C::kAccStride;
@@ -631,6 +746,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           phase = next_phase;
         }
         if (elected && !dead) ptx::umma_commit<CG>(tfull0 + acc_bar * 8);
+        ++it;
       }
       if (dead) atomicOr(p.status, kStTimeoutFull | kStTimeoutTmemEmpty);
     }
@@ -676,8 +792,17 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       int pend_head = 0, pend_cnt = 0;
       // The announcement is a relaxed system-scope add issued after wait_group has reported the piece's
       // stores complete, i.e. acknowledged by the peer's memory: the counter update leaves this GPU only
-      // after the data is in place, and the consumer reads both from its own memory.  (A release here
-      // would also wait for the newer stores still in flight, several microseconds per piece.)
+      // after the data is in place, and the consumer reads both from its own memory.  That order rests on
+      // how bulk stores complete over NVLink, not on the PTX memory model, which orders an async-proxy
+      // write before a later generic-proxy write of the same thread only through a proxy fence and a
+      // release.  tp_release_announce selects that form: one fence pair per batch of due announcements
+      // (it also waits for the newer stores in flight, which is why it is not the default).
+      auto release_fences = [&]() {
+        if (p.tp_release_announce) {
+          asm volatile("fence.proxy.async;" ::: "memory");
+          asm volatile("fence.acq_rel.sys;" ::: "memory");
+        }
+      };
       auto announce_head = [&]() {
         uint32_t* flag = p.tp_peer_sync[pend_rank[pend_head]] + kTpSyncFlags + pend_block[pend_head];
         asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(flag), "r"(1u) : "memory");
@@ -695,15 +820,17 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (dead) break;             // a staging load never landed: push and announce nothing more
         const bool refill = n_st >= rlag && ld_it.valid();
         if (elected) {
-          while (pend_cnt > 0 && n_st >= pend_due[pend_head]) {
+          if (pend_cnt > 0 && n_st >= pend_due[pend_head]) {
             ptx::bulk_wait_group<C::kTpLag>();
-            announce_head();
+            release_fences();
+            while (pend_cnt > 0 && n_st >= pend_due[pend_head]) announce_head();
           }
           if (peer_ok) ptx::bulk_store(st_it.dst(p), buf0 + b * ch, st_it.bytes);
           ptx::bulk_commit_group();
           if (st_it.last_of_piece && peer_ok) {
             if (pend_cnt == C::kTpPend) {
               ptx::bulk_wait_group<1>();   // everything but the store just issued
+              release_fences();
               announce_head();
             }
             const int slot = (pend_head + pend_cnt) % C::kTpPend;
@@ -724,6 +851,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
       if (elected && pend_cnt > 0) {
         ptx::bulk_wait_group<0>();
+        release_fences();
         while (pend_cnt > 0) announce_head();
       }
       if (elected) ptx::bulk_wait_group<0>();
@@ -746,8 +874,13 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     uint8_t* stage_buf = sEpi + warp * 4096;                     // this warp's 32 x 128-byte staging tile
     uint32_t n_store = 0;                                        // TMA stores issued so far (staging rotation)
     int32_t it = 0;
-    for (int32_t t = cluster_idx; t < total_tiles; t += num_clusters, ++it) {
-      const TileInfo ti = decode_tile(ctl, p, t, C::kTileM);
+    uint32_t step = 0;
+    for (int32_t w = first_work; w >= 0; w = DYN ? sched_consume<CG>(ctl, step++, dead) : static_next(w)) {
+      if (w >= total_work) continue;
+      const WorkItem wi = decode_work(w, split_from);
+      const TileInfo ti = decode_tile(ctl, p, wi.t, C::kTileM);
+      const int32_t tile_col0 = ti.tn * BN + wi.half * (BN / 2);       // first output column of this work item
+      const int n_pairs = wi.split ? C::kPairs / 2 : C::kPairs;          // a half tile fills the accumulator's first BN / 2 columns
       // One alpha / beta per group when the arrays are given (grouped GEMM), else the scalars.
       const float alpha = p.alpha_array ? __ldg(p.alpha_array + ti.g) : alpha_all;
       const float beta = p.beta_array ? __ldg(p.beta_array + ti.g) : beta_all;
@@ -782,8 +915,8 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const int n_bufs = out_kind == kOutBf16 ? 1 : out_kind == kOutMxfp8 ? 2 : 4;
 
 #pragma unroll 1
-      for (int pi = 0; pi < C::kPairs; ++pi) {
-        const int pr = reverse ? (C::kPairs - 1 - pi) : pi;
+      for (int pi = 0; pi < n_pairs; ++pi) {
+        const int pr = reverse ? (n_pairs - 1 - pi) : pi;
         uint32_t v[2][32];
         ptx::tmem_ld_32x32b_x32(lane_addr + pr * 64, v[0]);
         ptx::tmem_ld_32x32b_x32(lane_addr + pr * 64 + 32, v[1]);
@@ -815,7 +948,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         uint32_t sf_pair = 0;       // quantised outputs: the scale-factor codes of this lane's row for these 64 columns
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const int32_t col0 = ti.tn * BN + pr * 64 + h * 32;
+          const int32_t col0 = tile_col0 + pr * 64 + h * 32;
           const int32_t cols_valid = p.N - col0;
           if (cols_valid <= 0 || (!row_ok && !tma_out)) continue;
 
@@ -962,10 +1095,10 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
           }
         }
-        if (out_kind != kOutBf16 && row_ok && ti.tn * BN + pr * 64 < p.N) {
+        if (out_kind != kOutBf16 && row_ok && tile_col0 + pr * 64 < p.N) {
           // Scale factors of this row for the 64 columns: consecutive bytes of one 512-byte atom of the interleaved
           // layout (4 per row for 16-wide blocks, 2 for 32-wide ones).
-          const int32_t pair_col0 = ti.tn * BN + pr * 64;
+          const int32_t pair_col0 = tile_col0 + pr * 64;
           const int32_t cols_left = p.N - pair_col0;
           const int32_t nb = pair_col0 / sfd_vec;
           uint8_t* sfp = p.SFD + (int64_t(ti.group_atom0) + lrow / 128) * (512ll * sfd_k_atoms) + (nb >> 2) * 512 +
@@ -986,12 +1119,13 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           __syncwarp();
           if (lane == 0) {
             // Column coordinate in bytes / elements of the D map: bf16 elements, e4m3 bytes, two e2m1 per byte.
-            const int32_t col = ti.tn * BN + pr * 64;
+            const int32_t col = tile_col0 + pr * 64;
             ptx::tma_store_3d(&tmD, ptx::smem_u32(sub_buf), out_kind == kOutNvfp4 ? col / 2 : col, warp_map_row0, ti.map_l);
             ptx::bulk_commit_group();
           }
         }
       }
+      ++it;
     }
     if (lane == 0) ptx::bulk_wait_group<0>();
     if (dead) atomicOr(p.status, kStTimeoutTmemFull);

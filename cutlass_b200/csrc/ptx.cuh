@@ -66,6 +66,39 @@ __device__ __forceinline__ void grid_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// Cluster launch control (the hardware's work stealing between the clusters of one grid): ask to cancel the launch of
+// a cluster that has not started yet; the 16-byte answer lands in this CTA's shared memory at `response` (16-byte
+// aligned) and completes 16 bytes on the mbarrier.  The reference issues the same request from its tile scheduler
+// (include/cutlass/gemm/kernel/sm100_tile_scheduler.hpp:400).  One thread per cluster asks.
+__device__ __forceinline__ void clc_try_cancel(uint32_t response, uint32_t bar) {
+  asm volatile("clusterlaunchcontrol.try_cancel.async.shared::cta.mbarrier::complete_tx::bytes.b128 [%0], [%1];"
+               ::"r"(response), "r"(bar)
+               : "memory");
+}
+// Decodes an answer: x of the first CTA of the cancelled cluster, or 0xFFFFFFFF when nothing was cancelled (no
+// cluster is left to start; no further request may be made after that).
+__device__ __forceinline__ uint32_t clc_query_first_ctaid_x(uint32_t response) {
+  uint32_t x, ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      ".reg .b128 r;\n\t"
+      "ld.shared.b128 r, [%2];\n\t"
+      "clusterlaunchcontrol.query_cancel.is_canceled.pred.b128 p, r;\n\t"
+      "selp.u32 %1, 1, 0, p;\n\t"
+      "mov.u32 %0, 0;\n\t"
+      "@p clusterlaunchcontrol.query_cancel.get_first_ctaid::x.b32.b128 %0, r;\n\t"
+      "}"
+      : "=r"(x), "=r"(ok)
+      : "r"(response)
+      : "memory");
+  return ok ? x : 0xFFFFFFFFu;
+}
+// 32-bit store into the shared memory of another CTA of the cluster (address from mapa).
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

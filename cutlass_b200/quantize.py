@@ -54,38 +54,3 @@ def quantize_blockscaled(x, mode=ScaleMode.Blockwise1x16, *, norm_constant=None,
     a.norm_constant = norm_constant.data_ptr() if norm_constant is not None else None
     L.check(L.load().bsg_quantize(C.byref(a), to_cuda_stream(stream)))
     return ScaledOperand(out, scale_out, mode, ScaleSwizzleMode.Swizzle32x4x4)
-
-
-def main() -> None:
-    """``python -m cutlass_b200.quantize --kind nvfp4 --rows 8192 --k 8192``: time the quantiser on a seeded matrix
-    (three input / output sets rotated, so that no launch finds its input in L2); prints one JSON line."""
-    import argparse
-    import json
-
-    import torch
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--kind", default="nvfp4", choices=["nvfp4", "mxfp8"])
-    ap.add_argument("--rows", type=int, default=8192)
-    ap.add_argument("--k", type=int, default=8192)
-    ap.add_argument("--iters", type=int, default=30)
-    a = ap.parse_args()
-    mode = ScaleMode.Blockwise1x16 if a.kind == "nvfp4" else ScaleMode.Blockwise1x32
-    gen = torch.Generator(device="cuda")
-    gen.manual_seed(0)
-    xs = [torch.randn((a.rows, a.k), device="cuda", generator=gen).to(torch.bfloat16) for _ in range(3)]
-    outs = [quantize_blockscaled(x, mode) for x in xs]
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(a.iters):
-        quantize_blockscaled(xs[i % 3], mode, out=outs[i % 3].quantized.tensor, scale_out=outs[i % 3].scale.tensor)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / a.iters
-    nbytes = a.rows * a.k * 2 + outs[0].quantized.tensor.numel() + outs[0].scale.tensor.numel()
-    print(json.dumps({"kind": a.kind, "rows": a.rows, "K": a.k, "ms": round(ms, 5), "algorithmic_bytes": nbytes,
-                      "GBs": round(nbytes / ms / 1e6, 1)}))
-
-
-if __name__ == "__main__":
-    main()

@@ -123,7 +123,8 @@ class TpGemm:
             blob = (C.c_uint8 * (64 * self.world)).from_buffer_copy(b"".join(handles))
             L.check(self._lib.bsg_tp_connect(self._comm, blob))
             dist.barrier(group)
-        # "kernel" | "copy_engine", optionally with "+single" (one gathered buffer instead of two); None: library default
+        # "kernel" | "copy_engine", optionally with "+single" (one gathered buffer instead of two) and / or "+release"
+        # (announcements behind release fences); None: library default
         mode = mode or os.environ.get("BSG_TP_MODE")
         if mode is not None:
             self.set_mode(mode)
@@ -143,8 +144,10 @@ class TpGemm:
 
     def set_mode(self, mode: str) -> None:
         """Only between calls, with every rank idle (device synchronised and a barrier passed), and the same on all ranks."""
-        base, _, opt = mode.partition("+")
-        code = {"kernel": 0, "copy_engine": 1}[base] | ({"": 0, "single": 2}[opt])
+        base, *opts = mode.split("+")
+        code = {"kernel": 0, "copy_engine": 1}[base]
+        for opt in opts:
+            code |= {"single": 2, "release": 4}[opt]       # one gathered buffer; release fences in front of the announcements
         self._L.check(self._lib.bsg_tp_set_mode(self._comm, code))
         self.mode = mode
 

@@ -303,8 +303,23 @@ int32_t bsg_quantize(const bsg_quant_args* args, void* cuda_stream);
  *                 BSG_TP_PUSH_COPY_ENGINE -- the GPU's copy engines on an internal side stream, one transfer per
  *                 band of row blocks followed by its announcement, joined back into the caller's stream
  *                 (the scheme of dist_gemm_universal_wrapper.hpp:578-593).  Default: kernel.  All ranks must use the same mode.
+ *
+ * A call needs the whole GPU.  Every CTA of a launch pushes pieces that a peer's CTAs wait for, so all CTAs of all
+ * ranks must be resident at the same time: the grid is sized from the number of clusters that fit (asked once per
+ * device), but another kernel that occupies SMs while a call runs (a second stream, another process under MPS) can
+ * leave CTAs unscheduled and the ranks waiting for one another until the bounded waits give up (BSG_ERR_TIMEOUT).
+ * After BSG_ERR_TIMEOUT the arrival counters of the ranks are out of step: destroy the communicators on all ranks
+ * (bsg_tp_destroy after a device synchronise and a barrier) and create them again before the next call.
+ *
+ * Ordering of the announcements.  A piece is announced to the peer by a relaxed system-scope counter increment issued
+ * after cp.async.bulk.wait_group has reported the piece's stores complete; the peer acquires the counter and issues a
+ * proxy fence before its TMA loads.  That the increment cannot overtake the data rests on how bulk stores complete
+ * over NVLink (observed, and guarded by tests that change A on every call), not on the PTX memory model.
+ * BSG_TP_RELEASE_ANNOUNCE, or-ed into the mode, puts a proxy fence and a system-scope release fence in front of every
+ * batch of increments: the form the memory model asks for, slower because the fence also waits for newer stores.
  */
-enum { BSG_TP_PUSH_KERNEL = 0, BSG_TP_PUSH_COPY_ENGINE = 1, BSG_TP_SINGLE_BUFFER = 2 /* or-ed in: every call uses the first gathered buffer */ };
+enum { BSG_TP_PUSH_KERNEL = 0, BSG_TP_PUSH_COPY_ENGINE = 1, BSG_TP_SINGLE_BUFFER = 2 /* or-ed in: every call uses the first gathered buffer */,
+       BSG_TP_RELEASE_ANNOUNCE = 4 /* or-ed in: see "Ordering of the announcements" above */ };
 typedef struct bsg_tp_comm bsg_tp_comm;
 int32_t bsg_tp_set_mode(bsg_tp_comm* comm, int32_t mode);
 int32_t bsg_tp_create(int32_t rank, int32_t world, int32_t kind, int64_t M, int64_t K, bsg_tp_comm** out,

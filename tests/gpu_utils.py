@@ -27,7 +27,7 @@ def make_operands(kind: int, M: int, N: int, K: int, seed: int, exact: bool):
 
 
 def run_dense(kind, M, N, K, A, sfa, B, sfb, Cb=None, alpha=1.0, beta=0.0, out_kind=0, st=None, tile_n=0, cta_group=0,
-              batch=1, check_status=True, bias=None, bias_per_row=False, activation=0):
+              batch=1, check_status=True, bias=None, bias_per_row=False, activation=0, sm_count=0, scheduler=0, use_pdl=0):
     """-> bf16 bits (batch*M, N), or (quantised values, SFD buffer) for out_kind 1 (NVFP4) / 2 (MXFP8)."""
     lib = L.load()
     dA, dB, dSFA, dSFB = dev(A), dev(B), dev(sfa), dev(sfb)
@@ -39,6 +39,7 @@ def run_dense(kind, M, N, K, A, sfa, B, sfb, Cb=None, alpha=1.0, beta=0.0, out_k
     a.C = dC.data_ptr() if dC is not None else None
     a.alpha, a.beta = alpha, beta
     a.tile_n, a.cta_group = tile_n, cta_group
+    a.sm_count, a.scheduler, a.use_pdl = sm_count, scheduler, use_pdl
     dbias = dev(np.asarray(bias, dtype=np.float32)) if bias is not None else None
     if dbias is not None:
         a.bias, a.bias_mode = dbias.data_ptr(), (L.BIAS_PER_ROW if bias_per_row else L.BIAS_PER_COLUMN)
@@ -86,7 +87,7 @@ def assert_close_bf16(got_bits, want_bits, rel_tol=1e-2):
 
 
 def run_grouped(kind, sizes, N, K, seed, exact=True, alpha=1.0, beta=0.0, tile_n=0, cta_group=0, with_bias=False, activation=0,
-                per_group_scalars=False):
+                per_group_scalars=False, scheduler=0):
     """Ragged grouped GEMM through the C ABI and the per-group oracle.  -> (got bits, want bits)."""
     rng = np.random.default_rng(seed)
     if kind == 0:
@@ -139,6 +140,7 @@ def run_grouped(kind, sizes, N, K, seed, exact=True, alpha=1.0, beta=0.0, tile_n
     if per_group_scalars:
         a.alpha_array, a.beta_array = dal.data_ptr(), dbe.data_ptr()
     a.activation = activation
+    a.scheduler = scheduler
     ws = torch.zeros(16, dtype=torch.uint8, device="cuda")
     L.check(lib.bsg_grouped_run(C.byref(a), ws.data_ptr(), 16, None))
     L.check(lib.bsg_read_device_status(ws.data_ptr(), None))

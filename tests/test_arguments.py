@@ -54,13 +54,13 @@ def test_shape_mismatches_raise():
     qa = torch.zeros((64, 64), dtype=torch.uint8)
     s = torch.zeros(128 * 8, dtype=torch.uint8)
     A = ops.ScaledOperand(qa, s, M16, SW)
-    with pytest.raises(ValueError, match="K dimension"):
+    with pytest.raises(ValueError, match="contraction extents differ"):
         ops.GemmArguments(A, ops.ScaledOperand(torch.zeros((64, 32), dtype=torch.uint8).t(), s, M16, SW),
                           torch.zeros((64, 64), dtype=torch.bfloat16), torch.float32)
     B = ops.ScaledOperand(torch.zeros((64, 64), dtype=torch.uint8).t(), s, M16, SW)
-    with pytest.raises(ValueError, match="M dimension"):
+    with pytest.raises(ValueError, match="out is 32 x 64 but A @ B is 64 x 64"):
         ops.GemmArguments(A, B, torch.zeros((32, 64), dtype=torch.bfloat16), torch.float32)
-    with pytest.raises(ValueError, match="N dimension"):
+    with pytest.raises(ValueError, match="out is 64 x 48 but A @ B is 64 x 64"):
         ops.GemmArguments(A, B, torch.zeros((64, 48), dtype=torch.bfloat16), torch.float32)
     with pytest.raises(ValueError, match="rank"):
         ops.GemmArguments(A, B, torch.zeros((64,), dtype=torch.bfloat16), torch.float32)

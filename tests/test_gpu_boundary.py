@@ -14,7 +14,7 @@ from cutlass_b200 import generators as G
 from cutlass_b200 import lib as L
 from oracle import ref_numpy as R
 
-from gpu_utils import dev, make_operands, oracle_bf16
+from gpu_utils import dev, make_operands, oracle_bf16, run_dense, run_grouped
 
 pytestmark = pytest.mark.gpu
 
@@ -162,3 +162,43 @@ def test_grouped_quantised_output_per_group(cuda_lib, out_kind, sizes):
             assert np.array_equal(sfd_g[idx], SFDw[idx]), f"group {g}: scale factors"
         row += m
         atom += atoms[g]
+
+
+@pytest.mark.parametrize("kind,M,N,K,tile_n", [(0, 2048, 2048, 512, 0), (1, 1024, 1536, 384, 0), (0, 4096, 5120, 256, 0), (1, 4096, 2560, 256, 128),
+                                              (0, 300, 456, 384, 0)])
+def test_dynamic_scheduler_dense(cuda_lib, kind, M, N, K, tile_n):
+    """BSG_SCHED_DYNAMIC: one cluster per tile is launched and running clusters take over the tiles of clusters that
+    have not started (320 and 320 tiles on 74 resident clusters in the larger cases).  Same results, bit for bit."""
+    rng, A, sfa, B, sfb = make_operands(kind, M, N, K, seed=60, exact=True)
+    Cb = G.bf16_normal((M, N), rng)
+    got = run_dense(kind, M, N, K, A, sfa, B, sfb, Cb, 1.0, 0.5, scheduler=L.SCHED_DYNAMIC, tile_n=tile_n)
+    assert np.array_equal(got, oracle_bf16(kind, M, N, K, A, sfa, B, sfb, Cb, 1.0, 0.5))
+
+
+@pytest.mark.parametrize("kind", [0, 1])
+def test_dynamic_scheduler_grouped_ragged(cuda_lib, kind):
+    """Grouped GEMM under the dynamic scheduler: the launch only knows an upper bound of the tile count (the group
+    sizes live on the device), surplus clusters find nothing to do."""
+    got, want = run_grouped(kind, [100, 0, 300, 1, 515, 2048, 77], 640, 512, seed=61, scheduler=L.SCHED_DYNAMIC)
+    assert np.array_equal(got, want)
+
+
+def test_dynamic_scheduler_repeated_launches_and_pdl(cuda_lib):
+    """Twenty launches in a row, alternately static and dynamic, with programmatic dependent launch."""
+    M, N, K = 2048, 2048, 256
+    rng, A, sfa, B, sfb = make_operands(0, M, N, K, seed=62, exact=True)
+    want = oracle_bf16(0, M, N, K, A, sfa, B, sfb)
+    t = [dev(x) for x in (A, B, sfa, sfb)]
+    outs = [torch.zeros((M, N), dtype=torch.int16, device="cuda") for _ in range(20)]
+    lib = L.load()
+    ws = torch.zeros(16, dtype=torch.uint8, device="cuda")
+    for i, D in enumerate(outs):
+        a = L.GemmArgs()
+        a.kind, a.batch, a.M, a.N, a.K = 0, 1, M, N, K
+        a.A, a.B, a.SFA, a.SFB, a.D = (x.data_ptr() for x in (*t, D))
+        a.alpha, a.use_pdl, a.scheduler = 1.0, 1, i % 2
+        L.check(lib.bsg_gemm_run(C.byref(a), ws.data_ptr(), 16, None))
+    L.check(lib.bsg_read_device_status(ws.data_ptr(), None))
+    torch.cuda.synchronize()
+    for i, D in enumerate(outs):
+        assert np.array_equal(D.cpu().numpy().view(np.uint16), want), f"launch {i}"

@@ -73,6 +73,25 @@ def test_alpha_beta_from_device_pointers(cuda_lib):
     assert np.array_equal(D.cpu().numpy().view(np.uint16), oracle_bf16(0, M, N, K, A, sfa, B, sfb, Cb, 0.5, -2.0))
 
 
+@pytest.mark.parametrize("kind,M,N,K,sms", [(0, 768, 768, 512, 8), (1, 768, 768, 256, 8), (0, 1280, 640, 256, 12), (1, 512, 1280, 384, 6),
+                                             (0, 2560, 2048, 256, 0)])
+def test_last_wave_tiles_split_in_halves(cuda_lib, kind, M, N, K, sms):
+    """Tile counts that leave a last wave at most half full (9 tiles on 4 clusters, 15 on 6, 10 on 3 with a partial
+    tile column, 80 on the whole GPU): those tiles are computed as two column halves by different clusters, and the
+    result must not change.  beta * C and the quantised output take the same path."""
+    rng, A, sfa, B, sfb = make_operands(kind, M, N, K, seed=40 + sms, exact=True)
+    Cb = G.bf16_normal((M, N), rng)
+    got = run_dense(kind, M, N, K, A, sfa, B, sfb, Cb, 1.0, 0.5, sm_count=sms)
+    assert np.array_equal(got, oracle_bf16(kind, M, N, K, A, sfa, B, sfb, Cb, 1.0, 0.5))
+    if kind == 0 and N % 32 == 0:
+        pre = oracle.gemm_fp32(0, A, sfa, B, sfb, M, N, K)
+        st = np.float32(448.0 * 6.0 / np.abs(pre).max())
+        D, SFD = run_dense(0, M, N, K, A, sfa, B, sfb, out_kind=1, st=float(st), sm_count=sms)
+        Dw, SFDw = oracle.quant_nvfp4(pre, st)
+        idx = R.sf_index(M, N // 16)
+        assert np.array_equal(D, Dw) and np.array_equal(SFD[idx], SFDw[idx])
+
+
 @pytest.mark.parametrize("kind", [0, 1])
 def test_batched(cuda_lib, kind):
     Lb, M, N, K = 3, 192, 256, 256

@@ -51,7 +51,7 @@ def _run_rank(tp, rank, world, kind, M, N, K, calls):
         assert bad == 0, f"call {call}: {bad} of {got.size} outputs differ from the oracle (rank {rank})"
 
 
-def _worker(rank, world, port, kind, M, N, K, calls, q):
+def _worker(rank, world, port, kind, M, N, K, calls, q, mode=None):
     try:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                           LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
@@ -59,7 +59,7 @@ def _worker(rank, world, port, kind, M, N, K, calls, q):
         from cutlass_b200 import tp as TP
         torch.cuda.set_device(rank)
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
-        tp = TP.TpGemm(kind, M, K)
+        tp = TP.TpGemm(kind, M, K, mode=mode)
         try:
             _run_rank(tp, rank, world, kind, M, N, K, calls)
         finally:
@@ -84,21 +84,38 @@ def test_tp_single_rank_matches_oracle(kind):
         tp.close()
 
 
-@pytest.mark.parametrize("kind,world,M,N,K", [(1, 2, 1024, 512, 2048), (0, 2, 1024, 512, 2048), (1, 2, 4096, 1024, 4096),
-                                              (1, 4, 2048, 1024, 2048)])
-def test_tp_gathers_a_inside_the_kernel(kind, world, M, N, K):
-    if torch.cuda.device_count() < world:
-        pytest.skip(f"needs {world} GPUs")
+def _spawn(world, kind, M, N, K, calls, mode=None, timeout=600):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, kind, M, N, K, 3, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, kind, M, N, K, calls, q, mode)) for r in range(world)]
     for p in procs:
         p.start()
-    results = sorted(q.get(timeout=300) for _ in range(world))
+    results = sorted(q.get(timeout=timeout) for _ in range(world))
     for p in procs:
         p.join(timeout=120)
     assert results == [(r, "ok") for r in range(world)], results
+
+
+@pytest.mark.parametrize("kind,world,M,N,K,mode", [(1, 2, 1024, 512, 2048, None), (0, 2, 1024, 512, 2048, None), (1, 2, 4096, 1024, 4096, None),
+                                                   (1, 2, 4096, 1024, 4096, "kernel+release"), (1, 2, 2048, 512, 2048, "copy_engine"),
+                                                   (1, 4, 2048, 1024, 2048, None), (0, 4, 4096, 1024, 4096, "kernel+release")])
+def test_tp_gathers_a_inside_the_kernel(kind, world, M, N, K, mode):
+    """A different A on every call, bit-exact against the oracle; also with the announcements behind release fences
+    (the form the PTX memory model asks for) and with the copy engines moving the rows."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _spawn(world, kind, M, N, K, 3, mode)
+
+
+def test_tp_eight_ranks_fifty_calls_at_the_benchmark_shard_size():
+    """Eight ranks with 2048 rows each (the row shard of the 16384-row benchmark problem), 50 calls in a row, every
+    one with a different A on every rank and every output element compared with the oracle: a rank that consumed a
+    peer's rows before they had arrived, or rows left from two calls earlier in the same gathered buffer, fails."""
+    world = 8
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _spawn(world, 1, 16384, 1024, 1024, 50, None, timeout=900)
 
 
 def _worker_peer_absent(rank, world, port, q):

@@ -54,6 +54,20 @@ def test_push_schedule_delivers_every_piece_once_and_nearest_consumer_first(worl
         assert TP.push_order(world, (dst + 1) % world)[0] == dst
 
 
+@pytest.mark.parametrize("grid", [2, 64, 100, 147])
+def test_push_schedule_covers_every_piece_when_fewer_ctas_are_launched(grid):
+    """The grid is clamped to the number of clusters that can be resident; the pieces are dealt out by CTA index
+    modulo the grid, so any grid size must still deliver every piece exactly once."""
+    world, M, ksplit = 4, 8192, 32
+    blocks = M // world // TP.ROW_BLOCK
+    seen = {}
+    for cta in range(grid):
+        for p in TP.copy_schedule(world, 1, M, ksplit, cta, grid):
+            key = (p.dst_rank, p.row_block, p.k_piece)
+            seen[key] = seen.get(key, 0) + 1
+    assert len(seen) == (world - 1) * blocks * ksplit and set(seen.values()) == {1}
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
