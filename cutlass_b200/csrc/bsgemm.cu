@@ -200,12 +200,13 @@ struct Plan {
 };
 
 int32_t validate(const Problem& q, Plan* plan) {
-  if (q.kind != BSG_KIND_NVFP4 && q.kind != BSG_KIND_MXFP8) return fail(BSG_ERR_NOT_SUPPORTED, "unknown operand kind %d", q.kind);
+  if (q.kind < BSG_KIND_NVFP4 || q.kind > BSG_KIND_MXFP8_MXFP4) return fail(BSG_ERR_NOT_SUPPORTED, "unknown operand kind %d", q.kind);
   if (q.out_kind != BSG_OUT_BF16 && q.out_kind != BSG_OUT_NVFP4 && q.out_kind != BSG_OUT_MXFP8) return fail(BSG_ERR_NOT_SUPPORTED, "unknown output kind %d", q.out_kind);
   if (q.num_groups < 1 || q.num_groups > BSG_MAX_GROUPS) return fail(BSG_ERR_INVALID_PROBLEM, "group / batch count %d outside [1, %d]", q.num_groups, BSG_MAX_GROUPS);
   if (q.N < 1 || q.K < 1 || q.total_rows < 0) return fail(BSG_ERR_INVALID_PROBLEM, "extents must be positive (rows=%lld N=%lld K=%lld)", (long long)q.total_rows, (long long)q.N, (long long)q.K);
   if (q.total_rows > 0x7FFFFFFF / 2 || q.N > 0x7FFFFFFF / 2 || q.K > 0x7FFFFFFF / 2) return fail(BSG_ERR_INVALID_PROBLEM, "extent exceeds 2^30");
-  const int64_t k_align = q.kind == BSG_KIND_NVFP4 ? 32 : 16;   // 16 bytes of K per row
+  // 16 bytes of K per row; the mixed kind expands B's e2m1 values in blocks of 128 on their way into shared memory
+  const int64_t k_align = q.kind == BSG_KIND_MXFP8 ? 16 : q.kind == BSG_KIND_MXFP8_MXFP4 ? 128 : 32;
   if (q.K % k_align != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "K=%lld must be a multiple of %lld", (long long)q.K, (long long)k_align);
   if (!q.A || !q.B || !q.SFA || !q.SFB || !q.D) return fail(BSG_ERR_INVALID_PROBLEM, "A, B, SFA, SFB and D must be non-null");
   if (!aligned16(q.A) || !aligned16(q.B) || !aligned16(q.D) || (q.C && !aligned16(q.C)))
@@ -253,6 +254,10 @@ int32_t validate(const Problem& q, Plan* plan) {
       return fail(BSG_ERR_NOT_SUPPORTED, "%scluster shape %d x %d is not available: this configuration runs clusters of %d x 1",
                   i ? "fallback " : "", q.cluster[i], q.cluster[i + 1], cg);
   }
+  if (q.kind >= BSG_KIND_MXFP4 && (cg != 2 || q.scheduler != BSG_SCHED_STATIC || q.tp))
+    return fail(BSG_ERR_NOT_SUPPORTED, "MXFP4 and mixed MXFP8 x MXFP4 operands run with cta_group 2 and the static scheduler only");
+  if (q.kind == BSG_KIND_MXFP8_MXFP4 && (reinterpret_cast<uintptr_t>(q.B) & 31u) != 0)
+    return fail(BSG_ERR_MISALIGNED_OPERAND, "B of the mixed kind must be 32-byte aligned");
   if (q.scheduler == BSG_SCHED_DYNAMIC && (q.tp || cg != 2)) return fail(BSG_ERR_NOT_SUPPORTED, "the dynamic scheduler needs cta_group 2 and is not available for the tensor-parallel GEMM");
   plan->cta_group = cg;
   plan->tile_n = tn;
@@ -309,8 +314,8 @@ template <int KIND, int CG, int BN, bool TP = false, bool DYN = false>
 int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_t stream, int sm_count, int dev, bool dry) {
   using Cf = bsg::Cfg<KIND, CG, BN, TP>;
   if (dry) return BSG_OK;
-  const bool fp4 = KIND == bsg::kKindNvfp4;
-  const int64_t k_bytes = fp4 ? q.K / 2 : q.K;
+  const bool a_fp4 = bsg::kind_packs_fp4(KIND), b_fp4 = KIND != bsg::kKindMxfp8;     // two values per byte in global memory
+  const int64_t ka_bytes = a_fp4 ? q.K / 2 : q.K, kb_bytes = b_fp4 ? q.K / 2 : q.K;
   const int64_t k_atoms = ((q.K + Cf::kSfVec - 1) / Cf::kSfVec + 3) / 4;
   const int64_t n_atoms = (q.N + 127) / 128;
   const int64_t b_groups = q.b_per_group ? q.num_groups : 1;
@@ -318,8 +323,8 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   int64_t sfa_row_atoms;
   if (q.offsets) sfa_row_atoms = q.total_rows / 128 + q.num_groups;   // upper bound; fetches are clamped per group
   else sfa_row_atoms = int64_t(q.num_groups) * ((q.rows_per_group + 127) / 128);
-  const int64_t lda_bytes = fp4 ? q.lda / 2 : q.lda, ldb_bytes = fp4 ? q.ldb / 2 : q.ldb;
-  const int64_t bsa_bytes = fp4 ? q.bs_a / 2 : q.bs_a, bsb_bytes = fp4 ? q.bs_b / 2 : q.bs_b;
+  const int64_t lda_bytes = a_fp4 ? q.lda / 2 : q.lda, ldb_bytes = b_fp4 ? q.ldb / 2 : q.ldb;
+  const int64_t bsa_bytes = a_fp4 ? q.bs_a / 2 : q.bs_a, bsb_bytes = b_fp4 ? q.bs_b / 2 : q.bs_b;
 
   CUtensorMap tmA, tmB, tmSFA, tmSFB, tmD;
   int32_t rc;
@@ -330,10 +335,19 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   const uint64_t d_rows = batched ? uint64_t(q.rows_per_group) : uint64_t(q.total_rows);
   if ((rc = make_out_map(&tmD, q.D, q.out_kind, uint64_t(q.N), d_rows, map_batches, uint64_t(q.ldd),
                          uint64_t(batched && q.num_groups > 1 ? q.bs_d : d_rows * q.ldd))) != BSG_OK) return rc;
-  if ((rc = make_operand_map(&tmA, q.A, uint64_t(k_bytes), map_rows, map_batches, uint64_t(lda_bytes),
+  if ((rc = make_operand_map(&tmA, q.A, uint64_t(ka_bytes), map_rows, map_batches, uint64_t(lda_bytes),
                              uint64_t(batched && q.num_groups > 1 ? bsa_bytes : int64_t(map_rows) * lda_bytes), Cf::kCtaM)) != BSG_OK) return rc;
-  if ((rc = make_operand_map(&tmB, q.B, uint64_t(k_bytes), uint64_t(q.N), uint64_t(b_groups), uint64_t(ldb_bytes),
-                             uint64_t(b_groups > 1 ? bsb_bytes : q.N * ldb_bytes), Cf::kBRowsCta)) != BSG_OK) return rc;
+  if (KIND == bsg::kKindMxfp8Mxfp4) {
+    // B is packed e2m1 in global memory; the TMA engine expands it to one value per byte (16 values -> 16 bytes),
+    // which is what kind::mxf8f6f4 reads.  Extents and the box are counted in elements, strides in bytes.
+    rc = g_maps.get(make_key(q.B, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             uint64_t(q.K), uint64_t(q.N), uint64_t(b_groups), uint64_t(ldb_bytes),
+                             uint64_t(b_groups > 1 ? bsb_bytes : q.N * ldb_bytes), 128, Cf::kBRowsCta, 1), &tmB);
+  } else {
+    rc = make_operand_map(&tmB, q.B, uint64_t(kb_bytes), uint64_t(q.N), uint64_t(b_groups), uint64_t(ldb_bytes),
+                          uint64_t(b_groups > 1 ? bsb_bytes : q.N * ldb_bytes), Cf::kBRowsCta);
+  }
+  if (rc != BSG_OK) return rc;
   if ((rc = make_sf_map(&tmSFA, q.SFA, k_atoms, TP ? 2 * sfa_row_atoms : sfa_row_atoms, Cf::kKAtoms, 1)) != BSG_OK) return rc;
   if ((rc = make_sf_map(&tmSFB, q.SFB, k_atoms, b_groups * n_atoms, Cf::kKAtoms, BN / 128)) != BSG_OK) return rc;
 
@@ -454,7 +468,7 @@ void fill_caps_for(bsg_caps* caps) {
 
 void fill_caps(const Problem& q, const Plan& plan, bsg_caps* caps) {
   if (!caps) return;
-  const bool fp4 = q.kind == BSG_KIND_NVFP4;
+  const bool fp4 = q.kind == BSG_KIND_NVFP4 || q.kind == BSG_KIND_MXFP4;     // the same tile extents and stage count
   if (plan.cta_group == 2 && plan.tile_n == 256) fp4 ? fill_caps_for<0, 2, 256>(caps) : fill_caps_for<1, 2, 256>(caps);
   else if (plan.cta_group == 2) fp4 ? fill_caps_for<0, 2, 128>(caps) : fill_caps_for<1, 2, 128>(caps);
   else if (plan.tile_n == 256) fp4 ? fill_caps_for<0, 1, 256>(caps) : fill_caps_for<1, 1, 256>(caps);
@@ -482,7 +496,11 @@ int32_t run_problem(const Problem& q, void* workspace, size_t ws_bytes, void* st
 
   uint32_t* status = static_cast<uint32_t*>(workspace);
   if (q.kind == BSG_KIND_NVFP4) return dispatch_shape<0>(q, plan, status, stream, sms, dev, false);
-  return dispatch_shape<1>(q, plan, status, stream, sms, dev, false);
+  if (q.kind == BSG_KIND_MXFP8) return dispatch_shape<1>(q, plan, status, stream, sms, dev, false);
+  // MXFP4 and the mixed kind: 2-CTA tiles, static scheduler (checked in validate)
+  if (q.kind == BSG_KIND_MXFP4)
+    return plan.tile_n == 256 ? launch<2, 2, 256>(q, plan, status, stream, sms, dev, false) : launch<2, 2, 128>(q, plan, status, stream, sms, dev, false);
+  return plan.tile_n == 256 ? launch<3, 2, 256>(q, plan, status, stream, sms, dev, false) : launch<3, 2, 128>(q, plan, status, stream, sms, dev, false);
 }
 
 Problem from_dense(const bsg_gemm_args* a) {

@@ -38,8 +38,11 @@
 namespace bsg {
 
 constexpr int kMaxGroups = 256;
-constexpr int kKindNvfp4 = 0;
-constexpr int kKindMxfp8 = 1;
+constexpr int kKindNvfp4 = 0;        // e2m1 x e2m1, ue4m3 scale per 16
+constexpr int kKindMxfp8 = 1;        // e4m3 x e4m3, ue8m0 scale per 32
+constexpr int kKindMxfp4 = 2;        // e2m1 x e2m1, ue8m0 scale per 32
+constexpr int kKindMxfp8Mxfp4 = 3;   // A e4m3, B e2m1 (expanded to one value per byte on its way into shared memory), ue8m0 per 32
+__host__ __device__ constexpr bool kind_packs_fp4(int kind) { return kind == kKindNvfp4 || kind == kKindMxfp4; }   // A and B: two values per byte
 constexpr int kOutBf16 = 0;
 constexpr int kOutNvfp4 = 1;
 constexpr int kOutMxfp8 = 2;
@@ -115,16 +118,16 @@ constexpr uint32_t kStTimeoutPeer = 64u;      // tensor parallel: a peer never p
 
 template <int KIND, int CG, int BN, bool TP = false>
 struct Cfg {
-  static_assert(KIND == kKindNvfp4 || KIND == kKindMxfp8, "kind");
+  static_assert(KIND >= kKindNvfp4 && KIND <= kKindMxfp8Mxfp4, "kind");
   static_assert(CG == 1 || CG == 2, "cta group");
   static_assert(BN == 128 || BN == 256, "tile n");
   static constexpr int kCtaM = 128;                       // accumulator rows per CTA (= TMEM lanes)
   static constexpr int kTileM = kCtaM * CG;               // rows per MMA tile
   static constexpr int kRowBytes = 128;                   // bytes of K per row per k-tile (one 128B swizzle atom)
-  static constexpr int kTileK = KIND == kKindNvfp4 ? 256 : 128;   // elements of K per k-tile
-  static constexpr int kMmaK = KIND == kKindNvfp4 ? 64 : 32;      // elements of K per instruction (32 bytes)
+  static constexpr int kTileK = kind_packs_fp4(KIND) ? 256 : 128;   // elements of K per k-tile
+  static constexpr int kMmaK = kind_packs_fp4(KIND) ? 64 : 32;      // elements of K per instruction (32 bytes)
   static constexpr int kSfVec = KIND == kKindNvfp4 ? 16 : 32;
-  static constexpr int kKAtoms = KIND == kKindNvfp4 ? 4 : 1;      // 512-byte SF atoms along K per k-tile
+  static constexpr int kKAtoms = kTileK / kSfVec / 4;               // 512-byte SF atoms (4 K-blocks each) along K per k-tile
   static constexpr int kBRowsCta = BN / CG;               // rows of B each CTA loads
   static constexpr int kABytes = kCtaM * kRowBytes;
   static constexpr int kBBytes = kBRowsCta * kRowBytes;
@@ -262,10 +265,12 @@ __device__ __forceinline__ uint64_t make_desc_sf(uint32_t smem_addr) {
 
 template <int KIND, int CG>
 __device__ __forceinline__ constexpr uint32_t make_idesc(uint32_t n) {
-  constexpr uint32_t fmt = KIND == kKindNvfp4 ? 1u : 0u;       // E2M1 (mxf4) / E4M3 (mxf8f6f4)
+  // Operand formats: the 4-bit kinds (mxf4nvf4, mxf4) number E2M1 as 1; kind::mxf8f6f4 numbers E4M3 as 0 and E2M1 as 5.
+  constexpr uint32_t a_fmt = kind_packs_fp4(KIND) ? 1u : 0u;
+  constexpr uint32_t b_fmt = kind_packs_fp4(KIND) ? 1u : (KIND == kKindMxfp8Mxfp4 ? 5u : 0u);
   constexpr uint32_t sf_fmt = KIND == kKindNvfp4 ? 0u : 1u;    // UE4M3 / UE8M0
   constexpr uint32_t m = 128u * CG;
-  return (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | (sf_fmt << 23) | ((m >> 4) << 24);
+  return (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | (sf_fmt << 23) | ((m >> 4) << 24);
 }
 
 // Work item w of the persistent walk -> (tile, half): items below split_from are whole tiles; above it every tile
@@ -728,8 +733,12 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               if (kb < n_mma) {
                 uint32_t sfa_t, sfb_t, id = idesc;
                 if constexpr (KIND == kKindNvfp4) {
-                  sfa_t = sfa_col + 4 * kb;
+                  sfa_t = sfa_col + 4 * kb;                            // four scale factors per instruction: a column group each
                   sfb_t = sfb_col + (BN / 32) * kb;
+                } else if constexpr (KIND == kKindMxfp4) {
+                  sfa_t = sfa_col + 4 * (kb >> 1);                     // two scale factors per instruction: half a column group
+                  sfb_t = sfb_col + (BN / 32) * (kb >> 1);
+                  id |= (uint32_t(kb & 1) << 5) | (uint32_t(kb & 1) << 30);   // lower / upper pair of the group's four bytes
                 } else {
                   sfa_t = sfa_col;
                   sfb_t = sfb_col;

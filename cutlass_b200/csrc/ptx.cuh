@@ -313,39 +313,29 @@ __device__ __forceinline__ void utccp_32x128b_warpx4(uint32_t taddr, uint64_t sd
     asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 
-// Block-scaled UMMA.  KIND 0: e2m1 x e2m1, ue4m3 scale per 16 (K = 64 per
-// instruction).  KIND 1: mxf8f6f4 with ue8m0 scale per 32 (K = 32).
+// Block-scaled UMMA.  KIND 0: e2m1 x e2m1, ue4m3 scale per 16 (K = 64 per instruction).  KIND 2: the same data
+// with ue8m0 scale per 32.  KIND 1 and 3: kind::mxf8f6f4 (8-bit containers; formats from the instruction
+// descriptor) with ue8m0 scale per 32 (K = 32).
+#define BSG_UMMA_ASM(CTA_GROUP, KIND_AND_SCALE)                                                                     \
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"                                                   \
+               "tcgen05.mma.cta_group::" CTA_GROUP ".kind::" KIND_AND_SCALE " [%0], %1, %2, %3, [%5], [%6], p;\n\t}" \
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)  \
+               : "memory")
 template <int KIND, int CG>
 __device__ __forceinline__ void umma_block_scaled(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                                   uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
   if constexpr (KIND == 0) {
-    if constexpr (CG == 2)
-      asm volatile(
-          "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-          "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-          ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
-          : "memory");
-    else
-      asm volatile(
-          "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-          "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-          ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
-          : "memory");
+    if constexpr (CG == 2) BSG_UMMA_ASM("2", "mxf4nvf4.block_scale.block16");
+    else BSG_UMMA_ASM("1", "mxf4nvf4.block_scale.block16");
+  } else if constexpr (KIND == 2) {
+    if constexpr (CG == 2) BSG_UMMA_ASM("2", "mxf4.block_scale.block32");
+    else BSG_UMMA_ASM("1", "mxf4.block_scale.block32");
   } else {
-    if constexpr (CG == 2)
-      asm volatile(
-          "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-          "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-          ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
-          : "memory");
-    else
-      asm volatile(
-          "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-          "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-          ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
-          : "memory");
+    if constexpr (CG == 2) BSG_UMMA_ASM("2", "mxf8f6f4.block_scale");
+    else BSG_UMMA_ASM("1", "mxf8f6f4.block_scale");
   }
 }
+#undef BSG_UMMA_ASM
 
 // Arrive on `bar` (same shared-memory offset in every CTA of `cta_mask`) once all
 // tcgen05 operations issued so far by this thread have completed.

@@ -38,6 +38,30 @@ def mxfp8_operand(rows: int, K: int, rng: np.random.Generator):
     return codes, sf, F.swizzle_sf(sf)
 
 
+def mxfp4_operand(rows: int, K: int, rng: np.random.Generator):
+    """MXFP4: the 15 distinct e2m1 values with ue8m0 scale factors per 32 elements, exponents uniform in [-3, 3].
+    -> (packed (rows, K/2) uint8, sf codes (rows, K/32) uint8, interleaved sf buffer)."""
+    codes = _E2M1_15[rng.integers(0, 15, size=(rows, K), dtype=np.uint8)]
+    sf = rng.integers(124, 131, size=(rows, F.ceil_div(K, 32)), dtype=np.uint8)
+    return F.pack_e2m1(codes), sf, F.swizzle_sf(sf)
+
+
+def exact_mxfp4_operand(rows: int, K: int, rng: np.random.Generator):
+    """MXFP4 data in {-1, 0, 1} with ue8m0 scales {1, 2, 4}: exact in fp32 in any accumulation order."""
+    codes = np.array([0, 2, 10], dtype=np.uint8)[rng.integers(0, 3, size=(rows, K), dtype=np.uint8)]
+    sf = np.array([127, 128, 129], dtype=np.uint8)[rng.integers(0, 3, size=(rows, F.ceil_div(K, 32)), dtype=np.uint8)]
+    return F.pack_e2m1(codes), sf, F.swizzle_sf(sf)
+
+
+def operand_generators(kind: int, exact: bool):
+    """(generator of A, generator of B) for an operand kind of the library: 0 NVFP4, 1 MXFP8, 2 MXFP4,
+    3 mixed (A MXFP8, B MXFP4)."""
+    table = {0: (nvfp4_operand, exact_nvfp4_operand), 1: (mxfp8_operand, exact_mxfp8_operand), 2: (mxfp4_operand, exact_mxfp4_operand)}
+    if kind == 3:
+        return table[1][exact], table[2][exact]
+    return table[kind][exact], table[kind][exact]
+
+
 def exact_nvfp4_operand(rows: int, K: int, rng: np.random.Generator):
     """Data in {-1, 0, 1} with power-of-two scales {1, 2, 4}: fp32 accumulation is exact
     in any order (the trick of operators/test/test_utils/gemm.py:366-403 in the reference)."""

@@ -27,6 +27,8 @@ STATUS_NAMES = {
 }
 KIND_NVFP4 = 0
 KIND_MXFP8 = 1
+KIND_MXFP4 = 2          # e2m1 data, ue8m0 scale per 32
+KIND_MXFP8_MXFP4 = 3    # A e4m3, B e2m1, ue8m0 scale per 32
 OUT_BF16 = 0
 OUT_NVFP4 = 1
 OUT_MXFP8 = 2

@@ -37,7 +37,7 @@ class OperatorMetadata:
 
     @property
     def tile_shape(self) -> tuple[int, int, int]:
-        return (128 * self.cta_group, self.tile_n, 256 if self.kind == L.KIND_NVFP4 else 128)
+        return (128 * self.cta_group, self.tile_n, 256 if self.kind in (L.KIND_NVFP4, L.KIND_MXFP4) else 128)
 
 
 @dataclass
@@ -97,15 +97,29 @@ def to_cuda_stream(stream) -> int:
         raise TypeError(f"cannot interpret {type(stream).__name__} as a CUDA stream") from exc
 
 
-def _operand_kind(op: ScaledOperand) -> int | None:
+def _operand_format(op: ScaledOperand) -> str | None:
+    """Data / scale format of one operand: "nvfp4" (e2m1, ue4m3 per 16), "mxfp8" (e4m3, ue8m0 per 32) or "mxfp4"
+    (e2m1, ue8m0 per 32; needs the packed fp4 dtype, since uint8 with 32-wide blocks means e4m3 codes)."""
     q, s = op.quantized.dtype, op.scale.dtype
+    is_fp4 = _FP4X2 is not None and q == _FP4X2
     if ScaleMode.compare(op.mode, ScaleMode.Blockwise1x16):
-        if (q == torch.uint8 or (_FP4X2 is not None and q == _FP4X2)) and s in (torch.uint8, torch.float8_e4m3fn):
-            return L.KIND_NVFP4
-    if ScaleMode.compare(op.mode, ScaleMode.Blockwise1x32):
-        if q in (torch.uint8, torch.float8_e4m3fn) and (s == torch.uint8 or (_E8M0 is not None and s == _E8M0)):
-            return L.KIND_MXFP8
+        if (q == torch.uint8 or is_fp4) and s in (torch.uint8, torch.float8_e4m3fn):
+            return "nvfp4"
+    if ScaleMode.compare(op.mode, ScaleMode.Blockwise1x32) and (s == torch.uint8 or (_E8M0 is not None and s == _E8M0)):
+        if q in (torch.uint8, torch.float8_e4m3fn):
+            return "mxfp8"
+        if is_fp4:
+            return "mxfp4"
     return None
+
+
+_PAIR_KINDS = {("nvfp4", "nvfp4"): L.KIND_NVFP4, ("mxfp8", "mxfp8"): L.KIND_MXFP8, ("mxfp4", "mxfp4"): L.KIND_MXFP4,
+               ("mxfp8", "mxfp4"): L.KIND_MXFP8_MXFP4}
+
+
+def _pair_kind(A: ScaledOperand, B: ScaledOperand) -> int | None:
+    """Library kind of an (A, B) pair, or None when the library has no kernel for the combination."""
+    return _PAIR_KINDS.get((_operand_format(A), _operand_format(B)))
 
 
 def _scalar_ptr(v) -> tuple[float, int | None]:
@@ -178,16 +192,19 @@ class Operator:
         for name, op in (("A", A), ("B", B)):
             if op.swizzle != ScaleSwizzleMode.Swizzle32x4x4:
                 return Status.fail(f"{name}: scale swizzle {op.swizzle} is not supported (need Swizzle32x4x4)")
-            if _operand_kind(op) is None:
+            if _operand_format(op) is None:
                 return Status.fail(f"{name}: unsupported combination of dtype {op.quantized.dtype}, scale dtype "
                                    f"{op.scale.dtype} and scale mode {op.mode}")
-        if not ScaleMode.compare(A.mode, B.mode) or _operand_kind(A) != _operand_kind(B):
-            return Status.fail("A and B must use the same data format, scale format and scale mode")
-        if _operand_kind(A) != md.kind:
+        if not ScaleMode.compare(A.mode, B.mode):
+            return Status.fail("A and B must use the same scale format and scale mode")
+        if _pair_kind(A, B) is None:
+            return Status.fail(f"no kernel for A {_operand_format(A)} with B {_operand_format(B)} (same format on both sides, or "
+                               "MXFP8 A with MXFP4 B)")
+        if _pair_kind(A, B) != md.kind:
             return Status.fail("operand format does not match this operator")
-        k_align = 32 if md.kind == L.KIND_NVFP4 else 16
+        k_align = {L.KIND_NVFP4: 32, L.KIND_MXFP8: 16, L.KIND_MXFP4: 32, L.KIND_MXFP8_MXFP4: 128}[md.kind]
         if K % k_align != 0:
-            return Status.fail(f"K={K} must be a multiple of {k_align} (16-byte rows)")
+            return Status.fail(f"K={K} must be a multiple of {k_align}")
         for name, op, shp in (("A", A, a_rows_shape), ("B", B, b_rows_shape)):
             want = ScaledOperand.numel_scale(shp, op.mode, op.swizzle)
             if op.scale.numel() != want:
@@ -206,15 +223,25 @@ class Operator:
 
 
 def _k_major_rows(t: torch.Tensor, rows_axis: int, k_axis: int) -> bool:
-    """True when ``t`` is dense with K contiguous and the batch / row dimensions packed."""
+    """True when ``t`` has K contiguous and rows / batch entries that start on 16-byte boundaries: a row pitch
+    larger than K and a batch stride larger than one matrix are fine (a slice of a larger buffer)."""
     shape, stride = t.shape, t.stride()
+    esz = t.element_size()
     if stride[k_axis] != 1:
         return False
-    if stride[rows_axis] != shape[k_axis]:
+    if shape[rows_axis] > 1 and (stride[rows_axis] < shape[k_axis] or (stride[rows_axis] * esz) % 16 != 0):
         return False
-    if t.dim() == 3 and shape[0] > 1 and stride[0] != shape[rows_axis] * shape[k_axis]:
+    if t.dim() == 3 and shape[0] > 1 and (stride[0] <= 0 or (stride[0] * esz) % 16 != 0):
         return False
     return True
+
+
+def _pitches(t: torch.Tensor, rows_axis: int, k_axis: int, elems_per_item: int) -> tuple[int, int]:
+    """(row pitch, batch stride) of ``t`` in logical elements; 0 where the extent is 1 (the library's dense default)."""
+    shape, stride = t.shape, t.stride()
+    row = stride[rows_axis] * elems_per_item if shape[rows_axis] > 1 else 0
+    batch = stride[0] * elems_per_item if (t.dim() == 3 and shape[0] > 1) else 0
+    return row, batch
 
 
 class BlockScaledGemmOperator(Operator):
@@ -233,13 +260,13 @@ class BlockScaledGemmOperator(Operator):
         if not st:
             return st
         if not _k_major_rows(args.A.quantized.tensor, -2, -1):
-            return Status.fail("A must be K-major (row-major (L, M, K)) and densely packed")
+            return Status.fail("A must be K-major (row-major (L, M, K)) with 16-byte aligned rows and batch entries")
         if not _k_major_rows(args.B.quantized.tensor, -1, -2):
             return Status.fail("B must be K-major: build it as (L, N, K) and transpose the last two dimensions")
         epi = args.epilogue or EpilogueDescriptor()
         out = args.out.tensor
-        if not out.is_contiguous():
-            return Status.fail("out must be contiguous")
+        if not _k_major_rows(out, -2, -1):
+            return Status.fail("out must be row-major with 16-byte aligned rows")
         if epi.out_quant is None:
             if out.dtype != torch.bfloat16:
                 return Status.fail(f"out dtype {out.dtype} is not supported (bf16, or packed fp4 with out_quant)")
@@ -270,8 +297,8 @@ class BlockScaledGemmOperator(Operator):
             if nc.numel() != 1 or nc.dtype != torch.float32:
                 return Status.fail("out_quant.norm_constant must be a one-element float32 tensor")
         if epi.C is not None:
-            if epi.C.dtype != torch.bfloat16 or tuple(epi.C.shape) != (tuple(out.shape[:-1]) + (ps.N,)) or not epi.C.is_contiguous():
-                return Status.fail("C must be a contiguous bf16 tensor of the logical output shape")
+            if epi.C.dtype != torch.bfloat16 or tuple(epi.C.shape) != (tuple(out.shape[:-1]) + (ps.N,)) or not _k_major_rows(epi.C, -2, -1):
+                return Status.fail("C must be a row-major bf16 tensor of the logical output shape (16-byte aligned rows)")
         else:
             beta = epi.beta
             if not isinstance(beta, torch.Tensor) and float(beta) != 0.0:
@@ -301,8 +328,15 @@ class BlockScaledGemmOperator(Operator):
         a.SFB = args.B.scale.data_ptr()
         a.C = epi.C.data_ptr() if epi.C is not None else None
         a.D = args.out.data_ptr()
-        a.ldc = ps.N
-        a.ldd = ps.N
+        # Row pitches and batch strides, in logical elements (a packed fp4 byte holds two)
+        a_fp4 = 2 if args.A.is_packed_fp4 else 1
+        b_fp4 = 2 if args.B.is_packed_fp4 else 1
+        d_fp4 = 2 if (epi.out_quant is not None and not isinstance(epi.out_quant, Mxfp8Quant)) else 1
+        a.lda, a.batch_stride_A = _pitches(args.A.quantized.tensor, -2, -1, a_fp4)
+        a.ldb, a.batch_stride_B = _pitches(args.B.quantized.tensor, -1, -2, b_fp4)
+        a.ldd, a.batch_stride_D = _pitches(args.out.tensor, -2, -1, d_fp4)
+        if epi.C is not None:
+            a.ldc, a.batch_stride_C = _pitches(epi.C, -2, -1, 1)
         a.alpha, alpha_ptr = _scalar_ptr(epi.alpha)
         a.beta, beta_ptr = _scalar_ptr(epi.beta)
         a.alpha_ptr = alpha_ptr
@@ -360,13 +394,28 @@ class GroupedBlockScaledGemmOperator(Operator):
         if not _k_major_rows(args.B.quantized.tensor, -1, -2):
             return Status.fail("B must be K-major: build it as (groups, N, K) and transpose the last two dimensions")
         out = args.out.tensor
-        if out.dtype != torch.bfloat16 or not out.is_contiguous():
-            return Status.fail("out must be a contiguous bf16 tensor")
-        if ps.N % 8 != 0:
-            return Status.fail("N must be a multiple of 8")
         epi = args.epilogue or EpilogueDescriptor()
-        if epi.out_quant is not None:
-            return Status.fail("NVFP4 output is not available for grouped GEMM")
+        if not out.is_contiguous():
+            return Status.fail("out must be contiguous")
+        if epi.out_quant is None:
+            if out.dtype != torch.bfloat16:
+                return Status.fail("out must be a bf16 tensor (or a quantised output with out_quant)")
+            if ps.N % 8 != 0:
+                return Status.fail("N must be a multiple of 8")
+        else:
+            # one interleaved scale layout per group, each padded to 128 rows: the form the next grouped GEMM takes as SFA
+            mx = isinstance(epi.out_quant, Mxfp8Quant)
+            vec_out = 32 if mx else 16
+            if ps.N % 32 != 0:
+                return Status.fail("N must be a multiple of 32 for a quantised output")
+            n_blocks4 = -(-(ps.N // vec_out) // 4) * 4
+            lo_sfd, hi_sfd = -(-ps.M // 128) * 128 * n_blocks4, (ps.M // 128 + ps.L) * 128 * n_blocks4
+            if not (lo_sfd <= epi.out_quant.scale.numel() <= hi_sfd) or not epi.out_quant.scale.is_contiguous():
+                return Status.fail(f"out_quant.scale must be contiguous with between {lo_sfd} and {hi_sfd} elements "
+                                   "(one 128-row-padded layout per group)")
+            nc = epi.out_quant.norm_constant
+            if (nc is None and not mx) or (nc is not None and (nc.numel() != 1 or nc.dtype != torch.float32)):
+                return Status.fail("out_quant.norm_constant must be a one-element float32 tensor")
         for name, v in (("alpha", epi.alpha), ("beta", epi.beta)):
             if isinstance(v, torch.Tensor) and (v.dtype != torch.float32 or v.numel() != ps.L or not v.is_contiguous()):
                 return Status.fail(f"grouped GEMM takes a scalar {name} or a contiguous fp32 tensor with one entry per group ({ps.L})")
@@ -389,7 +438,10 @@ class GroupedBlockScaledGemmOperator(Operator):
         epi = args.epilogue or EpilogueDescriptor()
         a = L.GroupedArgs()
         a.kind = md.kind
-        a.out_kind = L.OUT_BF16
+        a.out_kind = L.OUT_BF16 if epi.out_quant is None else (L.OUT_MXFP8 if isinstance(epi.out_quant, Mxfp8Quant) else L.OUT_NVFP4)
+        if epi.out_quant is not None:
+            a.SFD = epi.out_quant.scale.data_ptr()
+            a.norm_constant = epi.out_quant.norm_constant.data_ptr() if epi.out_quant.norm_constant is not None else None
         a.num_groups = ps.L
         a.total_M, a.N, a.K = ps.M, ps.N, ps.K
         a.A = args.A.quantized.data_ptr()
@@ -425,7 +477,8 @@ _TILE_CHOICES = ((2, 256), (2, 128), (1, 256), (1, 128))   # (cta_group, tile_n)
 
 
 def _name(kind: int, grouped: bool, cg: int, tn: int) -> str:
-    fmt = "nvfp4_ue4m3x16" if kind == L.KIND_NVFP4 else "mxfp8_ue8m0x32"
+    fmt = {L.KIND_NVFP4: "nvfp4_ue4m3x16", L.KIND_MXFP8: "mxfp8_ue8m0x32", L.KIND_MXFP4: "mxfp4_ue8m0x32",
+           L.KIND_MXFP8_MXFP4: "mxfp8_mxfp4_ue8m0x32"}[kind]
     fam = "GroupedBlockScaledGemm" if grouped else "BlockScaledGemm"
     return f"native.{fam}_sm100_tn_{fmt}_acc_f32_{cg}cta_tile{128 * cg}x{tn}"
 
@@ -433,8 +486,10 @@ def _name(kind: int, grouped: bool, cg: int, tn: int) -> str:
 def all_operators() -> list[Operator]:
     """Every operator configuration the library offers."""
     ops: list[Operator] = []
-    for kind in (L.KIND_NVFP4, L.KIND_MXFP8):
+    for kind in (L.KIND_NVFP4, L.KIND_MXFP8, L.KIND_MXFP4, L.KIND_MXFP8_MXFP4):
         for cg, tn in _TILE_CHOICES:
+            if kind >= L.KIND_MXFP4 and cg != 2:
+                continue          # the two newer kinds are built for the 2-CTA tiles only
             ops.append(BlockScaledGemmOperator(OperatorMetadata(_name(kind, False, cg, tn), kind, tn, cg, False)))
             ops.append(GroupedBlockScaledGemmOperator(OperatorMetadata(_name(kind, True, cg, tn), kind, tn, cg, True)))
     return ops

@@ -32,10 +32,14 @@ typedef enum bsg_status {
   BSG_ERR_CUDA = 8
 } bsg_status;
 
-/* Operand formats (A and B share one format; scale format follows it). */
+/* Operand formats (data format of A and B, and the scale format that goes with it). */
 enum {
   BSG_KIND_NVFP4 = 0,       /* e2m1 data, ue4m3 scale per 16 K-elements */
-  BSG_KIND_MXFP8 = 1        /* e4m3 data, ue8m0 scale per 32 K-elements */
+  BSG_KIND_MXFP8 = 1,       /* e4m3 data, ue8m0 scale per 32 K-elements */
+  BSG_KIND_MXFP4 = 2,       /* e2m1 data, ue8m0 scale per 32 K-elements */
+  BSG_KIND_MXFP8_MXFP4 = 3  /* A e4m3, B e2m1 (packed, 32-byte aligned), both with ue8m0 scale per 32: the mixed form of the
+                               reference's examples/72_blackwell_narrow_precision_gemm/72c_blackwell_mixed_mxfp8_bf16_gemm.cu;
+                               K must be a multiple of 128.  Kinds 2 and 3: cta_group 2, static scheduler, not tensor parallel. */
 };
 
 /* Output formats. */

@@ -117,10 +117,15 @@ uint16_t bsg_oracle_f32_to_bf16(float f) {
   return (uint16_t)(u >> 16);
 }
 
+/* Operand kinds: 0 NVFP4 (e2m1 data, ue4m3 scale per 16), 1 MXFP8 (e4m3, ue8m0 per 32), 2 MXFP4 (e2m1, ue8m0 per 32),
+ * 3 mixed (A e4m3, B e2m1, both ue8m0 per 32: the reference's example 72c). */
+static int kind_is_fp4(int kind, int is_b) { return kind == 0 || kind == 2 || (kind == 3 && is_b); }
+
 /* value * scale for every element of a packed K-major operand -> rows x K floats */
-static void expand_operand(int kind, const uint8_t* data, const uint8_t* sf, int64_t rows, int64_t K, int64_t row_begin,
+static void expand_operand(int kind, int is_b, const uint8_t* data, const uint8_t* sf, int64_t rows, int64_t K, int64_t row_begin,
                            int64_t row_count, float* out) {
   const int vec = kind == 0 ? 16 : 32;
+  const int fp4 = kind_is_fp4(kind, is_b);
   const int64_t kblocks = (K + vec - 1) / vec, k_atoms = (kblocks + 3) / 4;
   int64_t r, k;
   (void)rows;
@@ -129,14 +134,13 @@ static void expand_operand(int kind, const uint8_t* data, const uint8_t* sf, int
     for (k = 0; k < K; ++k) {
       const uint8_t sc = sf[bsg_oracle_sf_offset(row, k / vec, k_atoms)];
       float v, s;
-      if (kind == 0) {
+      if (fp4) {
         const uint8_t byte = data[row * (K / 2) + k / 2];
         v = kE2m1[(k & 1) ? (byte >> 4) : (byte & 0xF)];
-        s = bsg_oracle_decode(2, sc);
       } else {
         v = e4m3_value(data[row * K + k]);
-        s = bsg_oracle_decode(3, sc);
       }
+      s = bsg_oracle_decode(kind == 0 ? 2 : 3, sc);
       out[r * K + k] = v * s;
     }
   }
@@ -168,13 +172,13 @@ int bsg_oracle_gemm_rows_epi(int kind, int64_t M, int64_t N, int64_t K, const ui
   float* b = (float*)malloc(sizeof(float) * (size_t)(N * K));
   int64_t mb, nb;
   if (!a || !b) { free(a); free(b); return 1; }
-  expand_operand(kind, A, SFA, M, K, m_begin, m_count, a);
+  expand_operand(kind, 0, A, SFA, M, K, m_begin, m_count, a);
   {
     int64_t n0;
 #pragma omp parallel for schedule(static)
     for (n0 = 0; n0 < N; n0 += 64) {
       const int64_t cnt = N - n0 < 64 ? N - n0 : 64;
-      expand_operand(kind, B, SFB, N, K, n0, cnt, b + n0 * K);
+      expand_operand(kind, 1, B, SFB, N, K, n0, cnt, b + n0 * K);
     }
   }
   {

@@ -27,7 +27,8 @@ using SfCfg = cutlass::detail::Sm1xxBlockScaledConfig<Vec>;
 template <int Vec>
 using SfOutCfg = cutlass::detail::Sm1xxBlockScaledOutputConfig<Vec>;
 
-template <class ElemAB, class ElemSF, int Vec, class ElemD, bool GenSfd, int SfdVec = 16, class ElemSFD = cutlass::float_ue4m3_t>
+template <class ElemAB, class ElemSF, int Vec, class ElemD, bool GenSfd, int SfdVec = 16, class ElemSFD = cutlass::float_ue4m3_t,
+          class ElemB = ElemAB>
 void run_gemm(int M, int N, int K, const void* A, const void* B, const void* SFA, const void* SFB,
               const cutlass::bfloat16_t* C, float alpha, float beta, void* D, void* SFD, float st) {
   auto layout_A = make_layout(make_shape(M, K, 1), make_stride(int64_t(K), _1{}, int64_t(M) * K));
@@ -37,7 +38,7 @@ void run_gemm(int M, int N, int K, const void* A, const void* B, const void* SFA
   auto layout_SFB = SfCfg<Vec>::tile_atom_to_shape_SFB(make_shape(M, N, K, 1));
 
   Tensor tA = make_tensor(recast_ptr<ElemAB>(const_cast<void*>(A)), layout_A);
-  Tensor tB = make_tensor(recast_ptr<ElemAB>(const_cast<void*>(B)), layout_B);
+  Tensor tB = make_tensor(recast_ptr<ElemB>(const_cast<void*>(B)), layout_B);
   Tensor tSFA = make_tensor(reinterpret_cast<ElemSF*>(const_cast<void*>(SFA)), layout_SFA);
   Tensor tSFB = make_tensor(reinterpret_cast<ElemSF*>(const_cast<void*>(SFB)), layout_SFB);
   cutlass::reference::host::GettBlockScalingMainloopParams<float, decltype(tA), decltype(tSFA), decltype(tB), decltype(tSFB)>
@@ -146,7 +147,7 @@ int64_t bsg_ref_sf_size(int vec, int rows, int K) {
   return int64_t(size(filter_zeros(SfCfg<32>::tile_atom_to_shape_SFA(make_shape(rows, 1, K, 1)))));
 }
 
-// kind 0 NVFP4 / 1 MXFP8.  out_mode 0: D fp32, 1: D bf16, 2: D e2m1 + SFD ue4m3 per 16 (NVFP4 re-quantisation with norm
+// kind 0 NVFP4 / 1 MXFP8 / 2 MXFP4 / 3 mixed (A e4m3, B e2m1; out_mode 0 and 1 only for 2 and 3).  out_mode 0: D fp32, 1: D bf16, 2: D e2m1 + SFD ue4m3 per 16 (NVFP4 re-quantisation with norm
 // constant st), 3: D e4m3 + SFD ue8m0 per 32 (MXFP8 re-quantisation).
 // C is bf16 (may be null when beta == 0).  Returns 0 on success.
 int bsg_ref_gemm(int kind, int out_mode, int M, int N, int K, const void* A, const void* B, const void* SFA, const void* SFB,
@@ -168,6 +169,20 @@ int bsg_ref_gemm(int kind, int out_mode, int M, int N, int K, const void* A, con
     else if (out_mode == 2) run_gemm<E, S, 32, cutlass::float_e2m1_t, true>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, SFD, st);
     else if (out_mode == 3) run_gemm<E, S, 32, cutlass::float_e4m3_t, true, 32, cutlass::float_ue8m0_t>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, SFD, st);
     else return 1;
+  } else if (kind == 2 || kind == 3) {
+    // MXFP4 (e2m1 x e2m1) and the mixed form of the reference's example 72c (A e4m3, B e2m1); ue8m0 scale per 32.
+    using S = cutlass::float_ue8m0_t;
+    using F4 = cutlass::float_e2m1_t;
+    using F8 = cutlass::float_e4m3_t;
+    if (kind == 2) {
+      if (out_mode == 0) run_gemm<F4, S, 32, float, false>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, nullptr, 0.f);
+      else if (out_mode == 1) run_gemm<F4, S, 32, cutlass::bfloat16_t, false>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, nullptr, 0.f);
+      else return 1;
+    } else {
+      if (out_mode == 0) run_gemm<F8, S, 32, float, false, 16, cutlass::float_ue4m3_t, F4>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, nullptr, 0.f);
+      else if (out_mode == 1) run_gemm<F8, S, 32, cutlass::bfloat16_t, false, 16, cutlass::float_ue4m3_t, F4>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, nullptr, 0.f);
+      else return 1;
+    }
   } else {
     return 1;
   }

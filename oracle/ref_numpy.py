@@ -53,17 +53,17 @@ def sf_index(rows: int, kblocks: int) -> np.ndarray:
     return (r // 128) * (512 * k_atoms) + (kb // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + (kb % 4)
 
 
-def decode_operand(kind: int, packed: np.ndarray, sf_buf: np.ndarray, rows: int, K: int) -> np.ndarray:
-    """Packed operand + interleaved scale factors -> (rows, K) fp32 of value * scale."""
+def decode_operand(kind: int, packed: np.ndarray, sf_buf: np.ndarray, rows: int, K: int, is_b: bool = False) -> np.ndarray:
+    """Packed operand + interleaved scale factors -> (rows, K) fp32 of value * scale.
+    kind 0 NVFP4, 1 MXFP8, 2 MXFP4 (e2m1 with ue8m0 per 32), 3 mixed (A as kind 1, B as kind 2)."""
     packed = np.asarray(packed, dtype=np.uint8).reshape(rows, -1)
-    if kind == 0:
+    if kind == 0 or kind == 2 or (kind == 3 and is_b):
         vals = np.empty((rows, K), dtype=np.float32)
         vals[:, 0::2] = E2M1_TABLE[packed & 0xF]
         vals[:, 1::2] = E2M1_TABLE[packed >> 4]
-        vec, table = 16, UE4M3_TABLE
     else:
         vals = E4M3_TABLE[packed]
-        vec, table = 32, UE8M0_TABLE
+    vec, table = (16, UE4M3_TABLE) if kind == 0 else (32, UE8M0_TABLE)
     kblocks = -(-K // vec)
     sf = table[np.asarray(sf_buf, dtype=np.uint8).reshape(-1)[sf_index(rows, kblocks)]]
     return (vals * np.repeat(sf, vec, axis=1)[:, :K]).astype(np.float32)
@@ -83,7 +83,7 @@ def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
 def gemm_fp32(kind, A, SFA, B, SFB, M, N, K, C_bits=None, alpha=1.0, beta=0.0) -> np.ndarray:
     """alpha * (A.SFA)(B.SFB)^T + beta * C in fp32 (before the output conversion)."""
     a = decode_operand(kind, A, SFA, M, K)
-    b = decode_operand(kind, B, SFB, N, K)
+    b = decode_operand(kind, B, SFB, N, K, is_b=True)
     acc = (a @ b.T).astype(np.float32)
     out = np.float32(alpha) * acc
     if C_bits is not None and beta != 0.0:

@@ -47,19 +47,22 @@ def main() -> None:
         out[f"sf_size_{vec}_{rows}_{K}"] = np.array([ref.bsg_ref_sf_size(vec, rows, K)], dtype=np.int64)
     # --- GEMMs (fp32 and bf16 outputs) and the block-scaled output quantisation (NVFP4 and MXFP8)
     cases = [("nvfp4_a", 0, 96, 80, 128, 1.0, 0.5), ("nvfp4_b", 0, 130, 48, 320, 0.75, 0.0),
-             ("mxfp8_a", 1, 96, 80, 128, 1.0, 0.5), ("mxfp8_b", 1, 40, 136, 96, -1.25, 2.0)]
+             ("mxfp8_a", 1, 96, 80, 128, 1.0, 0.5), ("mxfp8_b", 1, 40, 136, 96, -1.25, 2.0),
+             ("mxfp4_a", 2, 72, 88, 256, 1.0, 0.5), ("mixed_a", 3, 100, 56, 384, 0.5, 1.0)]
     for name, kind, M, N, K, alpha, beta in cases:
         rng = np.random.default_rng(abs(hash(name)) % (2 ** 31))
         rng = np.random.default_rng(sum(ord(c) for c in name))
-        gen = G.nvfp4_operand if kind == 0 else G.mxfp8_operand
-        A, _, sfa = gen(M, K, rng)
-        B, _, sfb = gen(N, K, rng)
+        gen_a, gen_b = G.operand_generators(kind, False)
+        A, _, sfa = gen_a(M, K, rng)
+        B, _, sfb = gen_b(N, K, rng)
         Cb = G.bf16_normal((M, N), rng)
         out[f"{name}_A"], out[f"{name}_B"], out[f"{name}_SFA"], out[f"{name}_SFB"], out[f"{name}_C"] = A, B, sfa, sfb, Cb
         out[f"{name}_dims"] = np.array([kind, M, N, K], dtype=np.int64)
         out[f"{name}_ab"] = np.array([alpha, beta], dtype=np.float32)
         out[f"{name}_D32"] = oracle.ref_gemm(kind, 0, A, sfa, B, sfb, M, N, K, Cb, alpha, beta)
         out[f"{name}_Dbf16"] = oracle.ref_gemm(kind, 1, A, sfa, B, sfb, M, N, K, Cb, alpha, beta)
+        if kind >= 2:
+            continue          # the general epilogue below is pinned on the two main kinds
         # the reference's general epilogue: act(alpha * acc + bias + beta * C), bias per column or per row
         bias_col, bias_row = (rng.standard_normal(n).astype(np.float32) * 3 for n in (N, M))
         out[f"{name}_bias_col"], out[f"{name}_bias_row"] = bias_col, bias_row

@@ -17,12 +17,9 @@ def dev(x: np.ndarray) -> torch.Tensor:
 
 def make_operands(kind: int, M: int, N: int, K: int, seed: int, exact: bool):
     rng = np.random.default_rng(seed)
-    if kind == 0:
-        gen = G.exact_nvfp4_operand if exact else G.nvfp4_operand
-    else:
-        gen = G.exact_mxfp8_operand if exact else G.mxfp8_operand
-    A, _, sfa = gen(M, K, rng)
-    B, _, sfb = gen(N, K, rng)
+    gen_a, gen_b = G.operand_generators(kind, exact)
+    A, _, sfa = gen_a(M, K, rng)
+    B, _, sfb = gen_b(N, K, rng)
     return rng, A, sfa, B, sfb
 
 
@@ -90,15 +87,12 @@ def run_grouped(kind, sizes, N, K, seed, exact=True, alpha=1.0, beta=0.0, tile_n
                 per_group_scalars=False, scheduler=0):
     """Ragged grouped GEMM through the C ABI and the per-group oracle.  -> (got bits, want bits)."""
     rng = np.random.default_rng(seed)
-    if kind == 0:
-        gen = G.exact_nvfp4_operand if exact else G.nvfp4_operand
-    else:
-        gen = G.exact_mxfp8_operand if exact else G.mxfp8_operand
+    gen, gen_b = G.operand_generators(kind, exact)
     total = int(np.sum(sizes))
     As, sfas, Bs, sfbs = [], [], [], []
     for m in sizes:
-        A, _, sfa = gen(int(m), K, rng) if m > 0 else (np.zeros((0, K // 2 if kind == 0 else K), np.uint8), None, np.zeros(0, np.uint8))
-        B, _, sfb = gen(N, K, rng)
+        A, _, sfa = gen(int(m), K, rng) if m > 0 else (np.zeros((0, K // 2 if kind in (0, 2) else K), np.uint8), None, np.zeros(0, np.uint8))
+        B, _, sfb = gen_b(N, K, rng)
         As.append(A); sfas.append(sfa); Bs.append(B); sfbs.append(sfb)
     Cb = G.bf16_normal((total, N), rng) if beta != 0 else None
     A_all = np.concatenate(As, axis=0)

@@ -78,7 +78,8 @@ def test_get_operators_orders_and_filters():
     assert len(only) == 1 and only[0].metadata.tile_shape == (128, 128, 256)
     assert all(o.metadata.kind == L.KIND_MXFP8 for o in ops.get_operators(mxfp8_args()))
     assert ops.get_operators(nvfp4_args(), target_sm="90a") == []
-    assert len(ops.all_operators()) == 16 and len({o.metadata.operator_name for o in ops.all_operators()}) == 16
+    # 2 kinds x 4 tile shapes + 2 kinds (MXFP4, MXFP8 x MXFP4) x 2 two-CTA tile shapes, each dense and grouped
+    assert len(ops.all_operators()) == 24 and len({o.metadata.operator_name for o in ops.all_operators()}) == 24
 
 
 def test_supports_rejections():
@@ -260,3 +261,48 @@ def test_get_operators_takes_the_reference_parameters():
     assert len(ops.get_operators(args, providers=[ops.NativeProvider])) == len(everything) > 0
     assert ops.get_operators(args, providers=[]) == []
     assert ops.get_operators(args, target_sm="90a") == []
+
+
+def test_mxfp4_and_mixed_pairs_are_discovered():
+    """MXFP4 needs the packed fp4 dtype (uint8 with 32-wide blocks means e4m3 codes); MXFP8 A with MXFP4 B is the mixed kind."""
+    fp4 = getattr(torch, "float4_e2m1fn_x2", None)
+    if fp4 is None:
+        pytest.skip("this torch has no packed fp4 dtype")
+    M, N, K = 128, 256, 256
+    sa = torch.zeros(ops.ScaledOperand.numel_scale((M, K), M32, SW), dtype=torch.uint8)
+    sb = torch.zeros(ops.ScaledOperand.numel_scale((N, K), M32, SW), dtype=torch.uint8)
+    a4 = ops.ScaledOperand(torch.zeros((M, K // 2), dtype=torch.uint8).view(fp4), sa, M32, SW)
+    a8 = ops.ScaledOperand(torch.zeros((M, K), dtype=torch.uint8), sa, M32, SW)
+    b4 = ops.ScaledOperand(torch.zeros((N, K // 2), dtype=torch.uint8).view(fp4).t(), sb, M32, SW)
+    out = torch.zeros((M, N), dtype=torch.bfloat16)
+    found = ops.get_operators(ops.GemmArguments(a4, b4, out, torch.float32))
+    assert found and all(o.metadata.kind == L.KIND_MXFP4 and o.metadata.cta_group == 2 for o in found)
+    found = ops.get_operators(ops.GemmArguments(a8, b4, out, torch.float32))
+    assert found and all(o.metadata.kind == L.KIND_MXFP8_MXFP4 for o in found)
+    # the other way round (MXFP4 A with MXFP8 B) has no kernel
+    b8 = ops.ScaledOperand(torch.zeros((N, K), dtype=torch.uint8).t(), sb, M32, SW)
+    assert ops.get_operators(ops.GemmArguments(a4, b8, out, torch.float32)) == []
+
+
+def test_row_pitch_and_batch_stride_reach_the_abi():
+    """A slice of a larger buffer (row pitch > K, batch entries further apart than one matrix) is accepted and its
+    strides arrive in bsg_gemm_args in logical elements."""
+    Lb, M, N, K = 2, 128, 128, 256
+    big = torch.zeros((Lb, M + 8, K // 2 + 32), dtype=torch.uint8)
+    A = ops.ScaledOperand(big[:, :M, :K // 2], torch.zeros(ops.ScaledOperand.numel_scale((Lb, M, K), M16, SW), dtype=torch.uint8), M16, SW)
+    B = ops.ScaledOperand(torch.zeros((Lb, N, K // 2), dtype=torch.uint8).transpose(1, 2),
+                          torch.zeros(ops.ScaledOperand.numel_scale((Lb, N, K), M16, SW), dtype=torch.uint8), M16, SW)
+    outbuf = torch.zeros((Lb, M, N + 16), dtype=torch.bfloat16)
+    args = ops.GemmArguments(A, B, outbuf[:, :, :N], torch.float32)
+    op = ops.get_operators(args)[0]
+    abi = op.build_args(args)
+    assert (abi.lda, abi.batch_stride_A) == ((K // 2 + 32) * 2, (M + 8) * (K // 2 + 32) * 2)
+    assert (abi.ldb, abi.batch_stride_B) == (K, N * K)
+    assert (abi.ldd, abi.batch_stride_D) == (N + 16, M * (N + 16))
+    # a row pitch that breaks the 16-byte alignment is refused
+    odd = torch.zeros((M, K // 2 + 8), dtype=torch.uint8)[:, :K // 2]
+    bad = ops.GemmArguments(ops.ScaledOperand(odd, torch.zeros(ops.ScaledOperand.numel_scale((M, K), M16, SW), dtype=torch.uint8), M16, SW),
+                            ops.ScaledOperand(torch.zeros((N, K // 2), dtype=torch.uint8).t(),
+                                              torch.zeros(ops.ScaledOperand.numel_scale((N, K), M16, SW), dtype=torch.uint8), M16, SW),
+                            torch.zeros((M, N), dtype=torch.bfloat16), torch.float32)
+    assert ops.get_operators(bad) == []

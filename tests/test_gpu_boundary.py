@@ -202,3 +202,26 @@ def test_dynamic_scheduler_repeated_launches_and_pdl(cuda_lib):
     torch.cuda.synchronize()
     for i, D in enumerate(outs):
         assert np.array_equal(D.cpu().numpy().view(np.uint16), want), f"launch {i}"
+
+
+@pytest.mark.parametrize("kind", [2, 3])
+@pytest.mark.parametrize("M,N,K,tile_n,exact", [(256, 512, 512, 0, True), (384, 640, 1024, 0, True), (512, 384, 256, 128, True),
+                                               (1024, 1024, 2048, 0, False)])
+def test_mxfp4_and_mixed_operands(cuda_lib, kind, M, N, K, tile_n, exact):
+    """MXFP4 (e2m1 with ue8m0 scale per 32) and the mixed MXFP8 x MXFP4 form against the oracle: bit for bit on
+    exact-arithmetic operands, within the bf16 tolerance on realistic ones (with beta * C)."""
+    rng, A, sfa, B, sfb = make_operands(kind, M, N, K, seed=70 + kind, exact=exact)
+    Cb = G.bf16_normal((M, N), rng)
+    got = run_dense(kind, M, N, K, A, sfa, B, sfb, Cb, 1.0, 0.5, tile_n=tile_n)
+    want = oracle_bf16(kind, M, N, K, A, sfa, B, sfb, Cb, 1.0, 0.5)
+    if exact:
+        assert np.array_equal(got, want)
+    else:
+        from gpu_utils import assert_close_bf16
+        assert_close_bf16(got, want)
+
+
+@pytest.mark.parametrize("kind", [2, 3])
+def test_mxfp4_and_mixed_grouped(cuda_lib, kind):
+    got, want = run_grouped(kind, [300, 0, 129, 512], 384, 512, seed=75 + kind)
+    assert np.array_equal(got, want)

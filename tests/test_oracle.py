@@ -10,7 +10,7 @@ from cutlass_b200 import formats as F
 from cutlass_b200 import generators as G
 from oracle import ref_numpy as R
 
-GEMM_CASES = ["nvfp4_a", "nvfp4_b", "mxfp8_a", "mxfp8_b"]
+GEMM_CASES = ["nvfp4_a", "nvfp4_b", "mxfp8_a", "mxfp8_b", "mxfp4_a", "mixed_a"]
 
 
 def _case(golden, name):
@@ -104,12 +104,13 @@ ref_missing = oracle.load_ref() is None
 
 
 @pytest.mark.skipif(ref_missing, reason="compiled reference driver (oracle/_ref) not present")
-@pytest.mark.parametrize("kind,M,N,K,alpha,beta", [(0, 200, 264, 416, 1.5, 0.5), (1, 129, 72, 224, 1.0, 0.0), (0, 64, 64, 1024, 1.0, 0.5)])
+@pytest.mark.parametrize("kind,M,N,K,alpha,beta", [(0, 200, 264, 416, 1.5, 0.5), (1, 129, 72, 224, 1.0, 0.0), (0, 64, 64, 1024, 1.0, 0.5),
+                                                   (2, 150, 200, 320, 1.25, 0.5), (3, 129, 136, 256, 1.0, -0.5)])
 def test_c_oracle_equals_compiled_reference(kind, M, N, K, alpha, beta):
     rng = np.random.default_rng(M * 7 + N)
-    gen = G.nvfp4_operand if kind == 0 else G.mxfp8_operand
-    A, _, sfa = gen(M, K, rng)
-    B, _, sfb = gen(N, K, rng)
+    gen_a, gen_b = G.operand_generators(kind, False)
+    A, _, sfa = gen_a(M, K, rng)
+    B, _, sfb = gen_b(N, K, rng)
     Cb = G.bf16_normal((M, N), rng)
     o = oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K, Cb, alpha, beta)
     r = oracle.ref_gemm(kind, 0, A, sfa, B, sfb, M, N, K, Cb, alpha, beta)
