@@ -192,6 +192,13 @@ struct Problem {
   const uint8_t* tp_peer_sfa[8];
   uint32_t* tp_peer_sync[8];
   int32_t* grid_ctas_out;     // receives the number of CTAs launched
+  // GEMM + reduce-scatter (RS kernel variant)
+  bool rs;
+  int32_t rs_world, rs_rank, rs_slice_rows, rs_parity;
+  uint32_t rs_epoch;
+  const void* rs_recv;        // this rank's receive buffers
+  void* rs_recv_left;         // receive buffers of rank - 1 (peer memory)
+  uint32_t *rs_flags, *rs_flags_left, *rs_sync, *rs_sync_left, *rs_sync_right;
 };
 
 struct Plan {
@@ -254,7 +261,7 @@ int32_t validate(const Problem& q, Plan* plan) {
       return fail(BSG_ERR_NOT_SUPPORTED, "%scluster shape %d x %d is not available: this configuration runs clusters of %d x 1",
                   i ? "fallback " : "", q.cluster[i], q.cluster[i + 1], cg);
   }
-  if (q.kind >= BSG_KIND_MXFP4 && (cg != 2 || q.scheduler != BSG_SCHED_STATIC || q.tp))
+  if (q.kind >= BSG_KIND_MXFP4 && (cg != 2 || q.scheduler != BSG_SCHED_STATIC || q.tp || q.rs))
     return fail(BSG_ERR_NOT_SUPPORTED, "MXFP4 and mixed MXFP8 x MXFP4 operands run with cta_group 2 and the static scheduler only");
   if (q.kind == BSG_KIND_MXFP8_MXFP4 && (reinterpret_cast<uintptr_t>(q.B) & 31u) != 0)
     return fail(BSG_ERR_MISALIGNED_OPERAND, "B of the mixed kind must be 32-byte aligned");
@@ -280,14 +287,14 @@ struct KernelSetup {
   int max_clusters[64] = {};
 };
 
-template <int KIND, int CG, int BN, bool TP, bool DYN>
+template <int KIND, int CG, int BN, bool TP, bool DYN, bool RS>
 int32_t kernel_setup(int dev, int* max_clusters) {
   using Cf = bsg::Cfg<KIND, CG, BN, TP>;
   static KernelSetup ks;
   if (dev < 0 || dev >= 64) return fail(BSG_ERR_NOT_SUPPORTED, "device ordinal %d is outside [0, 64)", dev);
   std::lock_guard<std::mutex> lock(ks.mu);
   if (!ks.done[dev]) {
-    auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN, TP, DYN>;
+    auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN, TP, DYN, RS>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::kSmemBytes);
     if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg;
@@ -310,7 +317,7 @@ int32_t kernel_setup(int dev, int* max_clusters) {
   return BSG_OK;
 }
 
-template <int KIND, int CG, int BN, bool TP = false, bool DYN = false>
+template <int KIND, int CG, int BN, bool TP = false, bool DYN = false, bool RS = false>
 int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_t stream, int sm_count, int dev, bool dry) {
   using Cf = bsg::Cfg<KIND, CG, BN, TP>;
   if (dry) return BSG_OK;
@@ -326,20 +333,27 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   const int64_t lda_bytes = a_fp4 ? q.lda / 2 : q.lda, ldb_bytes = b_fp4 ? q.ldb / 2 : q.ldb;
   const int64_t bsa_bytes = a_fp4 ? q.bs_a / 2 : q.bs_a, bsb_bytes = b_fp4 ? q.bs_b / 2 : q.bs_b;
 
-  CUtensorMap tmA, tmB, tmSFA, tmSFB, tmD;
+  CUtensorMap tmA, tmB, tmSFA, tmSFB, tmD, tmDpeer;
   int32_t rc;
   // Rows of the A and D maps: one batch entry (batched form), all groups (grouped), or the two gathered buffers of
   // the tensor-parallel GEMM, which lie back to back.
   const uint64_t map_rows = batched ? uint64_t(q.rows_per_group) : uint64_t(TP ? 2 * q.total_rows : q.total_rows);
   const uint64_t map_batches = batched ? uint64_t(q.num_groups) : 1u;
-  const uint64_t d_rows = batched ? uint64_t(q.rows_per_group) : uint64_t(q.total_rows);
+  // Reduce-scatter: D is this rank's slice of the result; the other stages store into rank - 1's receive buffers
+  // (two halves of world - 1 slices each, N columns wide).
+  const uint64_t d_rows = RS ? uint64_t(q.rs_slice_rows) : batched ? uint64_t(q.rows_per_group) : uint64_t(q.total_rows);
   if ((rc = make_out_map(&tmD, q.D, q.out_kind, uint64_t(q.N), d_rows, map_batches, uint64_t(q.ldd),
                          uint64_t(batched && q.num_groups > 1 ? q.bs_d : d_rows * q.ldd))) != BSG_OK) return rc;
+  tmDpeer = tmD;
+  if (RS && q.rs_world > 1) {
+    const uint64_t peer_rows = 2ull * uint64_t(q.rs_world - 1) * uint64_t(q.rs_slice_rows);
+    if ((rc = make_out_map(&tmDpeer, q.rs_recv_left, BSG_OUT_BF16, uint64_t(q.N), peer_rows, 1, uint64_t(q.N), peer_rows * uint64_t(q.N))) != BSG_OK) return rc;
+  }
   if ((rc = make_operand_map(&tmA, q.A, uint64_t(ka_bytes), map_rows, map_batches, uint64_t(lda_bytes),
                              uint64_t(batched && q.num_groups > 1 ? bsa_bytes : int64_t(map_rows) * lda_bytes), Cf::kCtaM)) != BSG_OK) return rc;
   if (KIND == bsg::kKindMxfp8Mxfp4) {
-    // B is packed e2m1 in global memory; the TMA engine expands it to one value per byte (16 values -> 16 bytes),
-    // which is what kind::mxf8f6f4 reads.  Extents and the box are counted in elements, strides in bytes.
+    // B is packed e2m1 in global memory; the TMA engine spreads it into the form kind::mxf8f6f4 reads (16 values in
+    // 8 bytes followed by 8 bytes of padding).  Extents and the box are counted in elements, strides in bytes.
     rc = g_maps.get(make_key(q.B, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                              uint64_t(q.K), uint64_t(q.N), uint64_t(b_groups), uint64_t(ldb_bytes),
                              uint64_t(b_groups > 1 ? bsb_bytes : q.N * ldb_bytes), 128, Cf::kBRowsCta, 1), &tmB);
@@ -385,6 +399,25 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   p.flag_target = q.flag_target;
   p.tile_m_rotate = q.tile_m_rotate;
   p.split_tail = 1;
+  if (RS) {
+    const int32_t tiles_per_slice = q.rs_slice_rows / (128 * CG);
+    p.rs_world = q.rs_world;
+    p.rs_tiles_per_slice = tiles_per_slice;
+    p.rs_slice_rows = q.rs_slice_rows;
+    p.rs_parity_rows = q.rs_parity ? (q.rs_world - 1) * q.rs_slice_rows : 0;
+    p.rs_flag_target = uint32_t(4 * CG) * ((q.rs_epoch + 1u) >> 1);
+    p.rs_ready_target = q.rs_epoch - 1u;
+    p.rs_epoch = q.rs_epoch;
+    p.rs_recv = static_cast<const __nv_bfloat16*>(q.rs_recv);
+    p.rs_flags = q.rs_flags; p.rs_flags_left = q.rs_flags_left;
+    p.rs_sync = q.rs_sync; p.rs_sync_left = q.rs_sync_left; p.rs_sync_right = q.rs_sync_right;
+    p.split_tail = 0;
+    // the walk starts at slice rank + 1 and ends at the rank's own slice; a band of the raster never straddles slices
+    p.tile_m_rotate = ((q.rs_rank + 1) % q.rs_world) * tiles_per_slice;
+    int32_t band = p.raster_band;
+    while (tiles_per_slice % band != 0) band >>= 1;
+    p.raster_band = band < 1 ? 1 : band;
+  }
   if (TP) {
     p.tp_world = q.tp_world; p.tp_rank = q.tp_rank; p.tp_rows_per_shard = q.tp_rows_per_shard; p.tp_ksplit = q.tp_ksplit; p.tp_push_in_kernel = q.tp_push_in_kernel;
     p.tp_epoch = q.tp_epoch;
@@ -399,8 +432,8 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
 #endif
 
   int max_clusters = 0;
-  if ((rc = kernel_setup<KIND, CG, BN, TP, DYN>(dev, &max_clusters)) != BSG_OK) return rc;
-  auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN, TP, DYN>;
+  if ((rc = kernel_setup<KIND, CG, BN, TP, DYN, RS>(dev, &max_clusters)) != BSG_OK) return rc;
+  auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN, TP, DYN, RS>;
 
   int64_t clusters = sm_count / CG;
   if (max_clusters > 0 && clusters > max_clusters) clusters = max_clusters;
@@ -434,13 +467,17 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.numAttrs = 2;
   }
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmSFA, tmSFB, tmD, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmSFA, tmSFB, tmD, tmDpeer, p);
   if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(e));
   return BSG_OK;
 }
 
 template <int KIND>
 int32_t dispatch_shape(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_t s, int sm, int dev, bool dry) {
+  if (q.rs) {
+    if (plan.cta_group != 2 || plan.tile_n != 256) return fail(BSG_ERR_NOT_SUPPORTED, "the reduce-scatter GEMM runs 256 x 256 tiles (cta_group 2)");
+    return launch<KIND, 2, 256, false, false, true>(q, plan, status, s, sm, dev, dry);
+  }
   if (q.tp) {
     if (plan.cta_group != 2) return fail(BSG_ERR_NOT_SUPPORTED, "the tensor-parallel GEMM needs cta_group 2");
     return plan.tile_n == 256 ? launch<KIND, 2, 256, true>(q, plan, status, s, sm, dev, dry) : launch<KIND, 2, 128, true>(q, plan, status, s, sm, dev, dry);
@@ -611,6 +648,19 @@ struct bsg_tp_comm {
   cudaStream_t side;       // set-up work; copy-engine mode: first of the transfer streams
   cudaStream_t lanes[4];   // copy-engine mode: parallel transfer streams (lanes[0] == side)
   cudaEvent_t ev_start, ev_done, ev_lane[4];
+};
+
+// Per-rank state of the GEMM + reduce-scatter: one device allocation with the receive buffers (two halves used by
+// alternate calls, world - 1 slices of M / world x N bf16 each), the arrival counters of their tiles, and the sync words.
+struct bsg_rs_comm {
+  int32_t rank, world;
+  int64_t M, N, slice_rows, tiles_per_slice, tiles_n;
+  size_t recv_off, flags_off, sync_off, total_bytes;
+  uint8_t* base;
+  uint8_t* peer_base[8];
+  bool opened[8];
+  bool connected;
+  uint32_t epoch;
 };
 
 extern "C" {
@@ -925,6 +975,105 @@ int32_t bsg_tp_gemm_run(bsg_tp_comm* c, const bsg_gemm_args* args, void* workspa
     if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "tensor-parallel peer transfers: %s", cudaGetErrorString(e));
   }
   c->epoch += 1;
+  return BSG_OK;
+}
+
+int32_t bsg_rs_create(int32_t rank, int32_t world, int64_t M, int64_t N, bsg_rs_comm** out, void* ipc_handle_out) {
+  if (!out || !ipc_handle_out) return fail(BSG_ERR_INVALID_PROBLEM, "null argument");
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(BSG_ERR_INVALID_PROBLEM, "rank %d / world %d outside [0, 8]", rank, world);
+  if (M < 1 || N < 8 || M % (int64_t(world) * 256) != 0) return fail(BSG_ERR_INVALID_PROBLEM, "M=%lld must be a multiple of 256 * world", (long long)M);
+  if (N % 8 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "N=%lld must be a multiple of 8", (long long)N);
+  bsg_rs_comm* c = new (std::nothrow) bsg_rs_comm();
+  if (!c) return fail(BSG_ERR_INTERNAL, "out of host memory");
+  memset(c, 0, sizeof(*c));
+  c->rank = rank; c->world = world; c->M = M; c->N = N;
+  c->slice_rows = M / world;
+  c->tiles_per_slice = c->slice_rows / 256;
+  c->tiles_n = (N + 255) / 256;
+  auto up = [](size_t v) { return (v + 1023) & ~size_t(1023); };
+  const size_t stages = size_t(world > 1 ? world - 1 : 1);
+  const size_t recv_bytes = 2 * stages * size_t(c->slice_rows) * size_t(N) * 2;
+  const size_t flag_bytes = 2 * stages * size_t(c->tiles_per_slice) * size_t(c->tiles_n) * 4;
+  c->recv_off = 0;
+  c->flags_off = up(recv_bytes);
+  c->sync_off = c->flags_off + up(flag_bytes);
+  c->total_bytes = c->sync_off + 1024;
+  cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->base), c->total_bytes);
+  if (e != cudaSuccess) { delete c; return fail(BSG_ERR_CUDA, "cudaMalloc(%zu): %s", c->total_bytes, cudaGetErrorString(e)); }
+  e = cudaMemset(c->base + c->flags_off, 0, c->total_bytes - c->flags_off);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, c->base);
+  if (e != cudaSuccess) { cudaFree(c->base); delete c; return fail(BSG_ERR_CUDA, "reduce-scatter buffer set-up: %s", cudaGetErrorString(e)); }
+  memcpy(ipc_handle_out, &h, 64);
+  c->peer_base[rank] = c->base;
+  c->connected = world == 1;
+  *out = c;
+  return BSG_OK;
+}
+
+int32_t bsg_rs_connect(bsg_rs_comm* c, const void* all_handles) {
+  if (!c || !all_handles) return fail(BSG_ERR_INVALID_PROBLEM, "null argument");
+  // only the two ring neighbours are mapped
+  const int nb[2] = {(c->rank + c->world - 1) % c->world, (c->rank + 1) % c->world};
+  for (int i = 0; i < 2; ++i) {
+    const int q = nb[i];
+    if (q == c->rank || c->opened[q]) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, static_cast<const uint8_t*>(all_handles) + size_t(q) * 64, 64);
+    void* ptr = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "cudaIpcOpenMemHandle(rank %d): %s", q, cudaGetErrorString(e));
+    c->peer_base[q] = static_cast<uint8_t*>(ptr);
+    c->opened[q] = true;
+  }
+  c->connected = true;
+  return BSG_OK;
+}
+
+int32_t bsg_rs_gemm_run(bsg_rs_comm* c, const bsg_gemm_args* args, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  if (!c || !args) return fail(BSG_ERR_INVALID_PROBLEM, "null argument");
+  if (!c->connected) return fail(BSG_ERR_INVALID_PROBLEM, "bsg_rs_connect has not been called");
+  if (args->M != c->M || args->N != c->N) return fail(BSG_ERR_INVALID_PROBLEM, "M and N must match the communicator");
+  if (args->batch > 1) return fail(BSG_ERR_NOT_SUPPORTED, "the reduce-scatter GEMM is not batched");
+  if (args->out_kind != BSG_OUT_BF16 || args->C || args->beta != 0.0f || args->beta_ptr || args->bias_mode != BSG_BIAS_NONE ||
+      args->activation != BSG_ACT_IDENTITY)
+    return fail(BSG_ERR_NOT_SUPPORTED, "the reduce-scatter GEMM computes bf16 D = alpha * A B^T only (partial sums travel as bf16)");
+  if (args->kind != BSG_KIND_NVFP4 && args->kind != BSG_KIND_MXFP8) return fail(BSG_ERR_NOT_SUPPORTED, "the reduce-scatter GEMM takes NVFP4 or MXFP8 operands");
+  bsg_gemm_args local = *args;
+  local.batch = 1;
+  local.cta_group = 2;
+  local.tile_n = 256;
+  local.scheduler = BSG_SCHED_STATIC;
+  local.use_pdl = 0;
+  Problem q = from_dense(&local);
+  // D holds this rank's slice only; the checks of validate() that look at D's extent use the slice pitch
+  q.rs = true;
+  q.rs_world = c->world; q.rs_rank = c->rank; q.rs_slice_rows = int32_t(c->slice_rows);
+  q.rs_epoch = c->epoch + 1;
+  q.rs_parity = int32_t(q.rs_epoch & 1u);
+  const int left = (c->rank + c->world - 1) % c->world, right = (c->rank + 1) % c->world;
+  q.rs_recv = c->base + c->recv_off;
+  q.rs_recv_left = c->peer_base[left] + c->recv_off;
+  q.rs_flags = reinterpret_cast<uint32_t*>(c->base + c->flags_off);
+  q.rs_flags_left = reinterpret_cast<uint32_t*>(c->peer_base[left] + c->flags_off);
+  q.rs_sync = reinterpret_cast<uint32_t*>(c->base + c->sync_off);
+  q.rs_sync_left = reinterpret_cast<uint32_t*>(c->peer_base[left] + c->sync_off);
+  q.rs_sync_right = reinterpret_cast<uint32_t*>(c->peer_base[right] + c->sync_off);
+  int32_t rc = run_problem(q, workspace, workspace_bytes, cuda_stream);
+  if (rc != BSG_OK) return rc;
+  c->epoch += 1;
+  return BSG_OK;
+}
+
+int32_t bsg_rs_destroy(bsg_rs_comm* c) {
+  if (!c) return BSG_OK;
+  cudaDeviceSynchronize();
+  for (int q = 0; q < c->world; ++q) {
+    if (c->opened[q]) cudaIpcCloseMemHandle(c->peer_base[q]);
+  }
+  if (c->base) cudaFree(c->base);
+  delete c;
   return BSG_OK;
 }
 

@@ -41,7 +41,7 @@ constexpr int kMaxGroups = 256;
 constexpr int kKindNvfp4 = 0;        // e2m1 x e2m1, ue4m3 scale per 16
 constexpr int kKindMxfp8 = 1;        // e4m3 x e4m3, ue8m0 scale per 32
 constexpr int kKindMxfp4 = 2;        // e2m1 x e2m1, ue8m0 scale per 32
-constexpr int kKindMxfp8Mxfp4 = 3;   // A e4m3, B e2m1 (expanded to one value per byte on its way into shared memory), ue8m0 per 32
+constexpr int kKindMxfp8Mxfp4 = 3;   // A e4m3, B e2m1 (spread by the TMA engine into the 16-byte groups kind::mxf8f6f4 reads), ue8m0 per 32
 __host__ __device__ constexpr bool kind_packs_fp4(int kind) { return kind == kKindNvfp4 || kind == kKindMxfp4; }   // A and B: two values per byte
 constexpr int kOutBf16 = 0;
 constexpr int kOutNvfp4 = 1;
@@ -107,11 +107,30 @@ struct GemmParams {
   int32_t tp_remote_row_offset;   // rows between the buffer this call gathers into and buffer 0 (0 or M)
   int64_t tp_row_bytes;       // bytes of one row of A
   int64_t tp_sfa_rowatom_bytes;   // bytes of one 128-row atom row of SFA (512 * k_atoms)
+  // GEMM + reduce-scatter (kernel template RS == true): every rank multiplies its K shard for all M x N; the partial
+  // sums of a slice of rows travel around the ring of ranks, one hop per stage, each hop adding its own partial, and
+  // end at the rank that owns the slice.  The walk over the M tiles starts at slice rank + 1 (tile_m_rotate), so
+  // stage s = walk position / rs_tiles_per_slice.  Stage 0 adds nothing; stages >= 1 add the partial received from
+  // rank + 1; stages < world - 1 store into the receive buffer of rank - 1; the last stage stores the result.
+  int32_t rs_world;
+  int32_t rs_tiles_per_slice;     // M tiles per slice (rs_slice_rows / tile M)
+  int32_t rs_slice_rows;
+  int32_t rs_parity_rows;         // first row, in the receive buffers, of the half that this call uses (calls alternate)
+  uint32_t rs_flag_target;        // arrivals a received tile must show: 4 * CG per call that used this half so far
+  uint32_t rs_ready_target;       // the left neighbour's receive half is free once it has launched this call number
+  uint32_t rs_epoch;
+  const __nv_bfloat16* rs_recv;   // this rank's receive buffers: [2 halves][world - 1 stages][rs_slice_rows][N] bf16
+  uint32_t* rs_flags;             // arrival counters of the tiles in rs_recv: [2][world - 1][rs_tiles_per_slice][tiles_n]
+  uint32_t* rs_flags_left;        // the same array of rank - 1
+  uint32_t* rs_sync;              // this rank's sync words: [0] = call number the right neighbour ... see kRsSync*
+  uint32_t* rs_sync_left;         // sync words of rank - 1
+  uint32_t* rs_sync_right;        // sync words of rank + 1
   const uint8_t* tp_peer_a[8];    // gathered A buffer of every rank that this call fills (own entry = source: local buffer 0)
   const uint8_t* tp_peer_sfa[8];
   uint32_t* tp_peer_sync[8];      // sync words of every rank: [0,8) "rank q has launched call n", [32, ...) row-block counters
 };
 
+constexpr int kRsSyncLaunched = 0;   // word 0 of a rank's reduce-scatter sync words: the call number its LEFT neighbour has launched
 constexpr int kTpSyncReady = 0;
 constexpr int kTpSyncFlags = 32;
 constexpr uint32_t kStTimeoutPeer = 64u;      // tensor parallel: a peer never published / finished
@@ -134,6 +153,9 @@ struct Cfg {
   static constexpr int kSfaBytes = kKAtoms * 512;
   static constexpr int kSfbBytes = (BN / 128) * kKAtoms * 512;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
+  // Bytes a stage's loads report to its barrier.  The mixed kind's B arrives as packed e2m1 that the TMA engine spreads
+  // over twice the space (16 values in 8 bytes, then 8 bytes of padding): the transaction counts the 8, not the 16.
+  static constexpr int kStageTxBytes = kStageBytes - (KIND == kKindMxfp8Mxfp4 ? kBBytes / 2 : 0);
 #ifdef BSG_PROFILE
   static constexpr int kDbgBytes = (512 + 1024 + 256) * 4;   // instrumented build: in-kernel timeline stamps
 #else
@@ -199,6 +221,7 @@ struct TileInfo {
   int32_t group_atom0;
   int32_t map_row0;   // row coordinate of the tile's first row in the A / D tensor maps
   int32_t map_l;      // third coordinate there (batch entry; 0 when rows run over all groups)
+  int32_t tm_walk;    // position of the tile row in the walk over M (before the rotation of the starting row)
 };
 
 __device__ __forceinline__ TileInfo decode_tile(const Ctl* ctl, const GemmParams& p, int32_t t, int32_t tile_m) {
@@ -219,6 +242,7 @@ __device__ __forceinline__ TileInfo decode_tile(const Ctl* ctl, const GemmParams
   const int32_t bh = min(band, tiles_m - b * band);
   int32_t tm = b * band + rem % bh;
   ti.tn = rem / bh;
+  ti.tm_walk = tm;
   if (p.tile_m_rotate != 0) tm = (tm + p.tile_m_rotate) % tiles_m;
   ti.tm = tm;
   ti.group_row0 = ctl->row0[lo];
@@ -442,11 +466,11 @@ __device__ __forceinline__ int32_t sched_consume(Ctl* ctl, uint32_t k, uint32_t&
   return dead ? -1 : w;
 }
 
-template <int KIND, int CG, int BN, bool TP = false, bool DYN = false>
+template <int KIND, int CG, int BN, bool TP = false, bool DYN = false, bool RS = false>
 __global__ void __launch_bounds__(TP ? 224 : 192, 1)
 bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
-                const __grid_constant__ CUtensorMap tmD, const GemmParams p) {
+                const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmDpeer, const GemmParams p) {
   using C = Cfg<KIND, CG, BN, TP>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -491,12 +515,21 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     ptx::prefetch_tmap(&tmSFA);
     ptx::prefetch_tmap(&tmSFB);
     ptx::prefetch_tmap(&tmD);
+    if constexpr (RS) ptx::prefetch_tmap(&tmDpeer);
   }
   // Programmatic dependent launch: everything above overlaps the tail of the previous kernel on the stream; from
   // here on global memory is touched, which needs that kernel complete.  The kernel after this one may start its
   // own set-up as soon as SMs free up (it waits at the same place).  Both are no-ops in an ordinary launch.
   ptx::grid_dependency_wait();
   ptx::grid_launch_dependents();
+  if constexpr (RS) {
+    // Launching this call means the previous one has finished reading its receive buffers: tell rank + 1, which
+    // stores into them, that the half of the call after this one may be overwritten.
+    if (blockIdx.x == 0 && threadIdx.x == 0 && p.rs_world > 1) {
+      __threadfence_system();
+      st_release_sys_u32(p.rs_sync_right + kRsSyncLaunched, p.rs_epoch);
+    }
+  }
   // Group table: end rows first (parallel), then a serial prefix by one thread.
   for (int g = threadIdx.x; g < p.num_groups; g += blockDim.x) {
     ctl->rows[g] = p.offsets ? p.offsets[g] : (g + 1) * p.rows_per_group;   // holds END rows for now
@@ -534,7 +567,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   // Tail of the walk: with T tiles on G clusters the last wave holds T mod G tiles; if that is at most G / 2 its tiles
   // are split (see split_tail), which shortens the last wave to half a tile time.
   int32_t split_from = total_tiles;
-  if (BN == 256 && !DYN && p.split_tail != 0 && total_tiles > num_clusters) {
+  if (BN == 256 && !DYN && !RS && p.split_tail != 0 && total_tiles > num_clusters) {
     const int32_t tail = total_tiles % num_clusters;
     if (tail > 0 && 2 * tail <= num_clusters) split_from = total_tiles - tail;
   }
@@ -625,7 +658,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // After a timeout nothing more is issued: free-running loads would overrun the barriers' byte counts.
         if (elected && !dead) {
           const uint32_t full_local = full0 + stage * 8;
-          if (is_leader) ptx::mbar_arrive_expect_tx(full_local, uint32_t(C::kStageBytes) * CG);
+          if (is_leader) ptx::mbar_arrive_expect_tx(full_local, uint32_t(C::kStageTxBytes) * CG);
           const uint32_t bar = full0_leader + stage * 8;
           ptx::tma_load_3d<CG>(sA0 + stage * C::kABytes, &tmA, bar, kt * C::kRowBytes, a_row, a_l);
           ptx::tma_load_3d<CG>(sB0 + stage * C::kBBytes, &tmB, bar, kt * C::kRowBytes, b_row, b_l);
@@ -893,7 +926,32 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       // One alpha / beta per group when the arrays are given (grouped GEMM), else the scalars.
       const float alpha = p.alpha_array ? __ldg(p.alpha_array + ti.g) : alpha_all;
       const float beta = p.beta_array ? __ldg(p.beta_array + ti.g) : beta_all;
-      const bool use_c = (p.C != nullptr) && (beta != 0.0f);
+      bool use_c = (p.C != nullptr) && (beta != 0.0f);
+      // Reduce-scatter: stage of this tile row, where its addend comes from and where its result goes.
+      int32_t rs_stage = 0;
+      bool rs_to_peer = false;
+      uint32_t* rs_flag_out = nullptr;
+      if constexpr (RS) {
+        rs_stage = ti.tm_walk / p.rs_tiles_per_slice;
+        rs_to_peer = rs_stage < p.rs_world - 1;
+        const int32_t tm_in_slice = ti.tm_walk - rs_stage * p.rs_tiles_per_slice;
+        const int32_t half = p.rs_parity_rows != 0 ? 1 : 0;
+        if (rs_stage >= 1) {
+          // the partial sums of this tile from rank + 1: wait (bounded) until all of its warps have announced their stores
+          const uint32_t* flag = p.rs_flags + ((int64_t(half) * (p.rs_world - 1) + (rs_stage - 1)) * p.rs_tiles_per_slice + tm_in_slice) * p.tiles_n + ti.tn;
+          if (lane == 0 && !wait_flag_ge(flag, p.rs_flag_target, ctl)) dead = 1;
+          dead = __shfl_sync(0xffffffffu, dead, 0);
+          use_c = true;
+        } else {
+          use_c = false;
+        }
+        if (rs_to_peer) {
+          rs_flag_out = p.rs_flags_left + ((int64_t(half) * (p.rs_world - 1) + rs_stage) * p.rs_tiles_per_slice + tm_in_slice) * p.tiles_n + ti.tn;
+          // the neighbour's receive half is free once it has launched the call before the one that reads it again
+          if (lane == 0 && !wait_flag_ge(p.rs_sync + kRsSyncLaunched, p.rs_ready_target, ctl)) dead = 1;
+          dead = __shfl_sync(0xffffffffu, dead, 0);
+        }
+      }
       const int acc_bar = it % C::kAccBars;
       const uint32_t acc_phase = uint32_t(it / C::kAccBars) & 1u;
       const uint32_t acc_col = uint32_t(it & 1) * C::kAccStride;
@@ -909,7 +967,10 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const int32_t lrow = grow - ti.group_row0;                 // row within the group
       const int32_t warp_map_row0 = ti.map_row0 + int32_t(cta_rank) * C::kCtaM + warp * 32;
       // Element offsets of this lane's row in C and D (the batch entry selects the batch stride).
-      const int64_t c_row_off = int64_t(ti.map_l) * p.batch_stride_c + int64_t(warp_map_row0 + lane) * p.ldc;
+      // Reduce-scatter: row of this lane inside its slice, and the rows of the receive buffers it reads / writes.
+      const int32_t rs_row_in_slice = RS ? (ti.tm_walk % p.rs_tiles_per_slice) * C::kTileM + int32_t(cta_rank) * C::kCtaM + warp * 32 : 0;
+      const int64_t c_row_off = RS ? int64_t(p.rs_parity_rows + (rs_stage - 1) * p.rs_slice_rows + rs_row_in_slice + lane) * p.N
+                                   : int64_t(ti.map_l) * p.batch_stride_c + int64_t(warp_map_row0 + lane) * p.ldc;
       const int64_t d_row_off = int64_t(ti.map_l) * p.batch_stride_d + int64_t(warp_map_row0 + lane) * p.ldd;
       const uint32_t lane_addr = tmem_base + (uint32_t(warp * 32) << 16) + acc_col;
       const bool reverse = (BN == 256) && ((it & 1) == 0);
@@ -985,24 +1046,26 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int j = 0; j < 32; ++j) x[j] = __fadd_rn(x[j], bv);
           }
           if (use_c && row_ok) {
-            const __nv_bfloat16* crow = p.C + c_row_off + col0;
+            const __nv_bfloat16* crow = (RS ? p.rs_recv : p.C) + c_row_off + col0;
+            const float beta_c = RS ? 1.0f : beta;
             if (cols_valid >= 32) {
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                const uint4 cv = __ldg(reinterpret_cast<const uint4*>(crow) + q);
+                // Reduce-scatter: the addend was written by another GPU during this kernel: no read-only cache path.
+                const uint4 cv = RS ? ld_global_v4(reinterpret_cast<const uint4*>(crow) + q) : __ldg(reinterpret_cast<const uint4*>(crow) + q);
                 const uint32_t w[4] = {cv.x, cv.y, cv.z, cv.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                   const float c_lo = __uint_as_float(w[e] << 16);
                   const float c_hi = __uint_as_float(w[e] & 0xFFFF0000u);
-                  x[q * 8 + e * 2 + 0] = __fadd_rn(__fmul_rn(beta, c_lo), x[q * 8 + e * 2 + 0]);
-                  x[q * 8 + e * 2 + 1] = __fadd_rn(__fmul_rn(beta, c_hi), x[q * 8 + e * 2 + 1]);
+                  x[q * 8 + e * 2 + 0] = __fadd_rn(__fmul_rn(beta_c, c_lo), x[q * 8 + e * 2 + 0]);
+                  x[q * 8 + e * 2 + 1] = __fadd_rn(__fmul_rn(beta_c, c_hi), x[q * 8 + e * 2 + 1]);
                 }
               }
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
-                if (j < cols_valid) x[j] = __fadd_rn(__fmul_rn(beta, __bfloat162float(crow[j])), x[j]);
+                if (j < cols_valid) x[j] = __fadd_rn(__fmul_rn(beta_c, __uint_as_float(uint32_t(*reinterpret_cast<const volatile uint16_t*>(crow + j)) << 16)), x[j]);
               }
             }
           }
@@ -1049,11 +1112,11 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             // this row held here, e4m3 values; same routine of the reference host GEMM as below.
             float amax = 0.f;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(x[j]));
+            for (int j = 0; j < 32; ++j) amax = ptx::fmax_nan(amax, fabsf(x[j]));     // NaN propagates, as in the reference
             const float pv = __fmul_rn(amax, st_scaled);
             const uint32_t q = ptx::cvt_ue8m0_rp(pv);
             float sc = __fmul_rn(st, __fdiv_rn(1.0f, ptx::ue8m0_to_f32(q)));
-            sc = fminf(sc, FLT_MAX);
+            sc = ptx::fmin_nan(sc, FLT_MAX);
             uint32_t w[8];
 #pragma unroll
             for (int e = 0; e < 8; ++e)
@@ -1079,12 +1142,12 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int b = 0; b < 2; ++b) {
               float amax = 0.f;
 #pragma unroll
-              for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(x[b * 16 + j]));
+              for (int j = 0; j < 16; ++j) amax = ptx::fmax_nan(amax, fabsf(x[b * 16 + j]));   // NaN propagates, as in the reference
               const float pv = __fmul_rn(amax, st_scaled);
               const uint32_t q = ptx::cvt_ue4m3(pv);
               const float qf = ptx::cvt_e4m3_to_f32(q);
               float sc = __fmul_rn(st, __fdiv_rn(1.0f, qf));
-              sc = fminf(sc, FLT_MAX);
+              sc = ptx::fmin_nan(sc, FLT_MAX);
               if (cols_valid >= 16 * (b + 1)) sf_pair |= q << (16 * h + 8 * b);
 #pragma unroll
               for (int e = 0; e < 2; ++e) {
@@ -1129,9 +1192,23 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           if (lane == 0) {
             // Column coordinate in bytes / elements of the D map: bf16 elements, e4m3 bytes, two e2m1 per byte.
             const int32_t col = tile_col0 + pr * 64;
-            ptx::tma_store_3d(&tmD, ptx::smem_u32(sub_buf), out_kind == kOutNvfp4 ? col / 2 : col, warp_map_row0, ti.map_l);
+            if (RS && rs_to_peer)
+              ptx::tma_store_3d(&tmDpeer, ptx::smem_u32(sub_buf), col, p.rs_parity_rows + rs_stage * p.rs_slice_rows + rs_row_in_slice, 0);
+            else if (RS)
+              ptx::tma_store_3d(&tmD, ptx::smem_u32(sub_buf), col, rs_row_in_slice, 0);
+            else
+              ptx::tma_store_3d(&tmD, ptx::smem_u32(sub_buf), out_kind == kOutNvfp4 ? col / 2 : col, warp_map_row0, ti.map_l);
             ptx::bulk_commit_group();
           }
+        }
+      }
+      if constexpr (RS) {
+        // Announce this warp's part of the tile to rank - 1: its stores must be complete (not only read from shared
+        // memory) and ordered before the counter, in the form the memory model asks for.
+        if (rs_to_peer && lane == 0 && !dead) {
+          ptx::bulk_wait_group<0>();
+          asm volatile("fence.proxy.async;" ::: "memory");
+          asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(rs_flag_out), "r"(1u) : "memory");
         }
       }
       ++it;

@@ -401,11 +401,24 @@ __device__ __forceinline__ float cvt_e4m3_to_f32(uint32_t code) {
   return __half2float(__low2half(h));
 }
 
-// fp32 (>= 0) -> ue8m0 code, rounding up (float8.h:1174 of the reference uses the same instruction).
+// fp32 (>= 0) -> ue8m0 code, rounding up (float8.h:1174 of the reference uses the same instruction).  Infinity
+// gives the NaN code 0xFF, as the reference's host conversion does (the format has no infinity; the instruction
+// alone would saturate to the largest finite value).
 __device__ __forceinline__ uint32_t cvt_ue8m0_rp(float x) {
   uint16_t out;
   asm volatile("cvt.rp.satfinite.ue8m0x2.f32 %0, %1, %2;" : "=h"(out) : "f"(0.0f), "f"(x));
-  return out & 0xFFu;
+  return __float_as_uint(x) == 0x7F800000u ? 0xFFu : (out & 0xFFu);
+}
+// Maximum / minimum that return NaN when an operand is NaN (fmaxf / fminf return the other operand).
+__device__ __forceinline__ float fmax_nan(float a, float b) {
+  float d;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+  return d;
+}
+__device__ __forceinline__ float fmin_nan(float a, float b) {
+  float d;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+  return d;
 }
 __device__ __forceinline__ float ue8m0_to_f32(uint32_t code) {
   if (code == 0xFFu) return __uint_as_float(0x7FC00000u);

@@ -104,6 +104,10 @@ SYMBOLS = {
     "bsg_tp_gemm_run": (C.c_int32, [C.c_void_p, C.POINTER(GemmArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "bsg_tp_set_mode": (C.c_int32, [C.c_void_p, C.c_int32]),
     "bsg_tp_destroy": (C.c_int32, [C.c_void_p]),
+    "bsg_rs_create": (C.c_int32, [C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.POINTER(C.c_void_p), C.c_void_p]),
+    "bsg_rs_connect": (C.c_int32, [C.c_void_p, C.c_void_p]),
+    "bsg_rs_gemm_run": (C.c_int32, [C.c_void_p, C.POINTER(GemmArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "bsg_rs_destroy": (C.c_int32, [C.c_void_p]),
 }
 
 _lib = None

@@ -96,6 +96,77 @@ class _DevicePointer:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
 
 
+def rs_hop_order(world: int, slice_index: int) -> list[int]:
+    """Ranks in the order in which they add their partial product to the running sum of a slice of rows in the
+    GEMM + reduce-scatter: the slice starts at rank slice - 1, moves left one rank per stage and ends at its owner."""
+    return [(slice_index - 1 - s) % world for s in range(world)]
+
+
+def rs_stage_slices(world: int, rank: int) -> list[int]:
+    """Slices in the order in which ``rank`` works on them (stage 0 first); the last one is its own."""
+    return [(rank + 1 + s) % world for s in range(world)]
+
+
+class RsGemm:
+    """Per-rank handle of the GEMM + reduce-scatter for a fixed (M, N): every rank holds the K shard of A (M x K/world)
+    and of B (N x K/world); ``run`` leaves rows [rank * M / world, (rank + 1) * M / world) of alpha * A @ B^T in ``out``.
+    Takes the role of the reference's reduce-scatter distributed GEMM schedules
+    (``include/cutlass/experimental/distributed/schedules/dist_gemm_1d_schedules.hpp:148``)."""
+
+    def __init__(self, M: int, N: int, group=None):
+        import torch
+        import torch.distributed as dist
+        from . import lib as L
+        self._L = L
+        self._lib = L.load()
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        if self.world > MAX_WORLD:
+            raise ValueError(f"at most {MAX_WORLD} ranks are supported")
+        shard_rows(M, self.world, self.rank)      # raises when M does not split into whole 256-row blocks per rank
+        self.M, self.N = M, N
+        self._comm = C.c_void_p()
+        handle = (C.c_uint8 * 64)()
+        L.check(self._lib.bsg_rs_create(self.rank, self.world, M, N, C.byref(self._comm), handle))
+        if self.world > 1:
+            handles = exchange_handles(bytes(handle), group)
+            blob = (C.c_uint8 * (64 * self.world)).from_buffer_copy(b"".join(handles))
+            L.check(self._lib.bsg_rs_connect(self._comm, blob))
+            dist.barrier(group)
+        self.workspace = torch.zeros(16, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+
+    def build_args(self, kind: int, A, SFA, B, SFB, out, alpha: float = 1.0):
+        """A: (M, K_local) packed K-major; B: (N, K_local); out: (M / world, N) bf16."""
+        L = self._L
+        a = L.GemmArgs()
+        a.kind, a.out_kind, a.batch = kind, L.OUT_BF16, 1
+        k_local = A.shape[-1] * (2 if kind == L.KIND_NVFP4 else 1)
+        a.M, a.N, a.K = self.M, self.N, k_local
+        a.A, a.SFA, a.B, a.SFB, a.D = A.data_ptr(), SFA.data_ptr(), B.data_ptr(), SFB.data_ptr(), out.data_ptr()
+        a.alpha = alpha
+        return a
+
+    def run(self, kind: int, A, SFA, B, SFB, out, alpha: float = 1.0, stream=None, abi_args=None) -> None:
+        from .operator import to_cuda_stream
+        a = abi_args if abi_args is not None else self.build_args(kind, A, SFA, B, SFB, out, alpha)
+        self._L.check(self._lib.bsg_rs_gemm_run(self._comm, C.byref(a), self.workspace.data_ptr(), 16, to_cuda_stream(stream)))
+
+    def check_device_status(self, stream=None) -> None:
+        from .operator import to_cuda_stream
+        self._L.check(self._lib.bsg_read_device_status(self.workspace.data_ptr(), to_cuda_stream(stream)))
+
+    def close(self) -> None:
+        if self._comm:
+            self._lib.bsg_rs_destroy(self._comm)
+            self._comm = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001
+            pass
+
+
 class TpGemm:
     """Per-rank handle of the tensor-parallel GEMM for a fixed (kind, M, K).
 

@@ -334,6 +334,35 @@ int32_t bsg_tp_gemm_run(bsg_tp_comm* comm, const bsg_gemm_args* args, void* work
                         void* cuda_stream);
 int32_t bsg_tp_destroy(bsg_tp_comm* comm);
 
+/*
+ * GEMM + reduce-scatter: the row-parallel half of a tensor-parallel layer.  K is sharded: every rank holds
+ * A[:, its K shard] (M x K/world) and B[:, its K shard] (N x K/world) with their scale factors and computes a partial
+ * product for all of M x N; the partial sums are reduced over the ranks and scattered over M: rank r ends up with rows
+ * [r * M / world, (r + 1) * M / world) of D = alpha * A B^T.  One kernel per rank does both: the M tiles are walked
+ * slice by slice (a slice = the rows one rank owns), starting at slice rank + 1; the epilogue of a tile adds the partial
+ * sums received from rank + 1 (none in the first stage), and stores the sum into the receive buffer of rank - 1 (TMA
+ * stores into peer memory, then a released counter increment per warp), or, in the last stage, into D.  Takes the role
+ * of the reference's ReduceScatter1D_TilingA_RotatingC schedule
+ * (include/cutlass/experimental/distributed/schedules/dist_gemm_1d_schedules.hpp:148), in which the running sums also
+ * travel around the ring in the output type: here bf16, rounded at every hop, fp32 only inside a hop.
+ *
+ * bsg_rs_create    allocates the receive buffers (two halves, used by alternate calls; (world - 1) * M / world * N bf16
+ *                  each) and returns a 64-byte CUDA IPC handle for the peers.  M a multiple of 256 * world.
+ * bsg_rs_connect   takes the `world` handles (64 bytes each, by rank) and maps the two ring neighbours.
+ * bsg_rs_gemm_run  enqueues one GEMM: args->M, N are the full extents, K the local shard, A / B / SFA / SFB the local
+ *                  shards, D the (M / world) x N bf16 result slice of this rank (ldd its pitch); alpha applies to every
+ *                  partial product; C, beta, bias, activation and quantised outputs are not available.  All ranks call
+ *                  it the same number of times; waits are bounded as for the all-gather GEMM (BSG_ERR_TIMEOUT), and the
+ *                  same rules hold for what a call needs (the whole GPU) and for recovery after a time-out.
+ * bsg_rs_destroy   after the device is idle on every rank and a barrier.
+ */
+typedef struct bsg_rs_comm bsg_rs_comm;
+int32_t bsg_rs_create(int32_t rank, int32_t world, int64_t M, int64_t N, bsg_rs_comm** out, void* ipc_handle_out);
+int32_t bsg_rs_connect(bsg_rs_comm* comm, const void* all_handles);
+int32_t bsg_rs_gemm_run(bsg_rs_comm* comm, const bsg_gemm_args* args, void* workspace, size_t workspace_bytes,
+                        void* cuda_stream);
+int32_t bsg_rs_destroy(bsg_rs_comm* comm);
+
 #ifdef __cplusplus
 }
 #endif

@@ -84,7 +84,7 @@ uint32_t bsg_oracle_encode(int fmt, float x) {
       if (isnan(x)) return 0x7;
       return nearest_even(fabsf(x), e2m1_grid, 8) | (sign << 3);
     case 1:
-      if (isnan(x)) return 0x7F | (sign << 7);
+      if (isnan(x)) return 0x7F;
       return nearest_even(fabsf(x), g_e4m3_grid, 127) | (sign << 7);
     case 2:
       if (isnan(x)) return 0x7F;
@@ -249,14 +249,16 @@ void bsg_oracle_quant(int kind, const float* x, int64_t M, int64_t N, float st, 
       float amax = 0.f, pv, qf, rcp, sc;
       uint32_t q;
       int j;
-      for (j = 0; j < V; ++j) { const float a = fabsf(v[j]); if (a > amax) amax = a; }
+      /* maximum and minimum propagate NaN (maximum_with_nan_propogation / minimum_with_nan_propagation, gett.hpp:390,463):
+       * one NaN in a block makes its scale factor and all of its values NaN codes (e2m1 has none: the largest value) */
+      for (j = 0; j < V; ++j) { const float a = fabsf(v[j]); if (isnan(a) || isnan(amax)) amax = NAN; else if (a > amax) amax = a; }
       pv = amax * st_scaled;
       q = bsg_oracle_encode(sf_fmt, pv);
       SFD[bsg_oracle_sf_offset(m, nb, k_atoms)] = (uint8_t)q;
       qf = bsg_oracle_decode(sf_fmt, q);
       rcp = 1.0f / qf;
       sc = st * rcp;
-      if (sc > FLT_MAX) sc = FLT_MAX;
+      if (!isnan(sc) && sc > FLT_MAX) sc = FLT_MAX;
       if (kind == 0) {
         for (j = 0; j < V; j += 2) {
           const uint32_t lo = bsg_oracle_encode(d_fmt, v[j] * sc), hi = bsg_oracle_encode(d_fmt, v[j + 1] * sc);

@@ -183,3 +183,72 @@ def test_tp_rank_that_never_launches_gives_a_timeout_status_not_a_hang():
     for p in procs:
         p.join(timeout=120)
     assert results == [(r, "ok") for r in range(world)], results
+
+
+# --------------------------------------------------------------------------- GEMM + reduce-scatter
+def _rs_worker(rank, world, port, kind, M, N, K, calls, q):
+    """K is sharded; rank r must end up with rows [r * M / world, ...) of the sum over ranks, where the running sum is
+    rounded to bf16 at every hop of the ring (the oracle follows the same hop order)."""
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                          LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+        import torch.distributed as dist
+        import oracle
+        from cutlass_b200 import generators as G
+        from cutlass_b200 import tp as TP
+        torch.cuda.set_device(rank)
+        if world > 1:
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        rs = TP.RsGemm(M, N)
+        try:
+            ms, kl = M // world, K // world
+            for call in range(calls):
+                rng = np.random.default_rng(300 + call)
+                gen_a, gen_b = G.operand_generators(kind, True)
+                shards = [(gen_a(M, kl, rng), gen_b(N, kl, rng)) for _ in range(world)]       # every rank's K shard, same on all ranks
+                (A, _, sfa), (B, _, sfb) = shards[rank]
+                dA, dSFA, dB, dSFB = (torch.from_numpy(np.ascontiguousarray(x)).cuda() for x in (A, sfa, B, sfb))
+                out = torch.full((ms, N), 0x7FC0, dtype=torch.int16, device="cuda")
+                rs.run(kind, dA, dSFA, dB, dSFB, out, alpha=0.5)
+                rs.check_device_status()
+                torch.cuda.synchronize()
+                run = None
+                vec = 16 if kind == 0 else 32
+                atom_bytes = 512 * (-(-(kl // vec) // 4))
+                for hop in TP.rs_hop_order(world, rank):
+                    (Ah, _, sfah), (Bh, _, sfbh) = shards[hop]
+                    rows = slice(rank * ms, (rank + 1) * ms)
+                    sfa_rows = sfah[(rank * ms // 128) * atom_bytes:((rank + 1) * ms // 128) * atom_bytes]
+                    pre = oracle.gemm_fp32(kind, Ah[rows], sfa_rows, Bh, sfbh, ms, N, kl, run, 0.5, 1.0 if run is not None else 0.0)
+                    run = oracle.to_bf16(pre)
+                got = out.cpu().numpy().view(np.uint16)
+                bad = int((got != run).sum())
+                assert bad == 0, f"call {call}: {bad} of {got.size} outputs differ from the oracle (rank {rank})"
+        finally:
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            rs.close()
+            if world > 1:
+                dist.barrier()
+                dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        q.put((rank, repr(e)))
+
+
+@pytest.mark.parametrize("kind,world,M,N,K", [(0, 1, 512, 384, 512), (1, 2, 1024, 512, 1024), (0, 2, 2048, 640, 2048), (1, 4, 2048, 1024, 2048),
+                                              (0, 8, 4096, 512, 4096)])
+def test_gemm_reduce_scatter(kind, world, M, N, K):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rs_worker, args=(r, world, port, kind, M, N, K, 4, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=600) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+    assert results == [(r, "ok") for r in range(world)], results

@@ -114,3 +114,21 @@ def test_scale_factor_pieces_are_spread_over_the_ctas(grid):
     blocks = M // world // TP.ROW_BLOCK
     assert sum(per_cta) == (world - 1) * blocks
     assert max(per_cta) <= 2
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_reduce_scatter_ring_schedule(world):
+    """GEMM + reduce-scatter: at every stage the slice a rank works on is the one its right neighbour worked on one
+    stage earlier (so the running sum it needs has been sent to it), every slice visits every rank once, and it ends
+    at its owner."""
+    for rank in range(world):
+        mine = TP.rs_stage_slices(world, rank)
+        assert sorted(mine) == list(range(world)) and mine[-1] == rank
+        right = TP.rs_stage_slices(world, (rank + 1) % world)
+        for s in range(1, world):
+            assert mine[s] == right[s - 1]
+    for j in range(world):
+        order = TP.rs_hop_order(world, j)
+        assert sorted(order) == list(range(world)) and order[-1] == j
+        for s, r in enumerate(order):
+            assert TP.rs_stage_slices(world, r)[s] == j
