@@ -167,7 +167,7 @@ struct Problem {
   int64_t ldc, ldd;
   int64_t lda, ldb;                         // row pitch of A / B in elements
   int64_t bs_a, bs_b, bs_c, bs_d;           // batch strides in elements (dense / batched form only)
-  int32_t use_pdl, scheduler;
+  int32_t use_pdl, scheduler, out_col_major;
   int32_t cluster[4];                       // cluster_m, cluster_n, fallback m, n (0 = default)
   float alpha, beta;
   const float *alpha_ptr, *beta_ptr, *norm_ptr;
@@ -219,7 +219,14 @@ int32_t validate(const Problem& q, Plan* plan) {
   if (!aligned16(q.A) || !aligned16(q.B) || !aligned16(q.D) || (q.C && !aligned16(q.C)))
     return fail(BSG_ERR_MISALIGNED_OPERAND, "A, B, C and D must be 16-byte aligned");
   if (!aligned16(q.SFA) || !aligned16(q.SFB)) return fail(BSG_ERR_MISALIGNED_OPERAND, "scale-factor tensors must be 16-byte aligned");
-  if (q.out_kind == BSG_OUT_BF16) {
+  if (q.out_col_major) {
+    // column-major quantised output: D is (N, M) with M contiguous, scale factors along M
+    if (q.out_kind == BSG_OUT_BF16) return fail(BSG_ERR_NOT_SUPPORTED, "the column-major layout is for quantised outputs");
+    if (q.offsets || q.num_groups != 1 || q.tp || q.rs) return fail(BSG_ERR_NOT_SUPPORTED, "the column-major output layout is for the dense, unbatched GEMM");
+    if (!q.SFD || (q.out_kind == BSG_OUT_NVFP4 && !q.norm_ptr)) return fail(BSG_ERR_INVALID_PROBLEM, "quantised output needs SFD (and norm_constant for NVFP4)");
+    if (q.rows_per_group % 32 != 0 || q.ldd % 32 != 0 || q.ldd < q.rows_per_group)
+      return fail(BSG_ERR_MISALIGNED_OPERAND, "column-major output needs M %% 32 == 0 and ldd (the pitch of a column, >= M) %% 32 == 0");
+  } else if (q.out_kind == BSG_OUT_BF16) {
     if (q.N % 8 != 0 || q.ldd % 8 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "bf16 output needs N and ldd to be multiples of 8");
   } else if (q.out_kind == BSG_OUT_MXFP8) {
     if (!q.SFD) return fail(BSG_ERR_INVALID_PROBLEM, "MXFP8 output needs SFD");
@@ -237,7 +244,7 @@ int32_t validate(const Problem& q, Plan* plan) {
   }
   if (q.activation < BSG_ACT_IDENTITY || q.activation > BSG_ACT_SILU) return fail(BSG_ERR_NOT_SUPPORTED, "unknown activation %d", q.activation);
   if (q.C && (q.ldc % 8 != 0)) return fail(BSG_ERR_MISALIGNED_OPERAND, "ldc must be a multiple of 8");
-  if (q.ldd < q.N || (q.C && q.ldc < q.N)) return fail(BSG_ERR_INVALID_PROBLEM, "row pitch smaller than N");
+  if ((!q.out_col_major && q.ldd < q.N) || (q.C && q.ldc < q.N)) return fail(BSG_ERR_INVALID_PROBLEM, "row pitch smaller than N");
   if (q.lda < q.K || q.ldb < q.K) return fail(BSG_ERR_INVALID_PROBLEM, "lda / ldb smaller than K");
   if (q.lda % k_align != 0 || q.ldb % k_align != 0)
     return fail(BSG_ERR_MISALIGNED_OPERAND, "lda=%lld and ldb=%lld must be multiples of %lld (16-byte rows)", (long long)q.lda, (long long)q.ldb, (long long)k_align);
@@ -342,8 +349,12 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   // Reduce-scatter: D is this rank's slice of the result; the other stages store into rank - 1's receive buffers
   // (two halves of world - 1 slices each, N columns wide).
   const uint64_t d_rows = RS ? uint64_t(q.rs_slice_rows) : batched ? uint64_t(q.rows_per_group) : uint64_t(q.total_rows);
-  if ((rc = make_out_map(&tmD, q.D, q.out_kind, uint64_t(q.N), d_rows, map_batches, uint64_t(q.ldd),
-                         uint64_t(batched && q.num_groups > 1 ? q.bs_d : d_rows * q.ldd))) != BSG_OK) return rc;
+  if (q.out_col_major)     // stored as its transpose (N rows of M values); the kernel writes it with plain stores, the map only describes it
+    rc = make_out_map(&tmD, q.D, q.out_kind, uint64_t(q.rows_per_group), uint64_t(q.N), 1, uint64_t(q.ldd), uint64_t(q.N) * uint64_t(q.ldd));
+  else
+    rc = make_out_map(&tmD, q.D, q.out_kind, uint64_t(q.N), d_rows, map_batches, uint64_t(q.ldd),
+                      uint64_t(batched && q.num_groups > 1 ? q.bs_d : d_rows * q.ldd));
+  if (rc != BSG_OK) return rc;
   tmDpeer = tmD;
   if (RS && q.rs_world > 1) {
     const uint64_t peer_rows = 2ull * uint64_t(q.rs_world - 1) * uint64_t(q.rs_slice_rows);
@@ -381,6 +392,7 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   p.tiles_n = int32_t((q.N + BN - 1) / BN);
   p.raster_band = q.raster_band > 0 ? q.raster_band : 16;
   p.out_kind = q.out_kind;
+  p.out_col_major = q.out_col_major;
   p.alpha_array = q.alpha_array; p.beta_array = q.beta_array;
   p.bias = q.bias; p.bias_mode = q.bias_mode; p.bias_group_stride = q.bias_group_stride; p.activation = q.activation;
   p.C = static_cast<const __nv_bfloat16*>(q.C);
@@ -554,7 +566,8 @@ Problem from_dense(const bsg_gemm_args* a) {
   q.offsets = nullptr;
   q.b_per_group = true;
   q.ldc = a->ldc ? a->ldc : a->N;
-  q.ldd = a->ldd ? a->ldd : a->N;
+  q.out_col_major = a->out_layout == BSG_LAYOUT_COL_MAJOR ? 1 : 0;
+  q.ldd = a->ldd ? a->ldd : (q.out_col_major ? a->M : a->N);
   q.lda = a->lda ? a->lda : a->K;
   q.ldb = a->ldb ? a->ldb : a->K;
   q.bs_a = a->batch_stride_A ? a->batch_stride_A : a->M * q.lda;

@@ -70,6 +70,8 @@ struct GemmParams {
   int32_t tiles_n;
   int32_t raster_band;
   int32_t out_kind;
+  int32_t out_col_major;      // quantised outputs only: D is stored column-major (M contiguous, ldd = its pitch) and the
+                              // scale factors cover 16 / 32 consecutive ROWS of a column: D^T with the K-major scale layout
   const __nv_bfloat16* C;
   void* D;
   uint8_t* SFD;
@@ -978,8 +980,9 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       // This warp's 32 rows lie inside the group: the output goes through shared memory and TMA stores.  (A TMA
       // store clips at the end of the matrix, not at the end of a group: the warp that holds a group's last rows
       // stores them row by row.)
-      const bool tma_out = cta_row0 + warp * 32 + 32 <= ti.row_end;
       const int out_kind = p.out_kind;
+      const bool col_major = out_kind != kOutBf16 && p.out_col_major != 0;
+      const bool tma_out = (cta_row0 + warp * 32 + 32 <= ti.row_end) && !col_major;
       // Staging sub-buffers a warp cycles through (4 KB per warp): bf16 uses all of it per 64 columns, e4m3 half,
       // e2m1 a quarter; a sub-buffer is rewritten once all but the newest n_bufs - 1 stores have read theirs.
       const int n_bufs = out_kind == kOutBf16 ? 1 : out_kind == kOutMxfp8 ? 2 : 4;
@@ -1075,7 +1078,71 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int j = 0; j < 32; ++j) x[j] = apply_activation(x[j], p.activation);
           }
 
-          if (out_kind == kOutBf16) {
+          if (col_major) {
+            // Column-major quantised output (the reference's Sm100BlockScaleFactorColStore,
+            // include/cutlass/epilogue/fusion/sm100_visitor_store_tma_warpspecialized.hpp:352): blocks run along M.
+            // The warp's 32 x 32 values are transposed through its staging buffer (128-byte rows, 16-byte chunks
+            // XOR-swizzled by the row index), after which lane n owns column col0 + n with its 32 rows, and the
+            // row-major arithmetic applies unchanged.  M is a multiple of 32, so a warp's rows are all valid or none.
+            float* tb = reinterpret_cast<float*>(stage_buf);
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) tb[j * 32 + ((((lane >> 2) ^ (j & 7)) << 2) | (lane & 3))] = x[j];
+            __syncwarp();
+            float y[32];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 v4 = *reinterpret_cast<const float4*>(tb + lane * 32 + ((i ^ (lane & 7)) << 2));
+              y[4 * i + 0] = v4.x; y[4 * i + 1] = v4.y; y[4 * i + 2] = v4.z; y[4 * i + 3] = v4.w;
+            }
+            __syncwarp();
+            const int32_t col = col0 + lane;
+            const int32_t m0 = lrow - lane;                                  // first row of the warp's slab (multiple of 32)
+            const int32_t m_k_atoms = ((p.rows_per_group + sfd_vec - 1) / sfd_vec + 3) / 4;
+            if (col < p.N && grow - lane < ti.row_end) {
+              uint8_t* sf_base = p.SFD + int64_t(col / 128) * (512ll * m_k_atoms) + 16 * (col & 31) + 4 * ((col & 127) >> 5);
+              if (out_kind == kOutNvfp4) {
+                uint32_t packed[4];
+                uint32_t codes = 0;
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                  float amax = 0.f;
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) amax = ptx::fmax_nan(amax, fabsf(y[b * 16 + j]));
+                  const uint32_t q = ptx::cvt_ue4m3(__fmul_rn(amax, st_scaled));
+                  float sc = __fmul_rn(st, __fdiv_rn(1.0f, ptx::cvt_e4m3_to_f32(q)));
+                  sc = ptx::fmin_nan(sc, FLT_MAX);
+                  codes |= q << (8 * b);
+#pragma unroll
+                  for (int e = 0; e < 2; ++e) {
+                    float z[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) z[j] = __fmul_rn(y[b * 16 + e * 8 + j], sc);
+                    packed[b * 2 + e] = ptx::cvt_e2m1x8(z);
+                  }
+                }
+                *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.D) + (int64_t(col) * p.ldd + m0) / 2) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                const int32_t mb = m0 >> 4;                                  // even: the two blocks share a 16-bit word
+                *reinterpret_cast<uint16_t*>(sf_base + (mb >> 2) * 512 + (mb & 3)) = uint16_t(codes);
+              } else {
+                float amax = 0.f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) amax = ptx::fmax_nan(amax, fabsf(y[j]));
+                const uint32_t q = ptx::cvt_ue8m0_rp(__fmul_rn(amax, st_scaled));
+                float sc = __fmul_rn(st, __fdiv_rn(1.0f, ptx::ue8m0_to_f32(q)));
+                sc = ptx::fmin_nan(sc, FLT_MAX);
+                uint32_t w[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                  w[e] = ptx::cvt_e4m3x4(__fmul_rn(y[e * 4 + 0], sc), __fmul_rn(y[e * 4 + 1], sc), __fmul_rn(y[e * 4 + 2], sc), __fmul_rn(y[e * 4 + 3], sc));
+                uint4* dcol = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.D) + int64_t(col) * p.ldd + m0);
+                dcol[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                dcol[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                const int32_t mb = m0 >> 5;
+                sf_base[(mb >> 2) * 512 + (mb & 3)] = uint8_t(q);
+              }
+            }
+          } else if (out_kind == kOutBf16) {
             if (tma_out) {
               // 128-byte-swizzled staging tile: 16-byte chunk c of row r lives at chunk (c ^ (r & 7)).
 #pragma unroll
@@ -1167,7 +1234,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
           }
         }
-        if (out_kind != kOutBf16 && row_ok && tile_col0 + pr * 64 < p.N) {
+        if (out_kind != kOutBf16 && !col_major && row_ok && tile_col0 + pr * 64 < p.N) {
           // Scale factors of this row for the 64 columns: consecutive bytes of one 512-byte atom of the interleaved
           // layout (4 per row for 16-wide blocks, 2 for 32-wide ones).
           const int32_t pair_col0 = tile_col0 + pr * 64;

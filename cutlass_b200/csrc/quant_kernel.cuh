@@ -7,11 +7,12 @@
 // every product separately rounded.  NVFP4: V = 16, SF ue4m3, q e2m1 (fp_max 6);  MXFP8: V = 32,
 // SF ue8m0 (the conversion rounds up), q e4m3 (fp_max 448).
 //
-// HBM-bound.  One CTA owns a tile of 128 rows x 128 elements (small tiles: an 8192 x 8192 operand is 4096 CTAs,
-// seven full waves of the GPU, where 128 x 256 tiles left the fourth wave half empty): a warp reads two rows of
-// the tile per step as 2 x 16 lanes x 16 bytes (256 contiguous bytes per row), the lanes that share a K-block
-// combine their maxima with shuffles, and every lane stores its own 8 quantised values (4 or 8 bytes).  The
-// tile's scale factors are collected in shared memory in atom order and leave as whole 512-byte atoms.
+// HBM-bound.  One CTA owns a tile of 128 rows x 256 elements: a warp reads one row of the tile per
+// step as 32 x 16 bytes (fully coalesced), the lanes that share a K-block combine their maxima with
+// shuffles, and every lane stores its own 8 quantised values (4 or 8 bytes, coalesced).  The tile's
+// scale factors are collected in shared memory in atom order and leave as whole 512-byte atoms.
+// (Tiles of 128 x 128, which fill the last wave of an 8192 x 8192 operand better, were measured slower at
+// every size: the per-CTA set-up and the atom write-out weigh more than the emptier last wave.)
 // Maximum and minimum propagate NaN as the reference's do (maximum_with_nan_propogation, gett.hpp:390): one NaN
 // in a block turns its scale factor and all of its values into NaN codes (e2m1 has none: the largest value).
 #pragma once
@@ -35,7 +36,7 @@ struct QuantParams {
 };
 
 constexpr int kQuantTileRows = 128;
-constexpr int kQuantTileK = 128;
+constexpr int kQuantTileK = 256;
 constexpr int kQuantThreads = 256;
 
 __device__ __forceinline__ float bf16_bits_to_f32(uint32_t b) { return __uint_as_float(b << 16); }
@@ -63,19 +64,18 @@ __global__ void __launch_bounds__(kQuantThreads, 4) bsg_quant_kernel(const Quant
 
   const float st = p.norm_ptr ? *p.norm_ptr : 1.0f;
   const float st_scaled = __fmul_rn(st, __fdiv_rn(1.0f, KIND == 0 ? 6.0f : 448.0f));
-  const int sub = lane >> 4, kl = lane & 15;                // which of the step's two rows, and where in it
-  const int k = k0 + kl * 8;
+  const int k = k0 + lane * 8;
   const bool k_ok = k < p.K;
-  const int blk = kl / kLanesPerBlock;                      // K-block of this lane inside the tile row
+  const int blk = lane / kLanesPerBlock;                    // K-block of this lane inside the tile row
 
-  // A warp owns rows 2 warp + sub + 16 (u + 4 g) of the tile (u < 4, g < 2).  The four loads of group g + 1 are
-  // issued before group g is processed, so that every warp always has loads in flight (the kernel is bound by
+  // A warp owns rows warp + 8 u + 32 g of the tile (u < 4, g < 4).  The four loads of group g + 1 are issued
+  // before group g is processed, so that every warp always has loads in flight (the kernel is bound by
   // memory latency x bytes in flight, not by arithmetic).
-  constexpr int kUnroll = 4, kGroups = kQuantTileRows / (16 * kUnroll);
+  constexpr int kUnroll = 4, kGroups = kQuantTileRows / (8 * kUnroll);
   auto load_group = [&](uint4 (&raw)[kUnroll], int g) {
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const int row = row0 + 2 * warp + sub + 16 * (u + kUnroll * g);
+      const int row = row0 + warp + 8 * u + 32 * g;
       raw[u] = make_uint4(0u, 0u, 0u, 0u);
       if (k_ok && row < p.rows) raw[u] = *reinterpret_cast<const uint4*>(p.X + int64_t(row) * p.ldx + k);
     }
@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(kQuantThreads, 4) bsg_quant_kernel(const Quant
     if (g + 1 < kGroups) load_group(nxt, g + 1);
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const int rt = 2 * warp + sub + 16 * (u + kUnroll * g), row = row0 + rt;
+      const int rt = warp + 8 * u + 32 * g, row = row0 + rt;
       float x[8];
       x[0] = bf16_bits_to_f32(raw[u].x & 0xFFFFu); x[1] = bf16_bits_to_f32(raw[u].x >> 16);
       x[2] = bf16_bits_to_f32(raw[u].y & 0xFFFFu); x[3] = bf16_bits_to_f32(raw[u].y >> 16);

@@ -1,6 +1,7 @@
-"""Run one dense block-scaled GEMM shape through the C ABI and time it.
+"""Run one dense block-scaled GEMM shape (or the quantiser in front of it) through the C ABI and time it.
 
   python -m cutlass_b200.gemm_cli --kind mxfp8 --m 16384 --n 3584 --k 8192 [--iters 20] [--sets 3]
+  python -m cutlass_b200.gemm_cli --op quantize --kind nvfp4 --m 8192 --k 8192
 
 Operands are seeded and generated on the device; ``--sets`` operand/output sets are rotated so
 that consecutive launches do not find their inputs in L2.  Prints one JSON line (milliseconds per
@@ -56,9 +57,36 @@ def run(kind: int, M: int, N: int, K: int, iters: int = 20, warmup: int = 5, set
             "ms": round(ms, 5), "tflops": round(2.0 * M * N * K / ms / 1e9, 1)}
 
 
+def run_quantize(kind: int, rows: int, K: int, iters: int = 30, warmup: int = 3, sets: int = 3) -> dict:
+    """bf16 (rows x K) -> block-scaled operand, `sets` inputs / outputs rotated (no launch finds its input in L2)."""
+    import torch
+    from . import lib as L
+    from .arguments import ScaleMode
+    from .quantize import quantize_blockscaled
+    mode = ScaleMode.Blockwise1x16 if kind == L.KIND_NVFP4 else ScaleMode.Blockwise1x32
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0)
+    xs = [torch.randn((rows, K), device="cuda", generator=gen).to(torch.bfloat16) for _ in range(sets)]
+    outs = [quantize_blockscaled(x, mode) for x in xs]
+    for i in range(warmup):
+        quantize_blockscaled(xs[i % sets], mode, out=outs[i % sets].quantized.tensor, scale_out=outs[i % sets].scale.tensor)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        quantize_blockscaled(xs[i % sets], mode, out=outs[i % sets].quantized.tensor, scale_out=outs[i % sets].scale.tensor)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    nbytes = rows * K * 2 + outs[0].quantized.tensor.numel() + outs[0].scale.tensor.numel()
+    return {"op": "quantize", "kind": "nvfp4" if kind == L.KIND_NVFP4 else "mxfp8", "rows": rows, "K": K, "iters": iters,
+            "ms": round(ms, 5), "algorithmic_bytes": nbytes, "GBs": round(nbytes / ms / 1e6, 1)}
+
+
 def main() -> None:
     from . import lib as L
     ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="gemm", choices=["gemm", "quantize"])
     ap.add_argument("--kind", default="nvfp4", choices=["nvfp4", "mxfp8"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -71,6 +99,9 @@ def main() -> None:
     ap.add_argument("--raster-band", type=int, default=0)
     a = ap.parse_args()
     kind = L.KIND_NVFP4 if a.kind == "nvfp4" else L.KIND_MXFP8
+    if a.op == "quantize":
+        print(json.dumps(run_quantize(kind, a.m, a.k, a.iters, a.warmup, a.sets)))
+        return
     print(json.dumps(run(kind, a.m, a.n, a.k, a.iters, a.warmup, a.sets, a.tile_n, a.cta_group, a.raster_band)))
 
 

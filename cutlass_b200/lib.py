@@ -36,6 +36,7 @@ ACT_IDENTITY, ACT_RELU, ACT_GELU, ACT_SILU = 0, 1, 2, 3
 BIAS_NONE, BIAS_PER_COLUMN, BIAS_PER_ROW = 0, 1, 2
 MAX_GROUPS = 256
 SCHED_STATIC, SCHED_DYNAMIC = 0, 1
+LAYOUT_ROW_MAJOR, LAYOUT_COL_MAJOR = 0, 1
 
 
 class GemmArgs(C.Structure):
@@ -53,6 +54,7 @@ class GemmArgs(C.Structure):
         ("batch_stride_A", C.c_int64), ("batch_stride_B", C.c_int64), ("batch_stride_C", C.c_int64), ("batch_stride_D", C.c_int64),
         ("use_pdl", C.c_int32), ("scheduler", C.c_int32),
         ("cluster_m", C.c_int32), ("cluster_n", C.c_int32), ("cluster_fallback_m", C.c_int32), ("cluster_fallback_n", C.c_int32),
+        ("out_layout", C.c_int32), ("reserved1", C.c_int32),
     ]
 
 

@@ -115,7 +115,18 @@ typedef struct bsg_gemm_args {
    * back from: 0 (default) or {cta_group, 1} are accepted, anything else is BSG_ERR_NOT_SUPPORTED. */
   int32_t cluster_m, cluster_n;
   int32_t cluster_fallback_m, cluster_fallback_n;
+  int32_t out_layout;       /* BSG_LAYOUT_*: quantised outputs only, batch 1 */
+  int32_t reserved1;
 } bsg_gemm_args;
+
+/* Layout of a quantised output.  ROW_MAJOR: D is (M, N) with N contiguous, one scale factor per 16 / 32 consecutive
+ * columns of a row, SFD interleaved over (M, N / V).  COL_MAJOR: D is stored column-major -- (N, M) with M contiguous,
+ * ldd its pitch in elements -- with one scale factor per 16 / 32 consecutive ROWS of a column and SFD interleaved over
+ * (N, M / V): the K-major operand form of D^T, which a following GEMM can take as its B with K := M (the reference's
+ * Sm100BlockScaleFactorColStore, include/cutlass/epilogue/fusion/sm100_visitor_store_tma_warpspecialized.hpp:352, and the
+ * M-major layout of Sm1xxBlockScaledOutputConfig, include/cutlass/detail/sm100_blockscaled_layout.hpp:192-228).  M must be a
+ * multiple of 32. */
+enum { BSG_LAYOUT_ROW_MAJOR = 0, BSG_LAYOUT_COL_MAJOR = 1 };
 
 /* Tile schedulers.  STATIC: persistent grid of one cluster per SM pair, tile index += cluster count (the
  * reference's StaticPersistentTileScheduler, python/CuTeDSL/cutlass/utils/static_persistent_tile_scheduler.py:376).

@@ -163,7 +163,9 @@ def to_bf16(x: np.ndarray) -> np.ndarray:
 
 
 def ref_gemm(kind: int, out_mode: int, A, SFA, B, SFB, M: int, N: int, K: int, C_bits=None, alpha=1.0, beta=0.0, st=0.0):
-    """Compiled reference: out_mode 0 fp32, 1 bf16 bits, 2 (packed e2m1, ue4m3 SFD per 16), 3 (e4m3, ue8m0 SFD per 32)."""
+    """Compiled reference: out_mode 0 fp32, 1 bf16 bits, 2 (packed e2m1, ue4m3 SFD per 16), 3 (e4m3, ue8m0 SFD per 32),
+    4 / 5 (NVFP4 operands only): as 2 / 3 with D column-major and the scale factors along M -- returned as the
+    transposed matrix (N x M values) and its K-major scale-factor buffer."""
     lib = load_ref()
     if lib is None:
         raise FileNotFoundError("oracle/_ref/libbsg_ref.so has not been built")
@@ -181,10 +183,16 @@ def ref_gemm(kind: int, out_mode: int, A, SFA, B, SFB, M: int, N: int, K: int, C
         D = np.zeros((M, N // 2), dtype=np.uint8)
         nb = N // 16
         sfd = np.zeros(-(-M // 128) * 128 * (-(-nb // 4)) * 4, dtype=np.uint8)
-    else:
+    elif out_mode == 3:
         D = np.zeros((M, N), dtype=np.uint8)
         nb = N // 32
         sfd = np.zeros(-(-M // 128) * 128 * (-(-nb // 4)) * 4, dtype=np.uint8)
+    else:
+        # column-major D (returned as its transpose: N rows of M values) with scale factors along M
+        vec = 16 if out_mode == 4 else 32
+        D = np.zeros((N, M // 2 if out_mode == 4 else M), dtype=np.uint8)
+        mb = M // vec
+        sfd = np.zeros(-(-N // 128) * 128 * (-(-mb // 4)) * 4, dtype=np.uint8)
     rc = lib.bsg_ref_gemm(kind, out_mode, M, N, K, _ptr(A), _ptr(B), _ptr(SFA), _ptr(SFB), _ptr(Cb), alpha, beta, _ptr(D),
                           _ptr(sfd), float(st))
     if rc != 0:

@@ -26,9 +26,11 @@ template <int Vec>
 using SfCfg = cutlass::detail::Sm1xxBlockScaledConfig<Vec>;
 template <int Vec>
 using SfOutCfg = cutlass::detail::Sm1xxBlockScaledOutputConfig<Vec>;
+template <int Vec>
+using SfOutCfgColMajor = cutlass::detail::Sm1xxBlockScaledOutputConfig<Vec, cute::UMMA::Major::MN>;
 
 template <class ElemAB, class ElemSF, int Vec, class ElemD, bool GenSfd, int SfdVec = 16, class ElemSFD = cutlass::float_ue4m3_t,
-          class ElemB = ElemAB>
+          class ElemB = ElemAB, bool ColMajorD = false>
 void run_gemm(int M, int N, int K, const void* A, const void* B, const void* SFA, const void* SFB,
               const cutlass::bfloat16_t* C, float alpha, float beta, void* D, void* SFD, float st) {
   auto layout_A = make_layout(make_shape(M, K, 1), make_stride(int64_t(K), _1{}, int64_t(M) * K));
@@ -45,6 +47,19 @@ void run_gemm(int M, int N, int K, const void* A, const void* B, const void* SFA
       mainloop{tA, tSFA, tB, tSFB};
 
   Tensor tC = make_tensor(const_cast<cutlass::bfloat16_t*>(C), layout_C);
+  if constexpr (GenSfd && ColMajorD) {
+    // D stored column-major (M contiguous), scale factors per SfdVec consecutive ROWS of a column, in the
+    // reference's M-major scale-factor layout (the branch of gett.hpp:392-430)
+    auto layout_D = make_layout(make_shape(M, N, 1), make_stride(_1{}, int64_t(M), int64_t(M) * N));
+    Tensor tD = make_tensor(recast_ptr<ElemD>(D), layout_D);
+    auto layout_SFD = SfOutCfgColMajor<SfdVec>::tile_atom_to_shape_SFD(make_shape(M, N, K, 1));
+    Tensor tSFD = make_tensor(reinterpret_cast<ElemSFD*>(SFD), layout_SFD);
+    cutlass::reference::host::GettBlockScalingEpilogueParams<float, float, float, decltype(tC), decltype(tD), decltype(tSFD),
+                                                             cute::Int<SfdVec>, cutlass::reference::host::SfStrategy::SfDGen>
+        epi{alpha, beta, tC, tD, tSFD, st};
+    cutlass::reference::host::Gemm3x(mainloop, epi);
+    return;
+  }
   Tensor tD = make_tensor(recast_ptr<ElemD>(D), layout_C);
   if constexpr (GenSfd) {
     auto layout_SFD = SfOutCfg<SfdVec>::tile_atom_to_shape_SFD(make_shape(M, N, K, 1));
@@ -148,7 +163,8 @@ int64_t bsg_ref_sf_size(int vec, int rows, int K) {
 }
 
 // kind 0 NVFP4 / 1 MXFP8 / 2 MXFP4 / 3 mixed (A e4m3, B e2m1; out_mode 0 and 1 only for 2 and 3).  out_mode 0: D fp32, 1: D bf16, 2: D e2m1 + SFD ue4m3 per 16 (NVFP4 re-quantisation with norm
-// constant st), 3: D e4m3 + SFD ue8m0 per 32 (MXFP8 re-quantisation).
+// constant st), 3: D e4m3 + SFD ue8m0 per 32 (MXFP8 re-quantisation); 4 / 5 (kind 0 only): as 2 / 3 with D stored
+// column-major (M contiguous) and the scale factors per 16 / 32 consecutive rows of a column.
 // C is bf16 (may be null when beta == 0).  Returns 0 on success.
 int bsg_ref_gemm(int kind, int out_mode, int M, int N, int K, const void* A, const void* B, const void* SFA, const void* SFB,
                  const void* C, float alpha, float beta, void* D, void* SFD, float st) {
@@ -160,6 +176,8 @@ int bsg_ref_gemm(int kind, int out_mode, int M, int N, int K, const void* A, con
     else if (out_mode == 1) run_gemm<E, S, 16, cutlass::bfloat16_t, false>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, nullptr, 0.f);
     else if (out_mode == 2) run_gemm<E, S, 16, cutlass::float_e2m1_t, true>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, SFD, st);
     else if (out_mode == 3) run_gemm<E, S, 16, cutlass::float_e4m3_t, true, 32, cutlass::float_ue8m0_t>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, SFD, st);
+    else if (out_mode == 4) run_gemm<E, S, 16, cutlass::float_e2m1_t, true, 16, cutlass::float_ue4m3_t, E, true>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, SFD, st);
+    else if (out_mode == 5) run_gemm<E, S, 16, cutlass::float_e4m3_t, true, 32, cutlass::float_ue8m0_t, E, true>(M, N, K, A, B, SFA, SFB, Cb, alpha, beta, D, SFD, st);
     else return 1;
   } else if (kind == 1) {
     using E = cutlass::float_e4m3_t;

@@ -40,7 +40,7 @@ def test_version_and_error_string(lib):
 def test_struct_sizes_match_header_layout():
     # 4 int32, 3 int64, 7 pointers, 2 int64, 2 float, 3 pointers, 4 int32; bias pointer, bias_mode, activation;
     # lda, ldb and four batch strides (int64); use_pdl, scheduler and four cluster extents (int32)
-    assert C.sizeof(L.GemmArgs) == 16 + 24 + 56 + 16 + 8 + 24 + 16 + 16 + 48 + 24
+    assert C.sizeof(L.GemmArgs) == 16 + 24 + 56 + 16 + 8 + 24 + 16 + 16 + 48 + 24 + 8      # + out_layout, reserved1
     # ... alpha_array, beta_array; SFD, norm_constant, use_pdl, scheduler
     assert C.sizeof(L.GroupedArgs) == 16 + 24 + 56 + 16 + 8 + 16 + 16 + 16 + 24
     assert C.sizeof(L.Caps) == 32

@@ -225,3 +225,35 @@ def test_mxfp4_and_mixed_operands(cuda_lib, kind, M, N, K, tile_n, exact):
 def test_mxfp4_and_mixed_grouped(cuda_lib, kind):
     got, want = run_grouped(kind, [300, 0, 129, 512], 384, 512, seed=75 + kind)
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("out_kind", [1, 2])
+@pytest.mark.parametrize("kind,M,N,K,pitch", [(0, 256, 512, 256, 0), (1, 384, 200, 512, 448), (0, 1280, 1096, 256, 0)])
+def test_column_major_quantised_output(cuda_lib, kind, out_kind, M, N, K, pitch):
+    """BSG_LAYOUT_COL_MAJOR: D stored as (N, M) with M contiguous, scale factors per 16 / 32 consecutive rows of a
+    column, in the K-major scale layout of the transposed matrix.  Bit for bit the oracle's row-major routine on the
+    transpose (pinned against the compiled reference's M-major output)."""
+    rng, A, sfa, B, sfb = make_operands(kind, M, N, K, seed=80, exact=True)
+    Cb = G.bf16_normal((M, N), rng)
+    pre = oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K, Cb, 1.0, 0.5)
+    st = float(np.float32(448.0 * 6.0 / np.abs(pre).max())) if out_kind == 1 else 0.25
+    vec = 16 if out_kind == 1 else 32
+    ldd = pitch or M
+    col_bytes = ldd // 2 if out_kind == 1 else ldd
+    dD = torch.full((N, col_bytes), 0x55, dtype=torch.uint8, device="cuda")
+    dSFD = torch.full((F.numel_scale(N, M, vec),), 0x7F, dtype=torch.uint8, device="cuda")
+    nc = torch.tensor([st], dtype=torch.float32, device="cuda")
+    t = [dev(x) for x in (A, B, sfa, sfb, Cb)]
+    a = L.GemmArgs()
+    a.kind, a.out_kind, a.batch, a.M, a.N, a.K = kind, out_kind, 1, M, N, K
+    a.A, a.B, a.SFA, a.SFB, a.C, a.D = (x.data_ptr() for x in (*t, dD))
+    a.SFD, a.norm_constant = dSFD.data_ptr(), nc.data_ptr()
+    a.alpha, a.beta, a.ldd, a.out_layout = 1.0, 0.5, ldd, L.LAYOUT_COL_MAJOR
+    _run(a)
+    Dw, SFDw = oracle.quant(0 if out_kind == 1 else 1, np.ascontiguousarray(pre.T), st)
+    got = dD.cpu().numpy()
+    used = M // 2 if out_kind == 1 else M
+    assert np.array_equal(got[:, :used], Dw)
+    assert np.all(got[:, used:] == 0x55), "the pitch padding of D must stay untouched"
+    idx = R.sf_index(N, M // vec)
+    assert np.array_equal(dSFD.cpu().numpy()[idx], SFDw[idx])

@@ -120,6 +120,22 @@ def test_fused_nvfp4_output_bit_exact(cuda_lib, exact, beta):
     assert np.array_equal(SFD[idx], SFDw[idx])
 
 
+@pytest.mark.parametrize("out_kind", [1, 2])
+def test_fused_quantisation_with_nan_and_infinity_matches_the_oracle(cuda_lib, out_kind):
+    """NaN / infinity reaching the fused output quantisation (through C): the same bytes as the oracle, whose handling of
+    such blocks is pinned against the compiled reference (NaN poisons its block; ue8m0 turns infinity into NaN)."""
+    M, N, K = 256, 512, 256
+    rng, A, sfa, B, sfb = make_operands(0, M, N, K, seed=13, exact=True)
+    Cb = G.bf16_normal((M, N), rng)
+    Cb[3, 5], Cb[7, 300], Cb[9, 17], Cb[200, 511], Cb[130, 64] = 0x7FC0, 0xFFC0, 0x7F80, 0xFF80, 0x7FC0
+    pre = oracle.gemm_fp32(0, A, sfa, B, sfb, M, N, K, Cb, 1.0, 1.0)
+    D, SFD = run_dense(0, M, N, K, A, sfa, B, sfb, Cb, 1.0, 1.0, out_kind=out_kind, st=2.0)
+    Dw, SFDw = oracle.quant(0 if out_kind == 1 else 1, pre, 2.0)
+    idx = R.sf_index(M, N // (16 if out_kind == 1 else 32))
+    assert np.array_equal(D, Dw)
+    assert np.array_equal(SFD[idx], SFDw[idx])
+
+
 @pytest.mark.parametrize("kind,exact,beta,st", [(0, True, 0.0, None), (0, False, 0.5, 3.0), (1, True, 0.0, 0.25), (1, False, 0.5, None)])
 def test_fused_mxfp8_output_bit_exact(cuda_lib, kind, exact, beta, st):
     """e4m3 data and ue8m0 scale factors (round-up conversion) of the fused MXFP8 re-quantisation against the oracle.

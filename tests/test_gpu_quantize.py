@@ -125,3 +125,24 @@ def test_quantiser_full_size_matches_oracle(kind):
     want_q, want_sf = oracle.quant(kind, x.float().cpu().numpy(), 3.0 if kind == 0 else 1.0)
     assert np.array_equal(q, want_q)
     assert np.array_equal(sf, want_sf)          # no padding at this size: the whole buffer is defined
+
+
+@pytest.mark.parametrize("kind", [0, 1])
+def test_nan_and_infinity_inputs_match_the_oracle(cuda_lib, kind):
+    """NaN and infinite inputs: the block maximum propagates NaN as the reference's does, so the kernel's bytes equal
+    the oracle's (itself pinned against the compiled reference on such inputs)."""
+    import cutlass_b200 as ops
+    rng = np.random.default_rng(5)
+    rows, K = 256, 512
+    x = rng.standard_normal((rows, K)).astype(np.float32)
+    x[3, 5], x[7, 300], x[9, 17], x[200, 511], x[130, 64] = np.nan, -np.nan, np.inf, -np.inf, np.nan
+    xb = torch.from_numpy(x).to(torch.bfloat16).cuda()
+    mode = ops.ScaleMode.Blockwise1x16 if kind == 0 else ops.ScaleMode.Blockwise1x32
+    q = ops.quantize_blockscaled(xb, mode)
+    torch.cuda.synchronize()
+    want_q, want_sf = oracle.quant(kind, xb.float().cpu().numpy(), 1.0)
+    vec = 16 if kind == 0 else 32
+    r, kb = np.meshgrid(np.arange(rows), np.arange(K // vec), indexing="ij")
+    idx = F.sf_offset(r, kb, F.sf_k_atoms(K, vec)).ravel()
+    assert np.array_equal(q.quantized.tensor.cpu().numpy().view(np.uint8), want_q)
+    assert np.array_equal(q.scale.tensor.cpu().numpy().view(np.uint8)[idx], want_sf[idx])

@@ -157,6 +157,51 @@ def test_both_output_quantisations_on_wide_magnitudes_equal_compiled_reference(s
 
 
 @pytest.mark.skipif(ref_missing, reason="compiled reference driver (oracle/_ref) not present")
+@pytest.mark.skipif(ref_missing, reason="compiled reference driver (oracle/_ref) not present")
+@pytest.mark.parametrize("M,N,K", [(160, 200, 128), (128, 64, 64), (96, 333 // 3 * 3 + 1, 192)])
+def test_column_major_quantised_output_is_the_row_major_routine_on_the_transpose(M, N, K):
+    """The reference's M-major scale-factor output (D column-major, one scale factor per 16 / 32 consecutive rows of a
+    column; gett.hpp:392-430 with Sm1xxBlockScaledOutputConfig<V, Major::MN>) equals the row-major routine applied to
+    the transposed matrix, values and scale-factor bytes alike: that is the oracle of the kernels' column-major output."""
+    rng = np.random.default_rng(M + N)
+    A, _, sfa = G.nvfp4_operand(M, K, rng)
+    B, _, sfb = G.nvfp4_operand(N, K, rng)
+    Cb = G.bf16_normal((M, N), rng)
+    pre = oracle.gemm_fp32(0, A, sfa, B, sfb, M, N, K, Cb, 1.0, 0.5)
+    for mode, qkind, vec in ((4, 0, 16), (5, 1, 32)):
+        Dr, Sr = oracle.ref_gemm(0, mode, A, sfa, B, sfb, M, N, K, Cb, 1.0, 0.5, 3.0)
+        Do, So = oracle.quant(qkind, np.ascontiguousarray(pre.T), 3.0)
+        idx = R.sf_index(N, M // vec)
+        assert np.array_equal(Dr, Do) and np.array_equal(Sr[idx], So[idx])
+
+
+@pytest.mark.skipif(ref_missing, reason="compiled reference driver (oracle/_ref) not present")
+def test_nan_and_infinity_in_a_block_equal_compiled_reference():
+    """The reference's block maximum and its clamp of the scale propagate NaN (maximum_with_nan_propogation,
+    minimum_with_nan_propagation): one NaN makes the block's scale factor a NaN code and every value of the block the
+    format's NaN code (e4m3) or its largest value (e2m1 has no NaN).  An infinite accumulator saturates the ue4m3
+    scale factor; ue8m0 has no infinity and turns it into its NaN code."""
+    rng = np.random.default_rng(1)
+    M, N, K = 128, 64, 64
+    A, _, sfa = G.nvfp4_operand(M, K, rng)
+    B, _, sfb = G.nvfp4_operand(N, K, rng)
+    Cb = G.bf16_normal((M, N), rng)
+    Cb[3, 5], Cb[7, 40], Cb[9, 17], Cb[11, 3] = 0x7FC0, 0xFFC0, 0x7F80, 0xFF80        # NaN, -NaN, +inf, -inf
+    pre = oracle.gemm_fp32(0, A, sfa, B, sfb, M, N, K, Cb, 1.0, 1.0)
+    for mode, qkind, vec in ((2, 0, 16), (3, 1, 32)):
+        Dr, Sr = oracle.ref_gemm(0, mode, A, sfa, B, sfb, M, N, K, Cb, 1.0, 1.0, 2.0)
+        Do, So = oracle.quant(qkind, pre, 2.0)
+        idx = R.sf_index(M, N // vec)
+        assert np.array_equal(Do, Dr) and np.array_equal(So[idx], Sr[idx])
+        # what those blocks look like
+        nan_sf = 0x7F if qkind == 0 else 0xFF
+        assert Sr[idx][3, 0] == nan_sf and Sr[idx][7, 40 // vec] == nan_sf
+        if qkind == 0:
+            assert np.all(Dr[3, :8] == 0x77) and Sr[idx][9, 1] == 0x7E
+        else:
+            assert np.all(Dr[3, :32] == 0x7F) and Sr[idx][9, 0] == 0xFF and np.all(Dr[9, :32] == 0x7F)
+
+
 @pytest.mark.parametrize("kind", [0, 1])
 @pytest.mark.parametrize("act,per_row", [(0, False), (1, True), (2, False), (3, True)])
 def test_epilogue_with_bias_and_activation_equals_compiled_reference(kind, act, per_row):
