@@ -27,6 +27,78 @@ def _shard_operand(rows: int, K: int, seed: int, device):
     return bench.gpu_mxfp8_operand(rows, K, gen, device)
 
 
+def _reduce_scatter_leg(dev, rank: int, world: int, stream, steps: int) -> dict:
+    """Times bsg_rs_gemm_run (MXFP8, M = 16384, N = 8192, K = 28672 / world per rank) against the unfused form (the dense
+    kernel into a bf16 M x N buffer, then ncclReduceScatter), and compares the two results (they differ by the bf16
+    rounding of the running sums at every hop of the ring, so the check is a tolerance, not bit equality)."""
+    import torch
+    import torch.distributed as dist
+    from cutlass_b200 import lib as L
+    from cutlass_b200 import tp as TP
+    M, N, K = 16384, 8192, 28672
+    kl, ms = K // world, M // world
+    kind = L.KIND_MXFP8
+    A, SFA = _shard_operand(M, kl, 7000 + rank, dev)
+    B, SFB = _shard_operand(N, kl, 8000 + rank, dev)
+    rs = TP.RsGemm(M, N)
+    outs = [torch.empty((ms, N), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    abi = [rs.build_args(kind, A, SFA, B, SFB, o) for o in outs]
+    for i in range(3):
+        rs.run(kind, A, SFA, B, SFB, outs[i % 2], stream=stream, abi_args=abi[i % 2])
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(steps):
+        rs.run(kind, A, SFA, B, SFB, outs[i % 2], stream=stream, abi_args=abi[i % 2])
+    e1.record(stream)
+    torch.cuda.synchronize()
+    rs.check_device_status(stream)
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    fused_ms = float(t.item()) / steps
+    # unfused: every rank's full partial product in bf16, then NCCL's reduce-scatter
+    lib = L.load()
+    full = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    ref_out = torch.empty((ms, N), dtype=torch.bfloat16, device=dev)
+    d = L.GemmArgs()
+    d.kind, d.batch, d.M, d.N, d.K = kind, 1, M, N, kl
+    d.A, d.SFA, d.B, d.SFB, d.D = A.data_ptr(), SFA.data_ptr(), B.data_ptr(), SFB.data_ptr(), full.data_ptr()
+    d.alpha = 1.0
+    ws = torch.zeros(16, dtype=torch.uint8, device=dev)
+
+    def unfused():
+        rc = lib.bsg_gemm_run(C.byref(d), ws.data_ptr(), 16, stream.cuda_stream)
+        assert rc == 0, L.last_error()
+        if world > 1:
+            dist.reduce_scatter_tensor(ref_out, full)
+        else:
+            ref_out.copy_(full)
+    for _ in range(2):
+        unfused()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0.record(stream)
+    for _ in range(steps):
+        unfused()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    unfused_ms = float(t.item()) / steps
+    diff = (outs[(steps - 1) % 2].float() - ref_out.float()).abs().max() / ref_out.float().abs().max().clamp_min(1e-30)
+    dt = torch.tensor([float(diff)], dtype=torch.float64, device=dev)
+    dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+    rs.close()
+    flops = 2.0 * M * N * K
+    return {"workload": f"MXFP8 GEMM + reduce-scatter M={M} N={N} K={K}: K sharded over the ranks, D reduced and scattered over M",
+            "ms_per_step": round(fused_ms, 4), "value": round(flops / fused_ms / 1e9, 1), "unit": "TFLOP/s", "steps": steps,
+            "unfused_nccl": {"ms_per_step": round(unfused_ms, 4), "value": round(flops / unfused_ms / 1e9, 1),
+                             "what": "the dense kernel into a bf16 M x N buffer, then ncclReduceScatter"},
+            "max_rel_diff_vs_unfused": float(dt.item()),
+            "note": "the fused form rounds the running sum to bf16 at every hop, NCCL's reduction rounds once"}
+
+
 def run(args) -> dict:
     import torch
     import torch.distributed as dist
@@ -227,6 +299,15 @@ def run(args) -> dict:
     e2e_ms = float(te.item()) / n_e2e
     tp.check_device_status(stream)
 
+    # ---- the row-parallel counterpart: GEMM + reduce-scatter (K sharded, the result reduced and scattered over M),
+    # the shape of the MLP's second projection: M = 16384, N = 8192, K = 28672 over all ranks
+    rs_out = None
+    if os.environ.get("BSG_BENCH_RS", "1") != "0":
+        try:
+            rs_out = _reduce_scatter_leg(dev, rank, world, stream, max(3, min(args.steps, 20)))
+        except Exception as exc:  # noqa: BLE001
+            rs_out = {"error": repr(exc)}
+
     peaks = bench.measured_peaks()
     long_region = region_ms >= 1000.0
     key = "bf16_tflops_sustained" if long_region else "bf16_tflops"
@@ -257,6 +338,7 @@ def run(args) -> dict:
         "scaling_base": base,
         "efficiency_vs_scaling_base": round(tflops / (world * base["value"]), 4) if base else None,
         "parity": parity,
+        "reduce_scatter": rs_out,
     }
     tp.close()
     dist.barrier()

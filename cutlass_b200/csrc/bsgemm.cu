@@ -179,7 +179,7 @@ struct Problem {
   int32_t tile_m_rotate;
   // tensor parallel (TP kernel variant)
   bool tp;
-  int32_t tp_world, tp_rank, tp_rows_per_shard, tp_ksplit, tp_push_in_kernel, tp_release_announce;
+  int32_t tp_world, tp_rank, tp_rows_per_shard, tp_ksplit, tp_push_in_kernel, tp_release_announce, tp_paced_push;
   uint32_t tp_epoch;
   const float* bias;
   const float* alpha_array;
@@ -434,6 +434,7 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
     p.tp_world = q.tp_world; p.tp_rank = q.tp_rank; p.tp_rows_per_shard = q.tp_rows_per_shard; p.tp_ksplit = q.tp_ksplit; p.tp_push_in_kernel = q.tp_push_in_kernel;
     p.tp_epoch = q.tp_epoch;
     p.tp_release_announce = q.tp_release_announce;
+    p.tp_paced_push = q.tp_paced_push;
     p.tp_ready_target = q.tp_ready_target;
     p.tp_remote_row_offset = q.tp_parity ? int32_t(q.total_rows) : 0;
     p.tp_row_bytes = q.tp_row_bytes; p.tp_sfa_rowatom_bytes = q.tp_sfa_rowatom_bytes;
@@ -942,6 +943,7 @@ int32_t bsg_tp_gemm_run(bsg_tp_comm* c, const bsg_gemm_args* args, void* workspa
   const bool copy_engine = c->world > 1 && (c->mode & BSG_TP_PUSH_COPY_ENGINE) != 0;
   q.tp_push_in_kernel = copy_engine ? 0 : 1;
   q.tp_release_announce = (c->mode & BSG_TP_RELEASE_ANNOUNCE) ? 1 : 0;
+  q.tp_paced_push = (c->mode & BSG_TP_PACED_PUSH) ? 1 : 0;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (copy_engine) {
     if (!workspace || workspace_bytes < 16) return fail(BSG_ERR_WORKSPACE_NULL, "workspace is null or smaller than 16 bytes");
@@ -1092,7 +1094,7 @@ int32_t bsg_rs_destroy(bsg_rs_comm* c) {
 
 int32_t bsg_tp_set_mode(bsg_tp_comm* c, int32_t mode) {
   if (!c) return fail(BSG_ERR_INVALID_PROBLEM, "null communicator");
-  if (mode < 0 || mode > (BSG_TP_PUSH_COPY_ENGINE | BSG_TP_SINGLE_BUFFER | BSG_TP_RELEASE_ANNOUNCE)) return fail(BSG_ERR_NOT_SUPPORTED, "unknown tensor-parallel mode %d", mode);
+  if (mode < 0 || mode > (BSG_TP_PUSH_COPY_ENGINE | BSG_TP_SINGLE_BUFFER | BSG_TP_RELEASE_ANNOUNCE | BSG_TP_PACED_PUSH)) return fail(BSG_ERR_NOT_SUPPORTED, "unknown tensor-parallel mode %d", mode);
   c->mode = mode;
   return BSG_OK;
 }

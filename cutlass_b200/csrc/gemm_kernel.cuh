@@ -104,6 +104,9 @@ struct GemmParams {
   int32_t tp_ksplit;          // pieces a 256-row block is cut into (one flag increment each)
   int32_t tp_push_in_kernel;  // 1: the push warp moves the data; 0: the host's copy-engine transfers do
   int32_t tp_release_announce; // 1: a batch of announcements is preceded by a proxy fence and a system-scope release fence
+  int32_t tp_paced_push;      // 1: the shard for the j-th nearest consumer is pushed while this CTA works on stage j - 1
+                              //    of its own walk (all ranks walk in step, so it arrives one stage before it is needed),
+                              //    instead of everything as fast as the links allow at the start of the kernel
   uint32_t tp_epoch;          // call counter, starts at 1; the peers use the same value
   uint32_t tp_ready_target;       // a peer's buffer may be filled once its "launched call" word has reached this
   int32_t tp_remote_row_offset;   // rows between the buffer this call gathers into and buffer 0 (0 or M)
@@ -205,6 +208,7 @@ struct alignas(16) Ctl {
   int32_t sched_w[4];
   uint32_t tmem_base;
   volatile uint32_t abort;
+  volatile int32_t tp_stage_now;   // tensor parallel: stage (shard index in consumption order) of the tile the producer is on
   int32_t total_tiles;
   int32_t pad;
   int32_t tile_start[kMaxGroups + 1];
@@ -508,6 +512,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       ptx::mbar_init(ptx::smem_u32(&ctl->clc_bar[s]), 1);
     }
     ctl->abort = 0;
+    ctl->tp_stage_now = 0;
     ptx::fence_mbar_init();
     ptx::fence_proxy_async();
   }
@@ -626,6 +631,9 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const TileInfo ti = decode_tile(ctl, p, wi.t, C::kTileM);
       // Tensor parallel: rows of other ranks are read from the gathered buffer of this call, which lies
       // tp_remote_row_offset rows behind buffer 0 in the same tensor map; own rows always from buffer 0.
+      if constexpr (TP) {
+        if (lane == 0) ctl->tp_stage_now = ti.tm_walk / (p.tp_rows_per_shard / C::kTileM);
+      }
       const bool tp_remote = TP && ti.row0 / p.tp_rows_per_shard != p.tp_rank;
       const int32_t tp_row_off = tp_remote ? p.tp_remote_row_offset : 0;
       const int32_t a_row = bcast(ti.map_row0 + int32_t(cta_rank) * C::kCtaM + tp_row_off);
@@ -699,6 +707,9 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       } else {
         w = static_next(w);
       }
+    }
+    if constexpr (TP) {
+      if (lane == 0) ctl->tp_stage_now = 1 << 20;      // nothing left to pace against
     }
     // Tail: every stage must have been released, so that no commit-arrive is still
     // in flight towards this CTA's shared memory when it exits.
@@ -856,6 +867,12 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       for (; st_it.valid(); st_it.next(p), ++n_st) {
         const uint32_t b = n_st % nb;
         if (st_it.dst_rank != checked) {
+          if (p.tp_paced_push) {
+            // j-th nearest consumer: its rows are due when it starts stage j, which is when this rank does too
+            const int j = (p.tp_rank - st_it.dst_rank + p.tp_world) % p.tp_world;
+            const long long t0 = clock64();
+            while (ctl->tp_stage_now < j - 1 && !ctl->abort && clock64() - t0 < 4000000000ll) __nanosleep(500);
+          }
           // The peer's buffer is free once the peer has launched the call after the one that last read it.
           if (!wait_flag_ge(sync + kTpSyncReady + st_it.dst_rank, p.tp_ready_target, ctl)) peer_ok = false;
           checked = st_it.dst_rank;
