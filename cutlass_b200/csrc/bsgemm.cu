@@ -57,10 +57,14 @@ struct MapKey {
   int32_t dtype, swizzle, l2;
 };
 
+// Set while the per-group maps of a pointer-array call are encoded: hundreds of one-off maps would only push the
+// dense calls' entries out of the cache.
+thread_local bool g_bypass_map_cache = false;
+
 class MapCache {
  public:
   int32_t get(const MapKey& k, CUtensorMap* out) {
-    {
+    if (!g_bypass_map_cache) {
       std::lock_guard<std::mutex> lock(mu_);
       for (int i = 0; i < kEntries; ++i) {
         if (used_[i] && memcmp(&keys_[i], &k, sizeof(MapKey)) == 0) {
@@ -85,6 +89,7 @@ class MapCache {
                   (unsigned long long)k.dims[0], (unsigned long long)k.dims[1], (unsigned long long)k.dims[2],
                   (unsigned long long)k.strides[0], (unsigned long long)k.strides[1]);
     memcpy(out, &m, sizeof(CUtensorMap));
+    if (g_bypass_map_cache) return BSG_OK;
     std::lock_guard<std::mutex> lock(mu_);
     int victim = 0;
     for (int i = 0; i < kEntries; ++i) {
@@ -294,14 +299,14 @@ struct KernelSetup {
   int max_clusters[64] = {};
 };
 
-template <int KIND, int CG, int BN, bool TP, bool DYN, bool RS>
+template <int KIND, int CG, int BN, bool TP, bool DYN, bool RS, bool PTR = false>
 int32_t kernel_setup(int dev, int* max_clusters) {
   using Cf = bsg::Cfg<KIND, CG, BN, TP>;
   static KernelSetup ks;
   if (dev < 0 || dev >= 64) return fail(BSG_ERR_NOT_SUPPORTED, "device ordinal %d is outside [0, 64)", dev);
   std::lock_guard<std::mutex> lock(ks.mu);
   if (!ks.done[dev]) {
-    auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN, TP, DYN, RS>;
+    auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN, TP, DYN, RS, PTR>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::kSmemBytes);
     if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg;
@@ -551,6 +556,165 @@ int32_t run_problem(const Problem& q, void* workspace, size_t ws_bytes, void* st
   if (q.kind == BSG_KIND_MXFP4)
     return plan.tile_n == 256 ? launch<2, 2, 256>(q, plan, status, stream, sms, dev, false) : launch<2, 2, 128>(q, plan, status, stream, sms, dev, false);
   return plan.tile_n == 256 ? launch<3, 2, 256>(q, plan, status, stream, sms, dev, false) : launch<3, 2, 128>(q, plan, status, stream, sms, dev, false);
+}
+
+
+// ------------------------------------------------------------------------------ pointer-array grouped form
+constexpr size_t kPtrTableOffset = 8192;      // the group table starts here in the workspace (the status word sits at 0)
+
+struct PtrGroup {
+  int64_t M, N, K, lda, ldb, ldc, ldd;
+  const void *A, *B, *SFA, *SFB, *C;
+  void *D, *SFD;
+};
+
+PtrGroup ptr_group(const bsg_ptr_array_args* a, int g) {
+  PtrGroup r;
+  r.M = a->problem_sizes[3 * g + 0]; r.N = a->problem_sizes[3 * g + 1]; r.K = a->problem_sizes[3 * g + 2];
+  r.lda = a->lda ? a->lda[g] : r.K; r.ldb = a->ldb ? a->ldb[g] : r.K;
+  r.ldc = a->ldc ? a->ldc[g] : r.N; r.ldd = a->ldd ? a->ldd[g] : r.N;
+  r.A = a->A[g]; r.B = a->B[g]; r.SFA = a->SFA[g]; r.SFB = a->SFB[g];
+  r.C = a->C ? a->C[g] : nullptr;
+  r.D = a->D[g];
+  r.SFD = a->SFD ? a->SFD[g] : nullptr;
+  return r;
+}
+
+// What bsg_ptr_array_initialize left in a workspace, remembered on the host so that a run can check that it
+// launches against a table made for the same problem.
+struct PtrTableInfo {
+  int32_t kind, out_kind, num_groups, tile_n;
+  int64_t total_tiles, total_rows;
+  uint64_t sizes_hash;
+};
+std::mutex g_ptr_tables_mutex;
+constexpr int kPtrTables = 256;
+struct { const void* ws; PtrTableInfo info; } g_ptr_tables[kPtrTables];
+int g_ptr_tables_next = 0;
+
+uint64_t hash_sizes(const int32_t* v, int n) {
+  uint64_t h = 1469598103934665603ull;
+  for (int i = 0; i < n; ++i) { h ^= uint64_t(uint32_t(v[i])); h *= 1099511628211ull; }
+  return h;
+}
+
+// Checks the call-level fields and every group (the dense rules, group by group); returns the tile width and counts.
+int32_t ptr_array_check(const bsg_ptr_array_args* a, PtrTableInfo* info) {
+  if (!a) return fail(BSG_ERR_INVALID_PROBLEM, "args is null");
+  if (a->kind != BSG_KIND_NVFP4 && a->kind != BSG_KIND_MXFP8) return fail(BSG_ERR_NOT_SUPPORTED, "the pointer-array form takes NVFP4 or MXFP8 operands (kind %d)", a->kind);
+  if (a->num_groups < 1 || a->num_groups > BSG_MAX_GROUPS) return fail(BSG_ERR_INVALID_PROBLEM, "group count %d outside [1, %d]", a->num_groups, BSG_MAX_GROUPS);
+  if (!a->problem_sizes || !a->A || !a->B || !a->SFA || !a->SFB || !a->D) return fail(BSG_ERR_INVALID_PROBLEM, "problem_sizes, A, B, SFA, SFB and D arrays must be non-null");
+  if (a->out_kind != BSG_OUT_BF16 && !a->SFD) return fail(BSG_ERR_INVALID_PROBLEM, "quantised output needs the SFD array");
+  if (a->tile_n != 0 && a->tile_n != 128 && a->tile_n != 256) return fail(BSG_ERR_NOT_SUPPORTED, "tile_n must be 0, 128 or 256");
+  if (a->use_pdl != 0 && a->use_pdl != 1) return fail(BSG_ERR_INVALID_PROBLEM, "use_pdl must be 0 or 1");
+  if ((a->beta != 0.0f || a->beta_array) && !a->C) return fail(BSG_ERR_INVALID_PROBLEM, "beta needs the C array");
+  int64_t max_n = 0, total_rows = 0;
+  for (int g = 0; g < a->num_groups; ++g) {
+    const PtrGroup r = ptr_group(a, g);
+    if (r.M < 0 || r.N < 0 || r.K < 1) return fail(BSG_ERR_INVALID_PROBLEM, "group %d: extents M=%lld N=%lld K=%lld", g, (long long)r.M, (long long)r.N, (long long)r.K);
+    if (r.M == 0 || r.N == 0) continue;
+    Problem q;
+    memset(&q, 0, sizeof(q));
+    q.kind = a->kind; q.out_kind = a->out_kind; q.num_groups = 1;
+    q.rows_per_group = r.M; q.total_rows = r.M; q.N = r.N; q.K = r.K;
+    q.A = r.A; q.B = r.B; q.SFA = r.SFA; q.SFB = r.SFB; q.C = r.C; q.D = r.D; q.SFD = r.SFD;
+    q.b_per_group = true;
+    q.lda = r.lda; q.ldb = r.ldb; q.ldc = r.ldc; q.ldd = r.ldd;
+    q.alpha = a->alpha; q.beta = r.C ? a->beta : 0.0f; q.norm_ptr = a->norm_constant;
+    q.activation = a->activation; q.cta_group = 2;
+    Plan plan;
+    const int32_t rc = validate(q, &plan);
+    if (rc != BSG_OK) {
+      char inner[400];
+      snprintf(inner, sizeof(inner), "%s", g_err);
+      return fail(rc, "group %d: %s", g, inner);
+    }
+    if ((a->beta != 0.0f || a->beta_array) && !r.C) return fail(BSG_ERR_INVALID_PROBLEM, "group %d: beta needs C", g);
+    max_n = r.N > max_n ? r.N : max_n;
+    total_rows += r.M;
+  }
+  const int32_t tn = a->tile_n ? a->tile_n : (max_n > 128 ? 256 : 128);
+  int64_t tiles = 0;
+  for (int g = 0; g < a->num_groups; ++g) {
+    const int64_t M = a->problem_sizes[3 * g], N = a->problem_sizes[3 * g + 1];
+    tiles += ((M + 255) / 256) * ((N + tn - 1) / tn);
+  }
+  if (tiles > 0x3FFFFFFF) return fail(BSG_ERR_INVALID_PROBLEM, "too many tiles for one launch");
+  info->kind = a->kind; info->out_kind = a->out_kind; info->num_groups = a->num_groups; info->tile_n = tn;
+  info->total_tiles = tiles; info->total_rows = total_rows;
+  info->sizes_hash = hash_sizes(a->problem_sizes, 3 * a->num_groups);
+  return BSG_OK;
+}
+
+template <int KIND, int BN>
+int32_t ptr_array_encode(const bsg_ptr_array_args* a, bsg::GroupDesc* table) {
+  using Cf = bsg::Cfg<KIND, 2, BN>;
+  const bool fp4 = bsg::kind_packs_fp4(KIND);
+  for (int g = 0; g < a->num_groups; ++g) {
+    const PtrGroup r = ptr_group(a, g);
+    bsg::GroupDesc& d = table[g];
+    d.M = int32_t(r.M); d.N = int32_t(r.N); d.K = int32_t(r.K);
+    d.C = static_cast<const __nv_bfloat16*>(r.C); d.D = r.D; d.SFD = static_cast<uint8_t*>(r.SFD);
+    d.ldc = r.ldc; d.ldd = r.ldd;
+    if (r.M == 0 || r.N == 0) continue;
+    const uint64_t k_bytes = uint64_t(fp4 ? r.K / 2 : r.K);
+    const uint64_t lda_bytes = uint64_t(fp4 ? r.lda / 2 : r.lda), ldb_bytes = uint64_t(fp4 ? r.ldb / 2 : r.ldb);
+    const uint64_t k_atoms = uint64_t(((r.K + Cf::kSfVec - 1) / Cf::kSfVec + 3) / 4);
+    int32_t rc;
+    if ((rc = make_operand_map(&d.tmA, r.A, k_bytes, uint64_t(r.M), 1, lda_bytes, uint64_t(r.M) * lda_bytes, Cf::kCtaM)) != BSG_OK) return rc;
+    if ((rc = make_operand_map(&d.tmB, r.B, k_bytes, uint64_t(r.N), 1, ldb_bytes, uint64_t(r.N) * ldb_bytes, Cf::kBRowsCta)) != BSG_OK) return rc;
+    if ((rc = make_sf_map(&d.tmSFA, r.SFA, k_atoms, uint64_t((r.M + 127) / 128), Cf::kKAtoms, 1)) != BSG_OK) return rc;
+    if ((rc = make_sf_map(&d.tmSFB, r.SFB, k_atoms, uint64_t((r.N + 127) / 128), Cf::kKAtoms, BN / 128)) != BSG_OK) return rc;
+    if ((rc = make_out_map(&d.tmD, r.D, a->out_kind, uint64_t(r.N), uint64_t(r.M), 1, uint64_t(r.ldd), uint64_t(r.M) * uint64_t(r.ldd))) != BSG_OK) return rc;
+  }
+  return BSG_OK;
+}
+
+template <int KIND, int BN>
+int32_t ptr_array_launch(const bsg_ptr_array_args* a, const PtrTableInfo& info, uint8_t* workspace, cudaStream_t stream, int sms, int dev) {
+  using Cf = bsg::Cfg<KIND, 2, BN>;
+  bsg::GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.num_groups = a->num_groups;
+  p.total_rows = int32_t(info.total_rows);
+  p.raster_band = a->raster_band > 0 ? a->raster_band : 16;
+  p.out_kind = a->out_kind;
+  p.alpha = a->alpha; p.beta = a->beta;
+  p.alpha_array = a->alpha_array; p.beta_array = a->beta_array;
+  p.norm_ptr = a->norm_constant;
+  p.activation = a->activation;
+  p.status = reinterpret_cast<uint32_t*>(workspace);
+  p.split_tail = 1;
+  p.group_desc = reinterpret_cast<const bsg::GroupDesc*>(workspace + kPtrTableOffset);
+  int max_clusters = 0;
+  int32_t rc = kernel_setup<KIND, 2, BN, false, false, false, true>(dev, &max_clusters);
+  if (rc != BSG_OK) return rc;
+  int64_t clusters = sms / 2;
+  if (max_clusters > 0 && clusters > max_clusters) clusters = max_clusters;
+  if (info.total_tiles < clusters) clusters = info.total_tiles;
+  if (clusters < 1) clusters = 1;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(unsigned(clusters * 2), 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = Cf::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (a->use_pdl) {
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
+  // The six map parameters of the kernel are not used in this form (every group brings its own in the table).
+  CUtensorMap none;
+  memset(&none, 0, sizeof(none));
+  cudaError_t e = cudaLaunchKernelEx(&cfg, bsg::bsg_gemm_kernel<KIND, 2, BN, false, false, false, true>, none, none, none, none, none, none, p);
+  if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(e));
+  return BSG_OK;
 }
 
 Problem from_dense(const bsg_gemm_args* a) {
@@ -810,6 +974,81 @@ int32_t bsg_quantize(const bsg_quant_args* a, void* cuda_stream) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "quantiser launch: %s", cudaGetErrorString(e));
   return BSG_OK;
+}
+
+int32_t bsg_ptr_array_workspace_size(const bsg_ptr_array_args* args, size_t* bytes) {
+  if (!args || !bytes) return fail(BSG_ERR_INVALID_PROBLEM, "null argument");
+  if (args->num_groups < 1 || args->num_groups > BSG_MAX_GROUPS) return fail(BSG_ERR_INVALID_PROBLEM, "group count %d outside [1, %d]", args->num_groups, BSG_MAX_GROUPS);
+  *bytes = kPtrTableOffset + size_t(args->num_groups) * sizeof(bsg::GroupDesc);
+  return BSG_OK;
+}
+
+int32_t bsg_ptr_array_initialize(const bsg_ptr_array_args* args, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  PtrTableInfo info;
+  int32_t rc = ptr_array_check(args, &info);
+  if (rc != BSG_OK) return rc;
+  if (!workspace) return fail(BSG_ERR_WORKSPACE_NULL, "workspace is null");
+  const size_t need = kPtrTableOffset + size_t(args->num_groups) * sizeof(bsg::GroupDesc);
+  if (workspace_bytes < need) return fail(BSG_ERR_WORKSPACE_NULL, "workspace of %zu bytes is smaller than the %zu needed", workspace_bytes, need);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 127u) != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "the workspace of the pointer-array form must be 128-byte aligned");
+  bsg::GroupDesc* table = static_cast<bsg::GroupDesc*>(calloc(size_t(args->num_groups), sizeof(bsg::GroupDesc)));
+  if (!table) return fail(BSG_ERR_INTERNAL, "out of host memory");
+  g_bypass_map_cache = true;
+  if (args->kind == BSG_KIND_NVFP4) rc = info.tile_n == 256 ? ptr_array_encode<0, 256>(args, table) : ptr_array_encode<0, 128>(args, table);
+  else rc = info.tile_n == 256 ? ptr_array_encode<1, 256>(args, table) : ptr_array_encode<1, 128>(args, table);
+  g_bypass_map_cache = false;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  cudaError_t e = cudaSuccess;
+  if (rc == BSG_OK) {
+    e = cudaMemsetAsync(workspace, 0, 16, stream);
+    // pageable source: the copy has left the host buffer when the call returns
+    if (e == cudaSuccess) e = cudaMemcpyAsync(static_cast<uint8_t*>(workspace) + kPtrTableOffset, table, size_t(args->num_groups) * sizeof(bsg::GroupDesc), cudaMemcpyHostToDevice, stream);
+  }
+  free(table);
+  if (rc != BSG_OK) return rc;
+  if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "uploading the group table: %s", cudaGetErrorString(e));
+  std::lock_guard<std::mutex> lock(g_ptr_tables_mutex);
+  int slot = -1;
+  for (int i = 0; i < kPtrTables; ++i) if (g_ptr_tables[i].ws == workspace) { slot = i; break; }
+  if (slot < 0) { slot = g_ptr_tables_next; g_ptr_tables_next = (g_ptr_tables_next + 1) % kPtrTables; }
+  g_ptr_tables[slot].ws = workspace;
+  g_ptr_tables[slot].info = info;
+  return BSG_OK;
+}
+
+int32_t bsg_ptr_array_run(const bsg_ptr_array_args* args, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  if (!args || !args->problem_sizes) return fail(BSG_ERR_INVALID_PROBLEM, "args or problem_sizes is null");
+  if (!workspace) return fail(BSG_ERR_WORKSPACE_NULL, "workspace is null");
+  if (args->num_groups < 1 || args->num_groups > BSG_MAX_GROUPS) return fail(BSG_ERR_INVALID_PROBLEM, "group count %d outside [1, %d]", args->num_groups, BSG_MAX_GROUPS);
+  PtrTableInfo info;
+  {
+    std::lock_guard<std::mutex> lock(g_ptr_tables_mutex);
+    int slot = -1;
+    for (int i = 0; i < kPtrTables; ++i) if (g_ptr_tables[i].ws == workspace) { slot = i; break; }
+    if (slot < 0) return fail(BSG_ERR_INVALID_PROBLEM, "bsg_ptr_array_initialize has not been called for this workspace");
+    info = g_ptr_tables[slot].info;
+  }
+  if (info.kind != args->kind || info.out_kind != args->out_kind || info.num_groups != args->num_groups ||
+      info.sizes_hash != hash_sizes(args->problem_sizes, 3 * args->num_groups) || (args->tile_n != 0 && args->tile_n != info.tile_n))
+    return fail(BSG_ERR_INVALID_PROBLEM, "the arguments differ from those the workspace was initialised with");
+  if (workspace_bytes < kPtrTableOffset + size_t(args->num_groups) * sizeof(bsg::GroupDesc)) return fail(BSG_ERR_WORKSPACE_NULL, "workspace too small");
+  if (args->use_pdl != 0 && args->use_pdl != 1) return fail(BSG_ERR_INVALID_PROBLEM, "use_pdl must be 0 or 1");
+  if (args->activation < BSG_ACT_IDENTITY || args->activation > BSG_ACT_SILU) return fail(BSG_ERR_NOT_SUPPORTED, "unknown activation %d", args->activation);
+  if (args->out_kind == BSG_OUT_NVFP4 && !args->norm_constant) return fail(BSG_ERR_INVALID_PROBLEM, "NVFP4 output needs norm_constant");
+  if ((args->beta != 0.0f || args->beta_array) && !args->C) return fail(BSG_ERR_INVALID_PROBLEM, "beta needs the C array");
+  int dev = 0, major = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (major != 10) return fail(BSG_ERR_ARCH_MISMATCH, "device compute capability %d.x is not sm_100", major);
+  if (args->sm_count > 0 && args->sm_count < sms) sms = args->sm_count;
+  if (info.total_tiles == 0) return BSG_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  if (args->kind == BSG_KIND_NVFP4)
+    return info.tile_n == 256 ? ptr_array_launch<0, 256>(args, info, ws, stream, sms, dev) : ptr_array_launch<0, 128>(args, info, ws, stream, sms, dev);
+  return info.tile_n == 256 ? ptr_array_launch<1, 256>(args, info, ws, stream, sms, dev) : ptr_array_launch<1, 128>(args, info, ws, stream, sms, dev);
 }
 
 int32_t bsg_tp_create(int32_t rank, int32_t world, int32_t kind, int64_t M, int64_t K, bsg_tp_comm** out, void* ipc_handle_out) {

@@ -56,6 +56,19 @@ constexpr uint32_t kStTimeoutTmemEmpty = 8u;  // MMA warp: accumulator never dra
 constexpr uint32_t kStTimeoutFlag = 16u;      // producer: row-ready flag never set
 constexpr uint32_t kStBadOffsets = 32u;       // grouped: offsets not monotone / out of range
 
+// Pointer-array grouped form (kernel template PTR == true): every group is a problem of its own, with its own
+// extents, tensors and tensor maps.  The host encodes one record per group and uploads the array; the kernel reads the
+// maps from global memory (after a tensor-map proxy fence) and the extents into its group table.
+struct alignas(128) GroupDesc {
+  CUtensorMap tmA, tmB, tmSFA, tmSFB, tmD;
+  int32_t M, N, K, pad;
+  const __nv_bfloat16* C;
+  void* D;
+  uint8_t* SFD;
+  int64_t ldc, ldd;      // elements
+};
+static_assert(sizeof(GroupDesc) == 768, "group record size is part of the workspace contract");
+
 struct GemmParams {
   int32_t num_groups;         // 1 for a dense GEMM
   int32_t rows_per_group;     // dense / batched: M of every group (offsets == nullptr)
@@ -130,6 +143,7 @@ struct GemmParams {
   uint32_t* rs_sync;              // this rank's sync words: [0] = call number the right neighbour ... see kRsSync*
   uint32_t* rs_sync_left;         // sync words of rank - 1
   uint32_t* rs_sync_right;        // sync words of rank + 1
+  const GroupDesc* group_desc;    // pointer-array grouped form: one record per group (device memory)
   const uint8_t* tp_peer_a[8];    // gathered A buffer of every rank that this call fills (own entry = source: local buffer 0)
   const uint8_t* tp_peer_sfa[8];
   uint32_t* tp_peer_sync[8];      // sync words of every rank: [0,8) "rank q has launched call n", [32, ...) row-block counters
@@ -215,6 +229,8 @@ struct alignas(16) Ctl {
   int32_t row0[kMaxGroups];
   int32_t rows[kMaxGroups];
   int32_t atom0[kMaxGroups];
+  int32_t gN[kMaxGroups];   // pointer-array grouped form: N and K of every group
+  int32_t gK[kMaxGroups];
 };
 static_assert(sizeof(Ctl) <= 8192, "control block too large");
 
@@ -228,21 +244,32 @@ struct TileInfo {
   int32_t map_row0;   // row coordinate of the tile's first row in the A / D tensor maps
   int32_t map_l;      // third coordinate there (batch entry; 0 when rows run over all groups)
   int32_t tm_walk;    // position of the tile row in the walk over M (before the rotation of the starting row)
+  int32_t N, K;       // extents of the tile's problem (those of its group in the pointer-array form)
 };
 
-__device__ __forceinline__ TileInfo decode_tile(const Ctl* ctl, const GemmParams& p, int32_t t, int32_t tile_m) {
-  int lo = 0, hi = p.num_groups;
+// Group that holds tile t (binary search in the prefix of tile counts).
+__device__ __forceinline__ int32_t group_of_tile(const Ctl* ctl, int32_t num_groups, int32_t t) {
+  int lo = 0, hi = num_groups;
   while (hi - lo > 1) {
     int mid = (lo + hi) >> 1;
     if (ctl->tile_start[mid] <= t) lo = mid; else hi = mid;
   }
+  return lo;
+}
+
+// `bn` / `ptr`: tile width and whether the groups have extents of their own (both compile-time at the call sites).
+__device__ __forceinline__ TileInfo decode_tile(const Ctl* ctl, const GemmParams& p, int32_t t, int32_t tile_m, int32_t bn, bool ptr) {
+  const int lo = group_of_tile(ctl, p.num_groups, t);
   TileInfo ti;
   ti.g = lo;
+  ti.N = ptr ? ctl->gN[lo] : p.N;
+  ti.K = ptr ? ctl->gK[lo] : p.K;
+  const int32_t tiles_n = ptr ? (ti.N + bn - 1) / bn : p.tiles_n;
   const int32_t local = t - ctl->tile_start[lo];
   const int32_t rows = ctl->rows[lo];
   const int32_t tiles_m = (rows + tile_m - 1) / tile_m;
   const int32_t band = p.raster_band;
-  const int32_t per_band = band * p.tiles_n;
+  const int32_t per_band = band * tiles_n;
   const int32_t b = local / per_band;
   const int32_t rem = local - b * per_band;
   const int32_t bh = min(band, tiles_m - b * band);
@@ -472,7 +499,7 @@ __device__ __forceinline__ int32_t sched_consume(Ctl* ctl, uint32_t k, uint32_t&
   return dead ? -1 : w;
 }
 
-template <int KIND, int CG, int BN, bool TP = false, bool DYN = false, bool RS = false>
+template <int KIND, int CG, int BN, bool TP = false, bool DYN = false, bool RS = false, bool PTR = false>
 __global__ void __launch_bounds__(TP ? 224 : 192, 1)
 bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
@@ -516,7 +543,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     ptx::fence_mbar_init();
     ptx::fence_proxy_async();
   }
-  if (warp == 5 && lane == 0) {
+  if (!PTR && warp == 5 && lane == 0) {
     ptx::prefetch_tmap(&tmA);
     ptx::prefetch_tmap(&tmB);
     ptx::prefetch_tmap(&tmSFA);
@@ -539,23 +566,40 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   }
   // Group table: end rows first (parallel), then a serial prefix by one thread.
   for (int g = threadIdx.x; g < p.num_groups; g += blockDim.x) {
-    ctl->rows[g] = p.offsets ? p.offsets[g] : (g + 1) * p.rows_per_group;   // holds END rows for now
+    if constexpr (PTR) {
+      const GroupDesc* gd = p.group_desc + g;
+      ctl->rows[g] = gd->M;
+      ctl->gN[g] = gd->N;
+      ctl->gK[g] = gd->K;
+    } else {
+      ctl->rows[g] = p.offsets ? p.offsets[g] : (g + 1) * p.rows_per_group;   // holds END rows for now
+    }
   }
   __syncthreads();
   if (threadIdx.x == 32) {
     int32_t prev_end = 0, tiles = 0, atoms = 0;
     bool bad = false;
     for (int g = 0; g < p.num_groups; ++g) {
-      int32_t end = ctl->rows[g];
-      if (end < prev_end || end > p.total_rows) { bad = true; end = prev_end; }
-      const int32_t rows = end - prev_end;
-      ctl->tile_start[g] = tiles;
-      ctl->row0[g] = prev_end;
-      ctl->rows[g] = rows;
-      ctl->atom0[g] = atoms;
-      tiles += ((rows + C::kTileM - 1) / C::kTileM) * p.tiles_n;
-      atoms += (rows + 127) / 128;
-      prev_end = end;
+      if constexpr (PTR) {
+        // every group starts at row 0 of its own tensors
+        const int32_t rows = max(ctl->rows[g], 0);
+        ctl->tile_start[g] = tiles;
+        ctl->row0[g] = 0;
+        ctl->rows[g] = rows;
+        ctl->atom0[g] = 0;
+        tiles += ((rows + C::kTileM - 1) / C::kTileM) * ((max(ctl->gN[g], 0) + BN - 1) / BN);
+      } else {
+        int32_t end = ctl->rows[g];
+        if (end < prev_end || end > p.total_rows) { bad = true; end = prev_end; }
+        const int32_t rows = end - prev_end;
+        ctl->tile_start[g] = tiles;
+        ctl->row0[g] = prev_end;
+        ctl->rows[g] = rows;
+        ctl->atom0[g] = atoms;
+        tiles += ((rows + C::kTileM - 1) / C::kTileM) * p.tiles_n;
+        atoms += (rows + 127) / 128;
+        prev_end = end;
+      }
     }
     ctl->tile_start[p.num_groups] = tiles;
     ctl->total_tiles = tiles;
@@ -628,7 +672,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
       if (w < total_work) {
       const WorkItem wi = decode_work(w, split_from);
-      const TileInfo ti = decode_tile(ctl, p, wi.t, C::kTileM);
+      const TileInfo ti = decode_tile(ctl, p, wi.t, C::kTileM, BN, PTR);
       // Tensor parallel: rows of other ranks are read from the gathered buffer of this call, which lies
       // tp_remote_row_offset rows behind buffer 0 in the same tensor map; own rows always from buffer 0.
       if constexpr (TP) {
@@ -647,6 +691,18 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const int32_t group_atoms = (ti.row_end - ti.group_row0 + 127) >> 7;
       const int32_t sfa_atom = bcast(min(ti.sf_atom + int32_t(cta_rank), ti.group_atom0 + max(group_atoms, 1) - 1) + (tp_row_off >> 7));
       const int32_t sfb_atom = bcast(ti.g * p.sfb_atoms_per_group + ti.tn * (BN / 128) + wi.half);
+      // Pointer-array form: the group's own tensor maps (in global memory) and depth.
+      const CUtensorMap *mapA = &tmA, *mapB = &tmB, *mapSFA = &tmSFA, *mapSFB = &tmSFB;
+      int32_t tile_k_tiles = k_tiles;
+      if constexpr (PTR) {
+        const GroupDesc* gd = p.group_desc + bcast(ti.g);
+        mapA = &gd->tmA; mapB = &gd->tmB; mapSFA = &gd->tmSFA; mapSFB = &gd->tmSFB;
+        tile_k_tiles = bcast((ti.K + C::kTileK - 1) / C::kTileK);
+        if (elected) {
+          ptx::fence_tensormap_acquire(mapA); ptx::fence_tensormap_acquire(mapB);
+          ptx::fence_tensormap_acquire(mapSFA); ptx::fence_tensormap_acquire(mapSFB);
+        }
+      }
       if (p.ready_flags != nullptr && (!TP || tp_remote)) {
         const uint32_t* flag = p.ready_flags + ti.row0 / p.rows_per_flag;
         const long long t0 = clock64();
@@ -662,7 +718,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         asm volatile("fence.proxy.async;" ::: "memory");
         __syncwarp();
       }
-      for (int32_t kt = 0; kt < k_tiles; ++kt) {
+      for (int32_t kt = 0; kt < tile_k_tiles; ++kt) {
         wait_barrier(empty0 + stage * 8, phase ^ 1u, ctl, dead);
         BSG_DBG(0, 1);
         // After a timeout nothing more is issued: free-running loads would overrun the barriers' byte counts.
@@ -670,10 +726,10 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           const uint32_t full_local = full0 + stage * 8;
           if (is_leader) ptx::mbar_arrive_expect_tx(full_local, uint32_t(C::kStageTxBytes) * CG);
           const uint32_t bar = full0_leader + stage * 8;
-          ptx::tma_load_3d<CG>(sA0 + stage * C::kABytes, &tmA, bar, kt * C::kRowBytes, a_row, a_l);
-          ptx::tma_load_3d<CG>(sB0 + stage * C::kBBytes, &tmB, bar, kt * C::kRowBytes, b_row, b_l);
-          ptx::tma_load_3d<CG>(sSFA0 + stage * C::kSfaBytes, &tmSFA, bar, 0, kt * C::kKAtoms, sfa_atom);
-          ptx::tma_load_3d<CG>(sSFB0 + stage * C::kSfbBytes, &tmSFB, bar, 0, kt * C::kKAtoms, sfb_atom);
+          ptx::tma_load_3d<CG>(sA0 + stage * C::kABytes, mapA, bar, kt * C::kRowBytes, a_row, a_l);
+          ptx::tma_load_3d<CG>(sB0 + stage * C::kBBytes, mapB, bar, kt * C::kRowBytes, b_row, b_l);
+          ptx::tma_load_3d<CG>(sSFA0 + stage * C::kSfaBytes, mapSFA, bar, 0, kt * C::kKAtoms, sfa_atom);
+          ptx::tma_load_3d<CG>(sSFB0 + stage * C::kSfbBytes, mapSFB, bar, 0, kt * C::kKAtoms, sfb_atom);
         }
         if (++stage == C::kStages) { stage = 0; phase ^= 1u; }
       }
@@ -740,11 +796,16 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int acc_bar = it % C::kAccBars;
         const uint32_t acc_phase = uint32_t(it / C::kAccBars) & 1u;
         const uint32_t d_tmem = tmem_base + uint32_t(it & 1) * C::kAccStride;
+        int32_t tile_K = p.K, tile_k_tiles = k_tiles;
+        if constexpr (PTR) {
+          tile_K = bcast(ctl->gK[group_of_tile(ctl, p.num_groups, decode_work(w, split_from).t)]);
+          tile_k_tiles = (tile_K + C::kTileK - 1) / C::kTileK;
+        }
         BSG_DBG(1, 9);
         wait_barrier(tempty0 + acc_bar * 8, acc_phase ^ 1u, ctl, dead);
         BSG_DBG(1, 10);
         ptx::tc_fence_after();
-        for (int32_t kt = 0; kt < k_tiles; ++kt) {
+        for (int32_t kt = 0; kt < tile_k_tiles; ++kt) {
           if (!ready) wait_barrier(full0 + stage * 8, phase, ctl, dead);
           BSG_DBG(1, 11);
           int next_stage = stage + 1;
@@ -756,7 +817,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           const uint32_t sfb_s = sSFB0 + stage * C::kSfbBytes;
           const uint64_t a_desc = make_desc_sw128(sA0 + stage * C::kABytes);
           const uint64_t b_desc = make_desc_sw128(sB0 + stage * C::kBBytes);
-          const int32_t k_left = p.K - kt * C::kTileK;
+          const int32_t k_left = tile_K - kt * C::kTileK;
           const int n_mma = k_left >= C::kTileK ? 4 : (k_left + C::kMmaK - 1) / C::kMmaK;
           const uint32_t acc_flag = kt > 0 ? 1u : 0u;
           const uint32_t sfa_col = tmem_base + C::kSfaCol;
@@ -929,7 +990,6 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       st_scaled = __fmul_rn(st, __fdiv_rn(1.0f, p.out_kind == kOutNvfp4 ? 6.0f : 448.0f));
     }
     const int32_t sfd_vec = p.out_kind == kOutMxfp8 ? 32 : 16;
-    const int32_t sfd_k_atoms = ((p.N + sfd_vec - 1) / sfd_vec + 3) / 4;
     const uint32_t tfull0 = ptx::smem_u32(&ctl->tmem_full[0]);
     const uint32_t tempty0 = ptx::smem_u32(&ctl->tmem_empty[0]);
     uint8_t* stage_buf = sEpi + warp * 4096;                     // this warp's 32 x 128-byte staging tile
@@ -939,13 +999,27 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     for (int32_t w = first_work; w >= 0; w = DYN ? sched_consume<CG>(ctl, step++, dead) : static_next(w)) {
       if (w >= total_work) continue;
       const WorkItem wi = decode_work(w, split_from);
-      const TileInfo ti = decode_tile(ctl, p, wi.t, C::kTileM);
+      const TileInfo ti = decode_tile(ctl, p, wi.t, C::kTileM, BN, PTR);
       const int32_t tile_col0 = ti.tn * BN + wi.half * (BN / 2);       // first output column of this work item
       const int n_pairs = wi.split ? C::kPairs / 2 : C::kPairs;          // a half tile fills the accumulator's first BN / 2 columns
       // One alpha / beta per group when the arrays are given (grouped GEMM), else the scalars.
       const float alpha = p.alpha_array ? __ldg(p.alpha_array + ti.g) : alpha_all;
       const float beta = p.beta_array ? __ldg(p.beta_array + ti.g) : beta_all;
-      bool use_c = (p.C != nullptr) && (beta != 0.0f);
+      // The problem this tile belongs to: the call's, or (pointer-array form) its group's own tensors and extents.
+      const __nv_bfloat16* Cg = p.C;
+      uint8_t* Dg = reinterpret_cast<uint8_t*>(p.D);
+      uint8_t* SFDg = p.SFD;
+      int64_t ldc = p.ldc, ldd = p.ldd;
+      const CUtensorMap* mapD = &tmD;
+      if constexpr (PTR) {
+        const GroupDesc* gd = p.group_desc + ti.g;
+        Cg = gd->C; Dg = reinterpret_cast<uint8_t*>(gd->D); SFDg = gd->SFD; ldc = gd->ldc; ldd = gd->ldd;
+        mapD = &gd->tmD;
+        if (lane == 0) ptx::fence_tensormap_acquire(mapD);
+      }
+      const int32_t prob_N = ti.N;
+      const int32_t sfd_k_atoms = ((prob_N + sfd_vec - 1) / sfd_vec + 3) / 4;
+      bool use_c = (Cg != nullptr) && (beta != 0.0f);
       // Reduce-scatter: stage of this tile row, where its addend comes from and where its result goes.
       int32_t rs_stage = 0;
       bool rs_to_peer = false;
@@ -989,8 +1063,8 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       // Reduce-scatter: row of this lane inside its slice, and the rows of the receive buffers it reads / writes.
       const int32_t rs_row_in_slice = RS ? (ti.tm_walk % p.rs_tiles_per_slice) * C::kTileM + int32_t(cta_rank) * C::kCtaM + warp * 32 : 0;
       const int64_t c_row_off = RS ? int64_t(p.rs_parity_rows + (rs_stage - 1) * p.rs_slice_rows + rs_row_in_slice + lane) * p.N
-                                   : int64_t(ti.map_l) * p.batch_stride_c + int64_t(warp_map_row0 + lane) * p.ldc;
-      const int64_t d_row_off = int64_t(ti.map_l) * p.batch_stride_d + int64_t(warp_map_row0 + lane) * p.ldd;
+                                   : int64_t(ti.map_l) * p.batch_stride_c + int64_t(warp_map_row0 + lane) * ldc;
+      const int64_t d_row_off = int64_t(ti.map_l) * p.batch_stride_d + int64_t(warp_map_row0 + lane) * ldd;
       const uint32_t lane_addr = tmem_base + (uint32_t(warp * 32) << 16) + acc_col;
       const bool reverse = (BN == 256) && ((it & 1) == 0);
       const uint32_t empty_bar = tempty0 + acc_bar * 8;
@@ -999,7 +1073,8 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       // stores them row by row.)
       const int out_kind = p.out_kind;
       const bool col_major = out_kind != kOutBf16 && p.out_col_major != 0;
-      const bool tma_out = (cta_row0 + warp * 32 + 32 <= ti.row_end) && !col_major;
+      // (Pointer-array form: every group has a map of its own, which clips at the group's last row.)
+      const bool tma_out = (PTR ? cta_row0 + warp * 32 < ti.row_end : cta_row0 + warp * 32 + 32 <= ti.row_end) && !col_major;
       // Staging sub-buffers a warp cycles through (4 KB per warp): bf16 uses all of it per 64 columns, e4m3 half,
       // e2m1 a quarter; a sub-buffer is rewritten once all but the newest n_bufs - 1 stores have read theirs.
       const int n_bufs = out_kind == kOutBf16 ? 1 : out_kind == kOutMxfp8 ? 2 : 4;
@@ -1039,7 +1114,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int32_t col0 = tile_col0 + pr * 64 + h * 32;
-          const int32_t cols_valid = p.N - col0;
+          const int32_t cols_valid = prob_N - col0;
           if (cols_valid <= 0 || (!row_ok && !tma_out)) continue;
 
           float x[32];
@@ -1066,7 +1141,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int j = 0; j < 32; ++j) x[j] = __fadd_rn(x[j], bv);
           }
           if (use_c && row_ok) {
-            const __nv_bfloat16* crow = (RS ? p.rs_recv : p.C) + c_row_off + col0;
+            const __nv_bfloat16* crow = (RS ? p.rs_recv : Cg) + c_row_off + col0;
             const float beta_c = RS ? 1.0f : beta;
             if (cols_valid >= 32) {
 #pragma unroll
@@ -1116,8 +1191,8 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const int32_t col = col0 + lane;
             const int32_t m0 = lrow - lane;                                  // first row of the warp's slab (multiple of 32)
             const int32_t m_k_atoms = ((p.rows_per_group + sfd_vec - 1) / sfd_vec + 3) / 4;
-            if (col < p.N && grow - lane < ti.row_end) {
-              uint8_t* sf_base = p.SFD + int64_t(col / 128) * (512ll * m_k_atoms) + 16 * (col & 31) + 4 * ((col & 127) >> 5);
+            if (col < prob_N && grow - lane < ti.row_end) {
+              uint8_t* sf_base = SFDg + int64_t(col / 128) * (512ll * m_k_atoms) + 16 * (col & 31) + 4 * ((col & 127) >> 5);
               if (out_kind == kOutNvfp4) {
                 uint32_t packed[4];
                 uint32_t codes = 0;
@@ -1138,7 +1213,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     packed[b * 2 + e] = ptx::cvt_e2m1x8(z);
                   }
                 }
-                *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.D) + (int64_t(col) * p.ldd + m0) / 2) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                *reinterpret_cast<uint4*>(Dg + (int64_t(col) * ldd + m0) / 2) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                 const int32_t mb = m0 >> 4;                                  // even: the two blocks share a 16-bit word
                 *reinterpret_cast<uint16_t*>(sf_base + (mb >> 2) * 512 + (mb & 3)) = uint16_t(codes);
               } else {
@@ -1152,7 +1227,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                 for (int e = 0; e < 8; ++e)
                   w[e] = ptx::cvt_e4m3x4(__fmul_rn(y[e * 4 + 0], sc), __fmul_rn(y[e * 4 + 1], sc), __fmul_rn(y[e * 4 + 2], sc), __fmul_rn(y[e * 4 + 3], sc));
-                uint4* dcol = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.D) + int64_t(col) * p.ldd + m0);
+                uint4* dcol = reinterpret_cast<uint4*>(Dg + int64_t(col) * ldd + m0);
                 dcol[0] = make_uint4(w[0], w[1], w[2], w[3]);
                 dcol[1] = make_uint4(w[4], w[5], w[6], w[7]);
                 const int32_t mb = m0 >> 5;
@@ -1173,7 +1248,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 *reinterpret_cast<uint4*>(stage_buf + lane * 128 + chunk * 16) = o;
               }
             } else {
-              __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D) + d_row_off + col0;
+              __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(Dg) + d_row_off + col0;
               if (cols_valid >= 32) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
@@ -1213,7 +1288,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               *reinterpret_cast<uint4*>(sub_buf + lane * 64 + (((h * 2 + 0) ^ sw) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
               *reinterpret_cast<uint4*>(sub_buf + lane * 64 + (((h * 2 + 1) ^ sw) * 16)) = make_uint4(w[4], w[5], w[6], w[7]);
             } else if (cols_valid >= 32) {
-              uint8_t* drow = reinterpret_cast<uint8_t*>(p.D) + d_row_off + col0;
+              uint8_t* drow = Dg + d_row_off + col0;
               reinterpret_cast<uint4*>(drow)[0] = make_uint4(w[0], w[1], w[2], w[3]);
               reinterpret_cast<uint4*>(drow)[1] = make_uint4(w[4], w[5], w[6], w[7]);
             }
@@ -1245,19 +1320,19 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               // 32-byte rows, no swizzle: a warp's 32 rows fill 1 KB back to back.
               *reinterpret_cast<uint4*>(sub_buf + lane * 32 + h * 16) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             } else {
-              uint8_t* drow = reinterpret_cast<uint8_t*>(p.D) + (d_row_off + col0) / 2;
+              uint8_t* drow = Dg + (d_row_off + col0) / 2;
               if (cols_valid >= 32) *reinterpret_cast<uint4*>(drow) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
               else if (cols_valid >= 16) *reinterpret_cast<uint2*>(drow) = make_uint2(packed[0], packed[1]);
             }
           }
         }
-        if (out_kind != kOutBf16 && !col_major && row_ok && tile_col0 + pr * 64 < p.N) {
+        if (out_kind != kOutBf16 && !col_major && row_ok && tile_col0 + pr * 64 < prob_N) {
           // Scale factors of this row for the 64 columns: consecutive bytes of one 512-byte atom of the interleaved
           // layout (4 per row for 16-wide blocks, 2 for 32-wide ones).
           const int32_t pair_col0 = tile_col0 + pr * 64;
-          const int32_t cols_left = p.N - pair_col0;
+          const int32_t cols_left = prob_N - pair_col0;
           const int32_t nb = pair_col0 / sfd_vec;
-          uint8_t* sfp = p.SFD + (int64_t(ti.group_atom0) + lrow / 128) * (512ll * sfd_k_atoms) + (nb >> 2) * 512 +
+          uint8_t* sfp = SFDg + (int64_t(ti.group_atom0) + lrow / 128) * (512ll * sfd_k_atoms) + (nb >> 2) * 512 +
                          16 * (lrow & 31) + 4 * ((lrow & 127) >> 5) + (nb & 3);
           if (out_kind == kOutNvfp4) {
             if (cols_left >= 64) *reinterpret_cast<uint32_t*>(sfp) = sf_pair;
@@ -1281,7 +1356,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             else if (RS)
               ptx::tma_store_3d(&tmD, ptx::smem_u32(sub_buf), col, rs_row_in_slice, 0);
             else
-              ptx::tma_store_3d(&tmD, ptx::smem_u32(sub_buf), out_kind == kOutNvfp4 ? col / 2 : col, warp_map_row0, ti.map_l);
+              ptx::tma_store_3d(mapD, ptx::smem_u32(sub_buf), out_kind == kOutNvfp4 ? col / 2 : col, warp_map_row0, ti.map_l);
             ptx::bulk_commit_group();
           }
         }

@@ -273,6 +273,11 @@ __device__ __forceinline__ void bulk_wait_group() {
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
+// A tensor map that lies in global memory and was written there through the generic proxy (a copy from the host):
+// the thread that hands it to the TMA engine first makes that write visible to the tensor-map proxy.
+__device__ __forceinline__ void fence_tensormap_acquire(const void* tmap) {
+  asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
+}
 
 // ---------------------------------------------------------------- tcgen05
 template <int CG>

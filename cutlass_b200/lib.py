@@ -80,6 +80,19 @@ class Caps(C.Structure):
     ]
 
 
+class PtrArrayArgs(C.Structure):
+    """``bsg_ptr_array_args`` of include/bsgemm.h, field for field (the arrays are HOST arrays)."""
+    _fields_ = [
+        ("kind", C.c_int32), ("out_kind", C.c_int32), ("num_groups", C.c_int32), ("activation", C.c_int32),
+        ("problem_sizes", C.c_void_p),
+        ("A", C.c_void_p), ("B", C.c_void_p), ("SFA", C.c_void_p), ("SFB", C.c_void_p), ("C", C.c_void_p), ("D", C.c_void_p), ("SFD", C.c_void_p),
+        ("lda", C.c_void_p), ("ldb", C.c_void_p), ("ldc", C.c_void_p), ("ldd", C.c_void_p),
+        ("alpha", C.c_float), ("beta", C.c_float),
+        ("alpha_array", C.c_void_p), ("beta_array", C.c_void_p), ("norm_constant", C.c_void_p),
+        ("tile_n", C.c_int32), ("sm_count", C.c_int32), ("raster_band", C.c_int32), ("use_pdl", C.c_int32),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/bsgemm.h declares.
 class QuantArgs(C.Structure):
     """``bsg_quant_args`` of include/bsgemm.h, field for field."""
@@ -99,6 +112,9 @@ SYMBOLS = {
     "bsg_workspace_init": (C.c_int32, [C.c_void_p, C.c_size_t, C.c_void_p]),
     "bsg_read_device_status": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "bsg_gemm_run_static": (C.c_int32, [C.POINTER(GemmArgs), C.c_void_p, C.POINTER(C.c_uint32)]),
+    "bsg_ptr_array_workspace_size": (C.c_int32, [C.POINTER(PtrArrayArgs), C.POINTER(C.c_size_t)]),
+    "bsg_ptr_array_initialize": (C.c_int32, [C.POINTER(PtrArrayArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "bsg_ptr_array_run": (C.c_int32, [C.POINTER(PtrArrayArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "bsg_quantize": (C.c_int32, [C.POINTER(QuantArgs), C.c_void_p]),
     "bsg_tp_create": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.POINTER(C.c_void_p), C.c_void_p]),
     "bsg_tp_connect": (C.c_int32, [C.c_void_p, C.c_void_p]),

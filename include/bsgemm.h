@@ -230,6 +230,61 @@ int32_t bsg_grouped_run(const bsg_grouped_args* args, void* workspace, size_t wo
 int32_t bsg_read_device_status(void* workspace, void* cuda_stream);
 
 /*
+ * Grouped GEMM in the pointer-array form: every group is a problem of its own -- its own (M, N, K), its own A, B,
+ * SFA, SFB, C, D (and SFD) tensors with their own row pitches.  Mirrors cutlass::library::GroupedGemmBlockScaledArguments
+ * with GroupProblemShape (tools/library/include/cutlass/library/library.h:558-605,
+ * include/cutlass/gemm/group_array_problem_shape.hpp:55-83; device-side tensor-map updates in
+ * include/cutlass/gemm/collective/sm100_blockscaled_mma_array_warpspecialized.hpp:1142-1343).
+ *
+ * Difference to the reference, which keeps its pointer arrays in device memory and rewrites one tensor map per
+ * operand on the device whenever a CTA moves to another group: here the problem sizes and pointer arrays are HOST
+ * arrays (the reference passes a host copy of the sizes too, problem_sizes_3x_host).  bsg_ptr_array_initialize encodes
+ * five tensor maps per group on the host and uploads them, with the extents, as one table into the workspace; the
+ * kernel reads a group's maps from that table.  bsg_ptr_array_run only launches.  A caller that holds device arrays
+ * copies them to the host once, where the reference's Operation::initialize runs (library.h:547-556).
+ *
+ * Per group g: A_g is (M_g, K_g) K-major with pitch lda[g], B_g is (N_g, K_g) with pitch ldb[g], SFA_g / SFB_g are
+ * interleaved layouts over (M_g, K_g / V) and (N_g, K_g / V), C_g / D_g are (M_g, N_g) with pitches ldc[g] / ldd[g],
+ * SFD_g an interleaved layout over (M_g, N_g / V_out).  Alignment rules per group are those of bsg_gemm_args.
+ * Groups with M_g == 0 or N_g == 0 are skipped.  Static scheduler, cta_group 2, row-major outputs.
+ */
+typedef struct bsg_ptr_array_args {
+  int32_t kind;                 /* BSG_KIND_NVFP4 or BSG_KIND_MXFP8 */
+  int32_t out_kind;             /* BSG_OUT_* */
+  int32_t num_groups;           /* 1..BSG_MAX_GROUPS */
+  int32_t activation;           /* BSG_ACT_* */
+  const int32_t* problem_sizes; /* HOST int32[num_groups][3]: M, N, K of every group */
+  const void* const* A;         /* HOST arrays of num_groups device pointers each */
+  const void* const* B;
+  const void* const* SFA;
+  const void* const* SFB;
+  const void* const* C;         /* or NULL (no C anywhere); single entries may be NULL too */
+  void* const* D;
+  void* const* SFD;             /* quantised outputs only, else NULL */
+  const int64_t* lda;           /* HOST int64[num_groups], elements; NULL: packed (K_g, K_g, N_g, N_g) */
+  const int64_t* ldb;
+  const int64_t* ldc;
+  const int64_t* ldd;
+  float alpha, beta;
+  const float* alpha_array;     /* device fp32[num_groups] or NULL, as in bsg_grouped_args */
+  const float* beta_array;
+  const float* norm_constant;   /* device fp32 scalar (NVFP4 output) */
+  int32_t tile_n;               /* 0 = auto, 128 or 256 */
+  int32_t sm_count;
+  int32_t raster_band;
+  int32_t use_pdl;
+} bsg_ptr_array_args;
+
+/* Workspace: the status word plus the per-group table (768 bytes per group). */
+int32_t bsg_ptr_array_workspace_size(const bsg_ptr_array_args* args, size_t* bytes);
+/* Checks every group, encodes its tensor maps and copies the table into the workspace (on the stream; the host
+ * arrays may be released when the call returns).  Call again whenever a pointer, size or pitch changes. */
+int32_t bsg_ptr_array_initialize(const bsg_ptr_array_args* args, void* workspace, size_t workspace_bytes, void* cuda_stream);
+/* Launches the grouped GEMM described by the table that bsg_ptr_array_initialize left in this workspace; of `args`
+ * the scalars (alpha, beta and their arrays, norm_constant, activation, use_pdl) and the problem sizes are read. */
+int32_t bsg_ptr_array_run(const bsg_ptr_array_args* args, void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/*
  * The same dense / batched GEMM as bsg_gemm_run for callers that have no device memory to hand over
  * as workspace and are not allowed to create any: code running under a framework that has frozen or
  * pre-reserved all device memory (an inference server after warm-up, a plug-in whose enqueue hook

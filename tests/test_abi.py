@@ -44,6 +44,8 @@ def test_struct_sizes_match_header_layout():
     # ... alpha_array, beta_array; SFD, norm_constant, use_pdl, scheduler
     assert C.sizeof(L.GroupedArgs) == 16 + 24 + 56 + 16 + 8 + 16 + 16 + 16 + 24
     assert C.sizeof(L.Caps) == 32
+    # 4 int32, the sizes pointer, 7 pointer arrays, 4 pitch arrays, 2 floats, 3 pointers, 4 int32
+    assert C.sizeof(L.PtrArrayArgs) == 16 + 8 + 56 + 32 + 8 + 24 + 16
 
 
 def _args(**kw):
@@ -140,3 +142,44 @@ def test_quantiser_rejects_bad_arguments_before_launching(lib, kw, code):
 
 def test_quantiser_accepts_an_empty_matrix(lib):
     assert lib.bsg_quantize(C.byref(_quant_args(rows=0)), None) == L.BSG_OK
+
+
+def _ptr_array_args(sizes, ptr=0x10000, **kw):
+    n = len(sizes)
+    keep = {"sizes": (C.c_int32 * (3 * n))(*[v for s in sizes for v in s])}
+    a = L.PtrArrayArgs()
+    a.kind, a.out_kind, a.num_groups = 0, 0, n
+    a.problem_sizes = C.cast(keep["sizes"], C.c_void_p)
+    for f in ("A", "B", "SFA", "SFB", "D"):
+        keep[f] = (C.c_void_p * n)(*([ptr] * n))        # never dereferenced by the checks
+        setattr(a, f, C.cast(keep[f], C.c_void_p))
+    a.alpha = 1.0
+    for k, v in kw.items():
+        setattr(a, k, v)
+    return a, keep
+
+
+def test_pointer_array_form_checks_every_group_before_touching_the_device(lib):
+    a, keep = _ptr_array_args([(300, 640, 512), (0, 256, 256), (64, 128, 256)])
+    n = C.c_size_t(0)
+    assert lib.bsg_ptr_array_workspace_size(C.byref(a), C.byref(n)) == 0 and n.value == 8192 + 3 * 768
+    # all groups pass the checks: the next thing looked at is the workspace
+    assert lib.bsg_ptr_array_initialize(C.byref(a), None, 0, None) == 4
+    assert lib.bsg_ptr_array_initialize(C.byref(a), 0x10040, n.value, None) == 1 and "128-byte" in L.last_error()
+    # a group whose K breaks the 16-byte row rule is named
+    b, keep_b = _ptr_array_args([(300, 640, 512), (64, 128, 48)])
+    assert lib.bsg_ptr_array_initialize(C.byref(b), None, 0, None) == 1 and L.last_error().startswith("group 1:")
+    # a misaligned pointer in one group
+    keep["B"][2] = 0x10008
+    assert lib.bsg_ptr_array_initialize(C.byref(a), None, 0, None) == 1 and L.last_error().startswith("group 2:")
+    keep["B"][2] = 0x10000
+    # beta without C, unknown kinds, too many groups
+    c, _k = _ptr_array_args([(128, 128, 128)], beta=1.0)
+    assert lib.bsg_ptr_array_initialize(C.byref(c), None, 0, None) == 2
+    d, _k2 = _ptr_array_args([(128, 128, 128)], kind=2)
+    assert lib.bsg_ptr_array_initialize(C.byref(d), None, 0, None) == 3
+    a.num_groups = 1000
+    assert lib.bsg_ptr_array_workspace_size(C.byref(a), C.byref(n)) == 2
+    a.num_groups = 3
+    # a run needs a table: this workspace has never been initialised
+    assert lib.bsg_ptr_array_run(C.byref(a), 0x20000, 1 << 20, None) == 2 and "initialize" in L.last_error()
