@@ -584,7 +584,33 @@ def run_single(args) -> dict:
         want3, secs3, kn3 = cpu_gemm_slab(0, A3[r0:r0 + rows3].cpu().numpy(), SFA3[a0 * 512 * katoms:(a0 + rows3 // 128) * 512 * katoms].cpu().numpy(),
                                           B3[e_big * N3:(e_big + 1) * N3].cpu().numpy(),
                                           SFB3[e_big * nat * 512 * katoms:(e_big + 1) * nat * 512 * katoms].cpu().numpy(), N3, K3)
+        # the same 64 problems through the pointer-array form (per-group tensors: views of the same buffers)
+        ptr_form = None
+        try:
+            from cutlass_b200.ptr_array import GroupProblem, PtrArrayGemm
+            row0s = np.concatenate([[0], np.cumsum(sizes)[:-1]]).astype(np.int64)
+            atom0s = np.concatenate([[0], np.cumsum(atoms)[:-1]]).astype(np.int64)
+            sfb_g = (N3 // 128) * 512 * katoms
+            pa_ops = []
+            for d in D3:
+                groups = [GroupProblem(A=A3[int(row0s[e]):int(row0s[e]) + int(sizes[e])],
+                                       SFA=SFA3[int(atom0s[e]) * 512 * katoms:],
+                                       B=B3[e * N3:(e + 1) * N3], SFB=SFB3[e * sfb_g:(e + 1) * sfb_g],
+                                       D=d[int(row0s[e]):int(row0s[e]) + int(sizes[e])]) for e in range(E)]
+                pa_ops.append(PtrArrayGemm(0, groups, stream=stream))
+            ms3p = time_steps(lambda i: pa_ops[i % 2].run(stream=stream), max(3, side_steps // 2), 2, stream)
+            launches += max(3, side_steps // 2)
+            for o in pa_ops:
+                o.check_device_status(stream)
+            same = bool(torch.equal(D3[0].view(torch.int16), D3[1].view(torch.int16)))
+            ptr_form = {"ms": round(ms3p, 5), "tflops": round(2.0 * total * N3 * K3 / ms3p / 1e9, 1),
+                        "what": "bsg_ptr_array_run: one problem per expert with its own pointers, extents and tensor maps",
+                        "output_equals_contiguous_form": same}
+            del pa_ops
+        except Exception as exc:  # noqa: BLE001
+            ptr_form = {"error": repr(exc)}
         record("c3_grouped_moe_64_experts", 0, 2.0 * total * N3 * K3, ms3, {
+            "pointer_array_form": ptr_form,
             "workload": "grouped NVFP4 GEMM, 64 experts, K=7168 -> N=2048, ragged M_g from a seeded Dirichlet(1) / multinomial draw, sum M_g = 131072, bf16 D",
             "group_rows_min_max": [int(sizes.min()), int(sizes.max())],
             "l2": "A 470 MB + B 470 MB + D 537 MB per launch: larger than L2 by itself; two output buffers rotated",
