@@ -91,7 +91,56 @@ def _reduce_scatter_leg(dev, rank: int, world: int, stream, steps: int) -> dict:
     dist.all_reduce(dt, op=dist.ReduceOp.MAX)
     rs.close()
     flops = 2.0 * M * N * K
-    return {"workload": f"MXFP8 GEMM + reduce-scatter M={M} N={N} K={K}: K sharded over the ranks, D reduced and scattered over M",
+    # GEMM + all-reduce: the same ring, every finished slice stored into every rank's output by the epilogue; against the
+    # dense kernel followed by ncclAllReduce of the M x N bf16 partial products
+    all_reduce = None
+    try:
+        if os.environ.get("BSG_BENCH_AR", "1") == "0":
+            raise RuntimeError("switched off (BSG_BENCH_AR=0)")
+        ar = TP.RsGemm(M, N, all_reduce=True)
+        res = None
+        for _ in range(3):
+            res = ar.run_all_reduce(kind, A, SFA, B, SFB, stream=stream)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0.record(stream)
+        for _ in range(steps):
+            res = ar.run_all_reduce(kind, A, SFA, B, SFB, stream=stream)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ar.check_device_status(stream)
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ar_ms = float(t.item()) / steps
+
+        def unfused_ar():
+            rc = lib.bsg_gemm_run(C.byref(d), ws.data_ptr(), 16, stream.cuda_stream)
+            assert rc == 0, L.last_error()
+            if world > 1:
+                dist.all_reduce(full)
+        for _ in range(2):
+            unfused_ar()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0.record(stream)
+        for _ in range(steps):
+            unfused_ar()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ar_unfused_ms = float(t.item()) / steps
+        ardiff = (res.float() - full.float()).abs().max() / full.float().abs().max().clamp_min(1e-30)
+        adt = torch.tensor([float(ardiff)], dtype=torch.float64, device=dev)
+        dist.all_reduce(adt, op=dist.ReduceOp.MAX)
+        all_reduce = {"ms_per_step": round(ar_ms, 4), "value": round(flops / ar_ms / 1e9, 1), "unit": "TFLOP/s",
+                      "unfused_nccl": {"ms_per_step": round(ar_unfused_ms, 4), "value": round(flops / ar_unfused_ms / 1e9, 1),
+                                       "what": "the dense kernel into a bf16 M x N buffer, then ncclAllReduce in place"},
+                      "max_rel_diff_vs_unfused": float(adt.item())}
+        ar.close()
+    except Exception as exc:  # noqa: BLE001
+        all_reduce = {"error": repr(exc)}
+    return {"all_reduce": all_reduce, "workload": f"MXFP8 GEMM + reduce-scatter M={M} N={N} K={K}: K sharded over the ranks, D reduced and scattered over M",
             "ms_per_step": round(fused_ms, 4), "value": round(flops / fused_ms / 1e9, 1), "unit": "TFLOP/s", "steps": steps,
             "unfused_nccl": {"ms_per_step": round(unfused_ms, 4), "value": round(flops / unfused_ms / 1e9, 1),
                              "what": "the dense kernel into a bf16 M x N buffer, then ncclReduceScatter"},

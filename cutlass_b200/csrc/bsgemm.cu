@@ -204,6 +204,11 @@ struct Problem {
   const void* rs_recv;        // this rank's receive buffers
   void* rs_recv_left;         // receive buffers of rank - 1 (peer memory)
   uint32_t *rs_flags, *rs_flags_left, *rs_sync, *rs_sync_left, *rs_sync_right;
+  // GEMM + all-reduce
+  int32_t rs_allreduce, rs_out_half;
+  uint32_t rs_done_target;
+  const void* rs_out_maps;
+  uint32_t* rs_peer_sync[8];
 };
 
 struct Plan {
@@ -428,6 +433,9 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
     p.rs_recv = static_cast<const __nv_bfloat16*>(q.rs_recv);
     p.rs_flags = q.rs_flags; p.rs_flags_left = q.rs_flags_left;
     p.rs_sync = q.rs_sync; p.rs_sync_left = q.rs_sync_left; p.rs_sync_right = q.rs_sync_right;
+    p.rs_allreduce = q.rs_allreduce; p.rs_rank = q.rs_rank; p.rs_out_half = q.rs_out_half; p.rs_done_target = q.rs_done_target;
+    p.rs_out_maps = static_cast<const CUtensorMap*>(q.rs_out_maps);
+    for (int i = 0; i < 8; ++i) p.rs_peer_sync[i] = q.rs_peer_sync[i];
     p.split_tail = 0;
     // the walk starts at slice rank + 1 and ends at the rank's own slice; a band of the raster never straddles slices
     p.tile_m_rotate = ((q.rs_rank + 1) % q.rs_world) * tiles_per_slice;
@@ -831,15 +839,33 @@ struct bsg_tp_comm {
 // Per-rank state of the GEMM + reduce-scatter: one device allocation with the receive buffers (two halves used by
 // alternate calls, world - 1 slices of M / world x N bf16 each), the arrival counters of their tiles, and the sync words.
 struct bsg_rs_comm {
-  int32_t rank, world;
+  int32_t rank, world, flags;
   int64_t M, N, slice_rows, tiles_per_slice, tiles_n;
-  size_t recv_off, flags_off, sync_off, total_bytes;
+  size_t recv_off, flags_off, sync_off, maps_off, out_off, total_bytes;   // out: two halves of M x N bf16 (all-reduce only)
   uint8_t* base;
   uint8_t* peer_base[8];
   bool opened[8];
   bool connected;
   uint32_t epoch;
+  uint32_t ar_calls;      // all-reduce calls so far (the arrival counter counts only those)
+  bool maps_uploaded;
 };
+
+// All-reduce: one map per rank over its output (N columns, M rows, two halves), stored in this rank's own memory where
+// the kernel reads them.
+static int32_t rs_upload_out_maps(bsg_rs_comm* c) {
+  CUtensorMap maps[8];
+  memset(maps, 0, sizeof(maps));
+  for (int q = 0; q < c->world; ++q) {
+    const int32_t rc = make_out_map(&maps[q], c->peer_base[q] + c->out_off, BSG_OUT_BF16, uint64_t(c->N), uint64_t(c->M), 2, uint64_t(c->N),
+                                    uint64_t(c->M) * uint64_t(c->N));
+    if (rc != BSG_OK) return rc;
+  }
+  cudaError_t e = cudaMemcpy(c->base + c->maps_off, maps, sizeof(maps), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "uploading the output maps: %s", cudaGetErrorString(e));
+  c->maps_uploaded = true;
+  return BSG_OK;
+}
 
 extern "C" {
 
@@ -1232,15 +1258,16 @@ int32_t bsg_tp_gemm_run(bsg_tp_comm* c, const bsg_gemm_args* args, void* workspa
   return BSG_OK;
 }
 
-int32_t bsg_rs_create(int32_t rank, int32_t world, int64_t M, int64_t N, bsg_rs_comm** out, void* ipc_handle_out) {
+int32_t bsg_rs_create(int32_t rank, int32_t world, int64_t M, int64_t N, int32_t flags, bsg_rs_comm** out, void* ipc_handle_out) {
   if (!out || !ipc_handle_out) return fail(BSG_ERR_INVALID_PROBLEM, "null argument");
+  if (flags & ~BSG_RS_WITH_ALLREDUCE) return fail(BSG_ERR_NOT_SUPPORTED, "unknown flags 0x%x", flags);
   if (world < 1 || world > 8 || rank < 0 || rank >= world) return fail(BSG_ERR_INVALID_PROBLEM, "rank %d / world %d outside [0, 8]", rank, world);
   if (M < 1 || N < 8 || M % (int64_t(world) * 256) != 0) return fail(BSG_ERR_INVALID_PROBLEM, "M=%lld must be a multiple of 256 * world", (long long)M);
   if (N % 8 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "N=%lld must be a multiple of 8", (long long)N);
   bsg_rs_comm* c = new (std::nothrow) bsg_rs_comm();
   if (!c) return fail(BSG_ERR_INTERNAL, "out of host memory");
   memset(c, 0, sizeof(*c));
-  c->rank = rank; c->world = world; c->M = M; c->N = N;
+  c->rank = rank; c->world = world; c->M = M; c->N = N; c->flags = flags;
   c->slice_rows = M / world;
   c->tiles_per_slice = c->slice_rows / 256;
   c->tiles_n = (N + 255) / 256;
@@ -1251,10 +1278,12 @@ int32_t bsg_rs_create(int32_t rank, int32_t world, int64_t M, int64_t N, bsg_rs_
   c->recv_off = 0;
   c->flags_off = up(recv_bytes);
   c->sync_off = c->flags_off + up(flag_bytes);
-  c->total_bytes = c->sync_off + 1024;
+  c->maps_off = c->sync_off + 1024;
+  c->out_off = c->maps_off + 1024;                 // 8 tensor maps of 128 bytes
+  c->total_bytes = c->out_off + ((flags & BSG_RS_WITH_ALLREDUCE) ? 2 * size_t(M) * size_t(N) * 2 : 0);
   cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&c->base), c->total_bytes);
   if (e != cudaSuccess) { delete c; return fail(BSG_ERR_CUDA, "cudaMalloc(%zu): %s", c->total_bytes, cudaGetErrorString(e)); }
-  e = cudaMemset(c->base + c->flags_off, 0, c->total_bytes - c->flags_off);
+  e = cudaMemset(c->base + c->flags_off, 0, c->out_off - c->flags_off);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   cudaIpcMemHandle_t h;
   if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, c->base);
@@ -1262,16 +1291,20 @@ int32_t bsg_rs_create(int32_t rank, int32_t world, int64_t M, int64_t N, bsg_rs_
   memcpy(ipc_handle_out, &h, 64);
   c->peer_base[rank] = c->base;
   c->connected = world == 1;
+  if (world == 1 && (flags & BSG_RS_WITH_ALLREDUCE)) {      // nobody to connect to: the only output map is this rank's own
+    const int32_t rc = rs_upload_out_maps(c);
+    if (rc != BSG_OK) { cudaFree(c->base); delete c; return rc; }
+  }
   *out = c;
   return BSG_OK;
 }
 
 int32_t bsg_rs_connect(bsg_rs_comm* c, const void* all_handles) {
   if (!c || !all_handles) return fail(BSG_ERR_INVALID_PROBLEM, "null argument");
-  // only the two ring neighbours are mapped
-  const int nb[2] = {(c->rank + c->world - 1) % c->world, (c->rank + 1) % c->world};
-  for (int i = 0; i < 2; ++i) {
-    const int q = nb[i];
+  // the ring needs the two neighbours only; the all-reduce stores into every rank's output
+  const int left_rank = (c->rank + c->world - 1) % c->world, right_rank = (c->rank + 1) % c->world;
+  for (int q = 0; q < c->world; ++q) {
+    if (!(c->flags & BSG_RS_WITH_ALLREDUCE) && q != left_rank && q != right_rank) continue;
     if (q == c->rank || c->opened[q]) continue;
     cudaIpcMemHandle_t h;
     memcpy(&h, static_cast<const uint8_t*>(all_handles) + size_t(q) * 64, 64);
@@ -1281,13 +1314,19 @@ int32_t bsg_rs_connect(bsg_rs_comm* c, const void* all_handles) {
     c->peer_base[q] = static_cast<uint8_t*>(ptr);
     c->opened[q] = true;
   }
+  if (c->flags & BSG_RS_WITH_ALLREDUCE) {
+    const int32_t rc = rs_upload_out_maps(c);
+    if (rc != BSG_OK) return rc;
+  }
   c->connected = true;
   return BSG_OK;
 }
 
-int32_t bsg_rs_gemm_run(bsg_rs_comm* c, const bsg_gemm_args* args, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+static int32_t rs_run(bsg_rs_comm* c, const bsg_gemm_args* args, void* workspace, size_t workspace_bytes, void* cuda_stream, bool allreduce, void** result) {
   if (!c || !args) return fail(BSG_ERR_INVALID_PROBLEM, "null argument");
   if (!c->connected) return fail(BSG_ERR_INVALID_PROBLEM, "bsg_rs_connect has not been called");
+  if (allreduce && !(c->flags & BSG_RS_WITH_ALLREDUCE)) return fail(BSG_ERR_INVALID_PROBLEM, "the communicator was created without BSG_RS_WITH_ALLREDUCE");
+  if (allreduce && !c->maps_uploaded) return fail(BSG_ERR_INTERNAL, "the output maps of the all-reduce have not been set up");
   if (args->M != c->M || args->N != c->N) return fail(BSG_ERR_INVALID_PROBLEM, "M and N must match the communicator");
   if (args->batch > 1) return fail(BSG_ERR_NOT_SUPPORTED, "the reduce-scatter GEMM is not batched");
   if (args->out_kind != BSG_OUT_BF16 || args->C || args->beta != 0.0f || args->beta_ptr || args->bias_mode != BSG_BIAS_NONE ||
@@ -1300,12 +1339,19 @@ int32_t bsg_rs_gemm_run(bsg_rs_comm* c, const bsg_gemm_args* args, void* workspa
   local.tile_n = 256;
   local.scheduler = BSG_SCHED_STATIC;
   local.use_pdl = 0;
+  const uint32_t epoch = c->epoch + 1;
+  const int32_t half = int32_t(epoch & 1u);
+  uint8_t* out_half = c->base + c->out_off + (half ? size_t(c->M) * size_t(c->N) * 2 : 0);
+  if (allreduce) {          // D of the arguments is not used: the result lands in the communicator's output
+    local.D = out_half;
+    local.ldd = c->N;
+  }
   Problem q = from_dense(&local);
   // D holds this rank's slice only; the checks of validate() that look at D's extent use the slice pitch
   q.rs = true;
   q.rs_world = c->world; q.rs_rank = c->rank; q.rs_slice_rows = int32_t(c->slice_rows);
-  q.rs_epoch = c->epoch + 1;
-  q.rs_parity = int32_t(q.rs_epoch & 1u);
+  q.rs_epoch = epoch;
+  q.rs_parity = half;
   const int left = (c->rank + c->world - 1) % c->world, right = (c->rank + 1) % c->world;
   q.rs_recv = c->base + c->recv_off;
   q.rs_recv_left = c->peer_base[left] + c->recv_off;
@@ -1314,10 +1360,29 @@ int32_t bsg_rs_gemm_run(bsg_rs_comm* c, const bsg_gemm_args* args, void* workspa
   q.rs_sync = reinterpret_cast<uint32_t*>(c->base + c->sync_off);
   q.rs_sync_left = reinterpret_cast<uint32_t*>(c->peer_base[left] + c->sync_off);
   q.rs_sync_right = reinterpret_cast<uint32_t*>(c->peer_base[right] + c->sync_off);
+  if (allreduce) {
+    q.rs_allreduce = 1;
+    q.rs_out_half = half;
+    q.rs_out_maps = c->base + c->maps_off;
+    for (int i = 0; i < c->world; ++i) q.rs_peer_sync[i] = reinterpret_cast<uint32_t*>(c->peer_base[i] + c->sync_off);
+    // every all-reduce call adds (world - 1) slices x tiles x 8 epilogue warps to the arrival counter
+    c->ar_calls += 1;
+    q.rs_done_target = uint32_t(c->ar_calls) * uint32_t(c->world - 1) * uint32_t(c->tiles_per_slice * c->tiles_n) * 8u;
+  }
   int32_t rc = run_problem(q, workspace, workspace_bytes, cuda_stream);
-  if (rc != BSG_OK) return rc;
+  if (rc != BSG_OK) { if (allreduce) c->ar_calls -= 1; return rc; }
   c->epoch += 1;
+  if (result) *result = out_half;
   return BSG_OK;
+}
+
+int32_t bsg_rs_gemm_run(bsg_rs_comm* c, const bsg_gemm_args* args, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  return rs_run(c, args, workspace, workspace_bytes, cuda_stream, false, nullptr);
+}
+
+int32_t bsg_rs_allreduce_run(bsg_rs_comm* c, const bsg_gemm_args* args, void* workspace, size_t workspace_bytes, void* cuda_stream, void** result) {
+  if (!result) return fail(BSG_ERR_INVALID_PROBLEM, "result is null");
+  return rs_run(c, args, workspace, workspace_bytes, cuda_stream, true, result);
 }
 
 int32_t bsg_rs_destroy(bsg_rs_comm* c) {

@@ -143,6 +143,14 @@ struct GemmParams {
   uint32_t* rs_sync;              // this rank's sync words: [0] = call number the right neighbour ... see kRsSync*
   uint32_t* rs_sync_left;         // sync words of rank - 1
   uint32_t* rs_sync_right;        // sync words of rank + 1
+  // GEMM + all-reduce on top of the reduce-scatter: in the last stage the finished slice is stored into EVERY rank's
+  // full-size output (M x N, two halves used by alternate calls) instead of this rank's D.
+  int32_t rs_allreduce;
+  int32_t rs_rank;
+  int32_t rs_out_half;            // which half of the outputs this call writes
+  uint32_t rs_done_target;        // this rank's arrival counter shows this once every peer's slice of this call is in place
+  const CUtensorMap* rs_out_maps; // [world] maps of the ranks' outputs (N, M, 2 halves), in this rank's global memory
+  uint32_t* rs_peer_sync[8];      // sync words of every rank: [8 + q] = call number rank q has launched, [16] = arrival counter
   const GroupDesc* group_desc;    // pointer-array grouped form: one record per group (device memory)
   const uint8_t* tp_peer_a[8];    // gathered A buffer of every rank that this call fills (own entry = source: local buffer 0)
   const uint8_t* tp_peer_sfa[8];
@@ -150,6 +158,8 @@ struct GemmParams {
 };
 
 constexpr int kRsSyncLaunched = 0;   // word 0 of a rank's reduce-scatter sync words: the call number its LEFT neighbour has launched
+constexpr int kRsSyncLaunchedBy = 8; // words 8 .. 15: the call number every rank has launched (all-reduce)
+constexpr int kRsSyncArrived = 16;   // word 16: finished sub-tiles of other ranks' slices stored into this rank's output (all-reduce)
 constexpr int kTpSyncReady = 0;
 constexpr int kTpSyncFlags = 32;
 constexpr uint32_t kStTimeoutPeer = 64u;      // tensor parallel: a peer never published / finished
@@ -562,6 +572,12 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if (blockIdx.x == 0 && threadIdx.x == 0 && p.rs_world > 1) {
       __threadfence_system();
       st_release_sys_u32(p.rs_sync_right + kRsSyncLaunched, p.rs_epoch);
+      // All-reduce: every rank stores into this rank's output; its half of two calls ago has been read by now.
+      if (p.rs_allreduce) {
+        for (int q = 0; q < p.rs_world; ++q) {
+          if (q != p.rs_rank) st_release_sys_u32(p.rs_peer_sync[q] + kRsSyncLaunchedBy + p.rs_rank, p.rs_epoch);
+        }
+      }
     }
   }
   // Group table: end rows first (parallel), then a serial prefix by one thread.
@@ -994,6 +1010,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const uint32_t tempty0 = ptx::smem_u32(&ctl->tmem_empty[0]);
     uint8_t* stage_buf = sEpi + warp * 4096;                     // this warp's 32 x 128-byte staging tile
     uint32_t n_store = 0;                                        // TMA stores issued so far (staging rotation)
+    bool ar_ready = false;                                       // all-reduce: the peers' outputs may be written (checked once)
     int32_t it = 0;
     uint32_t step = 0;
     for (int32_t w = first_work; w >= 0; w = DYN ? sched_consume<CG>(ctl, step++, dead) : static_next(w)) {
@@ -1037,6 +1054,17 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           use_c = true;
         } else {
           use_c = false;
+        }
+        if (!rs_to_peer && p.rs_allreduce && !ar_ready) {
+          // the finished slice goes to every rank: each must have launched this call (its output half is free then)
+          if (lane == 0) {
+            for (int q = 0; q < p.rs_world; ++q) {
+              if (q != p.rs_rank && !wait_flag_ge(p.rs_sync + kRsSyncLaunchedBy + q, p.rs_epoch, ctl)) dead = 1;
+              ptx::fence_tensormap_acquire(p.rs_out_maps + q);
+            }
+          }
+          dead = __shfl_sync(0xffffffffu, dead, 0);
+          ar_ready = true;
         }
         if (rs_to_peer) {
           rs_flag_out = p.rs_flags_left + ((int64_t(half) * (p.rs_world - 1) + rs_stage) * p.rs_tiles_per_slice + tm_in_slice) * p.tiles_n + ti.tn;
@@ -1353,7 +1381,12 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const int32_t col = tile_col0 + pr * 64;
             if (RS && rs_to_peer)
               ptx::tma_store_3d(&tmDpeer, ptx::smem_u32(sub_buf), col, p.rs_parity_rows + rs_stage * p.rs_slice_rows + rs_row_in_slice, 0);
-            else if (RS)
+            else if (RS && p.rs_allreduce) {
+              if (!dead) {
+                for (int q = 0; q < p.rs_world; ++q)
+                  ptx::tma_store_3d(p.rs_out_maps + q, ptx::smem_u32(sub_buf), col, p.rs_rank * p.rs_slice_rows + rs_row_in_slice, p.rs_out_half);
+              }
+            } else if (RS)
               ptx::tma_store_3d(&tmD, ptx::smem_u32(sub_buf), col, rs_row_in_slice, 0);
             else
               ptx::tma_store_3d(mapD, ptx::smem_u32(sub_buf), out_kind == kOutNvfp4 ? col / 2 : col, warp_map_row0, ti.map_l);
@@ -1369,10 +1402,26 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           asm volatile("fence.proxy.async;" ::: "memory");
           asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(rs_flag_out), "r"(1u) : "memory");
         }
+        // All-reduce: this warp's part of a finished tile is in every rank's output once its stores are complete.
+        if (!rs_to_peer && p.rs_allreduce && p.rs_world > 1 && lane == 0 && !dead) {
+          ptx::bulk_wait_group<0>();
+          asm volatile("fence.proxy.async;" ::: "memory");
+          for (int q = 0; q < p.rs_world; ++q) {
+            if (q != p.rs_rank)
+              asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.rs_peer_sync[q] + kRsSyncArrived), "r"(1u) : "memory");
+          }
+        }
       }
       ++it;
     }
     if (lane == 0) ptx::bulk_wait_group<0>();
+    if constexpr (RS) {
+      // All-reduce: the kernel ends only when the other ranks' slices have arrived, so that whatever follows on the
+      // stream finds the whole result (one thread of the grid waits; bounded).
+      if (p.rs_allreduce && p.rs_world > 1 && blockIdx.x == 0 && warp == 0 && lane == 0 && !dead) {
+        if (!wait_flag_ge(p.rs_sync + kRsSyncArrived, p.rs_done_target, ctl)) atomicOr(p.status, kStTimeoutPeer);
+      }
+    }
     if (dead) atomicOr(p.status, kStTimeoutTmemFull);
   }
 

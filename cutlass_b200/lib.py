@@ -37,6 +37,7 @@ BIAS_NONE, BIAS_PER_COLUMN, BIAS_PER_ROW = 0, 1, 2
 MAX_GROUPS = 256
 SCHED_STATIC, SCHED_DYNAMIC = 0, 1
 LAYOUT_ROW_MAJOR, LAYOUT_COL_MAJOR = 0, 1
+RS_WITH_ALLREDUCE = 1
 
 
 class GemmArgs(C.Structure):
@@ -122,9 +123,10 @@ SYMBOLS = {
     "bsg_tp_gemm_run": (C.c_int32, [C.c_void_p, C.POINTER(GemmArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "bsg_tp_set_mode": (C.c_int32, [C.c_void_p, C.c_int32]),
     "bsg_tp_destroy": (C.c_int32, [C.c_void_p]),
-    "bsg_rs_create": (C.c_int32, [C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.POINTER(C.c_void_p), C.c_void_p]),
+    "bsg_rs_create": (C.c_int32, [C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.POINTER(C.c_void_p), C.c_void_p]),
     "bsg_rs_connect": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "bsg_rs_gemm_run": (C.c_int32, [C.c_void_p, C.POINTER(GemmArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "bsg_rs_allreduce_run": (C.c_int32, [C.c_void_p, C.POINTER(GemmArgs), C.c_void_p, C.c_size_t, C.c_void_p, C.POINTER(C.c_void_p)]),
     "bsg_rs_destroy": (C.c_int32, [C.c_void_p]),
 }
 

@@ -113,7 +113,7 @@ class RsGemm:
     Takes the role of the reference's reduce-scatter distributed GEMM schedules
     (``include/cutlass/experimental/distributed/schedules/dist_gemm_1d_schedules.hpp:148``)."""
 
-    def __init__(self, M: int, N: int, group=None):
+    def __init__(self, M: int, N: int, group=None, all_reduce: bool = False):
         import torch
         import torch.distributed as dist
         from . import lib as L
@@ -127,7 +127,8 @@ class RsGemm:
         self.M, self.N = M, N
         self._comm = C.c_void_p()
         handle = (C.c_uint8 * 64)()
-        L.check(self._lib.bsg_rs_create(self.rank, self.world, M, N, C.byref(self._comm), handle))
+        self.all_reduce = all_reduce
+        L.check(self._lib.bsg_rs_create(self.rank, self.world, M, N, L.RS_WITH_ALLREDUCE if all_reduce else 0, C.byref(self._comm), handle))
         if self.world > 1:
             handles = exchange_handles(bytes(handle), group)
             blob = (C.c_uint8 * (64 * self.world)).from_buffer_copy(b"".join(handles))
@@ -142,7 +143,8 @@ class RsGemm:
         a.kind, a.out_kind, a.batch = kind, L.OUT_BF16, 1
         k_local = A.shape[-1] * (2 if kind == L.KIND_NVFP4 else 1)
         a.M, a.N, a.K = self.M, self.N, k_local
-        a.A, a.SFA, a.B, a.SFB, a.D = A.data_ptr(), SFA.data_ptr(), B.data_ptr(), SFB.data_ptr(), out.data_ptr()
+        a.A, a.SFA, a.B, a.SFB = A.data_ptr(), SFA.data_ptr(), B.data_ptr(), SFB.data_ptr()
+        a.D = out.data_ptr() if out is not None else None
         a.alpha = alpha
         return a
 
@@ -150,6 +152,17 @@ class RsGemm:
         from .operator import to_cuda_stream
         a = abi_args if abi_args is not None else self.build_args(kind, A, SFA, B, SFB, out, alpha)
         self._L.check(self._lib.bsg_rs_gemm_run(self._comm, C.byref(a), self.workspace.data_ptr(), 16, to_cuda_stream(stream)))
+
+    def run_all_reduce(self, kind: int, A, SFA, B, SFB, alpha: float = 1.0, stream=None):
+        """GEMM + all-reduce (``all_reduce=True`` at construction): every rank gets all of alpha * A @ B^T.  Returns a
+        bf16 (M, N) view of the communicator's output for this call, valid until the call after the next one."""
+        import torch
+        from .operator import to_cuda_stream
+        a = self.build_args(kind, A, SFA, B, SFB, None, alpha)
+        res = C.c_void_p()
+        self._L.check(self._lib.bsg_rs_allreduce_run(self._comm, C.byref(a), self.workspace.data_ptr(), 16, to_cuda_stream(stream), C.byref(res)))
+        dev = torch.device("cuda", torch.cuda.current_device())
+        return torch.as_tensor(_DevicePointer(res.value, self.M * self.N * 2), device=dev).view(torch.bfloat16).view(self.M, self.N)
 
     def check_device_status(self, stream=None) -> None:
         from .operator import to_cuda_stream

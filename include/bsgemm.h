@@ -416,19 +416,31 @@ int32_t bsg_tp_destroy(bsg_tp_comm* comm);
  *
  * bsg_rs_create    allocates the receive buffers (two halves, used by alternate calls; (world - 1) * M / world * N bf16
  *                  each) and returns a 64-byte CUDA IPC handle for the peers.  M a multiple of 256 * world.
- * bsg_rs_connect   takes the `world` handles (64 bytes each, by rank) and maps the two ring neighbours.
+ * bsg_rs_connect   takes the `world` handles (64 bytes each, by rank) and maps the two ring neighbours (all ranks with
+ *                  BSG_RS_WITH_ALLREDUCE).
  * bsg_rs_gemm_run  enqueues one GEMM: args->M, N are the full extents, K the local shard, A / B / SFA / SFB the local
  *                  shards, D the (M / world) x N bf16 result slice of this rank (ldd its pitch); alpha applies to every
  *                  partial product; C, beta, bias, activation and quantised outputs are not available.  All ranks call
  *                  it the same number of times; waits are bounded as for the all-gather GEMM (BSG_ERR_TIMEOUT), and the
  *                  same rules hold for what a call needs (the whole GPU) and for recovery after a time-out.
+ * bsg_rs_allreduce_run  GEMM + all-reduce (communicators created with BSG_RS_WITH_ALLREDUCE): the same ring, but the
+ *                  epilogue of the last stage stores the finished slice into the full-size output of EVERY rank (TMA
+ *                  stores into peer memory, a released counter increment per warp and destination), and the kernel ends
+ *                  only once the slices of all other ranks have arrived, so the next kernel on the stream finds all of
+ *                  D = alpha * A B^T.  The output (M x N bf16, pitch N) belongs to the communicator, which holds two of
+ *                  them for alternate calls: *result points at the one this call fills, valid until the call after the
+ *                  next one is enqueued.  args->D is not used.  (The reference's schedules stop at the reduce-scatter;
+ *                  this is that schedule followed by the all-gather of its result, inside the same kernel.)
  * bsg_rs_destroy   after the device is idle on every rank and a barrier.
  */
 typedef struct bsg_rs_comm bsg_rs_comm;
-int32_t bsg_rs_create(int32_t rank, int32_t world, int64_t M, int64_t N, bsg_rs_comm** out, void* ipc_handle_out);
+enum { BSG_RS_WITH_ALLREDUCE = 1 };   /* flags of bsg_rs_create: also allocate the two M x N outputs of bsg_rs_allreduce_run */
+int32_t bsg_rs_create(int32_t rank, int32_t world, int64_t M, int64_t N, int32_t flags, bsg_rs_comm** out, void* ipc_handle_out);
 int32_t bsg_rs_connect(bsg_rs_comm* comm, const void* all_handles);
 int32_t bsg_rs_gemm_run(bsg_rs_comm* comm, const bsg_gemm_args* args, void* workspace, size_t workspace_bytes,
                         void* cuda_stream);
+int32_t bsg_rs_allreduce_run(bsg_rs_comm* comm, const bsg_gemm_args* args, void* workspace, size_t workspace_bytes,
+                             void* cuda_stream, void** result);
 int32_t bsg_rs_destroy(bsg_rs_comm* comm);
 
 #ifdef __cplusplus

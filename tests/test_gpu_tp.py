@@ -188,7 +188,7 @@ def test_tp_rank_that_never_launches_gives_a_timeout_status_not_a_hang():
 
 
 # --------------------------------------------------------------------------- GEMM + reduce-scatter
-def _rs_worker(rank, world, port, kind, M, N, K, calls, q):
+def _rs_worker(rank, world, port, kind, M, N, K, calls, q, all_reduce=False):
     """K is sharded; rank r must end up with rows [r * M / world, ...) of the sum over ranks, where the running sum is
     rounded to bf16 at every hop of the ring (the oracle follows the same hop order)."""
     try:
@@ -201,7 +201,7 @@ def _rs_worker(rank, world, port, kind, M, N, K, calls, q):
         torch.cuda.set_device(rank)
         if world > 1:
             dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
-        rs = TP.RsGemm(M, N)
+        rs = TP.RsGemm(M, N, all_reduce=all_reduce)
         try:
             ms, kl = M // world, K // world
             for call in range(calls):
@@ -210,19 +210,33 @@ def _rs_worker(rank, world, port, kind, M, N, K, calls, q):
                 shards = [(gen_a(M, kl, rng), gen_b(N, kl, rng)) for _ in range(world)]       # every rank's K shard, same on all ranks
                 (A, _, sfa), (B, _, sfb) = shards[rank]
                 dA, dSFA, dB, dSFB = (torch.from_numpy(np.ascontiguousarray(x)).cuda() for x in (A, sfa, B, sfb))
+                vec = 16 if kind == 0 else 32
+                atom_bytes = 512 * (-(-(kl // vec) // 4))
+
+                def slice_oracle(sl):
+                    run = None
+                    for hop in TP.rs_hop_order(world, sl):
+                        (Ah, _, sfah), (Bh, _, sfbh) = shards[hop]
+                        rows = slice(sl * ms, (sl + 1) * ms)
+                        sfa_rows = sfah[(sl * ms // 128) * atom_bytes:((sl + 1) * ms // 128) * atom_bytes]
+                        pre = oracle.gemm_fp32(kind, Ah[rows], sfa_rows, Bh, sfbh, ms, N, kl, run, 0.5, 1.0 if run is not None else 0.0)
+                        run = oracle.to_bf16(pre)
+                    return run
+                if all_reduce:
+                    # every rank ends up with every slice; the result lives in the communicator (two buffers, alternating)
+                    full = rs.run_all_reduce(kind, dA, dSFA, dB, dSFB, alpha=0.5)
+                    rs.check_device_status()
+                    torch.cuda.synchronize()
+                    got = full.view(torch.int16).cpu().numpy().view(np.uint16)
+                    for sl in range(world):
+                        bad = int((got[sl * ms:(sl + 1) * ms] != slice_oracle(sl)).sum())
+                        assert bad == 0, f"call {call}: {bad} outputs of slice {sl} differ from the oracle (rank {rank})"
+                    continue
                 out = torch.full((ms, N), 0x7FC0, dtype=torch.int16, device="cuda")
                 rs.run(kind, dA, dSFA, dB, dSFB, out, alpha=0.5)
                 rs.check_device_status()
                 torch.cuda.synchronize()
-                run = None
-                vec = 16 if kind == 0 else 32
-                atom_bytes = 512 * (-(-(kl // vec) // 4))
-                for hop in TP.rs_hop_order(world, rank):
-                    (Ah, _, sfah), (Bh, _, sfbh) = shards[hop]
-                    rows = slice(rank * ms, (rank + 1) * ms)
-                    sfa_rows = sfah[(rank * ms // 128) * atom_bytes:((rank + 1) * ms // 128) * atom_bytes]
-                    pre = oracle.gemm_fp32(kind, Ah[rows], sfa_rows, Bh, sfbh, ms, N, kl, run, 0.5, 1.0 if run is not None else 0.0)
-                    run = oracle.to_bf16(pre)
+                run = slice_oracle(rank)
                 got = out.cpu().numpy().view(np.uint16)
                 bad = int((got != run).sum())
                 assert bad == 0, f"call {call}: {bad} of {got.size} outputs differ from the oracle (rank {rank})"
@@ -248,6 +262,25 @@ def test_gemm_reduce_scatter(kind, world, M, N, K):
     q = ctx.Queue()
     port = _free_port()
     procs = [ctx.Process(target=_rs_worker, args=(r, world, port, kind, M, N, K, 4, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted(q.get(timeout=600) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+    assert results == [(r, "ok") for r in range(world)], results
+
+
+@pytest.mark.parametrize("kind,world,M,N,K", [(1, 1, 512, 384, 512), (0, 2, 1024, 512, 1024), (1, 2, 2048, 640, 2048), (0, 4, 2048, 1024, 2048),
+                                              (1, 8, 4096, 512, 4096)])
+def test_gemm_all_reduce(kind, world, M, N, K):
+    """GEMM + all-reduce: the reduce-scatter ring, then every finished slice stored into every rank's output by the
+    epilogue; every rank compares all M rows with the oracle's ring sums, over several calls (the outputs alternate)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rs_worker, args=(r, world, port, kind, M, N, K, 4, q, True)) for r in range(world)]
     for p in procs:
         p.start()
     results = sorted(q.get(timeout=600) for _ in range(world))
