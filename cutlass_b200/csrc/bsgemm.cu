@@ -1208,7 +1208,7 @@ int32_t bsg_tp_gemm_run(bsg_tp_comm* c, const bsg_gemm_args* args, void* workspa
   const bool copy_engine = c->world > 1 && (c->mode & BSG_TP_PUSH_COPY_ENGINE) != 0;
   q.tp_push_in_kernel = copy_engine ? 0 : 1;
   q.tp_release_announce = (c->mode & BSG_TP_RELEASE_ANNOUNCE) ? 1 : 0;
-  q.tp_paced_push = (c->mode & BSG_TP_PACED_PUSH) ? 1 : 0;
+  q.tp_paced_push = (c->mode & BSG_TP_SPREAD_PUSH) ? 2 : (c->mode & BSG_TP_PACED_PUSH) ? 1 : 0;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (copy_engine) {
     if (!workspace || workspace_bytes < 16) return fail(BSG_ERR_WORKSPACE_NULL, "workspace is null or smaller than 16 bytes");
@@ -1398,7 +1398,7 @@ int32_t bsg_rs_destroy(bsg_rs_comm* c) {
 
 int32_t bsg_tp_set_mode(bsg_tp_comm* c, int32_t mode) {
   if (!c) return fail(BSG_ERR_INVALID_PROBLEM, "null communicator");
-  if (mode < 0 || mode > (BSG_TP_PUSH_COPY_ENGINE | BSG_TP_SINGLE_BUFFER | BSG_TP_RELEASE_ANNOUNCE | BSG_TP_PACED_PUSH)) return fail(BSG_ERR_NOT_SUPPORTED, "unknown tensor-parallel mode %d", mode);
+  if (mode < 0 || mode > (BSG_TP_PUSH_COPY_ENGINE | BSG_TP_SINGLE_BUFFER | BSG_TP_RELEASE_ANNOUNCE | BSG_TP_PACED_PUSH | BSG_TP_SPREAD_PUSH)) return fail(BSG_ERR_NOT_SUPPORTED, "unknown tensor-parallel mode %d", mode);
   c->mode = mode;
   return BSG_OK;
 }

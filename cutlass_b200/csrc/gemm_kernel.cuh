@@ -117,7 +117,7 @@ struct GemmParams {
   int32_t tp_ksplit;          // pieces a 256-row block is cut into (one flag increment each)
   int32_t tp_push_in_kernel;  // 1: the push warp moves the data; 0: the host's copy-engine transfers do
   int32_t tp_release_announce; // 1: a batch of announcements is preceded by a proxy fence and a system-scope release fence
-  int32_t tp_paced_push;      // 1: the shard for the j-th nearest consumer is pushed while this CTA works on stage j - 1
+  int32_t tp_paced_push;      // 2: as 1, and the pieces are spread over that stage; 1: the shard for the j-th nearest consumer is pushed while this CTA works on stage j - 1
                               //    of its own walk (all ranks walk in step, so it arrives one stage before it is needed),
                               //    instead of everything as fast as the links allow at the start of the kernel
   uint32_t tp_epoch;          // call counter, starts at 1; the peers use the same value
@@ -233,6 +233,8 @@ struct alignas(16) Ctl {
   uint32_t tmem_base;
   volatile uint32_t abort;
   volatile int32_t tp_stage_now;   // tensor parallel: stage (shard index in consumption order) of the tile the producer is on
+  volatile int32_t tp_progress;    // how far this CTA's producer is through its own work, in 1/1024 of a stage (all CTAs of all
+                                   // ranks work through their items at the same rate, so this is also the time in stages)
   int32_t total_tiles;
   int32_t pad;
   int32_t tile_start[kMaxGroups + 1];
@@ -550,6 +552,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     ctl->abort = 0;
     ctl->tp_stage_now = 0;
+    ctl->tp_progress = 0;
     ptx::fence_mbar_init();
     ptx::fence_proxy_async();
   }
@@ -673,6 +676,8 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     int stage = 0;
     uint32_t phase = 0;
     uint32_t step = 0;
+    // work items of this cluster in the static walk (tensor parallel: the measure of its progress)
+    const int32_t tp_own_items = max(1, (total_work - cluster_idx + num_clusters - 1) / num_clusters);
     for (int32_t w = first_work; w >= 0; ++step) {
       if constexpr (DYN) {
         if (is_leader) {
@@ -735,6 +740,10 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         __syncwarp();
       }
       for (int32_t kt = 0; kt < tile_k_tiles; ++kt) {
+        if constexpr (TP) {
+          if (p.tp_paced_push == 2 && lane == 0 && (kt & 7) == 0)
+            ctl->tp_progress = int32_t((int64_t(step) * tile_k_tiles + kt) * 1024 * p.tp_world / (int64_t(tp_own_items) * tile_k_tiles));
+        }
         wait_barrier(empty0 + stage * 8, phase ^ 1u, ctl, dead);
         BSG_DBG(0, 1);
         // After a timeout nothing more is issued: free-running loads would overrun the barriers' byte counts.
@@ -781,7 +790,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
     }
     if constexpr (TP) {
-      if (lane == 0) ctl->tp_stage_now = 1 << 20;      // nothing left to pace against
+      if (lane == 0) { ctl->tp_stage_now = 1 << 20; ctl->tp_progress = 1 << 30; }     // nothing left to pace against
     }
     // Tail: every stage must have been released, so that no commit-arrive is still
     // in flight towards this CTA's shared memory when it exits.
@@ -914,7 +923,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           ptx::bulk_load(buf0 + n_ld * ch, ld_it.src(p), ld_it.bytes, bar0 + n_ld * 8);
         }
       }
-      int checked = -1;
+      int checked = -1, paced_piece = -1;
       // Ring of staging buffers: chunk n goes through buffer n % nb.  A buffer is refilled `rlag` stores
       // after its own store was issued (by then that store has read it), so neither the load latency nor
       // the store's read latency is waited for in line.  A finished piece is announced kTpLag chunks
@@ -943,8 +952,19 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       };
       for (; st_it.valid(); st_it.next(p), ++n_st) {
         const uint32_t b = n_st % nb;
+        if (p.tp_paced_push == 2 && st_it.c != paced_piece) {
+          // Spread push: the pieces for the j-th nearest consumer leave evenly over the first three quarters of
+          // stage j - 1 of this CTA's walk (piece `rem` of the shard's `per_shard` at that fraction), so that the links
+          // carry a steady flow instead of one burst per stage.
+          const int j = st_it.c / st_it.per_shard + 1;
+          const int rem = st_it.c - (j - 1) * st_it.per_shard;
+          const int need = (j - 1) * 1024 + 768 * rem / st_it.per_shard;
+          const long long t0 = clock64();
+          while (ctl->tp_progress < need && !ctl->abort && clock64() - t0 < 4000000000ll) __nanosleep(200);
+          paced_piece = st_it.c;
+        }
         if (st_it.dst_rank != checked) {
-          if (p.tp_paced_push) {
+          if (p.tp_paced_push == 1) {
             // j-th nearest consumer: its rows are due when it starts stage j, which is when this rank does too
             const int j = (p.tp_rank - st_it.dst_rank + p.tp_world) % p.tp_world;
             const long long t0 = clock64();

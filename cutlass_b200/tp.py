@@ -231,7 +231,7 @@ class TpGemm:
         base, *opts = mode.split("+")
         code = {"kernel": 0, "copy_engine": 1}[base]
         for opt in opts:
-            code |= {"single": 2, "release": 4, "paced": 8}[opt]   # one gathered buffer; release-fenced announcements; paced push
+            code |= {"single": 2, "release": 4, "paced": 8, "spread": 16}[opt]   # one gathered buffer; release-fenced announcements; paced / spread push
         self._L.check(self._lib.bsg_tp_set_mode(self._comm, code))
         self.mode = mode
 

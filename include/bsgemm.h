@@ -391,7 +391,9 @@ int32_t bsg_quantize(const bsg_quant_args* args, void* cuda_stream);
 enum { BSG_TP_PUSH_KERNEL = 0, BSG_TP_PUSH_COPY_ENGINE = 1, BSG_TP_SINGLE_BUFFER = 2 /* or-ed in: every call uses the first gathered buffer */,
        BSG_TP_RELEASE_ANNOUNCE = 4 /* or-ed in: see "Ordering of the announcements" above */,
        BSG_TP_PACED_PUSH = 8 /* or-ed in: a CTA pushes the rows for its j-th nearest consumer while it works on stage j - 1 of
-                                its own walk (they arrive a stage before they are needed) instead of everything at once */ };
+                                its own walk (they arrive a stage before they are needed) instead of everything at once */,
+       BSG_TP_SPREAD_PUSH = 16 /* or-ed in: as BSG_TP_PACED_PUSH, with the pieces of a stage leaving evenly over the first three
+                                 quarters of that stage instead of in one burst at its start */ };
 typedef struct bsg_tp_comm bsg_tp_comm;
 int32_t bsg_tp_set_mode(bsg_tp_comm* comm, int32_t mode);
 int32_t bsg_tp_create(int32_t rank, int32_t world, int32_t kind, int64_t M, int64_t K, bsg_tp_comm** out,

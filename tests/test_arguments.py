@@ -306,3 +306,18 @@ def test_row_pitch_and_batch_stride_reach_the_abi():
                                               torch.zeros(ops.ScaledOperand.numel_scale((N, K), M16, SW), dtype=torch.uint8), M16, SW),
                             torch.zeros((M, N), dtype=torch.bfloat16), torch.float32)
     assert ops.get_operators(bad) == []
+
+
+def test_pointer_array_groups_are_checked_on_the_host():
+    """GroupProblem tensors: K must agree between A and B, tensors are two-dimensional with a contiguous last dimension."""
+    import torch
+    from cutlass_b200 import lib as L
+    from cutlass_b200.ptr_array import GroupProblem, PtrArrayGemm
+    u8 = lambda *s: torch.zeros(s, dtype=torch.uint8)  # noqa: E731
+    with pytest.raises(ValueError, match="disagree on K"):
+        PtrArrayGemm(L.KIND_NVFP4, [GroupProblem(A=u8(128, 64), SFA=u8(512), B=u8(128, 32), SFB=u8(512), D=torch.zeros((128, 128), dtype=torch.bfloat16))])
+    with pytest.raises(ValueError, match="contiguous last dimension"):
+        PtrArrayGemm(L.KIND_MXFP8, [GroupProblem(A=u8(128, 256)[:, ::2], SFA=u8(512), B=u8(128, 128), SFB=u8(512),
+                                                 D=torch.zeros((128, 128), dtype=torch.bfloat16))])
+    with pytest.raises(ValueError, match="at least one group"):
+        PtrArrayGemm(L.KIND_MXFP8, [])
