@@ -960,7 +960,10 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           const int rem = st_it.c - (j - 1) * st_it.per_shard;
           const int need = (j - 1) * 1024 + 768 * rem / st_it.per_shard;
           const long long t0 = clock64();
-          while (ctl->tp_progress < need && !ctl->abort && clock64() - t0 < 4000000000ll) __nanosleep(200);
+          // A CTA whose tile is already at stage s counts as that far whatever its own pace (in a small problem a CTA
+          // may start at a late stage and stand still there, waiting for rows that the peers send by the same rule).
+          while (max(ctl->tp_progress, min(ctl->tp_stage_now, 1 << 10) * 1024) < need && !ctl->abort && clock64() - t0 < 4000000000ll)
+            __nanosleep(200);
           paced_piece = st_it.c;
         }
         if (st_it.dst_rank != checked) {
