@@ -627,24 +627,27 @@ def run_single(args) -> dict:
         xs = [torch.randn((M, K), device=dev, generator=gen).to(torch.bfloat16) for _ in range(3)]   # 3 x 134 MB > L2
         qo = [ops.quantize_blockscaled(x, mode) for x in xs]
         torch.cuda.synchronize()
-        q_launch = lambda i: ops.quantize_blockscaled(xs[i % 3], mode, out=qo[i % 3].quantized.tensor, scale_out=qo[i % 3].scale.tensor,  # noqa: E731
-                                                      stream=stream)
+        q_launch = lambda i, s=stream: ops.quantize_blockscaled(xs[i % 3], mode, out=qo[i % 3].quantized.tensor,  # noqa: E731
+                                                                scale_out=qo[i % 3].scale.tensor, stream=s)
         q_ms_loop = time_steps(q_launch, 30, 3, stream)
         # A 30 us kernel launched from Python is bound by the host's launch rate whenever the host is busy: the same 30
         # launches captured once in a CUDA graph give the device time.
         q_ms, q_how = q_ms_loop, "30 launches from the host"
         try:
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                for i in range(30):
-                    q_launch(i)
-            graph.replay()
+            cap = torch.cuda.Stream()          # a capture needs a stream of its own
             torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(3):
+            with torch.cuda.graph(graph, stream=cap):
+                for i in range(30):
+                    q_launch(i, cap)
+            with torch.cuda.stream(cap):
                 graph.replay()
-            e1.record()
+                cap.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(cap)
+                for _ in range(3):
+                    graph.replay()
+                e1.record(cap)
             torch.cuda.synchronize()
             q_ms, q_how = e0.elapsed_time(e1) / 90, "3 replays of a CUDA graph of 30 launches (three operand sets rotated)"
             launches += 120

@@ -146,6 +146,12 @@ int32_t make_sf_map(CUtensorMap* map, const void* base, uint64_t k_atoms, uint64
 // bf16: 128 bytes per row, 128-byte swizzle; e4m3: 64 bytes, 64-byte swizzle; packed e2m1: 32 bytes, no swizzle.
 int32_t make_out_map(CUtensorMap* map, const void* base, int32_t out_kind, uint64_t cols, uint64_t rows, uint64_t batches,
                      uint64_t pitch_elems, uint64_t batch_stride_elems) {
+  if (out_kind == BSG_OUT_F16)
+    return g_maps.get(make_key(base, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                               cols, rows, batches, pitch_elems * 2, batch_stride_elems * 2, 64, 32, 1), map);
+  if (out_kind == BSG_OUT_F32)      // 32 columns are 128 bytes: half a pair per store
+    return g_maps.get(make_key(base, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                               cols, rows, batches, pitch_elems * 4, batch_stride_elems * 4, 32, 32, 1), map);
   if (out_kind == BSG_OUT_BF16)
     return g_maps.get(make_key(base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                                cols, rows, batches, pitch_elems * 2, batch_stride_elems * 2, 64, 32, 1), map);
@@ -218,7 +224,9 @@ struct Plan {
 
 int32_t validate(const Problem& q, Plan* plan) {
   if (q.kind < BSG_KIND_NVFP4 || q.kind > BSG_KIND_MXFP8_MXFP4) return fail(BSG_ERR_NOT_SUPPORTED, "unknown operand kind %d", q.kind);
-  if (q.out_kind != BSG_OUT_BF16 && q.out_kind != BSG_OUT_NVFP4 && q.out_kind != BSG_OUT_MXFP8) return fail(BSG_ERR_NOT_SUPPORTED, "unknown output kind %d", q.out_kind);
+  if (q.out_kind < BSG_OUT_BF16 || q.out_kind > BSG_OUT_F32) return fail(BSG_ERR_NOT_SUPPORTED, "unknown output kind %d", q.out_kind);
+  const bool quantised_out = q.out_kind == BSG_OUT_NVFP4 || q.out_kind == BSG_OUT_MXFP8;
+  if (q.rs && q.out_kind != BSG_OUT_BF16) return fail(BSG_ERR_NOT_SUPPORTED, "the reduce-scatter GEMM writes bf16");
   if (q.num_groups < 1 || q.num_groups > BSG_MAX_GROUPS) return fail(BSG_ERR_INVALID_PROBLEM, "group / batch count %d outside [1, %d]", q.num_groups, BSG_MAX_GROUPS);
   if (q.N < 1 || q.K < 1 || q.total_rows < 0) return fail(BSG_ERR_INVALID_PROBLEM, "extents must be positive (rows=%lld N=%lld K=%lld)", (long long)q.total_rows, (long long)q.N, (long long)q.K);
   if (q.total_rows > 0x7FFFFFFF / 2 || q.N > 0x7FFFFFFF / 2 || q.K > 0x7FFFFFFF / 2) return fail(BSG_ERR_INVALID_PROBLEM, "extent exceeds 2^30");
@@ -231,13 +239,15 @@ int32_t validate(const Problem& q, Plan* plan) {
   if (!aligned16(q.SFA) || !aligned16(q.SFB)) return fail(BSG_ERR_MISALIGNED_OPERAND, "scale-factor tensors must be 16-byte aligned");
   if (q.out_col_major) {
     // column-major quantised output: D is (N, M) with M contiguous, scale factors along M
-    if (q.out_kind == BSG_OUT_BF16) return fail(BSG_ERR_NOT_SUPPORTED, "the column-major layout is for quantised outputs");
+    if (!quantised_out) return fail(BSG_ERR_NOT_SUPPORTED, "the column-major layout is for quantised outputs");
     if (q.offsets || q.num_groups != 1 || q.tp || q.rs) return fail(BSG_ERR_NOT_SUPPORTED, "the column-major output layout is for the dense, unbatched GEMM");
     if (!q.SFD || (q.out_kind == BSG_OUT_NVFP4 && !q.norm_ptr)) return fail(BSG_ERR_INVALID_PROBLEM, "quantised output needs SFD (and norm_constant for NVFP4)");
     if (q.rows_per_group % 32 != 0 || q.ldd % 32 != 0 || q.ldd < q.rows_per_group)
       return fail(BSG_ERR_MISALIGNED_OPERAND, "column-major output needs M %% 32 == 0 and ldd (the pitch of a column, >= M) %% 32 == 0");
-  } else if (q.out_kind == BSG_OUT_BF16) {
-    if (q.N % 8 != 0 || q.ldd % 8 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "bf16 output needs N and ldd to be multiples of 8");
+  } else if (q.out_kind == BSG_OUT_BF16 || q.out_kind == BSG_OUT_F16) {
+    if (q.N % 8 != 0 || q.ldd % 8 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "bf16 / fp16 output needs N and ldd to be multiples of 8");
+  } else if (q.out_kind == BSG_OUT_F32) {
+    if (q.N % 4 != 0 || q.ldd % 4 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "fp32 output needs N and ldd to be multiples of 4");
   } else if (q.out_kind == BSG_OUT_MXFP8) {
     if (!q.SFD) return fail(BSG_ERR_INVALID_PROBLEM, "MXFP8 output needs SFD");
     if (q.N % 32 != 0 || q.ldd % 16 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "MXFP8 output needs N %% 32 == 0 and ldd %% 16 == 0");
@@ -260,7 +270,7 @@ int32_t validate(const Problem& q, Plan* plan) {
     return fail(BSG_ERR_MISALIGNED_OPERAND, "lda=%lld and ldb=%lld must be multiples of %lld (16-byte rows)", (long long)q.lda, (long long)q.ldb, (long long)k_align);
   if (!q.offsets && q.num_groups > 1) {
     if (q.bs_a % k_align != 0 || q.bs_b % k_align != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "batch strides of A and B must be multiples of %lld elements", (long long)k_align);
-    const int64_t d_align = q.out_kind == BSG_OUT_BF16 ? 8 : q.out_kind == BSG_OUT_MXFP8 ? 16 : 32;
+    const int64_t d_align = q.out_kind == BSG_OUT_F32 ? 4 : !quantised_out ? 8 : q.out_kind == BSG_OUT_MXFP8 ? 16 : 32;
     if (q.bs_d % d_align != 0 || (q.C && q.bs_c % 8 != 0)) return fail(BSG_ERR_MISALIGNED_OPERAND, "batch strides of C and D must keep every matrix 16-byte aligned");
     if (q.bs_a < 0 || q.bs_b < 0 || q.bs_c < 0 || q.bs_d < q.rows_per_group * q.ldd) return fail(BSG_ERR_INVALID_PROBLEM, "negative batch stride, or output matrices that overlap");
   }
@@ -612,7 +622,7 @@ int32_t ptr_array_check(const bsg_ptr_array_args* a, PtrTableInfo* info) {
   if (a->kind != BSG_KIND_NVFP4 && a->kind != BSG_KIND_MXFP8) return fail(BSG_ERR_NOT_SUPPORTED, "the pointer-array form takes NVFP4 or MXFP8 operands (kind %d)", a->kind);
   if (a->num_groups < 1 || a->num_groups > BSG_MAX_GROUPS) return fail(BSG_ERR_INVALID_PROBLEM, "group count %d outside [1, %d]", a->num_groups, BSG_MAX_GROUPS);
   if (!a->problem_sizes || !a->A || !a->B || !a->SFA || !a->SFB || !a->D) return fail(BSG_ERR_INVALID_PROBLEM, "problem_sizes, A, B, SFA, SFB and D arrays must be non-null");
-  if (a->out_kind != BSG_OUT_BF16 && !a->SFD) return fail(BSG_ERR_INVALID_PROBLEM, "quantised output needs the SFD array");
+  if ((a->out_kind == BSG_OUT_NVFP4 || a->out_kind == BSG_OUT_MXFP8) && !a->SFD) return fail(BSG_ERR_INVALID_PROBLEM, "quantised output needs the SFD array");
   if (a->tile_n != 0 && a->tile_n != 128 && a->tile_n != 256) return fail(BSG_ERR_NOT_SUPPORTED, "tile_n must be 0, 128 or 256");
   if (a->use_pdl != 0 && a->use_pdl != 1) return fail(BSG_ERR_INVALID_PROBLEM, "use_pdl must be 0 or 1");
   if ((a->beta != 0.0f || a->beta_array) && !a->C) return fail(BSG_ERR_INVALID_PROBLEM, "beta needs the C array");

@@ -46,6 +46,9 @@ __host__ __device__ constexpr bool kind_packs_fp4(int kind) { return kind == kKi
 constexpr int kOutBf16 = 0;
 constexpr int kOutNvfp4 = 1;
 constexpr int kOutMxfp8 = 2;
+constexpr int kOutF16 = 3;
+constexpr int kOutF32 = 4;
+__host__ __device__ constexpr bool out_is_quantised(int out_kind) { return out_kind == kOutNvfp4 || out_kind == kOutMxfp8; }
 constexpr int kActIdentity = 0, kActRelu = 1, kActGelu = 2, kActSilu = 3;
 
 // Bits of the device status word.
@@ -357,6 +360,10 @@ __device__ __forceinline__ WorkItem decode_work(int32_t w, int32_t split_from) {
   return wi;
 }
 
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -1024,7 +1031,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const float alpha_all = p.alpha_ptr ? *p.alpha_ptr : p.alpha;
     const float beta_all = p.beta_ptr ? *p.beta_ptr : p.beta;
     float st = 0.f, st_scaled = 0.f;
-    if (p.out_kind != kOutBf16) {
+    if (out_is_quantised(p.out_kind)) {
       st = p.norm_ptr ? *p.norm_ptr : 1.0f;
       st_scaled = __fmul_rn(st, __fdiv_rn(1.0f, p.out_kind == kOutNvfp4 ? 6.0f : 448.0f));
     }
@@ -1123,12 +1130,13 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       // store clips at the end of the matrix, not at the end of a group: the warp that holds a group's last rows
       // stores them row by row.)
       const int out_kind = p.out_kind;
-      const bool col_major = out_kind != kOutBf16 && p.out_col_major != 0;
+      const bool quantised = out_is_quantised(out_kind);
+      const bool col_major = quantised && p.out_col_major != 0;
       // (Pointer-array form: every group has a map of its own, which clips at the group's last row.)
       const bool tma_out = (PTR ? cta_row0 + warp * 32 < ti.row_end : cta_row0 + warp * 32 + 32 <= ti.row_end) && !col_major;
       // Staging sub-buffers a warp cycles through (4 KB per warp): bf16 uses all of it per 64 columns, e4m3 half,
       // e2m1 a quarter; a sub-buffer is rewritten once all but the newest n_bufs - 1 stores have read theirs.
-      const int n_bufs = out_kind == kOutBf16 ? 1 : out_kind == kOutMxfp8 ? 2 : 4;
+      const int n_bufs = !quantised ? 1 : out_kind == kOutMxfp8 ? 2 : 4;
 
 #pragma unroll 1
       for (int pi = 0; pi < n_pairs; ++pi) {
@@ -1285,35 +1293,69 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 sf_base[(mb >> 2) * 512 + (mb & 3)] = uint8_t(q);
               }
             }
-          } else if (out_kind == kOutBf16) {
+          } else if (out_kind == kOutF32) {
+            // fp32 output: 32 columns are 128 bytes, so each half of the pair fills the staging tile (128-byte swizzle:
+            // 16-byte chunk c of row r lives at chunk c ^ (r & 7)) and leaves with a store of its own.
+            if (tma_out) {
+              if (h == 1) {
+                if (lane == 0) ptx::bulk_wait_group_read<0>();
+                __syncwarp();
+              }
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                *reinterpret_cast<float4*>(stage_buf + lane * 128 + ((q ^ (lane & 7)) * 16)) = make_float4(x[q * 4], x[q * 4 + 1], x[q * 4 + 2], x[q * 4 + 3]);
+              if (h == 0) {
+                ptx::fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) {
+                  ptx::tma_store_3d(mapD, ptx::smem_u32(stage_buf), col0, warp_map_row0, ti.map_l);
+                  ptx::bulk_commit_group();
+                }
+              }
+            } else {
+              float* drow = reinterpret_cast<float*>(Dg) + d_row_off + col0;
+              if (cols_valid >= 32) {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) reinterpret_cast<float4*>(drow)[q] = make_float4(x[q * 4], x[q * 4 + 1], x[q * 4 + 2], x[q * 4 + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  if (j < cols_valid) drow[j] = x[j];
+                }
+              }
+            }
+          } else if (!quantised) {
+            // bf16 or fp16 output
+            const bool f16 = out_kind == kOutF16;
+            uint4 o[4];
+            if (f16) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                o[q] = make_uint4(pack_f16x2(x[q * 8 + 0], x[q * 8 + 1]), pack_f16x2(x[q * 8 + 2], x[q * 8 + 3]),
+                                  pack_f16x2(x[q * 8 + 4], x[q * 8 + 5]), pack_f16x2(x[q * 8 + 6], x[q * 8 + 7]));
+            } else {
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                o[q] = make_uint4(pack_bf16x2(x[q * 8 + 0], x[q * 8 + 1]), pack_bf16x2(x[q * 8 + 2], x[q * 8 + 3]),
+                                  pack_bf16x2(x[q * 8 + 4], x[q * 8 + 5]), pack_bf16x2(x[q * 8 + 6], x[q * 8 + 7]));
+            }
             if (tma_out) {
               // 128-byte-swizzled staging tile: 16-byte chunk c of row r lives at chunk (c ^ (r & 7)).
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                uint4 o;
-                o.x = pack_bf16x2(x[q * 8 + 0], x[q * 8 + 1]);
-                o.y = pack_bf16x2(x[q * 8 + 2], x[q * 8 + 3]);
-                o.z = pack_bf16x2(x[q * 8 + 4], x[q * 8 + 5]);
-                o.w = pack_bf16x2(x[q * 8 + 6], x[q * 8 + 7]);
                 const int chunk = (h * 4 + q) ^ (lane & 7);
-                *reinterpret_cast<uint4*>(stage_buf + lane * 128 + chunk * 16) = o;
+                *reinterpret_cast<uint4*>(stage_buf + lane * 128 + chunk * 16) = o[q];
               }
             } else {
-              __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(Dg) + d_row_off + col0;
+              uint16_t* drow = reinterpret_cast<uint16_t*>(Dg) + d_row_off + col0;
               if (cols_valid >= 32) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  uint4 o;
-                  o.x = pack_bf16x2(x[q * 8 + 0], x[q * 8 + 1]);
-                  o.y = pack_bf16x2(x[q * 8 + 2], x[q * 8 + 3]);
-                  o.z = pack_bf16x2(x[q * 8 + 4], x[q * 8 + 5]);
-                  o.w = pack_bf16x2(x[q * 8 + 6], x[q * 8 + 7]);
-                  reinterpret_cast<uint4*>(drow)[q] = o;
-                }
+                for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(drow)[q] = o[q];
               } else {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
-                  if (j < cols_valid) drow[j] = __float2bfloat16_rn(x[j]);
+                  const uint32_t w = j < 8 ? (&o[0].x)[j >> 1] : j < 16 ? (&o[1].x)[(j - 8) >> 1] : j < 24 ? (&o[2].x)[(j - 16) >> 1] : (&o[3].x)[(j - 24) >> 1];
+                  if (j < cols_valid) drow[j] = uint16_t((j & 1) ? (w >> 16) : (w & 0xFFFFu));
                 }
               }
             }
@@ -1377,7 +1419,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
           }
         }
-        if (out_kind != kOutBf16 && !col_major && row_ok && tile_col0 + pr * 64 < prob_N) {
+        if (quantised && !col_major && row_ok && tile_col0 + pr * 64 < prob_N) {
           // Scale factors of this row for the 64 columns: consecutive bytes of one 512-byte atom of the interleaved
           // layout (4 per row for 16-wide blocks, 2 for 32-wide ones).
           const int32_t pair_col0 = tile_col0 + pr * 64;
@@ -1412,7 +1454,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             } else if (RS)
               ptx::tma_store_3d(&tmD, ptx::smem_u32(sub_buf), col, rs_row_in_slice, 0);
             else
-              ptx::tma_store_3d(mapD, ptx::smem_u32(sub_buf), out_kind == kOutNvfp4 ? col / 2 : col, warp_map_row0, ti.map_l);
+              ptx::tma_store_3d(mapD, ptx::smem_u32(sub_buf), out_kind == kOutNvfp4 ? col / 2 : out_kind == kOutF32 ? col + 32 : col, warp_map_row0, ti.map_l);
             ptx::bulk_commit_group();
           }
         }

@@ -32,6 +32,8 @@ KIND_MXFP8_MXFP4 = 3    # A e4m3, B e2m1, ue8m0 scale per 32
 OUT_BF16 = 0
 OUT_NVFP4 = 1
 OUT_MXFP8 = 2
+OUT_F16 = 3
+OUT_F32 = 4
 ACT_IDENTITY, ACT_RELU, ACT_GELU, ACT_SILU = 0, 1, 2, 3
 BIAS_NONE, BIAS_PER_COLUMN, BIAS_PER_ROW = 0, 1, 2
 MAX_GROUPS = 256

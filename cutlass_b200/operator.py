@@ -222,6 +222,15 @@ class Operator:
         raise NotImplementedError
 
 
+# Unquantised output types (the reference's operator lists Float32 / Float16 / BFloat16 among its output types,
+# providers/cutedsl/gemm/sm100_dense_blockscaled_static_persistent.py:454-460).
+_PLAIN_OUT_KINDS = {torch.bfloat16: L.OUT_BF16, torch.float16: L.OUT_F16, torch.float32: L.OUT_F32}
+
+
+def _plain_out_kind(t: torch.Tensor) -> int:
+    return _PLAIN_OUT_KINDS[t.dtype]
+
+
 def _k_major_rows(t: torch.Tensor, rows_axis: int, k_axis: int) -> bool:
     """True when ``t`` has K contiguous and rows / batch entries that start on 16-byte boundaries: a row pitch
     larger than K and a batch stride larger than one matrix are fine (a slice of a larger buffer)."""
@@ -268,10 +277,10 @@ class BlockScaledGemmOperator(Operator):
         if not _k_major_rows(out, -2, -1):
             return Status.fail("out must be row-major with 16-byte aligned rows")
         if epi.out_quant is None:
-            if out.dtype != torch.bfloat16:
-                return Status.fail(f"out dtype {out.dtype} is not supported (bf16, or packed fp4 with out_quant)")
-            if ps.N % 8 != 0:
-                return Status.fail("N must be a multiple of 8 for bf16 output")
+            if out.dtype not in _PLAIN_OUT_KINDS:
+                return Status.fail(f"out dtype {out.dtype} is not supported (bf16, fp16, fp32, or a quantised output with out_quant)")
+            if ps.N % (4 if out.dtype == torch.float32 else 8) != 0:
+                return Status.fail("N must be a multiple of 8 for bf16 / fp16 output, of 4 for fp32")
         elif isinstance(epi.out_quant, Mxfp8Quant):
             if out.dtype not in (torch.uint8, torch.float8_e4m3fn):
                 return Status.fail("MXFP8 output needs a uint8 / float8_e4m3fn out tensor")
@@ -319,7 +328,7 @@ class BlockScaledGemmOperator(Operator):
         epi = args.epilogue or EpilogueDescriptor()
         a = L.GemmArgs()
         a.kind = md.kind
-        a.out_kind = L.OUT_BF16 if epi.out_quant is None else (L.OUT_MXFP8 if isinstance(epi.out_quant, Mxfp8Quant) else L.OUT_NVFP4)
+        a.out_kind = _plain_out_kind(args.out.tensor) if epi.out_quant is None else (L.OUT_MXFP8 if isinstance(epi.out_quant, Mxfp8Quant) else L.OUT_NVFP4)
         a.batch = ps.L
         a.M, a.N, a.K = ps.M, ps.N, ps.K
         a.A = args.A.quantized.data_ptr()
@@ -398,10 +407,10 @@ class GroupedBlockScaledGemmOperator(Operator):
         if not out.is_contiguous():
             return Status.fail("out must be contiguous")
         if epi.out_quant is None:
-            if out.dtype != torch.bfloat16:
-                return Status.fail("out must be a bf16 tensor (or a quantised output with out_quant)")
-            if ps.N % 8 != 0:
-                return Status.fail("N must be a multiple of 8")
+            if out.dtype not in _PLAIN_OUT_KINDS:
+                return Status.fail("out must be a bf16, fp16 or fp32 tensor (or a quantised output with out_quant)")
+            if ps.N % (4 if out.dtype == torch.float32 else 8) != 0:
+                return Status.fail("N must be a multiple of 8 (4 for fp32 output)")
         else:
             # one interleaved scale layout per group, each padded to 128 rows: the form the next grouped GEMM takes as SFA
             mx = isinstance(epi.out_quant, Mxfp8Quant)
@@ -438,7 +447,7 @@ class GroupedBlockScaledGemmOperator(Operator):
         epi = args.epilogue or EpilogueDescriptor()
         a = L.GroupedArgs()
         a.kind = md.kind
-        a.out_kind = L.OUT_BF16 if epi.out_quant is None else (L.OUT_MXFP8 if isinstance(epi.out_quant, Mxfp8Quant) else L.OUT_NVFP4)
+        a.out_kind = _plain_out_kind(args.out.tensor) if epi.out_quant is None else (L.OUT_MXFP8 if isinstance(epi.out_quant, Mxfp8Quant) else L.OUT_NVFP4)
         if epi.out_quant is not None:
             a.SFD = epi.out_quant.scale.data_ptr()
             a.norm_constant = epi.out_quant.norm_constant.data_ptr() if epi.out_quant.norm_constant is not None else None

@@ -46,7 +46,9 @@ enum {
 enum {
   BSG_OUT_BF16 = 0,         /* D = bf16(alpha*acc + beta*C) */
   BSG_OUT_NVFP4 = 1,        /* D = e2m1 packed + SFD ue4m3 per 16 N-elements, interleaved layout */
-  BSG_OUT_MXFP8 = 2         /* D = e4m3 + SFD ue8m0 (round-up conversion) per 32 N-elements, interleaved layout */
+  BSG_OUT_MXFP8 = 2,        /* D = e4m3 + SFD ue8m0 (round-up conversion) per 32 N-elements, interleaved layout */
+  BSG_OUT_F16 = 3,          /* D = fp16(...)  (C, when given, stays bf16) */
+  BSG_OUT_F32 = 4           /* D = fp32(...): the epilogue's own precision, nothing rounded */
 };
 
 /*
@@ -81,7 +83,7 @@ typedef struct bsg_gemm_args {
   const void* SFA;
   const void* SFB;
   const void* C;            /* bf16, may be NULL when beta == 0 */
-  void* D;                  /* bf16; packed e2m1 (BSG_OUT_NVFP4); e4m3 (BSG_OUT_MXFP8) */
+  void* D;                  /* bf16; packed e2m1 (BSG_OUT_NVFP4); e4m3 (BSG_OUT_MXFP8); fp16; fp32 */
   void* SFD;                /* scale factors of D, interleaved over (M, N/16) or (M, N/32); quantised outputs only */
   int64_t ldc;              /* C row pitch in elements (0 = N) */
   int64_t ldd;              /* D row pitch in elements (0 = N) */

@@ -112,8 +112,13 @@ def test_supports_rejections():
     assert "accumulator" in str(op.supports(bad).error)
     # output dtype
     bad = nvfp4_args()
-    bad.out = ops.DenseTensor(torch.zeros((256, 256), dtype=torch.float16))
+    bad.out = ops.DenseTensor(torch.zeros((256, 256), dtype=torch.float64))
     assert "out dtype" in str(op.supports(bad).error)
+    # fp16 and fp32 outputs are taken as they are
+    for dt in (torch.float16, torch.float32):
+        good = nvfp4_args()
+        good.out = ops.DenseTensor(torch.zeros((256, 256), dtype=dt))
+        assert op.supports(good)
     # beta without C
     assert "beta" in str(op.supports(nvfp4_args(epilogue=ops.EpilogueDescriptor(beta=0.5))).error)
     # dense operands are not block-scaled

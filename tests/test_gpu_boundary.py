@@ -257,3 +257,92 @@ def test_column_major_quantised_output(cuda_lib, kind, out_kind, M, N, K, pitch)
     assert np.all(got[:, used:] == 0x55), "the pitch padding of D must stay untouched"
     idx = R.sf_index(N, M // vec)
     assert np.array_equal(dSFD.cpu().numpy()[idx], SFDw[idx])
+
+
+def _plain_out(out_kind, shape):
+    dt = {0: torch.bfloat16, 3: torch.float16, 4: torch.float32}[out_kind]
+    return torch.full(shape, float("nan"), dtype=dt, device="cuda")       # NaN: cells that are never written show up
+
+
+def _as_out(pre_fp32, out_kind):
+    """The oracle's fp32 epilogue value in the output type (round to nearest even, as the device conversions)."""
+    if out_kind == 4:
+        return pre_fp32.astype(np.float32)
+    if out_kind == 3:
+        return pre_fp32.astype(np.float16)
+    return oracle.to_bf16(pre_fp32)
+
+
+@pytest.mark.parametrize("out_kind", [3, 4])
+@pytest.mark.parametrize("kind,M,N,K,batch,tile_n", [(0, 512, 512, 256, 1, 0), (1, 300, 392, 512, 1, 0), (0, 256, 1096, 256, 2, 0), (1, 640, 128, 256, 1, 128)])
+def test_fp16_and_fp32_outputs(cuda_lib, kind, out_kind, M, N, K, batch, tile_n):
+    """Unquantised outputs other than bf16 (the reference's operator offers Float16 / Float32 outputs too): the same
+    epilogue value, converted to fp16 or stored as fp32; C stays bf16.  Bit for bit on exact operands, ragged M and N."""
+    rng = np.random.default_rng(41)
+    gen_a, gen_b = G.operand_generators(kind, True)
+    As, Bs, pres = [], [], []
+    Cb = G.bf16_normal((batch * M, N), rng)
+    for b in range(batch):
+        A, _, sfa = gen_a(M, K, rng)
+        B, _, sfb = gen_b(N, K, rng)
+        As.append((A, sfa)); Bs.append((B, sfb))
+        pres.append(oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K, Cb[b * M:(b + 1) * M], 0.5, 2.0))
+    want = _as_out(np.concatenate(pres, axis=0), out_kind)
+    dA, dSFA = dev(np.concatenate([a for a, _ in As], axis=0)), dev(np.concatenate([s for _, s in As]))
+    dB, dSFB = dev(np.concatenate([b for b, _ in Bs], axis=0)), dev(np.concatenate([s for _, s in Bs]))
+    dC = dev(Cb)
+    dD = _plain_out(out_kind, (batch * M, N))
+    a = L.GemmArgs()
+    a.kind, a.out_kind, a.batch, a.M, a.N, a.K = kind, out_kind, batch, M, N, K
+    a.A, a.SFA, a.B, a.SFB, a.C, a.D = (t.data_ptr() for t in (dA, dSFA, dB, dSFB, dC, dD))
+    a.alpha, a.beta, a.tile_n = 0.5, 2.0, tile_n
+    _run(a)
+    got = dD.cpu().numpy()
+    assert not np.isnan(got).any(), "unwritten outputs"
+    assert np.array_equal(got.view(np.uint16 if out_kind == 3 else np.uint32), want.view(np.uint16 if out_kind == 3 else np.uint32))
+
+
+@pytest.mark.parametrize("out_kind", [3, 4])
+def test_fp16_and_fp32_outputs_grouped_ragged(cuda_lib, out_kind):
+    """The same through the grouped call with ragged groups: the warp that holds a group's last rows stores row by row."""
+    kind, N, K = 0, 392, 256
+    sizes = [100, 0, 300, 1, 515]
+    rng = np.random.default_rng(43)
+    total = int(np.sum(sizes))
+    As, sfas, Bs, sfbs = [], [], [], []
+    for m in sizes:
+        A, _, sfa = G.exact_nvfp4_operand(int(m), K, rng) if m > 0 else (np.zeros((0, K // 2), np.uint8), None, np.zeros(0, np.uint8))
+        B, _, sfb = G.exact_nvfp4_operand(N, K, rng)
+        As.append(A); sfas.append(sfa); Bs.append(B); sfbs.append(sfb)
+    want = np.concatenate([_as_out(oracle.gemm_fp32(kind, As[g], sfas[g], Bs[g], sfbs[g], int(m), N, K), out_kind)
+                           for g, m in enumerate(sizes) if m > 0], axis=0)
+    dA, dB = dev(np.concatenate(As, axis=0)), dev(np.stack(Bs))
+    dSFA, dSFB = dev(np.concatenate(sfas)), dev(np.concatenate(sfbs))
+    offs = torch.tensor(np.cumsum(sizes), dtype=torch.int32, device="cuda")
+    dD = _plain_out(out_kind, (total, N))
+    g = L.GroupedArgs()
+    g.kind, g.out_kind, g.num_groups, g.total_M, g.N, g.K = kind, out_kind, len(sizes), total, N, K
+    g.A, g.B, g.SFA, g.SFB, g.D, g.offsets = (t.data_ptr() for t in (dA, dB, dSFA, dSFB, dD, offs))
+    g.alpha = 1.0
+    lib = L.load()
+    ws = torch.zeros(16, dtype=torch.uint8, device="cuda")
+    L.check(lib.bsg_grouped_run(C.byref(g), ws.data_ptr(), 16, None))
+    L.check(lib.bsg_read_device_status(ws.data_ptr(), None))
+    torch.cuda.synchronize()
+    got = dD.cpu().numpy()
+    assert not np.isnan(got).any(), "unwritten outputs"
+    assert np.array_equal(got.view(np.uint16 if out_kind == 3 else np.uint32), want.view(np.uint16 if out_kind == 3 else np.uint32))
+
+
+def test_fp32_output_through_the_operator_api(cuda_lib):
+    import cutlass_b200 as ops
+    kind, M, N, K = 0, 384, 512, 512
+    rng, A, sfa, B, sfb = make_operands(kind, M, N, K, 47, True)
+    Aop = ops.ScaledOperand(dev(A), dev(sfa), ops.ScaleMode.Blockwise1x16, ops.ScaleSwizzleMode.Swizzle32x4x4)
+    Bop = ops.ScaledOperand(dev(B).t(), dev(sfb), ops.ScaleMode.Blockwise1x16, ops.ScaleSwizzleMode.Swizzle32x4x4)
+    out = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    args = ops.GemmArguments(Aop, Bop, out, torch.float32)
+    op = ops.get_operators(args)[0]
+    op.run(args)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K).astype(np.float32))
