@@ -1052,6 +1052,38 @@ int32_t bsg_ptr_array_initialize(const bsg_ptr_array_args* args, void* workspace
   return BSG_OK;
 }
 
+int32_t bsg_ptr_array_initialize_from_device(const bsg_ptr_array_args* args, void* workspace, size_t workspace_bytes, void* cuda_stream) {
+  if (!args) return fail(BSG_ERR_INVALID_PROBLEM, "args is null");
+  if (args->num_groups < 1 || args->num_groups > BSG_MAX_GROUPS) return fail(BSG_ERR_INVALID_PROBLEM, "group count %d outside [1, %d]", args->num_groups, BSG_MAX_GROUPS);
+  const size_t n = size_t(args->num_groups);
+  // host copies of the twelve arrays: sizes (3 int32 per group), seven pointer arrays, four pitch arrays
+  int32_t sizes[3 * BSG_MAX_GROUPS];
+  static_assert(sizeof(void*) == sizeof(int64_t), "pointer and pitch arrays share the staging type");
+  int64_t* host = static_cast<int64_t*>(malloc(11 * n * sizeof(int64_t)));
+  if (!host) return fail(BSG_ERR_INTERNAL, "out of host memory");
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  bsg_ptr_array_args local = *args;
+  cudaError_t e = cudaSuccess;
+  auto fetch = [&](const void* dev_array, void* dst, size_t bytes) {
+    if (dev_array && e == cudaSuccess) e = cudaMemcpyAsync(dst, dev_array, bytes, cudaMemcpyDeviceToHost, stream);
+  };
+  fetch(args->problem_sizes, sizes, 3 * n * sizeof(int32_t));
+  const void* const dev_arrays[11] = {args->A, args->B, args->SFA, args->SFB, args->C, args->D, args->SFD, args->lda, args->ldb, args->ldc, args->ldd};
+  for (int i = 0; i < 11; ++i) fetch(dev_arrays[i], host + size_t(i) * n, n * sizeof(int64_t));
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) { free(host); return fail(BSG_ERR_CUDA, "copying the argument arrays to the host: %s", cudaGetErrorString(e)); }
+  auto at = [&](int i) { return dev_arrays[i] ? host + size_t(i) * n : nullptr; };
+  local.problem_sizes = args->problem_sizes ? sizes : nullptr;
+  local.A = reinterpret_cast<const void* const*>(at(0)); local.B = reinterpret_cast<const void* const*>(at(1));
+  local.SFA = reinterpret_cast<const void* const*>(at(2)); local.SFB = reinterpret_cast<const void* const*>(at(3));
+  local.C = reinterpret_cast<const void* const*>(at(4));
+  local.D = reinterpret_cast<void* const*>(at(5)); local.SFD = reinterpret_cast<void* const*>(at(6));
+  local.lda = at(7); local.ldb = at(8); local.ldc = at(9); local.ldd = at(10);
+  const int32_t rc = bsg_ptr_array_initialize(&local, workspace, workspace_bytes, cuda_stream);
+  free(host);
+  return rc;
+}
+
 int32_t bsg_ptr_array_run(const bsg_ptr_array_args* args, void* workspace, size_t workspace_bytes, void* cuda_stream) {
   if (!args || !args->problem_sizes) return fail(BSG_ERR_INVALID_PROBLEM, "args or problem_sizes is null");
   if (!workspace) return fail(BSG_ERR_WORKSPACE_NULL, "workspace is null");

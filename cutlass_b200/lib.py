@@ -117,6 +117,7 @@ SYMBOLS = {
     "bsg_gemm_run_static": (C.c_int32, [C.POINTER(GemmArgs), C.c_void_p, C.POINTER(C.c_uint32)]),
     "bsg_ptr_array_workspace_size": (C.c_int32, [C.POINTER(PtrArrayArgs), C.POINTER(C.c_size_t)]),
     "bsg_ptr_array_initialize": (C.c_int32, [C.POINTER(PtrArrayArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "bsg_ptr_array_initialize_from_device": (C.c_int32, [C.POINTER(PtrArrayArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "bsg_ptr_array_run": (C.c_int32, [C.POINTER(PtrArrayArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "bsg_quantize": (C.c_int32, [C.POINTER(QuantArgs), C.c_void_p]),
     "bsg_tp_create": (C.c_int32, [C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.POINTER(C.c_void_p), C.c_void_p]),

@@ -282,6 +282,11 @@ int32_t bsg_ptr_array_workspace_size(const bsg_ptr_array_args* args, size_t* byt
 /* Checks every group, encodes its tensor maps and copies the table into the workspace (on the stream; the host
  * arrays may be released when the call returns).  Call again whenever a pointer, size or pitch changes. */
 int32_t bsg_ptr_array_initialize(const bsg_ptr_array_args* args, void* workspace, size_t workspace_bytes, void* cuda_stream);
+/* The same for a caller whose arrays are where the reference keeps them, in DEVICE memory (ptr_A ... ptr_D, the pitches
+ * and problem_sizes_3x of library.h:558-605): every non-null array member of `args` is then a device pointer.  The
+ * arrays are copied to the host first (the stream is synchronised), after which this is bsg_ptr_array_initialize; a later
+ * bsg_ptr_array_run wants problem_sizes readable on the host (the reference passes problem_sizes_3x_host as well). */
+int32_t bsg_ptr_array_initialize_from_device(const bsg_ptr_array_args* args, void* workspace, size_t workspace_bytes, void* cuda_stream);
 /* Launches the grouped GEMM described by the table that bsg_ptr_array_initialize left in this workspace; of `args`
  * the scalars (alpha, beta and their arrays, norm_constant, activation, use_pdl) and the problem sizes are read. */
 int32_t bsg_ptr_array_run(const bsg_ptr_array_args* args, void* workspace, size_t workspace_bytes, void* cuda_stream);

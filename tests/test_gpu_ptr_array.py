@@ -140,3 +140,36 @@ def test_run_without_initialize_and_changed_sizes_are_refused(cuda_lib):
     op._host["sizes"][0] = 64            # M of group 0 changed behind the table's back
     rc = lib.bsg_ptr_array_run(C.byref(op.args), op._ws_ptr, op._ws_bytes, None)
     assert rc == 2 and "differ" in L.last_error()
+
+
+def test_argument_arrays_in_device_memory(cuda_lib):
+    """The reference keeps the pointer, pitch and size arrays in device memory: the same table results when they are
+    handed over there (bsg_ptr_array_initialize_from_device copies them to the host first)."""
+    kind = 1
+    rng = np.random.default_rng(21)
+    shapes = [(300, 256, 512), (129, 384, 256)]
+    hosts, groups = zip(*[_group(kind, M, N, K, rng, exact=True) for (M, N, K) in shapes])
+    n = len(groups)
+    i64 = lambda v: torch.tensor(v, dtype=torch.int64, device="cuda")  # noqa: E731
+    sizes = torch.tensor([v for s in shapes for v in s], dtype=torch.int32, device="cuda")
+    arrays = {k: i64([getattr(g, k).data_ptr() for g in groups]) for k in ("A", "B", "SFA", "SFB", "D")}
+    a = L.PtrArrayArgs()
+    a.kind, a.out_kind, a.num_groups = kind, 0, n
+    a.problem_sizes = sizes.data_ptr()
+    for k, t in arrays.items():
+        setattr(a, k, t.data_ptr())
+    a.alpha = 1.0
+    lib = L.load()
+    need = C.c_size_t()
+    L.check(lib.bsg_ptr_array_workspace_size(C.byref(a), C.byref(need)))
+    ws = torch.zeros(need.value + 128, dtype=torch.uint8, device="cuda")
+    ptr = (ws.data_ptr() + 127) & ~127
+    L.check(lib.bsg_ptr_array_initialize_from_device(C.byref(a), ptr, need.value, None))
+    host_sizes = (C.c_int32 * (3 * n))(*[v for s in shapes for v in s])
+    a.problem_sizes = C.cast(host_sizes, C.c_void_p)          # a run reads the sizes on the host
+    L.check(lib.bsg_ptr_array_run(C.byref(a), ptr, need.value, None))
+    L.check(lib.bsg_read_device_status(ptr, None))
+    torch.cuda.synchronize()
+    for i, (h, g) in enumerate(zip(hosts, groups)):
+        want = oracle.to_bf16(oracle.gemm_fp32(kind, h["A"], h["sfa"], h["B"], h["sfb"], h["M"], h["N"], h["K"]))
+        assert np.array_equal(g.D.cpu().numpy().view(np.uint16), want), f"group {i}"
