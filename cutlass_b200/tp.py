@@ -80,6 +80,73 @@ def copy_schedule(world: int, rank: int, M: int, ksplit: int, cta: int, grid: in
     return out
 
 
+def push_gate_open(mode: str, j: int, rem: int, per_shard: int, stage_now: int, progress: int) -> bool:
+    """May a CTA send a piece for its j-th nearest consumer (piece ``rem`` of the shard's ``per_shard``)?  Restates the
+    kernel's gates.  ``stage_now``: stage of the tile the CTA's producer is on (published BEFORE it waits for that
+    tile's rows; a large number once the CTA has no tiles left); ``progress``: how far the CTA is through its own
+    tiles, in 1/1024 of a stage.  "eager": always; "paced": from stage j - 1 on; "spread": piece by piece over the first
+    three quarters of stage j - 1, a CTA that is already at a later stage counting as that far."""
+    if mode == "eager":
+        return True
+    if mode == "paced":
+        return stage_now >= j - 1
+    if mode == "spread":
+        need = (j - 1) * 1024 + 768 * rem // per_shard
+        return max(progress, min(stage_now, 1 << 10) * 1024) >= need
+    raise ValueError(mode)
+
+
+def simulate_gather(world: int, blocks_per_shard: int, tiles_n: int, clusters: int, ksplit: int, mode: str,
+                    gate=push_gate_open) -> bool:
+    """Event-free model of one tensor-parallel call on every rank: clusters walk their tiles (tile t of the walk belongs
+    to stage t // (blocks_per_shard * tiles_n) and needs one 256-row block of the shard consumed at that stage), CTAs
+    push the pieces ``copy_schedule`` deals them, in order, as their gates open; a tile completes once its block has
+    arrived.  Returns True when every tile of every rank completes, False when the ranks end up waiting for one another."""
+    per_stage = blocks_per_shard * tiles_n
+    total = world * per_stage
+    clusters = min(clusters, total)
+    grid = 2 * clusters
+    M = world * blocks_per_shard * ROW_BLOCK
+    pieces = [[copy_schedule(world, r, M, ksplit, c, grid) for c in range(grid)] for r in range(world)]
+    sent = [[0] * grid for _ in range(world)]                       # pieces already pushed, per CTA
+    arrived = [dict() for _ in range(world)]                        # rank -> {global row block: pieces arrived}
+    pos = [[0] * clusters for _ in range(world)]                    # tiles completed, per cluster
+    own = [len(range(c, total, clusters)) for c in range(clusters)]
+
+    def tile_block(rank: int, t: int) -> tuple[int, int]:
+        """(stage, global row block) of walk position t: bands of the walk are stages, blocks cycle inside a band."""
+        stage, rem = divmod(t, per_stage)
+        shard = (rank + stage) % world
+        return stage, shard * blocks_per_shard + rem % blocks_per_shard
+
+    changed = True
+    while changed:
+        changed = False
+        for r in range(world):
+            for c in range(clusters):
+                # the cluster's current tile
+                if pos[r][c] < own[c]:
+                    stage, blk = tile_block(r, c + pos[r][c] * clusters)
+                    stage_now = stage
+                    if stage == 0 or arrived[r].get(blk, 0) >= ksplit:
+                        pos[r][c] += 1
+                        changed = True
+                else:
+                    stage_now = 1 << 20
+                progress = (1 << 30) if pos[r][c] >= own[c] else 1024 * world * pos[r][c] // own[c]
+                for cta in (2 * c, 2 * c + 1):
+                    while sent[r][cta] < len(pieces[r][cta]):
+                        pc = pieces[r][cta][sent[r][cta]]
+                        j = (r - pc.dst_rank) % world
+                        rem = (pc.row_block - r * blocks_per_shard) * ksplit + pc.k_piece
+                        if not gate(mode, j, rem, blocks_per_shard * ksplit, stage_now, progress):
+                            break
+                        arrived[pc.dst_rank][pc.row_block] = arrived[pc.dst_rank].get(pc.row_block, 0) + 1
+                        sent[r][cta] += 1
+                        changed = True
+    return all(pos[r][c] >= own[c] for r in range(world) for c in range(clusters))
+
+
 def exchange_handles(handle: bytes, group=None) -> list[bytes]:
     """All-gather one opaque per-rank blob (the CUDA IPC handle) over ``torch.distributed``."""
     import torch.distributed as dist

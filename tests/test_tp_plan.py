@@ -132,3 +132,22 @@ def test_reduce_scatter_ring_schedule(world):
         assert sorted(order) == list(range(world)) and order[-1] == j
         for s, r in enumerate(order):
             assert TP.rs_stage_slices(world, r)[s] == j
+
+
+@pytest.mark.parametrize("mode", ["eager", "paced", "spread"])
+@pytest.mark.parametrize("world,blocks,tiles_n,clusters", [(2, 8, 2, 74), (4, 4, 4, 74), (8, 8, 14, 74), (8, 1, 2, 74), (4, 2, 1, 3), (8, 1, 1, 8)])
+def test_push_gates_never_leave_the_ranks_waiting_for_one_another(mode, world, blocks, tiles_n, clusters):
+    """Model of a call on every rank (clusters walking their tiles, CTAs pushing their pieces as the gates open): every
+    tile completes, for the benchmark shape, for shapes with one tile per cluster and for grids smaller than the work."""
+    for ksplit in (4, 32):
+        assert TP.simulate_gather(world, blocks, tiles_n, clusters, ksplit, mode)
+
+
+def test_spreading_by_own_pace_alone_would_deadlock_small_problems():
+    """Why the spread gate also counts the stage a CTA is at: with one tile per cluster a CTA may start at a late stage
+    and stand still there, and a gate that looked only at its pace would hold back the rows the others wait for."""
+    def pace_only(mode, j, rem, per_shard, stage_now, progress):
+        return progress >= (j - 1) * 1024 + 768 * rem // per_shard
+    # 32 tiles on 32 clusters, 256 pieces over their 64 CTAs: the shape of the 2-rank NVFP4 test (M 4096, N 1024, K 4096)
+    assert not TP.simulate_gather(2, 8, 2, 74, 32, "spread", gate=pace_only)
+    assert TP.simulate_gather(2, 8, 2, 74, 32, "spread")
