@@ -957,6 +957,16 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         pend_head = (pend_head + 1) % C::kTpPend;
         --pend_cnt;
       };
+      // Before the warp sits down at a closed gate it announces what it has stored so far: a consumer may be waiting
+      // for exactly those pieces, and the gate may only open once that consumer's rank has moved on in turn.
+      auto flush_pending = [&]() {
+        if (elected && pend_cnt > 0) {
+          ptx::bulk_wait_group<0>();
+          release_fences();
+          while (pend_cnt > 0) announce_head();
+        }
+        __syncwarp();
+      };
       for (; st_it.valid(); st_it.next(p), ++n_st) {
         const uint32_t b = n_st % nb;
         if (p.tp_paced_push == 2 && st_it.c != paced_piece) {
@@ -966,19 +976,25 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           const int j = st_it.c / st_it.per_shard + 1;
           const int rem = st_it.c - (j - 1) * st_it.per_shard;
           const int need = (j - 1) * 1024 + 768 * rem / st_it.per_shard;
-          const long long t0 = clock64();
           // A CTA whose tile is already at stage s counts as that far whatever its own pace (in a small problem a CTA
           // may start at a late stage and stand still there, waiting for rows that the peers send by the same rule).
-          while (max(ctl->tp_progress, min(ctl->tp_stage_now, 1 << 10) * 1024) < need && !ctl->abort && clock64() - t0 < 4000000000ll)
-            __nanosleep(200);
+          auto closed = [&]() { return max(ctl->tp_progress, min(ctl->tp_stage_now, 1 << 10) * 1024) < need; };
+          if (bcast(int32_t(closed())) != 0) {       // one lane's look decides for the warp (flush_pending synchronises it)
+            flush_pending();
+            const long long t0 = clock64();
+            while (closed() && !ctl->abort && clock64() - t0 < 4000000000ll) __nanosleep(200);
+          }
           paced_piece = st_it.c;
         }
         if (st_it.dst_rank != checked) {
           if (p.tp_paced_push == 1) {
             // j-th nearest consumer: its rows are due when it starts stage j, which is when this rank does too
             const int j = (p.tp_rank - st_it.dst_rank + p.tp_world) % p.tp_world;
-            const long long t0 = clock64();
-            while (ctl->tp_stage_now < j - 1 && !ctl->abort && clock64() - t0 < 4000000000ll) __nanosleep(500);
+            if (bcast(int32_t(ctl->tp_stage_now < j - 1)) != 0) {
+              flush_pending();
+              const long long t0 = clock64();
+              while (ctl->tp_stage_now < j - 1 && !ctl->abort && clock64() - t0 < 4000000000ll) __nanosleep(500);
+            }
           }
           // The peer's buffer is free once the peer has launched the call after the one that last read it.
           if (!wait_flag_ge(sync + kTpSyncReady + st_it.dst_rank, p.tp_ready_target, ctl)) peer_ok = false;

@@ -97,19 +97,23 @@ def push_gate_open(mode: str, j: int, rem: int, per_shard: int, stage_now: int, 
 
 
 def simulate_gather(world: int, blocks_per_shard: int, tiles_n: int, clusters: int, ksplit: int, mode: str,
-                    gate=push_gate_open) -> bool:
+                    gate=push_gate_open, flush_at_closed_gate: bool = True) -> bool:
     """Event-free model of one tensor-parallel call on every rank: clusters walk their tiles (tile t of the walk belongs
     to stage t // (blocks_per_shard * tiles_n) and needs one 256-row block of the shard consumed at that stage), CTAs
     push the pieces ``copy_schedule`` deals them, in order, as their gates open; a tile completes once its block has
-    arrived.  Returns True when every tile of every rank completes, False when the ranks end up waiting for one another."""
+    been ANNOUNCED complete.  As in the kernel, a piece is announced only when the CTA has moved on to its next piece
+    (the announcement trails the stores), at the end of the CTA's list, or -- ``flush_at_closed_gate`` -- when the CTA
+    finds its next gate closed.  Returns True when every tile of every rank completes, False when the ranks end up
+    waiting for one another."""
     per_stage = blocks_per_shard * tiles_n
     total = world * per_stage
     clusters = min(clusters, total)
     grid = 2 * clusters
     M = world * blocks_per_shard * ROW_BLOCK
     pieces = [[copy_schedule(world, r, M, ksplit, c, grid) for c in range(grid)] for r in range(world)]
-    sent = [[0] * grid for _ in range(world)]                       # pieces already pushed, per CTA
-    arrived = [dict() for _ in range(world)]                        # rank -> {global row block: pieces arrived}
+    sent = [[0] * grid for _ in range(world)]                       # pieces already stored, per CTA
+    announced = [[0] * grid for _ in range(world)]                  # ... and announced
+    arrived = [dict() for _ in range(world)]                        # rank -> {global row block: pieces announced}
     pos = [[0] * clusters for _ in range(world)]                    # tiles completed, per cluster
     own = [len(range(c, total, clusters)) for c in range(clusters)]
 
@@ -119,12 +123,20 @@ def simulate_gather(world: int, blocks_per_shard: int, tiles_n: int, clusters: i
         shard = (rank + stage) % world
         return stage, shard * blocks_per_shard + rem % blocks_per_shard
 
+    def announce_up_to(r: int, cta: int, n: int) -> bool:
+        did = False
+        while announced[r][cta] < n:
+            pc = pieces[r][cta][announced[r][cta]]
+            arrived[pc.dst_rank][pc.row_block] = arrived[pc.dst_rank].get(pc.row_block, 0) + 1
+            announced[r][cta] += 1
+            did = True
+        return did
+
     changed = True
     while changed:
         changed = False
         for r in range(world):
             for c in range(clusters):
-                # the cluster's current tile
                 if pos[r][c] < own[c]:
                     stage, blk = tile_block(r, c + pos[r][c] * clusters)
                     stage_now = stage
@@ -135,15 +147,20 @@ def simulate_gather(world: int, blocks_per_shard: int, tiles_n: int, clusters: i
                     stage_now = 1 << 20
                 progress = (1 << 30) if pos[r][c] >= own[c] else 1024 * world * pos[r][c] // own[c]
                 for cta in (2 * c, 2 * c + 1):
-                    while sent[r][cta] < len(pieces[r][cta]):
-                        pc = pieces[r][cta][sent[r][cta]]
+                    mine = pieces[r][cta]
+                    while sent[r][cta] < len(mine):
+                        pc = mine[sent[r][cta]]
                         j = (r - pc.dst_rank) % world
                         rem = (pc.row_block - r * blocks_per_shard) * ksplit + pc.k_piece
                         if not gate(mode, j, rem, blocks_per_shard * ksplit, stage_now, progress):
+                            if flush_at_closed_gate:
+                                changed |= announce_up_to(r, cta, sent[r][cta])
                             break
-                        arrived[pc.dst_rank][pc.row_block] = arrived[pc.dst_rank].get(pc.row_block, 0) + 1
+                        changed |= announce_up_to(r, cta, sent[r][cta])       # the piece before this one
                         sent[r][cta] += 1
                         changed = True
+                    if sent[r][cta] == len(mine):
+                        changed |= announce_up_to(r, cta, len(mine))
     return all(pos[r][c] >= own[c] for r in range(world) for c in range(clusters))
 
 

@@ -135,7 +135,8 @@ def test_reduce_scatter_ring_schedule(world):
 
 
 @pytest.mark.parametrize("mode", ["eager", "paced", "spread"])
-@pytest.mark.parametrize("world,blocks,tiles_n,clusters", [(2, 8, 2, 74), (4, 4, 4, 74), (8, 8, 14, 74), (8, 1, 2, 74), (4, 2, 1, 3), (8, 1, 1, 8)])
+@pytest.mark.parametrize("world,blocks,tiles_n,clusters", [(2, 8, 2, 74), (4, 4, 4, 74), (4, 4, 1, 74), (8, 8, 14, 74), (8, 1, 2, 74), (4, 2, 1, 3),
+                                                           (8, 1, 1, 8)])
 def test_push_gates_never_leave_the_ranks_waiting_for_one_another(mode, world, blocks, tiles_n, clusters):
     """Model of a call on every rank (clusters walking their tiles, CTAs pushing their pieces as the gates open): every
     tile completes, for the benchmark shape, for shapes with one tile per cluster and for grids smaller than the work."""
@@ -151,3 +152,15 @@ def test_spreading_by_own_pace_alone_would_deadlock_small_problems():
     # 32 tiles on 32 clusters, 256 pieces over their 64 CTAs: the shape of the 2-rank NVFP4 test (M 4096, N 1024, K 4096)
     assert not TP.simulate_gather(2, 8, 2, 74, 32, "spread", gate=pace_only)
     assert TP.simulate_gather(2, 8, 2, 74, 32, "spread")
+
+
+def test_announcements_must_not_wait_behind_a_closed_gate():
+    """A piece is announced only when its CTA moves on to the next piece.  If the CTA then waits at a closed gate with
+    the last pieces of the previous destination still unannounced, CTAs of different ranks that stand at the same stage
+    wait for one another around the ring (seen on 4 GPUs: M 4096, N 1024, K 2048, spread push): the kernel announces
+    what it has stored before it waits at a gate."""
+    assert not TP.simulate_gather(4, 4, 1, 74, 16, "spread", flush_at_closed_gate=False)
+    assert TP.simulate_gather(4, 4, 1, 74, 16, "spread")
+    for mode in ("paced", "spread"):
+        for shape in ((4, 4, 1, 74), (8, 8, 14, 74), (2, 8, 2, 74), (8, 1, 1, 8)):
+            assert TP.simulate_gather(*shape, 16, mode)
