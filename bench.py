@@ -481,6 +481,39 @@ def run_single(args) -> dict:
         c0 = DenseCase(0, 1024, 1024, 1024, dev, gen, with_c=True, beta=0.5, min_sets=8, max_sets=64)
         ms0 = run_case(lib, L, c0, ws, stream, max(side_steps, 50), 5)
         launches += max(side_steps, 50)
+        # the same launches replayed from a CUDA graph, with and without programmatic dependent launch: what the device
+        # needs per call when the host's launch rate is out of the picture
+        graph_ms = {}
+        for pdl in (0, 1):
+            try:
+                cap = torch.cuda.Stream()
+                ws_g = torch.zeros(16, dtype=torch.uint8, device=dev)
+                for a0 in c0.args:
+                    a0.use_pdl = pdl
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=cap):
+                    for i in range(c0.n_sets):
+                        rc = lib.bsg_gemm_run(C.byref(c0.args[i]), ws_g.data_ptr(), 16, cap.cuda_stream)
+                        if rc != 0:
+                            raise RuntimeError(L.last_error())
+                with torch.cuda.stream(cap):
+                    graph.replay()
+                    cap.synchronize()
+                    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    g0.record(cap)
+                    for _ in range(4):
+                        graph.replay()
+                    g1.record(cap)
+                torch.cuda.synchronize()
+                L.check(lib.bsg_read_device_status(ws_g.data_ptr(), None))
+                graph_ms["with_pdl" if pdl else "plain"] = round(g0.elapsed_time(g1) / (4 * c0.n_sets), 5)
+                launches += 5 * c0.n_sets
+                del graph
+            except Exception as exc:  # noqa: BLE001
+                graph_ms["with_pdl" if pdl else "plain"] = repr(exc)
+        for a0 in c0.args:
+            a0.use_pdl = 0
         s = c0.sets[0]
         A0, SFA0, B0, SFB0 = slab_of(c0, s, 1024)
         Cb = s["C"].view(torch.int16).cpu().numpy().view(np.uint16)
@@ -491,6 +524,7 @@ def run_single(args) -> dict:
             "workload": "NVFP4 GEMM M=N=K=1024, alpha=1, beta=0.5, bf16 C and D", "operand_sets_rotated": c0.n_sets,
             "cpu_baseline": cpu_baseline_entry(1024, 1024, 1024, secs0, kn0, "the whole problem"),
             "parity_max_rel_err": bf16_rel_err(s["D"].view(torch.int16).cpu().numpy().view(np.uint16), want0),
+            "ms_per_call_replayed_from_a_cuda_graph": graph_ms,
             "note": "16 output tiles on 148 SMs: the time is launch latency plus one tile, not throughput"})
         del c0, s
         torch.cuda.empty_cache()

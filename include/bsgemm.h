@@ -402,7 +402,7 @@ enum { BSG_TP_PUSH_KERNEL = 0, BSG_TP_PUSH_COPY_ENGINE = 1, BSG_TP_SINGLE_BUFFER
        BSG_TP_SPREAD_PUSH = 16 /* or-ed in: as BSG_TP_PACED_PUSH, with the pieces of a stage leaving evenly over the first three
                                  quarters of that stage instead of in one burst at its start */ };
 typedef struct bsg_tp_comm bsg_tp_comm;
-/* A new communicator starts in BSG_TP_PUSH_KERNEL | BSG_TP_PACED_PUSH; bsg_tp_set_mode replaces the whole mode word (0 = the
+/* A new communicator starts in BSG_TP_PUSH_KERNEL | BSG_TP_SPREAD_PUSH; bsg_tp_set_mode replaces the whole mode word (0 = the
  * kernel pushes everything as fast as the links allow).  Only between calls, with every rank idle, the same on all ranks. */
 int32_t bsg_tp_set_mode(bsg_tp_comm* comm, int32_t mode);
 int32_t bsg_tp_create(int32_t rank, int32_t world, int32_t kind, int64_t M, int64_t K, bsg_tp_comm** out,

@@ -99,13 +99,13 @@ def _spawn(world, kind, M, N, K, calls, mode=None, timeout=600):
 
 @pytest.mark.parametrize("kind,world,M,N,K,mode", [(1, 2, 1024, 512, 2048, None), (0, 2, 1024, 512, 2048, None), (1, 2, 4096, 1024, 4096, None),
                                                    (1, 2, 4096, 1024, 4096, "kernel+release"), (1, 2, 2048, 512, 2048, "copy_engine"),
-                                                   (1, 2, 4096, 1024, 4096, "kernel"), (0, 2, 4096, 1024, 4096, "kernel+spread"),
+                                                   (1, 2, 4096, 1024, 4096, "kernel"), (0, 2, 4096, 1024, 4096, "kernel+paced"),
                                                    (1, 4, 2048, 1024, 2048, None), (0, 4, 4096, 1024, 4096, "kernel+release"),
-                                                   (1, 4, 4096, 1024, 2048, "kernel"), (1, 4, 4096, 1024, 2048, "kernel+spread")])
+                                                   (1, 4, 4096, 1024, 2048, "kernel"), (1, 4, 4096, 1024, 2048, "kernel+paced"), (1, 4, 4096, 1024, 2048, None)])
 def test_tp_gathers_a_inside_the_kernel(kind, world, M, N, K, mode):
-    """A different A on every call, bit-exact against the oracle; mode None is the library's default (paced push), "kernel"
-    the eager push; also with the announcements behind release fences (the form the PTX memory model asks for), with the
-    pieces spread over the stage before, and with the copy engines moving the rows."""
+    """A different A on every call, bit-exact against the oracle; mode None is the library's default (spread push), "kernel"
+    the eager push, "kernel+paced" the push paced by stages; also with the announcements behind release fences (the form
+    the PTX memory model asks for) and with the copy engines moving the rows."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     _spawn(world, kind, M, N, K, 3, mode)
