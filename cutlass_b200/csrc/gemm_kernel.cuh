@@ -1122,6 +1122,18 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const int acc_bar = it % C::kAccBars;
       const uint32_t acc_phase = uint32_t(it / C::kAccBars) & 1u;
       const uint32_t acc_col = uint32_t(it & 1) * C::kAccStride;
+      // While the mainloop of this tile still runs, the warp asks for its rows of C to be brought into L2 (a lane reads
+      // 128 bytes of one row per 64 columns: without this every pair of the epilogue pays a DRAM round trip in line).
+      const uint8_t* c_lane_row = nullptr;
+      if (!RS && use_c) {
+        const int32_t r_in_tile = int32_t(cta_rank) * C::kCtaM + warp * 32 + lane;
+        if (ti.row0 + r_in_tile < ti.row_end) {
+          c_lane_row = reinterpret_cast<const uint8_t*>(Cg + int64_t(ti.map_l) * p.batch_stride_c + int64_t(ti.map_row0 + r_in_tile) * ldc + tile_col0);
+          const int32_t row_bytes = min(n_pairs * 128, (prob_N - tile_col0) * 2);
+          for (int32_t o = 0; o < row_bytes; o += 128) ptx::prefetch_l2(c_lane_row + o);
+          if (row_bytes > 0) ptx::prefetch_l2(c_lane_row + row_bytes - 1);       // a row need not start on a line boundary
+        }
+      }
       if (warp == 0) BSG_DBG(2, 19);
       wait_barrier(tfull0 + acc_bar * 8, acc_phase, ctl, dead);
       if (warp == 0) BSG_DBG(2, 20);
@@ -1157,6 +1169,14 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll 1
       for (int pi = 0; pi < n_pairs; ++pi) {
         const int pr = reverse ? (n_pairs - 1 - pi) : pi;
+        // ... and the rows of the pair after this one into L1 while this one is worked on
+        if (c_lane_row != nullptr && pi + 1 < n_pairs) {
+          const int32_t nxt = (reverse ? (n_pairs - 2 - pi) : (pi + 1)) * 128;
+          if (nxt < (prob_N - tile_col0) * 2) {
+            ptx::prefetch_l1(c_lane_row + nxt);
+            ptx::prefetch_l1(c_lane_row + min(nxt + 127, (prob_N - tile_col0) * 2 - 1));
+          }
+        }
         uint32_t v[2][32];
         ptx::tmem_ld_32x32b_x32(lane_addr + pr * 64, v[0]);
         ptx::tmem_ld_32x32b_x32(lane_addr + pr * 64 + 32, v[1]);
