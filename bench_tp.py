@@ -96,7 +96,7 @@ def _reduce_scatter_leg(dev, rank: int, world: int, stream, steps: int) -> dict:
     all_reduce = None
     try:
         # Legs beside the headline run by default only at the GPU counts at which their multi-rank tests have been seen
-        # green (tests/test_gpu_tp.py on 2 and 4 GPUs; profiles/tp_tests_*): a fault in a side leg must not cost the line.
+        # green (tests/test_gpu_tp.py, so far on 2 and 4 GPUs): a fault in a side leg must not cost the line.
         if os.environ.get("BSG_BENCH_AR", "1" if world <= 4 else "0") == "0":
             raise RuntimeError("not run at this GPU count by default (BSG_BENCH_AR=1 runs it)")
         ar = TP.RsGemm(M, N, all_reduce=True)

@@ -47,7 +47,7 @@ EncodeTiledFn get_encode_fn() {
 
 // Tensor maps are pure descriptions (address, extents, strides, box, swizzle), so one encoded for a given
 // description stays valid for as long as that memory is used with that shape.  A small cache, guarded by a mutex,
-// keeps the most recently used ones: a steady-state run encodes nothing.  (SURVEY of the reference: it encodes its
+// keeps the most recently used ones: a steady-state run encodes nothing.  (The reference encodes its
 // descriptors in GemmUniversalAdapter::initialize and reuses them across run() calls, gemm_universal_adapter.h:313-375.)
 struct MapKey {
   const void* base;
