@@ -1005,9 +1005,19 @@ int32_t bsg_quantize(const bsg_quant_args* a, void* cuda_stream) {
   p.k_atoms = int32_t((a->K / vec + 3) / 4);
   dim3 grid(unsigned((a->K + bsg::kQuantTileK - 1) / bsg::kQuantTileK), unsigned((a->rows + bsg::kQuantTileRows - 1) / bsg::kQuantTileRows));
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-  if (a->kind == BSG_KIND_NVFP4) bsg::bsg_quant_kernel<0><<<grid, bsg::kQuantThreads, 0, stream>>>(p);
-  else bsg::bsg_quant_kernel<1><<<grid, bsg::kQuantThreads, 0, stream>>>(p);
-  cudaError_t e = cudaGetLastError();
+  if (a->use_pdl != 0 && a->use_pdl != 1) return fail(BSG_ERR_INVALID_PROBLEM, "use_pdl must be 0 or 1");
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(bsg::kQuantThreads, 1, 1);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = a->use_pdl ? 1 : 0;
+  cudaError_t e = a->kind == BSG_KIND_NVFP4 ? cudaLaunchKernelEx(&cfg, bsg::bsg_quant_kernel<0>, p) : cudaLaunchKernelEx(&cfg, bsg::bsg_quant_kernel<1>, p);
+  if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "quantiser launch: %s", cudaGetErrorString(e));
   return BSG_OK;
 }

@@ -79,6 +79,10 @@ __global__ void __launch_bounds__(kQuantThreads, 4) bsg_quant_kernel(const Quant
   const int k0 = blockIdx.x * kQuantTileK;
   for (int i = threadIdx.x; i < kAtomsPerTile * 512 / 4; i += kQuantThreads) reinterpret_cast<uint32_t*>(s_sf)[i] = 0u;
   __syncthreads();
+  // Programmatic dependent launch (no-ops otherwise): X may come from the kernel before this one on the stream, which
+  // must be complete before the first read; the kernel after this one may begin its own set-up right away.
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
 
   const float st = p.norm_ptr ? *p.norm_ptr : 1.0f;
   const float st_scaled = __fmul_rn(st, __fdiv_rn(1.0f, KIND == 0 ? 6.0f : 448.0f));

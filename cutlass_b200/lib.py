@@ -99,7 +99,7 @@ class PtrArrayArgs(C.Structure):
 # name -> (restype, argtypes); every symbol include/bsgemm.h declares.
 class QuantArgs(C.Structure):
     """``bsg_quant_args`` of include/bsgemm.h, field for field."""
-    _fields_ = [("kind", C.c_int32), ("reserved0", C.c_int32), ("rows", C.c_int64), ("K", C.c_int64), ("X", C.c_void_p),
+    _fields_ = [("kind", C.c_int32), ("use_pdl", C.c_int32), ("rows", C.c_int64), ("K", C.c_int64), ("X", C.c_void_p),
                 ("ldx", C.c_int64), ("Q", C.c_void_p), ("SF", C.c_void_p), ("norm_constant", C.c_void_p)]
 
 

@@ -16,13 +16,15 @@ from .arguments import ScaledOperand, ScaleMode, ScaleSwizzleMode
 from .formats import numel_scale
 
 
-def quantize_blockscaled(x, mode=ScaleMode.Blockwise1x16, *, norm_constant=None, out=None, scale_out=None, stream=None) -> ScaledOperand:
+def quantize_blockscaled(x, mode=ScaleMode.Blockwise1x16, *, norm_constant=None, out=None, scale_out=None, stream=None,
+                         use_pdl: bool = False) -> ScaledOperand:
     """Quantise ``x`` (rows, K) bf16, row-major (last stride 1), on its CUDA device.
 
     ``norm_constant``: fp32 device tensor with one element (the ``st`` of the reference; NVFP4 callers
     usually pass 448 * 6 / amax(x)), or None for 1.  ``out`` / ``scale_out`` may be given to reuse
     buffers (uint8; ``scale_out`` must hold exactly ``numel_scale`` bytes).  The returned operand's
-    logical value is ``scale * quantized / norm_constant``.  Asynchronous on ``stream``."""
+    logical value is ``scale * quantized / norm_constant``.  Asynchronous on ``stream``.  ``use_pdl``: launch as a
+    programmatic dependent launch (its set-up overlaps the kernel before it, the next kernel's set-up overlaps its tail)."""
     import torch
     from . import lib as L
     from .operator import to_cuda_stream
@@ -48,7 +50,7 @@ def quantize_blockscaled(x, mode=ScaleMode.Blockwise1x16, *, norm_constant=None,
     if norm_constant is not None and (norm_constant.dtype != torch.float32 or norm_constant.numel() != 1 or not norm_constant.is_cuda):
         raise ValueError("norm_constant must be a one-element fp32 CUDA tensor")
     a = L.QuantArgs()
-    a.kind, a.rows, a.K = kind, rows, K
+    a.kind, a.rows, a.K, a.use_pdl = kind, rows, K, int(use_pdl)
     a.X, a.ldx = x.data_ptr(), x.stride(0) if rows > 1 else max(K, x.stride(0))
     a.Q, a.SF = out.data_ptr(), scale_out.data_ptr()
     a.norm_constant = norm_constant.data_ptr() if norm_constant is not None else None

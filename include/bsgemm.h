@@ -336,7 +336,9 @@ int32_t bsg_gemm_run_static(const bsg_gemm_args* args, void* cuda_stream, uint32
  */
 typedef struct bsg_quant_args {
   int32_t kind;
-  int32_t reserved0;
+  int32_t use_pdl;          /* 1: launched as a programmatic dependent launch (as bsg_gemm_args.use_pdl): the kernel's set-up
+                               overlaps the tail of the kernel before it on the stream, and a GEMM launched with use_pdl behind
+                               it starts its own set-up while this one drains */
   int64_t rows, K;
   const void* X;
   int64_t ldx;

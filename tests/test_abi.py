@@ -75,6 +75,7 @@ def test_query_accepts_valid_problem_and_reports_plan(lib):
     (dict(A=0x10001), 1),            # misaligned pointer
     (dict(N=100), 1),                # bf16 rows not 16-byte multiples
     (dict(kind=7), 3),
+    (dict(use_pdl=2), 2),
     (dict(tile_n=192), 3),
     (dict(cta_group=3), 3),
     (dict(N=0), 2),

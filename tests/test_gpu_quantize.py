@@ -146,3 +146,34 @@ def test_nan_and_infinity_inputs_match_the_oracle(cuda_lib, kind):
     idx = F.sf_offset(r, kb, F.sf_k_atoms(K, vec)).ravel()
     assert np.array_equal(q.quantized.tensor.cpu().numpy().view(np.uint8), want_q)
     assert np.array_equal(q.scale.tensor.cpu().numpy().view(np.uint8)[idx], want_sf[idx])
+
+
+def test_quantise_gemm_chain_with_programmatic_dependent_launch(cuda_lib):
+    """quantise(x) -> GEMM -> quantise(result) launched back to back with use_pdl on every kernel: each kernel's set-up
+    overlaps its predecessor's tail, its first global read waits for the predecessor.  Results equal the plain launches'."""
+    import cutlass_b200 as ops
+    from cutlass_b200.quantize import quantize_blockscaled
+    M, N, K = 512, 768, 1024
+    rng = np.random.default_rng(19)
+    x = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32)).to(torch.bfloat16).cuda()
+    w = torch.from_numpy(rng.standard_normal((N, K)).astype(np.float32)).to(torch.bfloat16).cuda()
+    mode = ops.ScaleMode.Blockwise1x32
+    Bq = quantize_blockscaled(w, mode)
+    Bop = ops.ScaledOperand(Bq.quantized.tensor.t(), Bq.scale.tensor, mode, ops.ScaleSwizzleMode.Swizzle32x4x4)
+    results = []
+    for pdl in (False, True):
+        out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+        for _ in range(3):                                   # repeated so that every kernel has a dependent predecessor
+            A = quantize_blockscaled(x, mode, use_pdl=pdl)
+            args = ops.GemmArguments(A, Bop, out, torch.float32)
+            op = ops.get_operators(args)[0]
+            abi = op.build_args(args)
+            abi.use_pdl = int(pdl)
+            ws = torch.zeros(16, dtype=torch.uint8, device="cuda")
+            L.check(L.load().bsg_gemm_run(C.byref(abi), ws.data_ptr(), 16, None))
+            Y = quantize_blockscaled(out, mode, use_pdl=pdl)
+        torch.cuda.synchronize()
+        L.check(L.load().bsg_read_device_status(ws.data_ptr(), None))
+        results.append((out.clone(), Y.quantized.tensor.clone(), Y.scale.tensor.clone()))
+    for a, b in zip(*results):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
