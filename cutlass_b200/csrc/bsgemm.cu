@@ -227,6 +227,9 @@ int32_t validate(const Problem& q, Plan* plan) {
   if (q.out_kind < BSG_OUT_BF16 || q.out_kind > BSG_OUT_F32) return fail(BSG_ERR_NOT_SUPPORTED, "unknown output kind %d", q.out_kind);
   const bool quantised_out = q.out_kind == BSG_OUT_NVFP4 || q.out_kind == BSG_OUT_MXFP8;
   if (q.rs && q.out_kind != BSG_OUT_BF16) return fail(BSG_ERR_NOT_SUPPORTED, "the reduce-scatter GEMM writes bf16");
+  if ((q.out_kind == BSG_OUT_F16 || q.out_kind == BSG_OUT_F32) &&
+      (q.kind > BSG_KIND_MXFP8 || q.tp || q.scheduler != BSG_SCHED_STATIC || (q.cta_group != 0 && q.cta_group != 2)))
+    return fail(BSG_ERR_NOT_SUPPORTED, "fp16 / fp32 outputs are available for NVFP4 and MXFP8 operands with cta_group 2 and the static scheduler, on one GPU");
   if (q.num_groups < 1 || q.num_groups > BSG_MAX_GROUPS) return fail(BSG_ERR_INVALID_PROBLEM, "group / batch count %d outside [1, %d]", q.num_groups, BSG_MAX_GROUPS);
   if (q.N < 1 || q.K < 1 || q.total_rows < 0) return fail(BSG_ERR_INVALID_PROBLEM, "extents must be positive (rows=%lld N=%lld K=%lld)", (long long)q.total_rows, (long long)q.N, (long long)q.K);
   if (q.total_rows > 0x7FFFFFFF / 2 || q.N > 0x7FFFFFFF / 2 || q.K > 0x7FFFFFFF / 2) return fail(BSG_ERR_INVALID_PROBLEM, "extent exceeds 2^30");
@@ -314,14 +317,14 @@ struct KernelSetup {
   int max_clusters[64] = {};
 };
 
-template <int KIND, int CG, int BN, bool TP, bool DYN, bool RS, bool PTR = false>
+template <int KIND, int CG, int BN, bool TP, bool DYN, bool RS, bool PTR = false, bool OUTX = false>
 int32_t kernel_setup(int dev, int* max_clusters) {
   using Cf = bsg::Cfg<KIND, CG, BN, TP>;
   static KernelSetup ks;
   if (dev < 0 || dev >= 64) return fail(BSG_ERR_NOT_SUPPORTED, "device ordinal %d is outside [0, 64)", dev);
   std::lock_guard<std::mutex> lock(ks.mu);
   if (!ks.done[dev]) {
-    auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN, TP, DYN, RS, PTR>;
+    auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN, TP, DYN, RS, PTR, OUTX>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cf::kSmemBytes);
     if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     cudaLaunchConfig_t cfg;
@@ -344,7 +347,7 @@ int32_t kernel_setup(int dev, int* max_clusters) {
   return BSG_OK;
 }
 
-template <int KIND, int CG, int BN, bool TP = false, bool DYN = false, bool RS = false>
+template <int KIND, int CG, int BN, bool TP = false, bool DYN = false, bool RS = false, bool OUTX = false>
 int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_t stream, int sm_count, int dev, bool dry) {
   using Cf = bsg::Cfg<KIND, CG, BN, TP>;
   if (dry) return BSG_OK;
@@ -468,8 +471,8 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
 #endif
 
   int max_clusters = 0;
-  if ((rc = kernel_setup<KIND, CG, BN, TP, DYN, RS>(dev, &max_clusters)) != BSG_OK) return rc;
-  auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN, TP, DYN, RS>;
+  if ((rc = kernel_setup<KIND, CG, BN, TP, DYN, RS, false, OUTX>(dev, &max_clusters)) != BSG_OK) return rc;
+  auto kernel = bsg::bsg_gemm_kernel<KIND, CG, BN, TP, DYN, RS, false, OUTX>;
 
   int64_t clusters = sm_count / CG;
   if (max_clusters > 0 && clusters > max_clusters) clusters = max_clusters;
@@ -510,6 +513,10 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
 
 template <int KIND>
 int32_t dispatch_shape(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_t s, int sm, int dev, bool dry) {
+  if (q.out_kind == BSG_OUT_F16 || q.out_kind == BSG_OUT_F32) {      // checked in validate: cta_group 2, static scheduler, one GPU
+    return plan.tile_n == 256 ? launch<KIND, 2, 256, false, false, false, true>(q, plan, status, s, sm, dev, dry)
+                              : launch<KIND, 2, 128, false, false, false, true>(q, plan, status, s, sm, dev, dry);
+  }
   if (q.rs) {
     if (plan.cta_group != 2 || plan.tile_n != 256) return fail(BSG_ERR_NOT_SUPPORTED, "the reduce-scatter GEMM runs 256 x 256 tiles (cta_group 2)");
     return launch<KIND, 2, 256, false, false, true>(q, plan, status, s, sm, dev, dry);
@@ -688,7 +695,7 @@ int32_t ptr_array_encode(const bsg_ptr_array_args* a, bsg::GroupDesc* table) {
   return BSG_OK;
 }
 
-template <int KIND, int BN>
+template <int KIND, int BN, bool OUTX>
 int32_t ptr_array_launch(const bsg_ptr_array_args* a, const PtrTableInfo& info, uint8_t* workspace, cudaStream_t stream, int sms, int dev) {
   using Cf = bsg::Cfg<KIND, 2, BN>;
   bsg::GemmParams p;
@@ -705,7 +712,7 @@ int32_t ptr_array_launch(const bsg_ptr_array_args* a, const PtrTableInfo& info, 
   p.split_tail = 1;
   p.group_desc = reinterpret_cast<const bsg::GroupDesc*>(workspace + kPtrTableOffset);
   int max_clusters = 0;
-  int32_t rc = kernel_setup<KIND, 2, BN, false, false, false, true>(dev, &max_clusters);
+  int32_t rc = kernel_setup<KIND, 2, BN, false, false, false, true, OUTX>(dev, &max_clusters);
   if (rc != BSG_OK) return rc;
   int64_t clusters = sms / 2;
   if (max_clusters > 0 && clusters > max_clusters) clusters = max_clusters;
@@ -730,7 +737,7 @@ int32_t ptr_array_launch(const bsg_ptr_array_args* a, const PtrTableInfo& info, 
   // The six map parameters of the kernel are not used in this form (every group brings its own in the table).
   CUtensorMap none;
   memset(&none, 0, sizeof(none));
-  cudaError_t e = cudaLaunchKernelEx(&cfg, bsg::bsg_gemm_kernel<KIND, 2, BN, false, false, false, true>, none, none, none, none, none, none, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, bsg::bsg_gemm_kernel<KIND, 2, BN, false, false, false, true, OUTX>, none, none, none, none, none, none, p);
   if (e != cudaSuccess) return fail(BSG_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(e));
   return BSG_OK;
 }
@@ -1124,9 +1131,13 @@ int32_t bsg_ptr_array_run(const bsg_ptr_array_args* args, void* workspace, size_
   if (info.total_tiles == 0) return BSG_OK;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
-  if (args->kind == BSG_KIND_NVFP4)
-    return info.tile_n == 256 ? ptr_array_launch<0, 256>(args, info, ws, stream, sms, dev) : ptr_array_launch<0, 128>(args, info, ws, stream, sms, dev);
-  return info.tile_n == 256 ? ptr_array_launch<1, 256>(args, info, ws, stream, sms, dev) : ptr_array_launch<1, 128>(args, info, ws, stream, sms, dev);
+  const bool outx = args->out_kind == BSG_OUT_F16 || args->out_kind == BSG_OUT_F32;
+  if (args->kind == BSG_KIND_NVFP4) {
+    if (outx) return info.tile_n == 256 ? ptr_array_launch<0, 256, true>(args, info, ws, stream, sms, dev) : ptr_array_launch<0, 128, true>(args, info, ws, stream, sms, dev);
+    return info.tile_n == 256 ? ptr_array_launch<0, 256, false>(args, info, ws, stream, sms, dev) : ptr_array_launch<0, 128, false>(args, info, ws, stream, sms, dev);
+  }
+  if (outx) return info.tile_n == 256 ? ptr_array_launch<1, 256, true>(args, info, ws, stream, sms, dev) : ptr_array_launch<1, 128, true>(args, info, ws, stream, sms, dev);
+  return info.tile_n == 256 ? ptr_array_launch<1, 256, false>(args, info, ws, stream, sms, dev) : ptr_array_launch<1, 128, false>(args, info, ws, stream, sms, dev);
 }
 
 int32_t bsg_tp_create(int32_t rank, int32_t world, int32_t kind, int64_t M, int64_t K, bsg_tp_comm** out, void* ipc_handle_out) {

@@ -518,7 +518,9 @@ __device__ __forceinline__ int32_t sched_consume(Ctl* ctl, uint32_t k, uint32_t&
   return dead ? -1 : w;
 }
 
-template <int KIND, int CG, int BN, bool TP = false, bool DYN = false, bool RS = false, bool PTR = false>
+// OUTX: the instantiations that also write fp16 / fp32 outputs.  They are separate because the extra epilogue branches,
+// although never taken for the other output kinds, were measured to cost the bf16 and the re-quantising epilogues 1 - 6 %.
+template <int KIND, int CG, int BN, bool TP = false, bool DYN = false, bool RS = false, bool PTR = false, bool OUTX = false>
 __global__ void __launch_bounds__(TP ? 224 : 192, 1)
 bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
@@ -1047,7 +1049,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const float alpha_all = p.alpha_ptr ? *p.alpha_ptr : p.alpha;
     const float beta_all = p.beta_ptr ? *p.beta_ptr : p.beta;
     float st = 0.f, st_scaled = 0.f;
-    if (out_is_quantised(p.out_kind)) {
+    if (OUTX ? out_is_quantised(p.out_kind) : p.out_kind != kOutBf16) {
       st = p.norm_ptr ? *p.norm_ptr : 1.0f;
       st_scaled = __fmul_rn(st, __fdiv_rn(1.0f, p.out_kind == kOutNvfp4 ? 6.0f : 448.0f));
     }
@@ -1158,7 +1160,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       // store clips at the end of the matrix, not at the end of a group: the warp that holds a group's last rows
       // stores them row by row.)
       const int out_kind = p.out_kind;
-      const bool quantised = out_is_quantised(out_kind);
+      const bool quantised = OUTX ? out_is_quantised(out_kind) : out_kind != kOutBf16;
       const bool col_major = quantised && p.out_col_major != 0;
       // (Pointer-array form: every group has a map of its own, which clips at the group's last row.)
       const bool tma_out = (PTR ? cta_row0 + warp * 32 < ti.row_end : cta_row0 + warp * 32 + 32 <= ti.row_end) && !col_major;
@@ -1169,14 +1171,6 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll 1
       for (int pi = 0; pi < n_pairs; ++pi) {
         const int pr = reverse ? (n_pairs - 1 - pi) : pi;
-        // ... and the rows of the pair after this one into L1 while this one is worked on
-        if (c_lane_row != nullptr && pi + 1 < n_pairs) {
-          const int32_t nxt = (reverse ? (n_pairs - 2 - pi) : (pi + 1)) * 128;
-          if (nxt < (prob_N - tile_col0) * 2) {
-            ptx::prefetch_l1(c_lane_row + nxt);
-            ptx::prefetch_l1(c_lane_row + min(nxt + 127, (prob_N - tile_col0) * 2 - 1));
-          }
-        }
         uint32_t v[2][32];
         ptx::tmem_ld_32x32b_x32(lane_addr + pr * 64, v[0]);
         ptx::tmem_ld_32x32b_x32(lane_addr + pr * 64 + 32, v[1]);
@@ -1329,7 +1323,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 sf_base[(mb >> 2) * 512 + (mb & 3)] = uint8_t(q);
               }
             }
-          } else if (out_kind == kOutF32) {
+          } else if (OUTX && out_kind == kOutF32) {
             // fp32 output: 32 columns are 128 bytes, so each half of the pair fills the staging tile (128-byte swizzle:
             // 16-byte chunk c of row r lives at chunk c ^ (r & 7)) and leaves with a store of its own.
             if (tma_out) {
@@ -1360,38 +1354,58 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
               }
             }
-          } else if (!quantised) {
-            // bf16 or fp16 output
-            const bool f16 = out_kind == kOutF16;
-            uint4 o[4];
-            if (f16) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q)
-                o[q] = make_uint4(pack_f16x2(x[q * 8 + 0], x[q * 8 + 1]), pack_f16x2(x[q * 8 + 2], x[q * 8 + 3]),
-                                  pack_f16x2(x[q * 8 + 4], x[q * 8 + 5]), pack_f16x2(x[q * 8 + 6], x[q * 8 + 7]));
-            } else {
-#pragma unroll
-              for (int q = 0; q < 4; ++q)
-                o[q] = make_uint4(pack_bf16x2(x[q * 8 + 0], x[q * 8 + 1]), pack_bf16x2(x[q * 8 + 2], x[q * 8 + 3]),
-                                  pack_bf16x2(x[q * 8 + 4], x[q * 8 + 5]), pack_bf16x2(x[q * 8 + 6], x[q * 8 + 7]));
-            }
+          } else if (out_kind == kOutBf16) {
             if (tma_out) {
               // 128-byte-swizzled staging tile: 16-byte chunk c of row r lives at chunk (c ^ (r & 7)).
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                o.x = pack_bf16x2(x[q * 8 + 0], x[q * 8 + 1]);
+                o.y = pack_bf16x2(x[q * 8 + 2], x[q * 8 + 3]);
+                o.z = pack_bf16x2(x[q * 8 + 4], x[q * 8 + 5]);
+                o.w = pack_bf16x2(x[q * 8 + 6], x[q * 8 + 7]);
                 const int chunk = (h * 4 + q) ^ (lane & 7);
-                *reinterpret_cast<uint4*>(stage_buf + lane * 128 + chunk * 16) = o[q];
+                *reinterpret_cast<uint4*>(stage_buf + lane * 128 + chunk * 16) = o;
               }
             } else {
-              uint16_t* drow = reinterpret_cast<uint16_t*>(Dg) + d_row_off + col0;
+              __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(Dg) + d_row_off + col0;
               if (cols_valid >= 32) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(drow)[q] = o[q];
+                for (int q = 0; q < 4; ++q) {
+                  uint4 o;
+                  o.x = pack_bf16x2(x[q * 8 + 0], x[q * 8 + 1]);
+                  o.y = pack_bf16x2(x[q * 8 + 2], x[q * 8 + 3]);
+                  o.z = pack_bf16x2(x[q * 8 + 4], x[q * 8 + 5]);
+                  o.w = pack_bf16x2(x[q * 8 + 6], x[q * 8 + 7]);
+                  reinterpret_cast<uint4*>(drow)[q] = o;
+                }
               } else {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
-                  const uint32_t w = j < 8 ? (&o[0].x)[j >> 1] : j < 16 ? (&o[1].x)[(j - 8) >> 1] : j < 24 ? (&o[2].x)[(j - 16) >> 1] : (&o[3].x)[(j - 24) >> 1];
-                  if (j < cols_valid) drow[j] = uint16_t((j & 1) ? (w >> 16) : (w & 0xFFFFu));
+                  if (j < cols_valid) drow[j] = __float2bfloat16_rn(x[j]);
+                }
+              }
+            }
+          } else if (OUTX && out_kind == kOutF16) {
+            // as bf16, with the other 16-bit conversion
+            if (tma_out) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 o = make_uint4(pack_f16x2(x[q * 8 + 0], x[q * 8 + 1]), pack_f16x2(x[q * 8 + 2], x[q * 8 + 3]),
+                                           pack_f16x2(x[q * 8 + 4], x[q * 8 + 5]), pack_f16x2(x[q * 8 + 6], x[q * 8 + 7]));
+                *reinterpret_cast<uint4*>(stage_buf + lane * 128 + (((h * 4 + q) ^ (lane & 7)) * 16)) = o;
+              }
+            } else {
+              __half* drow = reinterpret_cast<__half*>(Dg) + d_row_off + col0;
+              if (cols_valid >= 32) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                  reinterpret_cast<uint4*>(drow)[q] = make_uint4(pack_f16x2(x[q * 8 + 0], x[q * 8 + 1]), pack_f16x2(x[q * 8 + 2], x[q * 8 + 3]),
+                                                                 pack_f16x2(x[q * 8 + 4], x[q * 8 + 5]), pack_f16x2(x[q * 8 + 6], x[q * 8 + 7]));
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  if (j < cols_valid) drow[j] = __float2half_rn(x[j]);
                 }
               }
             }
@@ -1490,7 +1504,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             } else if (RS)
               ptx::tma_store_3d(&tmD, ptx::smem_u32(sub_buf), col, rs_row_in_slice, 0);
             else
-              ptx::tma_store_3d(mapD, ptx::smem_u32(sub_buf), out_kind == kOutNvfp4 ? col / 2 : out_kind == kOutF32 ? col + 32 : col, warp_map_row0, ti.map_l);
+              ptx::tma_store_3d(mapD, ptx::smem_u32(sub_buf), out_kind == kOutNvfp4 ? col / 2 : (OUTX && out_kind == kOutF32) ? col + 32 : col, warp_map_row0, ti.map_l);
             ptx::bulk_commit_group();
           }
         }
