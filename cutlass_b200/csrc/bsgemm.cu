@@ -227,9 +227,9 @@ int32_t validate(const Problem& q, Plan* plan) {
   if (q.out_kind < BSG_OUT_BF16 || q.out_kind > BSG_OUT_F32) return fail(BSG_ERR_NOT_SUPPORTED, "unknown output kind %d", q.out_kind);
   const bool quantised_out = q.out_kind == BSG_OUT_NVFP4 || q.out_kind == BSG_OUT_MXFP8;
   if (q.rs && q.out_kind != BSG_OUT_BF16) return fail(BSG_ERR_NOT_SUPPORTED, "the reduce-scatter GEMM writes bf16");
-  if ((q.out_kind == BSG_OUT_F16 || q.out_kind == BSG_OUT_F32) &&
+  if ((q.out_kind == BSG_OUT_F16 || q.out_kind == BSG_OUT_F32 || q.out_col_major) &&
       (q.kind > BSG_KIND_MXFP8 || q.tp || q.scheduler != BSG_SCHED_STATIC || (q.cta_group != 0 && q.cta_group != 2)))
-    return fail(BSG_ERR_NOT_SUPPORTED, "fp16 / fp32 outputs are available for NVFP4 and MXFP8 operands with cta_group 2 and the static scheduler, on one GPU");
+    return fail(BSG_ERR_NOT_SUPPORTED, "fp16 / fp32 outputs and column-major quantised outputs are available for NVFP4 and MXFP8 operands with cta_group 2 and the static scheduler, on one GPU");
   if (q.num_groups < 1 || q.num_groups > BSG_MAX_GROUPS) return fail(BSG_ERR_INVALID_PROBLEM, "group / batch count %d outside [1, %d]", q.num_groups, BSG_MAX_GROUPS);
   if (q.N < 1 || q.K < 1 || q.total_rows < 0) return fail(BSG_ERR_INVALID_PROBLEM, "extents must be positive (rows=%lld N=%lld K=%lld)", (long long)q.total_rows, (long long)q.N, (long long)q.K);
   if (q.total_rows > 0x7FFFFFFF / 2 || q.N > 0x7FFFFFFF / 2 || q.K > 0x7FFFFFFF / 2) return fail(BSG_ERR_INVALID_PROBLEM, "extent exceeds 2^30");
@@ -513,7 +513,7 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
 
 template <int KIND>
 int32_t dispatch_shape(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_t s, int sm, int dev, bool dry) {
-  if (q.out_kind == BSG_OUT_F16 || q.out_kind == BSG_OUT_F32) {      // checked in validate: cta_group 2, static scheduler, one GPU
+  if (q.out_kind == BSG_OUT_F16 || q.out_kind == BSG_OUT_F32 || q.out_col_major) {      // checked in validate: cta_group 2, static scheduler, one GPU
     return plan.tile_n == 256 ? launch<KIND, 2, 256, false, false, false, true>(q, plan, status, s, sm, dev, dry)
                               : launch<KIND, 2, 128, false, false, false, true>(q, plan, status, s, sm, dev, dry);
   }

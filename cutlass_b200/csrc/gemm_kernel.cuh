@@ -518,8 +518,9 @@ __device__ __forceinline__ int32_t sched_consume(Ctl* ctl, uint32_t k, uint32_t&
   return dead ? -1 : w;
 }
 
-// OUTX: the instantiations that also write fp16 / fp32 outputs.  They are separate because the extra epilogue branches,
-// although never taken for the other output kinds, were measured to cost the bf16 and the re-quantising epilogues 1 - 6 %.
+// OUTX: the instantiations that also write fp16 / fp32 outputs and column-major quantised outputs.  They are separate
+// because the extra epilogue branches, although never taken otherwise, were measured to cost the bf16 and the
+// re-quantising epilogues 1 - 6 % (and the column-major path alone 38 registers per thread).
 template <int KIND, int CG, int BN, bool TP = false, bool DYN = false, bool RS = false, bool PTR = false, bool OUTX = false>
 __global__ void __launch_bounds__(TP ? 224 : 192, 1)
 bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -1161,7 +1162,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       // stores them row by row.)
       const int out_kind = p.out_kind;
       const bool quantised = OUTX ? out_is_quantised(out_kind) : out_kind != kOutBf16;
-      const bool col_major = quantised && p.out_col_major != 0;
+      const bool col_major = OUTX && quantised && p.out_col_major != 0;
       // (Pointer-array form: every group has a map of its own, which clips at the group's last row.)
       const bool tma_out = (PTR ? cta_row0 + warp * 32 < ti.row_end : cta_row0 + warp * 32 + 32 <= ti.row_end) && !col_major;
       // Staging sub-buffers a warp cycles through (4 KB per warp): bf16 uses all of it per 64 columns, e4m3 half,
