@@ -155,7 +155,7 @@ int32_t make_out_map(CUtensorMap* map, const void* base, int32_t out_kind, uint6
   if (out_kind == BSG_OUT_BF16)
     return g_maps.get(make_key(base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                                cols, rows, batches, pitch_elems * 2, batch_stride_elems * 2, 64, 32, 1), map);
-  if (out_kind == BSG_OUT_MXFP8)
+  if (out_kind == BSG_OUT_MXFP8 || out_kind == BSG_OUT_E4M3 || out_kind == BSG_OUT_E5M2)
     return g_maps.get(make_key(base, CU_TENSOR_MAP_DATA_TYPE_UINT8, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                                cols, rows, batches, pitch_elems, batch_stride_elems, 64, 32, 1), map);
   return g_maps.get(make_key(base, CU_TENSOR_MAP_DATA_TYPE_UINT8, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
@@ -224,12 +224,12 @@ struct Plan {
 
 int32_t validate(const Problem& q, Plan* plan) {
   if (q.kind < BSG_KIND_NVFP4 || q.kind > BSG_KIND_MXFP8_MXFP4) return fail(BSG_ERR_NOT_SUPPORTED, "unknown operand kind %d", q.kind);
-  if (q.out_kind < BSG_OUT_BF16 || q.out_kind > BSG_OUT_F32) return fail(BSG_ERR_NOT_SUPPORTED, "unknown output kind %d", q.out_kind);
+  if (q.out_kind < BSG_OUT_BF16 || q.out_kind > BSG_OUT_E5M2) return fail(BSG_ERR_NOT_SUPPORTED, "unknown output kind %d", q.out_kind);
   const bool quantised_out = q.out_kind == BSG_OUT_NVFP4 || q.out_kind == BSG_OUT_MXFP8;
   if (q.rs && q.out_kind != BSG_OUT_BF16) return fail(BSG_ERR_NOT_SUPPORTED, "the reduce-scatter GEMM writes bf16");
-  if ((q.out_kind == BSG_OUT_F16 || q.out_kind == BSG_OUT_F32 || q.out_col_major) &&
+  if ((q.out_kind >= BSG_OUT_F16 || q.out_col_major) &&
       (q.kind > BSG_KIND_MXFP8 || q.tp || q.scheduler != BSG_SCHED_STATIC || (q.cta_group != 0 && q.cta_group != 2)))
-    return fail(BSG_ERR_NOT_SUPPORTED, "fp16 / fp32 outputs and column-major quantised outputs are available for NVFP4 and MXFP8 operands with cta_group 2 and the static scheduler, on one GPU");
+    return fail(BSG_ERR_NOT_SUPPORTED, "fp16 / fp32 / e4m3 / e5m2 outputs and column-major quantised outputs are available for NVFP4 and MXFP8 operands with cta_group 2 and the static scheduler, on one GPU");
   if (q.num_groups < 1 || q.num_groups > BSG_MAX_GROUPS) return fail(BSG_ERR_INVALID_PROBLEM, "group / batch count %d outside [1, %d]", q.num_groups, BSG_MAX_GROUPS);
   if (q.N < 1 || q.K < 1 || q.total_rows < 0) return fail(BSG_ERR_INVALID_PROBLEM, "extents must be positive (rows=%lld N=%lld K=%lld)", (long long)q.total_rows, (long long)q.N, (long long)q.K);
   if (q.total_rows > 0x7FFFFFFF / 2 || q.N > 0x7FFFFFFF / 2 || q.K > 0x7FFFFFFF / 2) return fail(BSG_ERR_INVALID_PROBLEM, "extent exceeds 2^30");
@@ -251,6 +251,8 @@ int32_t validate(const Problem& q, Plan* plan) {
     if (q.N % 8 != 0 || q.ldd % 8 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "bf16 / fp16 output needs N and ldd to be multiples of 8");
   } else if (q.out_kind == BSG_OUT_F32) {
     if (q.N % 4 != 0 || q.ldd % 4 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "fp32 output needs N and ldd to be multiples of 4");
+  } else if (q.out_kind == BSG_OUT_E4M3 || q.out_kind == BSG_OUT_E5M2) {
+    if (q.N % 16 != 0 || q.ldd % 16 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "e4m3 / e5m2 output needs N and ldd to be multiples of 16");
   } else if (q.out_kind == BSG_OUT_MXFP8) {
     if (!q.SFD) return fail(BSG_ERR_INVALID_PROBLEM, "MXFP8 output needs SFD");
     if (q.N % 32 != 0 || q.ldd % 16 != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "MXFP8 output needs N %% 32 == 0 and ldd %% 16 == 0");
@@ -273,7 +275,7 @@ int32_t validate(const Problem& q, Plan* plan) {
     return fail(BSG_ERR_MISALIGNED_OPERAND, "lda=%lld and ldb=%lld must be multiples of %lld (16-byte rows)", (long long)q.lda, (long long)q.ldb, (long long)k_align);
   if (!q.offsets && q.num_groups > 1) {
     if (q.bs_a % k_align != 0 || q.bs_b % k_align != 0) return fail(BSG_ERR_MISALIGNED_OPERAND, "batch strides of A and B must be multiples of %lld elements", (long long)k_align);
-    const int64_t d_align = q.out_kind == BSG_OUT_F32 ? 4 : !quantised_out ? 8 : q.out_kind == BSG_OUT_MXFP8 ? 16 : 32;
+    const int64_t d_align = q.out_kind == BSG_OUT_F32 ? 4 : (q.out_kind == BSG_OUT_E4M3 || q.out_kind == BSG_OUT_E5M2) ? 16 : !quantised_out ? 8 : q.out_kind == BSG_OUT_MXFP8 ? 16 : 32;
     if (q.bs_d % d_align != 0 || (q.C && q.bs_c % 8 != 0)) return fail(BSG_ERR_MISALIGNED_OPERAND, "batch strides of C and D must keep every matrix 16-byte aligned");
     if (q.bs_a < 0 || q.bs_b < 0 || q.bs_c < 0 || q.bs_d < q.rows_per_group * q.ldd) return fail(BSG_ERR_INVALID_PROBLEM, "negative batch stride, or output matrices that overlap");
   }
@@ -513,7 +515,7 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
 
 template <int KIND>
 int32_t dispatch_shape(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_t s, int sm, int dev, bool dry) {
-  if (q.out_kind == BSG_OUT_F16 || q.out_kind == BSG_OUT_F32 || q.out_col_major) {      // checked in validate: cta_group 2, static scheduler, one GPU
+  if (q.out_kind >= BSG_OUT_F16 || q.out_col_major) {      // checked in validate: cta_group 2, static scheduler, one GPU
     return plan.tile_n == 256 ? launch<KIND, 2, 256, false, false, false, true>(q, plan, status, s, sm, dev, dry)
                               : launch<KIND, 2, 128, false, false, false, true>(q, plan, status, s, sm, dev, dry);
   }
@@ -1131,7 +1133,7 @@ int32_t bsg_ptr_array_run(const bsg_ptr_array_args* args, void* workspace, size_
   if (info.total_tiles == 0) return BSG_OK;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
-  const bool outx = args->out_kind == BSG_OUT_F16 || args->out_kind == BSG_OUT_F32;
+  const bool outx = args->out_kind >= BSG_OUT_F16;
   if (args->kind == BSG_KIND_NVFP4) {
     if (outx) return info.tile_n == 256 ? ptr_array_launch<0, 256, true>(args, info, ws, stream, sms, dev) : ptr_array_launch<0, 128, true>(args, info, ws, stream, sms, dev);
     return info.tile_n == 256 ? ptr_array_launch<0, 256, false>(args, info, ws, stream, sms, dev) : ptr_array_launch<0, 128, false>(args, info, ws, stream, sms, dev);

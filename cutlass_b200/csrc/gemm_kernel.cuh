@@ -48,6 +48,8 @@ constexpr int kOutNvfp4 = 1;
 constexpr int kOutMxfp8 = 2;
 constexpr int kOutF16 = 3;
 constexpr int kOutF32 = 4;
+constexpr int kOutE4m3 = 5;      // e4m3 / e5m2 values without scale factors (saturating conversion)
+constexpr int kOutE5m2 = 6;
 __host__ __device__ constexpr bool out_is_quantised(int out_kind) { return out_kind == kOutNvfp4 || out_kind == kOutMxfp8; }
 constexpr int kActIdentity = 0, kActRelu = 1, kActGelu = 2, kActSilu = 3;
 
@@ -1409,6 +1411,26 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                   if (j < cols_valid) drow[j] = __float2half_rn(x[j]);
                 }
               }
+            }
+          } else if (OUTX && (out_kind == kOutE4m3 || out_kind == kOutE5m2)) {
+            // 8-bit floating-point output without scale factors: round to nearest even, saturating
+            uint32_t w[8];
+            if (out_kind == kOutE4m3) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) w[e] = ptx::cvt_e4m3x4(x[e * 4 + 0], x[e * 4 + 1], x[e * 4 + 2], x[e * 4 + 3]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) w[e] = ptx::cvt_e5m2x4(x[e * 4 + 0], x[e * 4 + 1], x[e * 4 + 2], x[e * 4 + 3]);
+            }
+            if (tma_out) {
+              // 64-byte rows, 64-byte swizzle: 16-byte chunk c of row r lives at chunk c ^ ((r >> 1) & 3).
+              const int sw = (lane >> 1) & 3;
+              *reinterpret_cast<uint4*>(sub_buf + lane * 64 + (((h * 2 + 0) ^ sw) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+              *reinterpret_cast<uint4*>(sub_buf + lane * 64 + (((h * 2 + 1) ^ sw) * 16)) = make_uint4(w[4], w[5], w[6], w[7]);
+            } else {
+              uint8_t* drow = Dg + d_row_off + col0;
+              if (cols_valid >= 16) reinterpret_cast<uint4*>(drow)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+              if (cols_valid >= 32) reinterpret_cast<uint4*>(drow)[1] = make_uint4(w[4], w[5], w[6], w[7]);
             }
           } else if (out_kind == kOutMxfp8) {
             // MXFP8 re-quantisation: one ue8m0 scale factor (round-up conversion) for the 32 columns of

@@ -104,14 +104,48 @@ def _round_to_grid(mag: np.ndarray, grid: np.ndarray) -> np.ndarray:
 
 
 def encode_e4m3(x: np.ndarray) -> np.ndarray:
-    """float32 -> e4m3, round-to-nearest-even, saturating; NaN -> 0x7F (sign kept)."""
+    """float32 -> e4m3, round-to-nearest-even, saturating; NaN of either sign -> 0x7F (as the reference's float_e4m3_t)."""
     x = np.asarray(x, dtype=np.float32)
     sign = (np.signbit(x).astype(np.uint8)) << 7
     mag = np.abs(x).astype(np.float64)
     nan = np.isnan(mag)
     idx = _round_to_grid(np.where(nan, 0.0, mag), _E4M3_POS)
-    idx = np.where(nan, 0x7F, idx).astype(np.uint8)
-    return (idx | sign).astype(np.uint8)
+    return np.where(nan, 0x7F, idx | sign).astype(np.uint8)
+
+
+def _e5m2_positive_table() -> np.ndarray:
+    """Values of the 124 finite non-negative e5m2 codes 0x00..0x7B (0x7C is infinity, 0x7D..0x7F NaN)."""
+    codes = np.arange(0x7C, dtype=np.int32)
+    e = codes >> 2
+    m = codes & 3
+    sub = (m / 4.0) * 2.0 ** (-14)
+    nor = (1.0 + m / 4.0) * np.exp2((e - 15).astype(np.float64))
+    return np.where(e == 0, sub, nor).astype(np.float64)
+
+
+_E5M2_POS = _e5m2_positive_table()
+E5M2_MAX = 57344.0
+
+
+def decode_e5m2(codes: np.ndarray) -> np.ndarray:
+    codes = np.asarray(codes, dtype=np.uint8)
+    mag = (codes & 0x7F).astype(np.int32)
+    out = np.full(codes.shape, np.nan, dtype=np.float32)
+    fin = mag < 0x7C
+    out[fin] = _E5M2_POS[mag[fin]].astype(np.float32)
+    out[mag == 0x7C] = np.inf
+    return np.where((codes & 0x80) != 0, -out, out).astype(np.float32)
+
+
+def encode_e5m2(x: np.ndarray) -> np.ndarray:
+    """float32 -> e5m2, round-to-nearest-even, saturating to the largest finite value (infinity too); NaN -> 0x7F
+    of either sign: the conversion of the reference's float_e5m2_t and of cvt.rn.satfinite.e5m2x2.f32."""
+    x = np.asarray(x, dtype=np.float32)
+    sign = (np.signbit(x).astype(np.uint8)) << 7
+    mag = np.abs(x).astype(np.float64)
+    nan = np.isnan(mag)
+    idx = _round_to_grid(np.where(nan, 0.0, mag), _E5M2_POS)
+    return np.where(nan, 0x7F, idx | sign).astype(np.uint8)
 
 
 def encode_ue4m3(x: np.ndarray) -> np.ndarray:

@@ -34,6 +34,8 @@ OUT_NVFP4 = 1
 OUT_MXFP8 = 2
 OUT_F16 = 3
 OUT_F32 = 4
+OUT_E4M3 = 5
+OUT_E5M2 = 6
 ACT_IDENTITY, ACT_RELU, ACT_GELU, ACT_SILU = 0, 1, 2, 3
 BIAS_NONE, BIAS_PER_COLUMN, BIAS_PER_ROW = 0, 1, 2
 MAX_GROUPS = 256

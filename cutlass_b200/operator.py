@@ -222,9 +222,11 @@ class Operator:
         raise NotImplementedError
 
 
-# Unquantised output types (the reference's operator lists Float32 / Float16 / BFloat16 among its output types,
+# Unquantised output types (the reference's operator lists Float32 / Float16 / BFloat16 / Float8E4M3FN / Float8E5M2,
 # providers/cutedsl/gemm/sm100_dense_blockscaled_static_persistent.py:454-460).
-_PLAIN_OUT_KINDS = {torch.bfloat16: L.OUT_BF16, torch.float16: L.OUT_F16, torch.float32: L.OUT_F32}
+_PLAIN_OUT_KINDS = {torch.bfloat16: L.OUT_BF16, torch.float16: L.OUT_F16, torch.float32: L.OUT_F32,
+                    torch.float8_e4m3fn: L.OUT_E4M3, torch.float8_e5m2: L.OUT_E5M2}
+_PLAIN_OUT_N_MULTIPLE = {torch.bfloat16: 8, torch.float16: 8, torch.float32: 4, torch.float8_e4m3fn: 16, torch.float8_e5m2: 16}
 
 
 def _plain_out_kind(t: torch.Tensor) -> int:
@@ -278,9 +280,9 @@ class BlockScaledGemmOperator(Operator):
             return Status.fail("out must be row-major with 16-byte aligned rows")
         if epi.out_quant is None:
             if out.dtype not in _PLAIN_OUT_KINDS:
-                return Status.fail(f"out dtype {out.dtype} is not supported (bf16, fp16, fp32, or a quantised output with out_quant)")
-            if ps.N % (4 if out.dtype == torch.float32 else 8) != 0:
-                return Status.fail("N must be a multiple of 8 for bf16 / fp16 output, of 4 for fp32")
+                return Status.fail(f"out dtype {out.dtype} is not supported (bf16, fp16, fp32, e4m3, e5m2, or a quantised output with out_quant)")
+            if ps.N % _PLAIN_OUT_N_MULTIPLE[out.dtype] != 0:
+                return Status.fail(f"N must be a multiple of {_PLAIN_OUT_N_MULTIPLE[out.dtype]} for {out.dtype} output (16-byte rows)")
         elif isinstance(epi.out_quant, Mxfp8Quant):
             if out.dtype not in (torch.uint8, torch.float8_e4m3fn):
                 return Status.fail("MXFP8 output needs a uint8 / float8_e4m3fn out tensor")
@@ -408,9 +410,9 @@ class GroupedBlockScaledGemmOperator(Operator):
             return Status.fail("out must be contiguous")
         if epi.out_quant is None:
             if out.dtype not in _PLAIN_OUT_KINDS:
-                return Status.fail("out must be a bf16, fp16 or fp32 tensor (or a quantised output with out_quant)")
-            if ps.N % (4 if out.dtype == torch.float32 else 8) != 0:
-                return Status.fail("N must be a multiple of 8 (4 for fp32 output)")
+                return Status.fail("out must be a bf16, fp16, fp32, e4m3 or e5m2 tensor (or a quantised output with out_quant)")
+            if ps.N % _PLAIN_OUT_N_MULTIPLE[out.dtype] != 0:
+                return Status.fail(f"N must be a multiple of {_PLAIN_OUT_N_MULTIPLE[out.dtype]} for {out.dtype} output")
         else:
             # one interleaved scale layout per group, each padded to 128 rows: the form the next grouped GEMM takes as SFA
             mx = isinstance(epi.out_quant, Mxfp8Quant)

@@ -48,7 +48,9 @@ enum {
   BSG_OUT_NVFP4 = 1,        /* D = e2m1 packed + SFD ue4m3 per 16 N-elements, interleaved layout */
   BSG_OUT_MXFP8 = 2,        /* D = e4m3 + SFD ue8m0 (round-up conversion) per 32 N-elements, interleaved layout */
   BSG_OUT_F16 = 3,          /* D = fp16(...)  (C, when given, stays bf16) */
-  BSG_OUT_F32 = 4           /* D = fp32(...): the epilogue's own precision, nothing rounded */
+  BSG_OUT_F32 = 4,          /* D = fp32(...): the epilogue's own precision, nothing rounded */
+  BSG_OUT_E4M3 = 5,         /* D = e4m3(...) without scale factors: round to nearest even, saturating at +-448, NaN -> 0x7F */
+  BSG_OUT_E5M2 = 6          /* D = e5m2(...) likewise, saturating at +-57344 (infinity too) */
 };
 
 /*
@@ -83,7 +85,7 @@ typedef struct bsg_gemm_args {
   const void* SFA;
   const void* SFB;
   const void* C;            /* bf16, may be NULL when beta == 0 */
-  void* D;                  /* bf16; packed e2m1 (BSG_OUT_NVFP4); e4m3 (BSG_OUT_MXFP8); fp16; fp32 */
+  void* D;                  /* bf16; packed e2m1 (BSG_OUT_NVFP4); e4m3 (BSG_OUT_MXFP8); fp16; fp32; e4m3 / e5m2 */
   void* SFD;                /* scale factors of D, interleaved over (M, N/16) or (M, N/32); quantised outputs only */
   int64_t ldc;              /* C row pitch in elements (0 = N) */
   int64_t ldd;              /* D row pitch in elements (0 = N) */

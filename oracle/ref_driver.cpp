@@ -128,9 +128,10 @@ int dispatch_epi(int M, int N, int K, const void* A, const void* B, const void* 
 
 extern "C" {
 
-// fmt: 0 e2m1 (4-bit code), 1 e4m3, 2 ue4m3, 3 ue8m0
+// fmt: 0 e2m1 (4-bit code), 1 e4m3, 2 ue4m3, 3 ue8m0, 4 e5m2
 float bsg_ref_decode(int fmt, uint32_t code) {
   switch (fmt) {
+    case 4: return float(cutlass::float_e5m2_t::bitcast(uint8_t(code)));
     case 0: return float(cutlass::float_e2m1_t::bitcast(uint8_t(code & 0xF)));
     case 1: return float(cutlass::float_e4m3_t::bitcast(uint8_t(code)));
     case 2: return float(cutlass::float_ue4m3_t::bitcast(uint8_t(code)));
@@ -140,6 +141,7 @@ float bsg_ref_decode(int fmt, uint32_t code) {
 
 uint32_t bsg_ref_encode(int fmt, float x) {
   switch (fmt) {
+    case 4: return cutlass::float_e5m2_t(x).raw();
     case 0: return cutlass::float_e2m1_t(x).raw() & 0xF;
     case 1: return cutlass::float_e4m3_t(x).raw();
     case 2: return cutlass::float_ue4m3_t(x).raw();

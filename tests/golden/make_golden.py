@@ -39,6 +39,15 @@ def main() -> None:
     out["encode_in"] = enc_in
     for fmt in (0, 1, 2, 3):
         out[f"encode_{fmt}"] = np.array([ref.bsg_ref_encode(fmt, float(x)) for x in enc_in], dtype=np.uint8)
+    # e5m2 (an output type of the GEMM): every code decoded; encodes of the sweep above plus every midpoint between
+    # neighbouring e5m2 values, their float32 neighbours, and the special values
+    out["decode_4"] = np.array([ref.bsg_ref_decode(4, c) for c in range(256)], dtype=np.float32)
+    pos5 = F.decode_e5m2(np.arange(0x7C, dtype=np.uint8))
+    mid5 = ((pos5[:-1].astype(np.float64) + pos5[1:]) / 2).astype(np.float32)
+    special = np.array([np.inf, -np.inf, np.nan, 57344.0, 61439.0, 61440.0, 65536.0, 1e9, -1e9, 0.0, -0.0], dtype=np.float32)
+    enc5_in = np.concatenate([enc_in, mid5, -mid5, np.nextafter(mid5, np.float32(np.inf)), np.nextafter(mid5, np.float32(0)), special]).astype(np.float32)
+    out["encode5_in"] = enc5_in
+    out["encode_4"] = np.array([ref.bsg_ref_encode(4, float(x)) for x in enc5_in], dtype=np.uint8)
     # --- scale-factor layout
     for vec, rows, K in ((16, 300, 448), (32, 130, 1024), (16, 128, 64)):
         kb = F.ceil_div(K, vec)

@@ -93,3 +93,20 @@ def test_bf16_round_matches_oracle():
     x = np.concatenate([rng.standard_normal(5000).astype(np.float32) * 100, np.array([0.0, -0.0, 1.00390625, 1.01171875, 3.4e38], np.float32)])
     assert np.array_equal(F.bf16_round(x), oracle.to_bf16(x))
     assert np.array_equal(R.f32_to_bf16_bits(x), oracle.to_bf16(x))
+
+
+def test_e5m2_codec_matches_reference(golden):
+    """e5m2 is an output type of the GEMM: decode of every code, and the encode sweep (every midpoint between
+    neighbouring values, their float32 neighbours, infinities, NaN, overflow) against the reference's float_e5m2_t."""
+    assert _same_float(F.decode_e5m2(np.arange(256, dtype=np.uint8)), golden["decode_4"])
+    x, want = golden["encode5_in"], golden["encode_4"]
+    got = F.encode_e5m2(x)
+    assert np.array_equal(got, want), [(float(x[i]), int(got[i]), int(want[i])) for i in np.nonzero(got != want)[0][:5]]
+    codes = np.arange(0x7C, dtype=np.uint8)
+    assert np.array_equal(F.encode_e5m2(F.decode_e5m2(codes)), codes)
+
+
+def test_nan_of_either_sign_encodes_as_the_positive_nan_code():
+    neg_nan = np.array([0xFFC00000, 0x7FC00000], dtype=np.uint32).view(np.float32)
+    assert F.encode_e4m3(neg_nan).tolist() == [0x7F, 0x7F]
+    assert F.encode_e5m2(neg_nan).tolist() == [0x7F, 0x7F]

@@ -346,3 +346,42 @@ def test_fp32_output_through_the_operator_api(cuda_lib):
     op.run(args)
     torch.cuda.synchronize()
     assert np.array_equal(out.cpu().numpy(), oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K).astype(np.float32))
+
+
+@pytest.mark.parametrize("out_kind", [5, 6])
+@pytest.mark.parametrize("kind,M,N,K,alpha", [(0, 512, 512, 256, 1.0), (1, 300, 400, 512, 0.37), (0, 256, 1104, 256, 700.0), (1, 384, 208, 128, 1.0e4)])
+def test_e4m3_and_e5m2_outputs_without_scale_factors(cuda_lib, kind, out_kind, M, N, K, alpha):
+    """8-bit floating-point outputs (no scale factors): the epilogue value converted with round-to-nearest-even and
+    saturation, as the reference's float_e4m3_t / float_e5m2_t do (the numpy codecs are pinned to those in the golden
+    vectors).  The alphas spread the results over the formats' ranges, past their largest finite values and into the
+    subnormals; ragged M and N."""
+    rng = np.random.default_rng(51)
+    gen_a, gen_b = G.operand_generators(kind, True)
+    A, _, sfa = gen_a(M, K, rng)
+    B, _, sfb = gen_b(N, K, rng)
+    Cb = G.bf16_normal((M, N), rng)
+    pre = oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K, Cb, alpha, 0.125)
+    want = (F.encode_e4m3 if out_kind == 5 else F.encode_e5m2)(pre)
+    dD = torch.full((M, N), 0x7F, dtype=torch.uint8, device="cuda")
+    a = L.GemmArgs()
+    a.kind, a.out_kind, a.batch, a.M, a.N, a.K = kind, out_kind, 1, M, N, K
+    dA, dSFA, dB, dSFB, dC = dev(A), dev(sfa), dev(B), dev(sfb), dev(Cb)
+    a.A, a.SFA, a.B, a.SFB, a.C, a.D = (t.data_ptr() for t in (dA, dSFA, dB, dSFB, dC, dD))
+    a.alpha, a.beta = alpha, 0.125
+    _run(a)
+    got = dD.cpu().numpy()
+    assert np.array_equal(got, want), f"{int((got != want).sum())} of {got.size} differ"
+
+
+def test_e5m2_output_through_the_operator_api(cuda_lib):
+    import cutlass_b200 as ops
+    kind, M, N, K = 1, 256, 320, 256
+    rng, A, sfa, B, sfb = make_operands(kind, M, N, K, 53, True)
+    Aop = ops.ScaledOperand(dev(A).view(torch.float8_e4m3fn), dev(sfa), ops.ScaleMode.Blockwise1x32, ops.ScaleSwizzleMode.Swizzle32x4x4)
+    Bop = ops.ScaledOperand(dev(B).view(torch.float8_e4m3fn).t(), dev(sfb), ops.ScaleMode.Blockwise1x32, ops.ScaleSwizzleMode.Swizzle32x4x4)
+    out = torch.empty((M, N), dtype=torch.float8_e5m2, device="cuda")
+    args = ops.GemmArguments(Aop, Bop, out, torch.float32)
+    op = ops.get_operators(args)[0]
+    op.run(args)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.view(torch.uint8).cpu().numpy(), F.encode_e5m2(oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K)))
