@@ -286,7 +286,9 @@ int32_t validate(const Problem& q, Plan* plan) {
   int32_t cg = q.cta_group == 0 ? 2 : q.cta_group;
   int32_t tn = q.tile_n == 0 ? (q.N > 128 ? 256 : 128) : q.tile_n;
   if (cg != 1 && cg != 2) return fail(BSG_ERR_NOT_SUPPORTED, "cta_group must be 1 or 2");
-  if (tn != 128 && tn != 256) return fail(BSG_ERR_NOT_SUPPORTED, "tile_n must be 128 or 256");
+  if (tn != 64 && tn != 128 && tn != 192 && tn != 256) return fail(BSG_ERR_NOT_SUPPORTED, "tile_n must be 64, 128, 192 or 256");
+  if ((tn == 64 || tn == 192) && (q.kind > BSG_KIND_MXFP8 || cg != 2 || q.scheduler != BSG_SCHED_STATIC || q.tp || q.rs || q.out_kind >= BSG_OUT_F16 || q.out_col_major))
+    return fail(BSG_ERR_NOT_SUPPORTED, "tiles of 64 and 192 columns are available for NVFP4 and MXFP8 operands with cta_group 2, the static scheduler and bf16 or re-quantised row-major output, on one GPU");
   // Cluster shapes: the cluster is the CTA group of one MMA, there is nothing larger to prefer or to fall back to.
   for (int i = 0; i < 4; i += 2) {
     if ((q.cluster[i] != 0 || q.cluster[i + 1] != 0) && !(q.cluster[i] == cg && q.cluster[i + 1] == 1))
@@ -399,7 +401,7 @@ int32_t launch(const Problem& q, const Plan& plan, uint32_t* status, cudaStream_
   }
   if (rc != BSG_OK) return rc;
   if ((rc = make_sf_map(&tmSFA, q.SFA, k_atoms, TP ? 2 * sfa_row_atoms : sfa_row_atoms, Cf::kKAtoms, 1)) != BSG_OK) return rc;
-  if ((rc = make_sf_map(&tmSFB, q.SFB, k_atoms, b_groups * n_atoms, Cf::kKAtoms, BN / 128)) != BSG_OK) return rc;
+  if ((rc = make_sf_map(&tmSFB, q.SFB, k_atoms, b_groups * n_atoms, Cf::kKAtoms, Cf::kSfbAtoms)) != BSG_OK) return rc;
 
   bsg::GemmParams p;
   memset(&p, 0, sizeof(p));
@@ -532,6 +534,8 @@ int32_t dispatch_shape(const Problem& q, const Plan& plan, uint32_t* status, cud
                               : launch<KIND, 2, 128, false, true>(q, plan, status, s, sm, dev, dry);
   }
   if (plan.cta_group == 2) {
+    if (plan.tile_n == 64) return launch<KIND, 2, 64>(q, plan, status, s, sm, dev, dry);
+    if (plan.tile_n == 192) return launch<KIND, 2, 192>(q, plan, status, s, sm, dev, dry);
     return plan.tile_n == 256 ? launch<KIND, 2, 256>(q, plan, status, s, sm, dev, dry) : launch<KIND, 2, 128>(q, plan, status, s, sm, dev, dry);
   }
   return plan.tile_n == 256 ? launch<KIND, 1, 256>(q, plan, status, s, sm, dev, dry) : launch<KIND, 1, 128>(q, plan, status, s, sm, dev, dry);
@@ -551,7 +555,9 @@ void fill_caps_for(bsg_caps* caps) {
 void fill_caps(const Problem& q, const Plan& plan, bsg_caps* caps) {
   if (!caps) return;
   const bool fp4 = q.kind == BSG_KIND_NVFP4 || q.kind == BSG_KIND_MXFP4;     // the same tile extents and stage count
-  if (plan.cta_group == 2 && plan.tile_n == 256) fp4 ? fill_caps_for<0, 2, 256>(caps) : fill_caps_for<1, 2, 256>(caps);
+  if (plan.cta_group == 2 && plan.tile_n == 64) fp4 ? fill_caps_for<0, 2, 64>(caps) : fill_caps_for<1, 2, 64>(caps);
+  else if (plan.cta_group == 2 && plan.tile_n == 192) fp4 ? fill_caps_for<0, 2, 192>(caps) : fill_caps_for<1, 2, 192>(caps);
+  else if (plan.cta_group == 2 && plan.tile_n == 256) fp4 ? fill_caps_for<0, 2, 256>(caps) : fill_caps_for<1, 2, 256>(caps);
   else if (plan.cta_group == 2) fp4 ? fill_caps_for<0, 2, 128>(caps) : fill_caps_for<1, 2, 128>(caps);
   else if (plan.tile_n == 256) fp4 ? fill_caps_for<0, 1, 256>(caps) : fill_caps_for<1, 1, 256>(caps);
   else fp4 ? fill_caps_for<0, 1, 128>(caps) : fill_caps_for<1, 1, 128>(caps);
@@ -691,7 +697,7 @@ int32_t ptr_array_encode(const bsg_ptr_array_args* a, bsg::GroupDesc* table) {
     if ((rc = make_operand_map(&d.tmA, r.A, k_bytes, uint64_t(r.M), 1, lda_bytes, uint64_t(r.M) * lda_bytes, Cf::kCtaM)) != BSG_OK) return rc;
     if ((rc = make_operand_map(&d.tmB, r.B, k_bytes, uint64_t(r.N), 1, ldb_bytes, uint64_t(r.N) * ldb_bytes, Cf::kBRowsCta)) != BSG_OK) return rc;
     if ((rc = make_sf_map(&d.tmSFA, r.SFA, k_atoms, uint64_t((r.M + 127) / 128), Cf::kKAtoms, 1)) != BSG_OK) return rc;
-    if ((rc = make_sf_map(&d.tmSFB, r.SFB, k_atoms, uint64_t((r.N + 127) / 128), Cf::kKAtoms, BN / 128)) != BSG_OK) return rc;
+    if ((rc = make_sf_map(&d.tmSFB, r.SFB, k_atoms, uint64_t((r.N + 127) / 128), Cf::kKAtoms, Cf::kSfbAtoms)) != BSG_OK) return rc;
     if ((rc = make_out_map(&d.tmD, r.D, a->out_kind, uint64_t(r.N), uint64_t(r.M), 1, uint64_t(r.ldd), uint64_t(r.M) * uint64_t(r.ldd))) != BSG_OK) return rc;
   }
   return BSG_OK;

@@ -173,7 +173,7 @@ template <int KIND, int CG, int BN, bool TP = false>
 struct Cfg {
   static_assert(KIND >= kKindNvfp4 && KIND <= kKindMxfp8Mxfp4, "kind");
   static_assert(CG == 1 || CG == 2, "cta group");
-  static_assert(BN == 128 || BN == 256, "tile n");
+  static_assert(BN == 64 || BN == 128 || BN == 192 || BN == 256, "tile n");
   static constexpr int kCtaM = 128;                       // accumulator rows per CTA (= TMEM lanes)
   static constexpr int kTileM = kCtaM * CG;               // rows per MMA tile
   static constexpr int kRowBytes = 128;                   // bytes of K per row per k-tile (one 128B swizzle atom)
@@ -185,7 +185,13 @@ struct Cfg {
   static constexpr int kABytes = kCtaM * kRowBytes;
   static constexpr int kBBytes = kBRowsCta * kRowBytes;
   static constexpr int kSfaBytes = kKAtoms * 512;
-  static constexpr int kSfbBytes = (BN / 128) * kKAtoms * 512;
+  // 128-row atoms of SFB that the columns of one tile touch.  Tiles of 64 or 192 columns start in the middle of an atom
+  // every other time: the atoms are fetched whole and the MMA is pointed at the right columns of tensor memory (a
+  // column holds 32 rows of the atom), as the reference does for these tile widths
+  // (include/cutlass/gemm/collective/sm100_blockscaled_mma_warpspecialized.hpp:719-741).
+  static constexpr int kSfbAtoms = (BN + 127) / 128;
+  static constexpr int kSfbCols = 4 * kSfbAtoms;            // tensor-memory columns of SFB per k-atom
+  static constexpr int kSfbBytes = kSfbAtoms * kKAtoms * 512;
   static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;
   // Bytes a stage's loads report to its barrier.  The mixed kind's B arrives as packed e2m1 that the TMA engine spreads
   // over twice the space (16 values in 8 bytes, then 8 bytes of padding): the transaction counts the 8, not the 16.
@@ -211,7 +217,7 @@ struct Cfg {
   // One set of scale-factor columns: a second set, used by alternate k-tiles so that a k-tile's copies need not
   // wait for the previous k-tile's MMAs, was measured for both kinds and gained nothing (the copies and the MMAs
   // of one issuing thread run strictly in order in the tensor pipe).
-  static constexpr int kAccStride = BN == 256 ? 208 : 128;
+  static constexpr int kAccStride = BN == 256 ? 208 : BN;
   static constexpr int kAccBars = BN == 256 ? 1 : 2;
   static constexpr int kSfaCol = 464;
   static constexpr int kSfbCol = 480;
@@ -723,7 +729,7 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       // scale-factor fetch inside the group's own atoms (its rows are never stored).
       const int32_t group_atoms = (ti.row_end - ti.group_row0 + 127) >> 7;
       const int32_t sfa_atom = bcast(min(ti.sf_atom + int32_t(cta_rank), ti.group_atom0 + max(group_atoms, 1) - 1) + (tp_row_off >> 7));
-      const int32_t sfb_atom = bcast(ti.g * p.sfb_atoms_per_group + ti.tn * (BN / 128) + wi.half);
+      const int32_t sfb_atom = bcast(ti.g * p.sfb_atoms_per_group + (ti.tn * BN) / 128 + wi.half);
       // Pointer-array form: the group's own tensor maps (in global memory) and depth.
       const CUtensorMap *mapA = &tmA, *mapB = &tmB, *mapSFA = &tmSFA, *mapSFB = &tmSFB;
       int32_t tile_k_tiles = k_tiles;
@@ -833,6 +839,12 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int acc_bar = it % C::kAccBars;
         const uint32_t acc_phase = uint32_t(it / C::kAccBars) & 1u;
         const uint32_t d_tmem = tmem_base + uint32_t(it & 1) * C::kAccStride;
+        // tiles of 64 / 192 columns: the tile's first column inside its first SFB atom, in 32-row columns of tensor memory
+        uint32_t sfb_off = 0;
+        if constexpr (BN == 64 || BN == 192) {
+          const TileInfo mti = decode_tile(ctl, p, decode_work(w, split_from).t, C::kTileM, BN, PTR);
+          sfb_off = uint32_t(bcast(((mti.tn * BN) & 127) >> 5));
+        }
         int32_t tile_K = p.K, tile_k_tiles = k_tiles;
         if constexpr (PTR) {
           tile_K = bcast(ctl->gK[group_of_tile(ctl, p.num_groups, decode_work(w, split_from).t)]);
@@ -865,10 +877,10 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               ptx::utccp_32x128b_warpx4<CG>(sfa_col + 4 * ka, make_desc_sf(sfa_s + ka * 512));
             }
 #pragma unroll
-            for (int ra = 0; ra < BN / 128; ++ra) {
+            for (int ra = 0; ra < C::kSfbAtoms; ++ra) {
 #pragma unroll
               for (int ka = 0; ka < C::kKAtoms; ++ka) {
-                ptx::utccp_32x128b_warpx4<CG>(sfb_col + (BN / 32) * ka + 4 * ra,
+                ptx::utccp_32x128b_warpx4<CG>(sfb_col + C::kSfbCols * ka + 4 * ra,
                                               make_desc_sf(sfb_s + (ra * C::kKAtoms + ka) * 512));
               }
             }
@@ -878,14 +890,14 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 uint32_t sfa_t, sfb_t, id = idesc;
                 if constexpr (KIND == kKindNvfp4) {
                   sfa_t = sfa_col + 4 * kb;                            // four scale factors per instruction: a column group each
-                  sfb_t = sfb_col + (BN / 32) * kb;
+                  sfb_t = sfb_col + C::kSfbCols * kb + sfb_off;
                 } else if constexpr (KIND == kKindMxfp4) {
                   sfa_t = sfa_col + 4 * (kb >> 1);                     // two scale factors per instruction: half a column group
-                  sfb_t = sfb_col + (BN / 32) * (kb >> 1);
+                  sfb_t = sfb_col + C::kSfbCols * (kb >> 1) + sfb_off;
                   id |= (uint32_t(kb & 1) << 5) | (uint32_t(kb & 1) << 30);   // lower / upper pair of the group's four bytes
                 } else {
                   sfa_t = sfa_col;
-                  sfb_t = sfb_col;
+                  sfb_t = sfb_col + sfb_off;
                   id |= (uint32_t(kb) << 4) | (uint32_t(kb) << 29);   // scale-factor byte of this K block
                 }
                 ptx::umma_block_scaled<KIND, CG>(d_tmem, a_desc + 2 * kb, b_desc + 2 * kb, id, sfa_t, sfb_t,

@@ -281,6 +281,8 @@ class BlockScaledGemmOperator(Operator):
         if epi.out_quant is None:
             if out.dtype not in _PLAIN_OUT_KINDS:
                 return Status.fail(f"out dtype {out.dtype} is not supported (bf16, fp16, fp32, e4m3, e5m2, or a quantised output with out_quant)")
+            if out.dtype != torch.bfloat16 and (md.tile_n in (64, 192) or md.cta_group != 2 or md.kind > L.KIND_MXFP8):
+                return Status.fail(f"{out.dtype} output is available with the 2-CTA tiles of 128 / 256 columns, NVFP4 or MXFP8 operands")
             if ps.N % _PLAIN_OUT_N_MULTIPLE[out.dtype] != 0:
                 return Status.fail(f"N must be a multiple of {_PLAIN_OUT_N_MULTIPLE[out.dtype]} for {out.dtype} output (16-byte rows)")
         elif isinstance(epi.out_quant, Mxfp8Quant):
@@ -320,7 +322,7 @@ class BlockScaledGemmOperator(Operator):
             want = ps.M if epi.bias_per_row else ps.N
             if epi.bias.dtype != torch.float32 or epi.bias.numel() != want or not epi.bias.is_contiguous():
                 return Status.fail(f"bias must be a contiguous fp32 vector of {want} entries")
-        if md.tile_n not in (128, 256) or md.cta_group not in (1, 2):
+        if md.tile_n not in (64, 128, 192, 256) or md.cta_group not in (1, 2):
             return Status.fail("invalid tile configuration")
         return Status.success()
 
@@ -411,6 +413,8 @@ class GroupedBlockScaledGemmOperator(Operator):
         if epi.out_quant is None:
             if out.dtype not in _PLAIN_OUT_KINDS:
                 return Status.fail("out must be a bf16, fp16, fp32, e4m3 or e5m2 tensor (or a quantised output with out_quant)")
+            if out.dtype != torch.bfloat16 and (self._metadata.tile_n in (64, 192) or self._metadata.cta_group != 2 or self._metadata.kind > L.KIND_MXFP8):
+                return Status.fail(f"{out.dtype} output is available with the 2-CTA tiles of 128 / 256 columns, NVFP4 or MXFP8 operands")
             if ps.N % _PLAIN_OUT_N_MULTIPLE[out.dtype] != 0:
                 return Status.fail(f"N must be a multiple of {_PLAIN_OUT_N_MULTIPLE[out.dtype]} for {out.dtype} output")
         else:
@@ -484,7 +488,8 @@ class GroupedBlockScaledGemmOperator(Operator):
         L.check(artifact.library.bsg_grouped_run(C.byref(a), ws.data_ptr(), ws.numel() * ws.element_size(), stream))
 
 
-_TILE_CHOICES = ((2, 256), (2, 128), (1, 256), (1, 128))   # (cta_group, tile_n), best first
+_TILE_CHOICES = ((2, 256), (2, 128), (1, 256), (1, 128), (2, 192), (2, 64))   # (cta_group, tile_n), best first; the last two
+# (the reference's mma_tiler_n also takes 64 and 192) exist for the two main kinds and unquantised-type-bf16 / re-quantised outputs
 
 
 def _name(kind: int, grouped: bool, cg: int, tn: int) -> str:
@@ -499,8 +504,8 @@ def all_operators() -> list[Operator]:
     ops: list[Operator] = []
     for kind in (L.KIND_NVFP4, L.KIND_MXFP8, L.KIND_MXFP4, L.KIND_MXFP8_MXFP4):
         for cg, tn in _TILE_CHOICES:
-            if kind >= L.KIND_MXFP4 and cg != 2:
-                continue          # the two newer kinds are built for the 2-CTA tiles only
+            if kind >= L.KIND_MXFP4 and (cg != 2 or tn in (64, 192)):
+                continue          # the two newer kinds are built for the 2-CTA tiles of 128 / 256 columns only
             ops.append(BlockScaledGemmOperator(OperatorMetadata(_name(kind, False, cg, tn), kind, tn, cg, False)))
             ops.append(GroupedBlockScaledGemmOperator(OperatorMetadata(_name(kind, True, cg, tn), kind, tn, cg, True)))
     return ops

@@ -94,7 +94,8 @@ typedef struct bsg_gemm_args {
   const float* alpha_ptr;   /* optional device scalars, override alpha / beta */
   const float* beta_ptr;
   const float* norm_constant; /* device fp32 scalar: required for BSG_OUT_NVFP4, optional (NULL = 1) for BSG_OUT_MXFP8 */
-  int32_t tile_n;           /* 0 = library default, else 128 or 256 */
+  int32_t tile_n;           /* 0 = library default (256, or 128 when N <= 128), else 64, 128, 192 or 256; 64 and 192: NVFP4 / MXFP8,
+                               cta_group 2, static scheduler, bf16 or re-quantised row-major output */
   int32_t cta_group;        /* 0 = default, else 1 or 2 (CTAs per MMA) */
   int32_t sm_count;         /* 0 = all SMs of the current device */
   int32_t raster_band;      /* 0 = default band height in tiles */

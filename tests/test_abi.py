@@ -67,6 +67,9 @@ def test_query_accepts_valid_problem_and_reports_plan(lib):
     assert caps.stages >= 4 and caps.smem_bytes <= 232448 and caps.num_tiles == 1
     assert lib.bsg_gemm_query(C.byref(_args(kind=1, tile_n=128, cta_group=1)), C.byref(caps)) == 0
     assert (caps.tile_m, caps.tile_n, caps.tile_k) == (128, 128, 128) and caps.num_tiles == 4
+    assert lib.bsg_gemm_query(C.byref(_args(N=384, tile_n=192)), C.byref(caps)) == 0
+    assert (caps.tile_n, caps.num_tiles, caps.stages) == (192, 2, 5)
+    assert lib.bsg_gemm_query(C.byref(_args(tile_n=64)), C.byref(caps)) == 0 and (caps.tile_n, caps.num_tiles) == (64, 4)
 
 
 @pytest.mark.parametrize("kw,code", [
@@ -76,7 +79,9 @@ def test_query_accepts_valid_problem_and_reports_plan(lib):
     (dict(N=100), 1),                # bf16 rows not 16-byte multiples
     (dict(kind=7), 3),
     (dict(use_pdl=2), 2),
-    (dict(tile_n=192), 3),
+    (dict(tile_n=96), 3),
+    (dict(tile_n=192, cta_group=1), 3),      # tiles of 64 / 192 columns need the 2-CTA form
+    (dict(tile_n=64, scheduler=1), 3),
     (dict(cta_group=3), 3),
     (dict(N=0), 2),
     (dict(A=None), 2),

@@ -71,15 +71,20 @@ def test_shape_mismatches_raise():
 
 def test_get_operators_orders_and_filters():
     found = ops.get_operators(nvfp4_args())
-    assert [type(o) for o in found] == [ops.BlockScaledGemmOperator] * 4
+    assert [type(o) for o in found] == [ops.BlockScaledGemmOperator] * 6
+    assert [(o.metadata.cta_group, o.metadata.tile_n) for o in found][4:] == [(2, 192), (2, 64)]
     assert (found[0].metadata.cta_group, found[0].metadata.tile_n) == (2, 256)
     assert all(o.metadata.kind == L.KIND_NVFP4 for o in found)
     only = ops.get_operators(nvfp4_args(), metadata_filter=lambda m: m.tile_n == 128 and m.cta_group == 1)
     assert len(only) == 1 and only[0].metadata.tile_shape == (128, 128, 256)
     assert all(o.metadata.kind == L.KIND_MXFP8 for o in ops.get_operators(mxfp8_args()))
     assert ops.get_operators(nvfp4_args(), target_sm="90a") == []
-    # 2 kinds x 4 tile shapes + 2 kinds (MXFP4, MXFP8 x MXFP4) x 2 two-CTA tile shapes, each dense and grouped
-    assert len(ops.all_operators()) == 24 and len({o.metadata.operator_name for o in ops.all_operators()}) == 24
+    # 2 kinds x 6 tile shapes + 2 kinds (MXFP4, MXFP8 x MXFP4) x 2 two-CTA tile shapes, each dense and grouped
+    assert len(ops.all_operators()) == 32 and len({o.metadata.operator_name for o in ops.all_operators()}) == 32
+    # the narrow tiles write bf16 or re-quantised outputs only
+    f32 = nvfp4_args()
+    f32.out = ops.DenseTensor(torch.zeros((256, 256), dtype=torch.float32))
+    assert sorted((o.metadata.cta_group, o.metadata.tile_n) for o in ops.get_operators(f32)) == [(2, 128), (2, 256)]
 
 
 def test_supports_rejections():

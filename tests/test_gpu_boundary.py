@@ -385,3 +385,44 @@ def test_e5m2_output_through_the_operator_api(cuda_lib):
     op.run(args)
     torch.cuda.synchronize()
     assert np.array_equal(out.view(torch.uint8).cpu().numpy(), F.encode_e5m2(oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K)))
+
+
+@pytest.mark.parametrize("tile_n", [64, 192])
+@pytest.mark.parametrize("kind,M,N,K,batch", [(0, 512, 768, 512, 1), (1, 300, 456, 384, 1), (0, 256, 1160, 256, 2), (1, 1024, 64, 1024, 1), (0, 384, 192, 2048, 1)])
+def test_tiles_of_64_and_192_columns(cuda_lib, kind, M, N, K, batch, tile_n):
+    """Tile widths 64 and 192 (the reference offers MMA tile N in {64, 128, 192, 256}): such tiles start in the middle of
+    a 128-row scale-factor atom of B every other time.  Bit for bit on exact operands with C, ragged M and N, batches."""
+    rng = np.random.default_rng(61)
+    gen_a, gen_b = G.operand_generators(kind, True)
+    parts = [(gen_a(M, K, rng), gen_b(N, K, rng)) for _ in range(batch)]
+    A = np.concatenate([p[0][0] for p in parts]); sfa = np.concatenate([p[0][2] for p in parts])
+    B = np.concatenate([p[1][0] for p in parts]); sfb = np.concatenate([p[1][2] for p in parts])
+    Cb = G.bf16_normal((batch * M, N), rng)
+    got = run_dense(kind, M, N, K, A, sfa, B, sfb, Cb=Cb, alpha=0.5, beta=1.0, tile_n=tile_n, batch=batch)
+    want = np.concatenate([oracle_bf16(kind, M, N, K, parts[b][0][0], parts[b][0][2], parts[b][1][0], parts[b][1][2], Cb[b * M:(b + 1) * M], 0.5, 1.0)
+                           for b in range(batch)])
+    assert np.array_equal(got, want), f"{int((got != want).sum())} of {got.size} differ"
+
+
+@pytest.mark.parametrize("tile_n", [64, 192])
+def test_tiles_of_64_and_192_columns_realistic_and_requantised(cuda_lib, tile_n):
+    kind, M, N, K = 0, 384, 960, 1024
+    rng, A, sfa, B, sfb = make_operands(kind, M, N, K, 63, False)
+    got = run_dense(kind, M, N, K, A, sfa, B, sfb, tile_n=tile_n)
+    want = oracle_bf16(kind, M, N, K, A, sfa, B, sfb)
+    from gpu_utils import assert_close_bf16
+    assert_close_bf16(got, want, rel_tol=1e-2)
+    # fused NVFP4 output on exact operands: values and scale factors bit for bit
+    rng, A, sfa, B, sfb = make_operands(kind, M, N, K, 65, True)
+    pre = oracle.gemm_fp32(kind, A, sfa, B, sfb, M, N, K)
+    st = float(np.float32(448.0 * 6.0 / np.abs(pre).max()))
+    gotD, gotSFD = run_dense(kind, M, N, K, A, sfa, B, sfb, out_kind=1, st=st, tile_n=tile_n)
+    Dw, SFDw = oracle.quant(0, pre, st)
+    idx = R.sf_index(M, N // 16)
+    assert np.array_equal(gotD, Dw) and np.array_equal(gotSFD[idx], SFDw[idx])
+
+
+@pytest.mark.parametrize("tile_n", [64, 192])
+def test_tiles_of_64_and_192_columns_grouped(cuda_lib, tile_n):
+    got, want = run_grouped(1, [100, 0, 300, 1, 515], 448, 512, seed=67, tile_n=tile_n)
+    assert np.array_equal(got, want)
