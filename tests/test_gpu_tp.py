@@ -111,6 +111,15 @@ def test_tp_gathers_a_inside_the_kernel(kind, world, M, N, K, mode):
     _spawn(world, kind, M, N, K, 3, mode)
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_tp_fifty_small_calls_in_a_row(world):
+    """The shape of the 8-rank case below on fewer GPUs: 2048 rows and 128 columns per rank, K 1024, 50 calls with a new A
+    each, no barrier between the calls (the ranks drift apart by up to a call)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _spawn(world, 1, 2048 * world, 128 * world, 1024, 50, None, timeout=900)
+
+
 def test_tp_eight_ranks_fifty_calls_at_the_benchmark_shard_size():
     """Eight ranks with 2048 rows each (the row shard of the 16384-row benchmark problem), 50 calls in a row, every
     one with a different A on every rank and every output element compared with the oracle: a rank that consumed a
