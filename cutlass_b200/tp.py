@@ -293,11 +293,11 @@ class TpGemm:
             dist.barrier(group)
         # "kernel" | "copy_engine", optionally with "+single" (one gathered buffer instead of two), "+release"
         # (announcements behind release fences), "+paced" / "+spread" (when the rows leave); None: the library's default
-        # ("kernel+spread"); plain "kernel" pushes everything at the start of the call
+        # ("kernel+spread+release"); plain "kernel" pushes everything at the start of the call, with relaxed announcements
         mode = mode or os.environ.get("BSG_TP_MODE")
         if mode is not None:
             self.set_mode(mode)
-        self.mode = mode or "kernel+spread"         # the library's default
+        self.mode = mode or "kernel+spread+release"   # the library's default
         ptrs = [C.c_void_p() for _ in range(4)]
         L.check(self._lib.bsg_tp_buffers(self._comm, *[C.byref(p) for p in ptrs]))
         row_bytes = K // 2 if kind == L.KIND_NVFP4 else K

@@ -393,12 +393,12 @@ int32_t bsg_quantize(const bsg_quant_args* args, void* cuda_stream);
  * After BSG_ERR_TIMEOUT the arrival counters of the ranks are out of step: destroy the communicators on all ranks
  * (bsg_tp_destroy after a device synchronise and a barrier) and create them again before the next call.
  *
- * Ordering of the announcements.  A piece is announced to the peer by a relaxed system-scope counter increment issued
- * after cp.async.bulk.wait_group has reported the piece's stores complete; the peer acquires the counter and issues a
- * proxy fence before its TMA loads.  That the increment cannot overtake the data rests on how bulk stores complete
- * over NVLink (observed, and guarded by tests that change A on every call), not on the PTX memory model.
- * BSG_TP_RELEASE_ANNOUNCE, or-ed into the mode, puts a proxy fence and a system-scope release fence in front of every
- * batch of increments: the form the memory model asks for, slower because the fence also waits for newer stores.
+ * Ordering of the announcements.  A piece is announced to the peer by a system-scope counter increment issued after
+ * cp.async.bulk.wait_group has reported the piece's stores complete; the peer acquires the counter and issues a proxy
+ * fence before its TMA loads.  With BSG_TP_RELEASE_ANNOUNCE (part of the default mode) a proxy fence and a system-scope
+ * release fence stand in front of every batch of increments: the form the PTX memory model asks for.  Without it the
+ * increment is relaxed and nothing but the way bulk stores complete over NVLink keeps it behind the data: faster, and
+ * seen to fail on 8 GPUs (a rank read a row block before its rows had landed, in a run of many small calls).
  */
 enum { BSG_TP_PUSH_KERNEL = 0, BSG_TP_PUSH_COPY_ENGINE = 1, BSG_TP_SINGLE_BUFFER = 2 /* or-ed in: every call uses the first gathered buffer */,
        BSG_TP_RELEASE_ANNOUNCE = 4 /* or-ed in: see "Ordering of the announcements" above */,
@@ -407,7 +407,7 @@ enum { BSG_TP_PUSH_KERNEL = 0, BSG_TP_PUSH_COPY_ENGINE = 1, BSG_TP_SINGLE_BUFFER
        BSG_TP_SPREAD_PUSH = 16 /* or-ed in: as BSG_TP_PACED_PUSH, with the pieces of a stage leaving evenly over the first three
                                  quarters of that stage instead of in one burst at its start */ };
 typedef struct bsg_tp_comm bsg_tp_comm;
-/* A new communicator starts in BSG_TP_PUSH_KERNEL | BSG_TP_SPREAD_PUSH; bsg_tp_set_mode replaces the whole mode word (0 = the
+/* A new communicator starts in BSG_TP_PUSH_KERNEL | BSG_TP_SPREAD_PUSH | BSG_TP_RELEASE_ANNOUNCE; bsg_tp_set_mode replaces the whole mode word (0 = the
  * kernel pushes everything as fast as the links allow).  Only between calls, with every rank idle, the same on all ranks. */
 int32_t bsg_tp_set_mode(bsg_tp_comm* comm, int32_t mode);
 int32_t bsg_tp_create(int32_t rank, int32_t world, int32_t kind, int64_t M, int64_t K, bsg_tp_comm** out,
