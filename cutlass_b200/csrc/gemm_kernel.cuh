@@ -955,13 +955,12 @@ bsg_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       int pend_rank[C::kTpPend], pend_block[C::kTpPend];
       uint32_t pend_due[C::kTpPend];
       int pend_head = 0, pend_cnt = 0;
-      // The announcement is a relaxed system-scope add issued after wait_group has reported the piece's
-      // stores complete, i.e. acknowledged by the peer's memory: the counter update leaves this GPU only
-      // after the data is in place, and the consumer reads both from its own memory.  That order rests on
-      // how bulk stores complete over NVLink, not on the PTX memory model, which orders an async-proxy
-      // write before a later generic-proxy write of the same thread only through a proxy fence and a
-      // release.  tp_release_announce selects that form: one fence pair per batch of due announcements
-      // (it also waits for the newer stores in flight, which is why it is not the default).
+      // The announcement is a system-scope add issued after wait_group has reported the piece's stores complete.
+      // tp_release_announce (the library's default) puts a proxy fence and a system-scope release fence in front of
+      // every batch of due announcements: the order the PTX memory model asks for between an async-proxy write and a
+      // later generic-proxy write of the same thread.  Without it the add is relaxed and only the way bulk stores
+      // complete over NVLink keeps it behind the data: faster (the fence also waits for the newer stores in flight),
+      // but on eight GPUs a run of many small calls had a rank read a row block before its rows had landed.
       auto release_fences = [&]() {
         if (p.tp_release_announce) {
           asm volatile("fence.proxy.async;" ::: "memory");
